@@ -1,0 +1,123 @@
+// The double-gated causal depthwise short convolution over a mixed batch, and its per-request state.
+//
+//   bcx = in_proj(n)  [R, 3H]:  B = bcx[:, :H], C = bcx[:, H:2H], x = bcx[:, 2H:]
+//   bx  = B * x;  conv_t = sum_j taps[:, j] * win_t[j]  (+ bias),  win_t = the K inputs ending at row t, oldest first
+//   y   = C * conv                                         (engine/models/lfm2_moe/ref.py:134-151)
+//   state after the step = the last K-1 inputs bx of the sequence  (ref.py:253)
+//
+// A request's rows in this step are consecutive. An input that lies before the step's first row comes
+// from the request's state slot (the K-1 inputs before the step, oldest first, 32-bit); an input before
+// position 0 of the sequence is zero whatever the slot holds. bx is formed in 32-bit from the stored
+// bcx in both cases, so a row's result does not depend on where the prompt was cut.
+// The state is rewritten by a second kernel after every row has read it.
+#include "common.cuh"
+
+namespace tl {
+
+constexpr int MAX_TAPS = 16;
+
+template <typename T>
+__global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
+                                  const float* __restrict__ bias, const float* __restrict__ state,
+                                  const int* __restrict__ state_slot, const int* __restrict__ req_of_row,
+                                  const int* __restrict__ row_start, const int* __restrict__ positions,
+                                  T* __restrict__ y, int hidden, int K) {
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= hidden) return;
+  const int b = req_of_row[r];
+  const int first = row_start[b];          // first row of this request in the step
+  const int pos = positions[r];            // absolute position of row r
+  const long long ld = 3LL * hidden;
+  const float* st = state + ((long long)state_slot[b] * (K - 1)) * hidden;
+  float acc = bias ? bias[c] : 0.f;
+  // tap j multiplies the input K-1-j rows back; tap K-1 the row itself
+  for (int j = 0; j < K; ++j) {
+    const int back = K - 1 - j;
+    if (pos - back < 0) continue;            // before the sequence's first token: zero
+    const int rr = r - back;
+    float v;
+    if (rr >= first) {
+      const T* row = bcx + (long long)rr * ld;
+      v = to_f32(row[c]) * to_f32(row[2 * hidden + c]);
+    } else {
+      // (first - rr) rows before the step's first row: state index K-1 - (first - rr)
+      v = st[(long long)(K - 1 - (first - rr)) * hidden + c];
+    }
+    acc = fmaf(taps[(long long)c * K + j], v, acc);
+  }
+  y[(long long)r * hidden + c] = from_f32<T>(to_f32(bcx[(long long)r * ld + hidden + c]) * acc);
+}
+
+// new state = last K-1 of [old state ; this step's bx rows], per request and channel; one thread does both
+// the reads and the writes of its channel, so no other thread's input is overwritten early.
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
+                                        const int* __restrict__ state_slot, const int* __restrict__ row_start,
+                                        const int* __restrict__ positions, int hidden, int K) {
+  const int b = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= hidden) return;
+  const int first = row_start[b], n = row_start[b + 1] - first;
+  if (n <= 0) return;
+  const int S = K - 1;
+  const long long ld = 3LL * hidden;
+  float* st = state + ((long long)state_slot[b] * S) * hidden;
+  const int start_pos = positions[first];
+  float keep[MAX_TAPS];
+#pragma unroll 1
+  for (int s = 0; s < S; ++s) {
+    // entry s of the new state is element n - S + s of the step's rows (negative: old state entry s + n)
+    const int i = n - S + s;
+    float v;
+    if (i >= 0) {
+      const T* row = bcx + (long long)(first + i) * ld;
+      v = to_f32(row[c]) * to_f32(row[2 * hidden + c]);
+    } else {
+      // old entry s + n sits S - (s + n) inputs before the step: before position 0 it is zero
+      v = (start_pos - (S - (s + n)) >= 0) ? st[(long long)(s + n) * hidden + c] : 0.f;
+    }
+    keep[s] = v;
+  }
+#pragma unroll 1
+  for (int s = 0; s < S; ++s) st[(long long)s * hidden + c] = keep[s];
+}
+
+}  // namespace tl
+
+using namespace tl;
+
+extern "C" int tl_short_conv(const void* bcx, const float* taps, const float* bias, const float* state,
+                             const int* state_slot, const int* req_of_row, const int* row_start, const int* positions,
+                             void* y, int rows, int hidden, int K, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  TL_REQUIRE(rows > 0 && hidden > 0, "short_conv: rows %d hidden %d", rows, hidden);
+  TL_REQUIRE(K >= 2 && K <= MAX_TAPS, "short_conv: %d taps; 2..%d are implemented", K, MAX_TAPS);
+  dim3 grid(rows, ceil_div(hidden, 256));
+  TL_REQUIRE(grid.y <= 65535, "short_conv: hidden size %d exceeds the grid limit", hidden);
+  if (dtype == TL_FP32)
+    short_conv_kernel<float><<<grid, 256, 0, stream>>>((const float*)bcx, taps, bias, state, state_slot, req_of_row,
+                                                       row_start, positions, (float*)y, hidden, K);
+  else
+    short_conv_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)bcx, taps, bias, state, state_slot, req_of_row,
+                                                      row_start, positions, (bf16*)y, hidden, K);
+  TL_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int tl_short_conv_state(const void* bcx, float* state, const int* state_slot, const int* row_start,
+                                   const int* positions, int requests, int hidden, int K, int dtype,
+                                   cudaStream_t stream) {
+  if (requests == 0) return 0;
+  TL_REQUIRE(requests > 0 && hidden > 0, "short_conv_state: requests %d hidden %d", requests, hidden);
+  TL_REQUIRE(K >= 2 && K <= MAX_TAPS, "short_conv_state: %d taps; 2..%d are implemented", K, MAX_TAPS);
+  dim3 grid(requests, ceil_div(hidden, 256));
+  if (dtype == TL_FP32)
+    short_conv_state_kernel<float><<<grid, 256, 0, stream>>>((const float*)bcx, state, state_slot, row_start, positions,
+                                                             hidden, K);
+  else
+    short_conv_state_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)bcx, state, state_slot, row_start, positions,
+                                                            hidden, K);
+  TL_LAUNCH_CHECK();
+  return 0;
+}

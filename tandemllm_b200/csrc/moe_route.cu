@@ -1,0 +1,243 @@
+// Routing of the sigmoid top-k experts: the choice, the expert-sorted plan of (row, slot) pairs with its
+// row-tile map, and the weighted combine. Everything stays on the device: no count comes back to the host.
+//
+//   s = sigmoid(logits); choice by s + expert_bias (bias for the choice only); w = s[chosen]
+//   w = w / (sum w + floor) when normalised; w *= scale            engine/models/lfm2_moe/ref.py:185-197
+//   ties go to the lower expert id                                  engine/models/lfm2_moe/kernels.py:265-287
+//   out[r] = sum over the row's experts in ascending expert id of w * expert(x[r])    ref.py:207-214
+//
+// The plan is a stable counting sort: pairs keep their row order inside an expert, so the order of every
+// sum is fixed by the inputs alone (no atomics).
+#include "common.cuh"
+
+namespace tl {
+
+constexpr int MAX_EXPERTS = 1024;
+constexpr int MAX_TOP_K = 32;
+
+// one warp per row
+__global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, long long ld,
+                                                          const float* __restrict__ bias, int rows, int E, int k,
+                                                          int normalize, float floor_, float scale,
+                                                          int* __restrict__ ids, float* __restrict__ wts) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const float* lg = logits + (long long)warp * ld;
+  constexpr int PER = MAX_EXPERTS / 32;
+  float score[PER], choice[PER];
+#pragma unroll
+  for (int t = 0; t < PER; ++t) {
+    const int e = lane + 32 * t;
+    if (e < E) {
+      const float s = 1.f / (1.f + expf(-lg[e]));
+      score[t] = s;
+      choice[t] = bias ? s + bias[e] : s;
+      if (!(choice[t] == choice[t])) choice[t] = -INFINITY;   // a NaN score is never chosen before a number
+    } else {
+      score[t] = 0.f;
+      choice[t] = -INFINITY;
+    }
+  }
+  float sum = 0.f, my_w = 0.f;
+  int my_id = 0;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    float best_s = 0.f;
+#pragma unroll
+    for (int t = 0; t < PER; ++t) {
+      const int e = lane + 32 * t;
+      if (e < E && choice[t] != -INFINITY && (choice[t] > best || (choice[t] == best && e < best_e))) {
+        best = choice[t];
+        best_e = e;
+        best_s = score[t];
+      }
+    }
+    // when everything left is -inf (only with NaN scores) fall back to the lowest untaken id
+    if (best_e == 0x7fffffff) {
+#pragma unroll
+      for (int t = 0; t < PER; ++t) {
+        const int e = lane + 32 * t;
+        if (e < E && score[t] != -1.f && e < best_e) {
+          best_e = e;
+          best_s = score[t];
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+        best_s = os;
+      }
+    }
+    // the owner retires the winner
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int t = 0; t < PER; ++t)
+        if (lane + 32 * t == best_e) {
+          choice[t] = -INFINITY;
+          score[t] = -1.f;
+        }
+    }
+    sum += best_s;
+    if (lane == j) {
+      my_id = best_e;
+      my_w = best_s;
+    }
+  }
+  if (lane < k) {
+    float w = my_w;
+    if (normalize) w = w / (sum + floor_);
+    ids[(long long)warp * k + lane] = my_id;
+    wts[(long long)warp * k + lane] = w * scale;
+  }
+}
+
+// grid E: block e counts the pairs routed to expert e
+__global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ ids, int P, int* __restrict__ counts) {
+  __shared__ float scratch[33];
+  const int e = blockIdx.x;
+  int n = 0;
+  for (int p = threadIdx.x; p < P; p += blockDim.x) n += ids[p] == e;
+  const float total = block_sum((float)n, scratch);   // exact below 2^24 pairs
+  if (threadIdx.x == 0) counts[e] = (int)(total + 0.5f);
+}
+
+// grid E: block e places its pairs, in pair order, at offsets[e].. of the sorted list and writes its row tiles
+__global__ void __launch_bounds__(256) moe_place_kernel(const int* __restrict__ ids, int P, int E, int tile_m,
+                                                        const int* __restrict__ counts, int* __restrict__ offsets,
+                                                        int* __restrict__ sorted_pairs, int* __restrict__ pos_of_pair,
+                                                        int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                                                        int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
+  __shared__ int warp_total[8];
+  __shared__ int s_base[2];
+  const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    int off = 0, tiles = 0;
+    for (int i = 0; i < e; ++i) {
+      off += counts[i];
+      tiles += ceil_div(counts[i], tile_m);
+    }
+    s_base[0] = off;
+    s_base[1] = tiles;
+    offsets[e] = off;
+    const int cnt = counts[e];
+    const int mine = ceil_div(cnt, tile_m);
+    for (int t = 0; t < mine; ++t) {
+      tile_group[tiles + t] = e;
+      tile_row0[tiles + t] = off + t * tile_m;
+      tile_rows[tiles + t] = min(tile_m, cnt - t * tile_m);
+    }
+    if (e == E - 1) {
+      offsets[E] = off + cnt;
+      *n_tiles = tiles + mine;
+    }
+  }
+  __syncthreads();
+  int running = s_base[0];
+  for (int p0 = 0; p0 < P; p0 += 256) {
+    const int p = p0 + tid;
+    const bool hit = p < P && ids[p] == e;
+    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) warp_total[warp] = __popc(ballot);
+    __syncthreads();
+    int before = 0, all = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      if (w < warp) before += warp_total[w];
+      all += warp_total[w];
+    }
+    if (hit) {
+      const int at = running + before + __popc(ballot & ((1u << lane) - 1u));
+      sorted_pairs[at] = p;
+      pos_of_pair[p] = at;
+    }
+    running += all;
+    __syncthreads();
+  }
+}
+
+// one block per row: out[r, :] = sum over the row's slots in ascending expert id of wts * y[pos_of_pair]
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
+                                                          const int* __restrict__ ids, const float* __restrict__ wts,
+                                                          T* __restrict__ out, int hidden, int k) {
+  __shared__ int s_src[MAX_TOP_K];
+  __shared__ float s_w[MAX_TOP_K];
+  const int r = blockIdx.x;
+  if (threadIdx.x == 0) {
+    int order[MAX_TOP_K];
+    for (int j = 0; j < k; ++j) {       // insertion sort of the slots by expert id (slot index breaks ties)
+      int i = j;
+      const int e = ids[(long long)r * k + j];
+      while (i > 0 && ids[(long long)r * k + order[i - 1]] > e) {
+        order[i] = order[i - 1];
+        --i;
+      }
+      order[i] = j;
+    }
+    for (int j = 0; j < k; ++j) {
+      s_src[j] = pos_of_pair[(long long)r * k + order[j]];
+      s_w[j] = wts[(long long)r * k + order[j]];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < k; ++j) acc = fmaf(s_w[j], y[(long long)s_src[j] * hidden + c], acc);
+    out[(long long)r * hidden + c] = from_f32<T>(acc);
+  }
+}
+
+}  // namespace tl
+
+using namespace tl;
+
+extern "C" int tl_router_topk(const float* logits, long long ld, const float* bias, int rows, int E, int k,
+                              int normalize, float floor_, float scale, int* ids, float* wts, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  TL_REQUIRE(E > 0 && E <= MAX_EXPERTS, "router: %d experts; up to %d are implemented", E, MAX_EXPERTS);
+  TL_REQUIRE(k > 0 && k <= E && k <= MAX_TOP_K, "router: top-%d of %d experts; up to top-%d is implemented", k, E,
+             MAX_TOP_K);
+  TL_REQUIRE(ld >= E, "router: row stride %lld for %d experts", ld, E);
+  router_topk_kernel<<<ceil_div(rows, 4), 128, 0, stream>>>(logits, ld, bias, rows, E, k, normalize, floor_, scale, ids,
+                                                            wts);
+  TL_LAUNCH_CHECK();
+  return 0;
+}
+
+// Upper bound on the row tiles of any plan over `pairs` pairs and E experts with tiles of tile_m rows.
+extern "C" int tl_moe_max_tiles(int pairs, int E, int tile_m) {
+  const int by_rows = ceil_div(pairs, tile_m) + E;
+  return by_rows < pairs ? by_rows : (pairs > 0 ? pairs : 1);
+}
+
+extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int* counts, int* offsets, int* sorted_pairs,
+                           int* pos_of_pair, int* tile_group, int* tile_row0, int* tile_rows, int* n_tiles,
+                           cudaStream_t stream) {
+  TL_REQUIRE(E > 0 && E <= 65535 && tile_m > 0, "moe plan: %d experts, tile of %d rows", E, tile_m);
+  TL_REQUIRE(pairs >= 0 && pairs < (1 << 24), "moe plan: %d pairs; fewer than 2^24 are implemented", pairs);
+  moe_count_kernel<<<E, 256, 0, stream>>>(ids, pairs, counts);
+  TL_LAUNCH_CHECK();
+  moe_place_kernel<<<E, 256, 0, stream>>>(ids, pairs, E, tile_m, counts, offsets, sorted_pairs, pos_of_pair, tile_group,
+                                          tile_row0, tile_rows, n_tiles);
+  TL_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int tl_moe_combine(const float* y, const int* pos_of_pair, const int* ids, const float* wts, void* out,
+                              int rows, int hidden, int k, int dtype, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  TL_REQUIRE(k > 0 && k <= MAX_TOP_K && hidden > 0, "moe combine: top-%d, hidden %d", k, hidden);
+  if (dtype == TL_FP32)
+    moe_combine_kernel<float><<<rows, 256, 0, stream>>>(y, pos_of_pair, ids, wts, (float*)out, hidden, k);
+  else
+    moe_combine_kernel<bf16><<<rows, 256, 0, stream>>>(y, pos_of_pair, ids, wts, (bf16*)out, hidden, k);
+  TL_LAUNCH_CHECK();
+  return 0;
+}

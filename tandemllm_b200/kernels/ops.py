@@ -1,0 +1,280 @@
+"""Python entry points of the CUDA kernels: tensors in, launches on torch's current stream.
+
+Each function checks what the kernel cannot (device, dtype, contiguity), passes raw pointers and the
+stream handle through ctypes, and raises `KernelError` with the library's own message when a launcher
+refuses its arguments. There is no fallback: a missing library is an error at load time.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import load
+
+FP32, BF16 = 0, 1
+TL_BAD_ARGUMENT = 100001
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return FP32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dtype} is not implemented; float32 and bfloat16 are")
+
+
+_SIGNATURES = {
+    "tl_embed_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tl_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "tl_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "tl_gemm_simt": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
+                     c_int, c_int, c_void_p],
+    "tl_gemm_simt_grouped": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
+                             c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_int, c_void_p],
+    "tl_gemm_simt_tile_rows": [],
+    "tl_short_conv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                      c_int, c_int, c_int, c_void_p],
+    "tl_short_conv_state": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "tl_qk_prepare": [c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                      c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p, c_void_p],
+    "tl_kv_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                    c_int, c_int, c_void_p, c_void_p],
+    "tl_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tl_router_topk": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p,
+                       c_void_p],
+    "tl_moe_max_tiles": [c_int, c_int, c_int],
+    "tl_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                    c_void_p, c_void_p],
+    "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "tl_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
+    "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_void_p, c_void_p],
+}
+
+_core = None
+
+
+def core():
+    """The loaded core library with its signatures declared (built at the first call)."""
+    global _core
+    if _core is None:
+        lib = load("core")
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        lib.tl_last_error.restype = ctypes.c_char_p
+        lib.tl_cuda_error_string.restype = ctypes.c_char_p
+        lib.tl_cuda_error_string.argtypes = [c_int]
+        _core = lib
+    return _core
+
+
+def check(code: int, what: str, lib=None) -> None:
+    if code == 0:
+        return
+    lib = lib or core()
+    if code == TL_BAD_ARGUMENT:
+        raise KernelError(lib.tl_last_error().decode())
+    raise KernelError(f"{what}: CUDA error {code}: {core().tl_cuda_error_string(code).decode()}")
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype: torch.dtype | None, name: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on CUDA tensors only")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} is {t.dtype}, expected {dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+
+
+# ------------------------------------------------------------------------------------------ rows
+def embed_rows(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor, status: torch.Tensor) -> None:
+    _need(table, None, "embedding table"); _need(tokens, torch.int32, "tokens"); _need(residual, torch.float32, "residual")
+    rows, hidden = residual.shape
+    check(core().tl_embed_rows(ptr(table), ptr(tokens), ptr(residual), rows, hidden, table.shape[0],
+                               dtype_code(table.dtype), ptr(status), stream()), "embed_rows")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, gather: torch.Tensor | None = None) -> torch.Tensor:
+    """residual += delta; out = weight * rms_normalised(residual). With `gather` (int32 row indices) the output row
+    i is computed from row gather[i] and the residual is left unchanged."""
+    _need(residual, torch.float32, "residual"); _need(weight, torch.float32, "norm weight"); _need(out, None, "normed")
+    if delta is not None:
+        _need(delta, out.dtype, "delta")
+    hidden = residual.shape[-1]
+    n_out = out.shape[0]
+    check(core().tl_add_rmsnorm(ptr(residual), ptr(delta), ptr(weight), ptr(out), ptr(gather), n_out, hidden,
+                                float(eps), dtype_code(out.dtype), stream()), "add_rmsnorm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(gate_up, out.dtype, "gate_up"); _need(out, None, "out")
+    rows, inter = out.shape
+    check(core().tl_silu_mul(ptr(gate_up), ptr(out), rows, inter, dtype_code(out.dtype), stream()), "silu_mul")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ products
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
+    """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) on the CUDA cores with 32-bit accumulation."""
+    _need(x, w.dtype, "x"); _need(w, None, "w"); _need(out, None, "out")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm shapes: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    check(core().tl_gemm_simt(ptr(x), x.stride(0), ptr(w), w.stride(0), ptr(bias), ptr(out), out.stride(0), M, N, K,
+                              dtype_code(x.dtype), dtype_code(out.dtype), stream()), "gemm_simt")
+    return out
+
+
+def gemm_simt_grouped(a: torch.Tensor, a_gather: torch.Tensor | None, a_div: int, w: torch.Tensor, out: torch.Tensor,
+                      plan: "MoePlan", swiglu: bool) -> torch.Tensor:
+    """Per sorted row i of the plan: out[i] = A[row(i)] @ w[expert(i)]^T, with w [E, N(*2 when swiglu), K]."""
+    _need(a, w.dtype, "a"); _need(w, None, "w"); _need(out, None, "out")
+    E, n_rows_w, K = w.shape
+    N = n_rows_w // 2 if swiglu else n_rows_w
+    check(core().tl_gemm_simt_grouped(ptr(a), a.stride(0), ptr(a_gather), a_div, ptr(w), w.stride(1), w.stride(0),
+                                      ptr(out), out.stride(0), plan.pairs, N, K, ptr(plan.tile_group),
+                                      ptr(plan.tile_row0), ptr(plan.tile_rows), ptr(plan.n_tiles), plan.max_tiles,
+                                      int(swiglu), dtype_code(a.dtype), dtype_code(out.dtype), stream()),
+          "gemm_simt_grouped")
+    return out
+
+
+def simt_tile_rows() -> int:
+    return core().tl_gemm_simt_tile_rows()
+
+
+# ------------------------------------------------------------------------------------------ short conv
+def short_conv(bcx, taps, bias, state, state_slot, req_of_row, row_start, positions, out) -> torch.Tensor:
+    _need(bcx, out.dtype, "bcx"); _need(taps, torch.float32, "taps"); _need(state, torch.float32, "conv state")
+    rows, hidden = out.shape
+    K = taps.shape[1]
+    check(core().tl_short_conv(ptr(bcx), ptr(taps), ptr(bias), ptr(state), ptr(state_slot), ptr(req_of_row),
+                               ptr(row_start), ptr(positions), ptr(out), rows, hidden, K, dtype_code(out.dtype),
+                               stream()), "short_conv")
+    return out
+
+
+def short_conv_state(bcx, state, state_slot, row_start, positions, requests: int, hidden: int, taps: int) -> None:
+    _need(bcx, None, "bcx"); _need(state, torch.float32, "conv state")
+    check(core().tl_short_conv_state(ptr(bcx), ptr(state), ptr(state_slot), ptr(row_start), ptr(positions), requests,
+                                     hidden, taps, dtype_code(bcx.dtype), stream()), "short_conv_state")
+
+
+# ------------------------------------------------------------------------------------------ attention
+def qk_prepare(qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions, req_of_row, block_table, page_size,
+               q_out, k_cache, v_cache, k_out, v_out, num_heads, num_kv_heads, head_dim, status) -> None:
+    _need(qkv, None, "qkv")
+    rows = qkv.shape[0]
+    max_pages = block_table.shape[1] if block_table is not None else 0
+    check(core().tl_qk_prepare(ptr(qkv), qkv.stride(0), ptr(q_weight), ptr(k_weight), float(eps), ptr(inv_freq),
+                               int(rotary_dim), ptr(positions), ptr(req_of_row), ptr(block_table), max_pages,
+                               int(page_size), ptr(q_out), ptr(k_cache), ptr(v_cache), ptr(k_out), ptr(v_out), rows,
+                               num_heads, num_kv_heads, head_dim, dtype_code(qkv.dtype), ptr(status), stream()),
+          "qk_prepare")
+
+
+def kv_store(k, v, positions, req_of_row, block_table, page_size, k_cache, v_cache, status) -> None:
+    _need(k, k_cache.dtype, "k"); _need(v, v_cache.dtype, "v")
+    rows, Hk, D = k.shape
+    check(core().tl_kv_store(ptr(k), ptr(v), ptr(positions), ptr(req_of_row), ptr(block_table), block_table.shape[1],
+                             int(page_size), ptr(k_cache), ptr(v_cache), rows, Hk, D, dtype_code(k.dtype), ptr(status),
+                             stream()), "kv_store")
+
+
+def paged_attention_simt(q, k_cache, v_cache, block_table, page_size, req_of_row, positions, scale, window, out,
+                         status) -> torch.Tensor:
+    _need(q, k_cache.dtype, "q"); _need(out, q.dtype, "out")
+    rows, Hq, D = q.shape
+    Hk = k_cache.shape[1]
+    check(core().tl_paged_attention_simt(ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.shape[1],
+                                         int(page_size), ptr(req_of_row), ptr(positions), float(scale),
+                                         int(window or 0), ptr(out), rows, Hq, Hk, D, dtype_code(q.dtype), ptr(status),
+                                         stream()), "paged_attention")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ experts
+def router_topk(logits, bias, k: int, normalize: bool, floor: float, scale: float, ids, wts) -> None:
+    _need(logits, torch.float32, "router logits"); _need(ids, torch.int32, "ids"); _need(wts, torch.float32, "weights")
+    rows, E = logits.shape
+    check(core().tl_router_topk(ptr(logits), logits.stride(0), ptr(bias), rows, E, k, int(normalize), float(floor),
+                                float(scale), ptr(ids), ptr(wts), stream()), "router_topk")
+
+
+class MoePlan:
+    """Device buffers of one routing plan: pairs sorted by expert and the map of row tiles."""
+
+    def __init__(self, max_pairs: int, num_experts: int, tile_rows: int, device):
+        self.num_experts, self.tile_m, self.max_pairs = num_experts, tile_rows, max_pairs
+        self.max_tiles_cap = core().tl_moe_max_tiles(max_pairs, num_experts, tile_rows)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.counts = torch.zeros(num_experts, **i32)
+        self.offsets = torch.zeros(num_experts + 1, **i32)
+        self.sorted_pairs = torch.zeros(max(max_pairs, 1), **i32)
+        self.pos_of_pair = torch.zeros(max(max_pairs, 1), **i32)
+        self.tile_group = torch.zeros(self.max_tiles_cap, **i32)
+        self.tile_row0 = torch.zeros(self.max_tiles_cap, **i32)
+        self.tile_rows = torch.zeros(self.max_tiles_cap, **i32)
+        self.n_tiles = torch.zeros(1, **i32)
+        self.pairs = 0
+        self.max_tiles = 1
+
+    def build(self, ids: torch.Tensor) -> "MoePlan":
+        pairs = ids.numel()
+        if pairs > self.max_pairs:
+            raise KernelError(f"routing plan sized for {self.max_pairs} pairs, got {pairs}")
+        self.pairs = pairs
+        self.max_tiles = core().tl_moe_max_tiles(pairs, self.num_experts, self.tile_m)
+        check(core().tl_moe_plan(ptr(ids), pairs, self.num_experts, self.tile_m, ptr(self.counts), ptr(self.offsets),
+                                 ptr(self.sorted_pairs), ptr(self.pos_of_pair), ptr(self.tile_group),
+                                 ptr(self.tile_row0), ptr(self.tile_rows), ptr(self.n_tiles), stream()), "moe_plan")
+        return self
+
+
+def moe_combine(y, plan: MoePlan, ids, wts, out) -> torch.Tensor:
+    _need(y, torch.float32, "expert outputs"); _need(out, None, "out")
+    rows, hidden = out.shape
+    check(core().tl_moe_combine(ptr(y), ptr(plan.pos_of_pair), ptr(ids), ptr(wts), ptr(out), rows, hidden, ids.shape[1],
+                                dtype_code(out.dtype), stream()), "moe_combine")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(logits, torch.float32, "logits"); _need(out, torch.int32, "out")
+    rows, V = logits.shape
+    check(core().tl_argmax(ptr(logits), logits.stride(0), rows, V, ptr(out), stream()), "argmax")
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, min_p, seed, position, out) -> torch.Tensor:
+    _need(logits, torch.float32, "logits"); _need(temperature, torch.float32, "temperature")
+    _need(top_k, torch.int32, "top_k"); _need(top_p, torch.float32, "top_p"); _need(min_p, torch.float32, "min_p")
+    _need(seed, torch.int64, "seed"); _need(position, torch.int32, "position"); _need(out, torch.int32, "out")
+    rows, V = logits.shape
+    check(core().tl_sample(ptr(logits), logits.stride(0), rows, V, ptr(temperature), ptr(top_k), ptr(top_p), ptr(min_p),
+                           ptr(seed), ptr(position), ptr(out), stream()), "sample")
+    return out

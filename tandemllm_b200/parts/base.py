@@ -1,0 +1,146 @@
+"""What a part of a layer is, and the registries parts are chosen from.
+
+A layer is put together from a mixer, a feed-forward, norms and (inside a mixer) a position encoding,
+arranged by a block arrangement. Each kind is registered under a name; a `ModelSpec` names kinds and
+gives every size and constant as a parameter. No part reads a model's configuration, knows the model
+it is in, or knows which other parts surround it.
+
+Interfaces (duck-typed; the base classes below document them and hold the shared plumbing):
+
+  Norm            weight_specs() -> [TensorSpec];  bind(read, runtime);
+                  add_norm(residual, delta, out, gather=None) -> out      residual += delta, out = norm(residual)
+  PositionEncoding  fused_rotary() -> (inv_freq, rotary_dim) | None      what the fused q/k kernel can apply itself
+                  apply(q, k, positions) -> None                         in place on [R, heads, D], else
+  Mixer           weight_specs(present) -> [TensorSpec];  bind(read, runtime);
+                  cache_need() -> PagedNeed | SlotNeed | None
+                  forward(x, step, cache) -> [R, hidden] in the compute dtype
+  FeedForward     weight_specs(present);  bind(read, runtime);  forward(x, step) -> [R, hidden]
+  Arrangement     run(layer, residual, pending, step, cache) -> pending  (the not-yet-added branch output)
+
+`step` is the `StepContext` of the running batch: rows of several requests flattened, with each row's
+request, position and the request's tables and slots. `cache` is what the cache manager made for the
+site from the mixer's `cache_need()`.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+from ..config.spec import PartSpec
+from ..weights.loader import TensorSpec
+
+MIXERS: dict[str, Callable[..., Any]] = {}
+FEED_FORWARDS: dict[str, Callable[..., Any]] = {}
+NORMS: dict[str, Callable[..., Any]] = {}
+POSITION_ENCODINGS: dict[str, Callable[..., Any]] = {}
+ARRANGEMENTS: dict[str, Callable[..., Any]] = {}
+
+_TABLES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position_encoding": POSITION_ENCODINGS,
+           "arrangement": ARRANGEMENTS}
+
+
+def register_part(family: str, kind: str):
+    """Class decorator: make `kind` available in the `family` registry
+    (mixer, feed_forward, norm, position_encoding, arrangement)."""
+    table = _TABLES[family]
+
+    def deco(cls):
+        table[kind] = cls
+        return cls
+    return deco
+
+
+def make_part(family: str, spec: PartSpec, **context):
+    table = _TABLES[family]
+    if spec.kind not in table:
+        raise ValueError(f"unknown {family} kind {spec.kind!r}; registered: {', '.join(sorted(table)) or 'none'}")
+    return table[spec.kind](spec, **context)
+
+
+@dataclass
+class Runtime:
+    """Where and in which precision a model runs. `dtype` is the compute dtype: torch.float32 (everything in
+    true 32-bit) or torch.bfloat16 (bfloat16 storage and products, 32-bit norms, softmax, router and residual)."""
+    device: torch.device
+    dtype: torch.dtype
+    status: torch.Tensor | None = None      # int32[1] on the device: kernels record a bad index here instead of faulting
+
+    def __post_init__(self) -> None:
+        if self.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype {self.dtype}: float32 and bfloat16 are implemented")
+        if self.status is None and self.device.type == "cuda":
+            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def matrix(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(device=self.device, dtype=self.dtype).contiguous()
+
+    def vector(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(device=self.device, dtype=torch.float32).contiguous()
+
+
+@dataclass(frozen=True)
+class PagedNeed:
+    """A cache that grows with the sequence: per token, `kv_heads * head_dim` keys and as many values.
+    `window`: only the last `window` positions are ever read (None: all), so pages behind it can be given back."""
+    kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class SlotNeed:
+    """Per-request state of fixed size, zeroed when a request takes the slot."""
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class PagedSiteCache:
+    group: int                  # index of the page group (which block table to use)
+    page_size: int
+    k: torch.Tensor             # [pages, kv_heads, page_size, head_dim]
+    v: torch.Tensor
+
+
+@dataclass
+class SlotSiteCache:
+    state: torch.Tensor         # [slots, *shape]
+
+
+@dataclass
+class StepContext:
+    """One batch: R rows of B requests, each request's rows consecutive and in position order."""
+    n_rows: int
+    n_requests: int
+    token_ids: torch.Tensor         # int32 [R]
+    positions: torch.Tensor         # int32 [R]  absolute position of the row's token in its sequence
+    req_of_row: torch.Tensor        # int32 [R]  index into this batch's requests
+    row_start: torch.Tensor         # int32 [B + 1]
+    state_slot: torch.Tensor        # int32 [B]  the request's slot in every SlotSiteCache
+    block_tables: list[torch.Tensor]  # per page group: int32 [B, max_pages], -1 where no page is held
+    out_rows: torch.Tensor          # int32 [n_out] rows whose logits are wanted
+    n_out: int
+    max_rows_per_request: int = 0   # host copies, for launch shapes
+    max_context: int = 0
+    host: dict = field(default_factory=dict)   # host-side copies of the lists above (for parts written in torch)
+
+
+class Part:
+    """Shared plumbing: a part keeps its spec and names its tensors under a prefix."""
+
+    def __init__(self, spec: PartSpec, prefix: str = "", hidden_size: int = 0, **_):
+        self.spec = spec
+        self.prefix = prefix
+        self.hidden_size = hidden_size
+
+    def weight_specs(self, present: set[str] | None = None) -> list[TensorSpec]:
+        return []
+
+    def bind(self, read: Callable[[str], torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+
+    def cache_need(self):
+        return None

@@ -1,0 +1,142 @@
+"""Feed-forward parts: the dense SwiGLU and the sigmoid-routed top-k SwiGLU experts.
+
+  dense    out = down( silu(gate n) * (up n) )                          engine/models/lfm2_moe/ref.py:180-183
+  experts  logits = router(n) in 32-bit; s = sigmoid(logits); the choice is the top-k of s + expert_bias
+           (the bias for the choice only); w = s[chosen], divided by (sum w + norm_floor) when normalised,
+           times scale; out = sum over the chosen experts in ascending expert id of w * expert(n)
+                                                                         ref.py:185-214
+
+Gate and up are fused into one matrix at bind time ([2I, H], gate first), per expert for the experts
+([E, 2I, H] and [E, H, I], engine/models/lfm2_moe/load.py:136-161). Experts may be stored one by one
+(`<experts>.<e>.<gate|up|down>.weight`) or stacked (`<experts>.gate_up_proj [E, 2I, H]`,
+`<experts>.down_proj [E, H, I]`); what the folder holds decides. Routing never leaves the device: the
+plan of (row, slot) pairs sorted by expert and its tile map are built by kernels, and the expert
+products skip experts nobody chose.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.loader import TensorSpec
+from .base import Part, register_part
+from .linear import linear
+
+_expert_impl = None     # set by kernels.tensorcore.enable(): .experts(part, x, ids, wts, out) -> bool
+
+
+def use_expert_kernel(impl) -> None:
+    global _expert_impl
+    _expert_impl = impl
+
+
+@register_part("feed_forward", "swiglu")
+class SwiGLU(Part):
+    def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
+        super().__init__(spec, prefix, hidden_size)
+        self.inter = int(spec["intermediate_size"])
+        self.n = {k: prefix + v for k, v in spec["names"].items()}
+
+    def weight_specs(self, present=None):
+        H, I = self.hidden_size, self.inter
+        return [TensorSpec(self.n["gate"] + ".weight", (I, H)), TensorSpec(self.n["up"] + ".weight", (I, H)),
+                TensorSpec(self.n["down"] + ".weight", (H, I))]
+
+    def bind(self, read, runtime):
+        self.runtime = runtime
+        self.w_gate_up = torch.cat([runtime.matrix(read(self.n["gate"] + ".weight")),
+                                    runtime.matrix(read(self.n["up"] + ".weight"))]).contiguous()
+        self.w_down = runtime.matrix(read(self.n["down"] + ".weight"))
+
+    def forward(self, x, step):
+        gu = linear(x, self.w_gate_up)
+        act = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
+        ops.silu_mul(gu, act)
+        return linear(act, self.w_down)
+
+
+@register_part("feed_forward", "sigmoid_topk_experts")
+class SigmoidTopKExperts(Part):
+    def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
+        super().__init__(spec, prefix, hidden_size)
+        self.num_experts = int(spec["num_experts"])
+        self.top_k = int(spec["top_k"])
+        self.inter = int(spec["intermediate_size"])
+        self.use_bias = bool(spec.get("expert_bias", True))
+        self.normalize = bool(spec.get("normalize", True))
+        self.scale = float(spec.get("scale", 1.0))
+        self.norm_floor = float(spec.get("norm_floor", 1e-6))
+        if not 0 < self.top_k <= self.num_experts:
+            raise ValueError(f"top-{self.top_k} of {self.num_experts} experts")
+        if self.num_experts > 1024 or self.top_k > 32:
+            raise ValueError(f"{self.num_experts} experts top-{self.top_k}: up to 1024 experts and top-32 are implemented")
+        self.n = dict(spec["names"])
+        self.base = prefix + self.n["experts"]
+        self._plan = None
+        self.stacked = False
+        self.load_counts = None     # int64 [E]: pairs routed to each expert since the last reset (when recording)
+
+    def _stacked(self, present) -> bool:
+        return present is not None and (self.base + ".gate_up_proj") in present
+
+    def weight_specs(self, present=None):
+        H, I, E = self.hidden_size, self.inter, self.num_experts
+        out = [TensorSpec(self.prefix + self.n["router"] + ".weight", (E, H))]
+        if self.use_bias:
+            out.append(TensorSpec(self.prefix + self.n["bias"], (E,), "vector", "bias"))
+        self.stacked = self._stacked(present)
+        if self.stacked:
+            out += [TensorSpec(self.base + ".gate_up_proj", (E, 2 * I, H)), TensorSpec(self.base + ".down_proj", (E, H, I))]
+        else:
+            for e in range(E):
+                out += [TensorSpec(f"{self.base}.{e}.{self.n['gate']}.weight", (I, H)),
+                        TensorSpec(f"{self.base}.{e}.{self.n['up']}.weight", (I, H)),
+                        TensorSpec(f"{self.base}.{e}.{self.n['down']}.weight", (H, I))]
+        return out
+
+    def bind(self, read, runtime):
+        self.runtime = runtime
+        H, I, E = self.hidden_size, self.inter, self.num_experts
+        self.w_router = runtime.matrix(read(self.prefix + self.n["router"] + ".weight"))
+        self.expert_bias = runtime.vector(read(self.prefix + self.n["bias"])) if self.use_bias else None
+        if self.stacked:
+            self.w_gate_up = runtime.matrix(read(self.base + ".gate_up_proj"))
+            self.w_down = runtime.matrix(read(self.base + ".down_proj"))
+        else:
+            self.w_gate_up = torch.empty(E, 2 * I, H, dtype=runtime.dtype, device=runtime.device)
+            self.w_down = torch.empty(E, H, I, dtype=runtime.dtype, device=runtime.device)
+            for e in range(E):
+                self.w_gate_up[e, :I].copy_(read(f"{self.base}.{e}.{self.n['gate']}.weight"))
+                self.w_gate_up[e, I:].copy_(read(f"{self.base}.{e}.{self.n['up']}.weight"))
+                self.w_down[e].copy_(read(f"{self.base}.{e}.{self.n['down']}.weight"))
+
+    def route(self, x):
+        """(ids int32 [R, k], weights float32 [R, k]) of the rows x."""
+        R = x.shape[0]
+        logits = linear(x, self.w_router, out_dtype=torch.float32)
+        ids = torch.empty(R, self.top_k, dtype=torch.int32, device=x.device)
+        wts = torch.empty(R, self.top_k, dtype=torch.float32, device=x.device)
+        ops.router_topk(logits, self.expert_bias, self.top_k, self.normalize, self.norm_floor, self.scale, ids, wts)
+        return ids, wts
+
+    def plan_for(self, pairs: int, device) -> ops.MoePlan:
+        if self._plan is None or self._plan.max_pairs < pairs:
+            cap = max(pairs, 64) if self._plan is None else max(pairs, 2 * self._plan.max_pairs)
+            self._plan = ops.MoePlan(cap, self.num_experts, ops.simt_tile_rows(), device)
+        return self._plan
+
+    def forward(self, x, step):
+        R, H = x.shape[0], self.hidden_size
+        ids, wts = self.route(x)
+        out = torch.empty(R, H, dtype=x.dtype, device=x.device)
+        if _expert_impl is not None and x.dtype == torch.bfloat16 and _expert_impl.experts(self, x, ids, wts, out):
+            return out
+        plan = self.plan_for(R * self.top_k, x.device).build(ids)
+        if self.load_counts is not None:
+            self.load_counts += plan.counts
+        act = torch.empty(R * self.top_k, self.inter, dtype=x.dtype, device=x.device)
+        ops.gemm_simt_grouped(x, plan.sorted_pairs, self.top_k, self.w_gate_up, act, plan, swiglu=True)
+        y = torch.empty(R * self.top_k, H, dtype=torch.float32, device=x.device)
+        ops.gemm_simt_grouped(act, None, 1, self.w_down, y, plan, swiglu=False)
+        return ops.moe_combine(y, plan, ids, wts, out)

@@ -1,0 +1,50 @@
+"""The tiny LFM2 MoE configurations of the tests, as config.json dictionaries, and their prompts.
+
+A and B differ in every size and option: layer count and order, width, head counts and grouping, head size,
+conv taps and conv bias, dense layer count and width, expert count, top-k, expert width, expert bias,
+renormalisation, scaling factor, vocabulary, rotary base, norm eps, tied or untied head. Widths and the
+vocabulary of B are no powers of two.
+"""
+
+from __future__ import annotations
+
+import torch
+
+TINY_A = dict(
+    model_type="lfm2_moe", architectures=["Lfm2MoeForCausalLM"], vocab_size=256, hidden_size=64,
+    intermediate_size=128, moe_intermediate_size=32, num_hidden_layers=4, num_attention_heads=4,
+    num_key_value_heads=2, head_dim=16, norm_eps=1e-5, max_position_embeddings=4096, conv_bias=False,
+    conv_L_cache=3, num_dense_layers=1, num_experts=4, num_experts_per_tok=2, use_expert_bias=True,
+    routed_scaling_factor=1.0, norm_topk_prob=True, tie_word_embeddings=True,
+    layer_types=["conv", "full_attention", "conv", "full_attention"],
+    rope_parameters={"rope_type": "default", "rope_theta": 10000.0}, eos_token_id=2, bos_token_id=1, pad_token_id=0,
+)
+
+TINY_B = dict(
+    model_type="lfm2_moe", architectures=["Lfm2MoeForCausalLM"], vocab_size=384, hidden_size=96,
+    intermediate_size=256, moe_intermediate_size=48, num_hidden_layers=6, num_attention_heads=3,
+    num_key_value_heads=1, head_dim=32, norm_eps=1e-6, max_position_embeddings=4096, conv_bias=True,
+    conv_L_cache=4, num_dense_layers=2, num_experts=8, num_experts_per_tok=3, use_expert_bias=False,
+    routed_scaling_factor=1.5, norm_topk_prob=False, tie_word_embeddings=False,
+    layer_types=["conv", "conv", "full_attention", "conv", "full_attention", "full_attention"],
+    rope_parameters={"rope_type": "default", "rope_theta": 1000000.0}, eos_token_id=3, bos_token_id=1, pad_token_id=0,
+)
+
+# B without the three options the reference refuses, so the reference itself can run it
+TINY_B_REFERENCE = {**TINY_B, "conv_bias": False, "norm_topk_prob": True}
+
+SEEDS = {"a": 0, "b": 1}
+STD = {"a": 0.02, "b": 0.05}
+
+
+def prompts(name: str) -> list[list[int]]:
+    """Seeded uniform-random token ids: A has prompts of 16 and 9 tokens, B of 33, 5 and 20."""
+    cfg, lens, seed = (TINY_A, (16, 9), 100) if name == "a" else (TINY_B, (33, 5, 20), 101)
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+
+
+def long_tokens(name: str, n: int, seed: int = 7) -> list[int]:
+    cfg = TINY_A if name == "a" else TINY_B
+    g = torch.Generator().manual_seed(seed * 1000 + n)
+    return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
