@@ -162,11 +162,10 @@ __global__ void __launch_bounds__(256) moe_place_kernel(const int* __restrict__ 
   }
 }
 
-// one block per row: out[r, :] = sum over the row's slots in ascending expert id of wts * y[pos_of_pair]
-template <typename T>
+// one block per row: out[r, :] = sum over the row's slots in ascending expert id of wts * y[pos_of_pair]  (32-bit)
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                                           const int* __restrict__ ids, const float* __restrict__ wts,
-                                                          T* __restrict__ out, int hidden, int k) {
+                                                          float* __restrict__ out, int hidden, int k) {
   __shared__ int s_src[MAX_TOP_K];
   __shared__ float s_w[MAX_TOP_K];
   const int r = blockIdx.x;
@@ -190,7 +189,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float acc = 0.f;
     for (int j = 0; j < k; ++j) acc = fmaf(s_w[j], y[(long long)s_src[j] * hidden + c], acc);
-    out[(long long)r * hidden + c] = from_f32<T>(acc);
+    out[(long long)r * hidden + c] = acc;
   }
 }
 
@@ -230,14 +229,11 @@ extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int* co
   return 0;
 }
 
-extern "C" int tl_moe_combine(const float* y, const int* pos_of_pair, const int* ids, const float* wts, void* out,
-                              int rows, int hidden, int k, int dtype, cudaStream_t stream) {
+extern "C" int tl_moe_combine(const float* y, const int* pos_of_pair, const int* ids, const float* wts, float* out,
+                              int rows, int hidden, int k, cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(k > 0 && k <= MAX_TOP_K && hidden > 0, "moe combine: top-%d, hidden %d", k, hidden);
-  if (dtype == TL_FP32)
-    moe_combine_kernel<float><<<rows, 256, 0, stream>>>(y, pos_of_pair, ids, wts, (float*)out, hidden, k);
-  else
-    moe_combine_kernel<bf16><<<rows, 256, 0, stream>>>(y, pos_of_pair, ids, wts, (bf16*)out, hidden, k);
+  moe_combine_kernel<<<rows, 256, 0, stream>>>(y, pos_of_pair, ids, wts, out, hidden, k);
   TL_LAUNCH_CHECK();
   return 0;
 }

@@ -39,34 +39,38 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
 }
 
-// One block per output row.
+// One block per output row. The branch output `delta` is 32-bit in both precisions.
 //   gather == nullptr: row r:  residual[r] += delta[r] (when delta);  normed[r] = w * residual[r] * rsqrt(mean + eps)
 //   gather != nullptr: output row i reads row gather[i]: x = residual[g] + delta[g]; normed[i] = norm(x);
 //                      the residual is left as it is (used for the final norm at the wanted rows only)
+// normed32 (optional) receives the same normalised row unrounded, for consumers that compute in 32-bit (the router).
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                    const float* __restrict__ weight, T* __restrict__ normed,
-                                   const int* __restrict__ gather, int hidden, float eps) {
+                                   float* __restrict__ normed32, const int* __restrict__ gather, int hidden, float eps) {
   extern __shared__ float row[];       // hidden floats, then 33 for the reduction
   float* scratch = row + hidden;
   const int out_r = blockIdx.x;
   const int r = gather ? gather[out_r] : out_r;
   float* res = residual + (size_t)r * hidden;
-  const T* del = delta ? delta + (size_t)r * hidden : nullptr;
+  const float* del = delta ? delta + (size_t)r * hidden : nullptr;
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float x = res[c];
-    if (del) x += to_f32(del[c]);
+    if (del) x += del[c];
     row[c] = x;
     ss += x * x;
   }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + eps);
   T* out = normed + (size_t)out_r * hidden;
+  float* out32 = normed32 ? normed32 + (size_t)out_r * hidden : nullptr;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     const float x = row[c];
     if (!gather && del) res[c] = x;
-    out[c] = from_f32<T>(weight[c] * (x * inv));
+    const float y = weight[c] * (x * inv);
+    out[c] = from_f32<T>(y);
+    if (out32) out32[c] = y;
   }
 }
 
@@ -100,8 +104,8 @@ extern "C" int tl_embed_rows(const void* table, const int* tokens, float* residu
   return 0;
 }
 
-extern "C" int tl_add_rmsnorm(float* residual, const void* delta, const float* weight, void* normed, const int* gather,
-                              int out_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
+extern "C" int tl_add_rmsnorm(float* residual, const float* delta, const float* weight, void* normed, float* normed32,
+                              const int* gather, int out_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
   if (out_rows == 0) return 0;
   TL_REQUIRE(out_rows > 0 && hidden > 0, "add_rmsnorm: rows %d hidden %d", out_rows, hidden);
   const size_t smem = (size_t)(hidden + 33) * sizeof(float);
@@ -111,12 +115,12 @@ extern "C" int tl_add_rmsnorm(float* residual, const void* delta, const float* w
   if (dtype == TL_FP32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<float><<<out_rows, threads, smem, stream>>>(residual, (const float*)delta, weight, (float*)normed,
+    add_rmsnorm_kernel<float><<<out_rows, threads, smem, stream>>>(residual, delta, weight, (float*)normed, normed32,
                                                                   gather, hidden, eps);
   } else {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<bf16><<<out_rows, threads, smem, stream>>>(residual, (const bf16*)delta, weight, (bf16*)normed,
+    add_rmsnorm_kernel<bf16><<<out_rows, threads, smem, stream>>>(residual, delta, weight, (bf16*)normed, normed32,
                                                                  gather, hidden, eps);
   }
   TL_LAUNCH_CHECK();

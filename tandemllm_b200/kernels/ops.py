@@ -32,7 +32,8 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 _SIGNATURES = {
     "tl_embed_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "tl_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "tl_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
+                       c_void_p],
     "tl_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_gemm_simt": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
                      c_int, c_int, c_void_p],
@@ -55,7 +56,7 @@ _SIGNATURES = {
     "tl_moe_max_tiles": [c_int, c_int, c_int],
     "tl_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_void_p],
-    "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_void_p, c_void_p],
@@ -115,16 +116,19 @@ def embed_rows(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
-                out: torch.Tensor, gather: torch.Tensor | None = None) -> torch.Tensor:
-    """residual += delta; out = weight * rms_normalised(residual). With `gather` (int32 row indices) the output row
-    i is computed from row gather[i] and the residual is left unchanged."""
+                out: torch.Tensor, gather: torch.Tensor | None = None, out32: torch.Tensor | None = None) -> torch.Tensor:
+    """residual += delta (32-bit); out = weight * rms_normalised(residual). With `gather` (int32 row indices) the
+    output row i is computed from row gather[i] and the residual is left unchanged. `out32` also receives the
+    normalised rows unrounded."""
     _need(residual, torch.float32, "residual"); _need(weight, torch.float32, "norm weight"); _need(out, None, "normed")
     if delta is not None:
-        _need(delta, out.dtype, "delta")
+        _need(delta, torch.float32, "delta")
+    if out32 is not None:
+        _need(out32, torch.float32, "normed32")
     hidden = residual.shape[-1]
     n_out = out.shape[0]
-    check(core().tl_add_rmsnorm(ptr(residual), ptr(delta), ptr(weight), ptr(out), ptr(gather), n_out, hidden,
-                                float(eps), dtype_code(out.dtype), stream()), "add_rmsnorm")
+    check(core().tl_add_rmsnorm(ptr(residual), ptr(delta), ptr(weight), ptr(out), ptr(out32), ptr(gather), n_out,
+                                hidden, float(eps), dtype_code(out.dtype), stream()), "add_rmsnorm")
     return out
 
 
@@ -255,10 +259,10 @@ class MoePlan:
 
 
 def moe_combine(y, plan: MoePlan, ids, wts, out) -> torch.Tensor:
-    _need(y, torch.float32, "expert outputs"); _need(out, None, "out")
+    _need(y, torch.float32, "expert outputs"); _need(out, torch.float32, "out")
     rows, hidden = out.shape
     check(core().tl_moe_combine(ptr(y), ptr(plan.pos_of_pair), ptr(ids), ptr(wts), ptr(out), rows, hidden, ids.shape[1],
-                                dtype_code(out.dtype), stream()), "moe_combine")
+                                stream()), "moe_combine")
     return out
 
 

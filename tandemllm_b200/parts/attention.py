@@ -106,4 +106,4 @@ class AttentionMixer(Part):
         if _attention_impl is None or not _attention_impl.attention(q, cache, table, step, self.scale, self.window, o):
             ops.paged_attention_simt(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions,
                                      self.scale, self.window, o, status)
-        return linear(o.view(R, Hq * D), self.w_out)
+        return linear(o.view(R, Hq * D), self.w_out, out_dtype=torch.float32)

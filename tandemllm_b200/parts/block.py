@@ -19,6 +19,9 @@ class PreNormResidual:
     def run(self, layer: "Layer", residual, pending, step, cache, writes_cache: bool = True):
         n = layer.mixer_norm.add_norm(residual, pending)
         d = layer.mixer.forward(n, step, cache, writes_cache=writes_cache)
+        if getattr(layer.feed_forward, "wants_x32", False):
+            n, n32 = layer.feed_forward_norm.add_norm(residual, d, want32=True)
+            return layer.feed_forward.forward(n, step, x32=n32)
         n = layer.feed_forward_norm.add_norm(residual, d)
         return layer.feed_forward.forward(n, step)
 

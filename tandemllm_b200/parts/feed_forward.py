@@ -49,11 +49,11 @@ class SwiGLU(Part):
                                     runtime.matrix(read(self.n["up"] + ".weight"))]).contiguous()
         self.w_down = runtime.matrix(read(self.n["down"] + ".weight"))
 
-    def forward(self, x, step):
+    def forward(self, x, step, x32=None):
         gu = linear(x, self.w_gate_up)
         act = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
         ops.silu_mul(gu, act)
-        return linear(act, self.w_down)
+        return linear(act, self.w_down, out_dtype=torch.float32)
 
 
 @register_part("feed_forward", "sigmoid_topk_experts")
@@ -98,7 +98,8 @@ class SigmoidTopKExperts(Part):
     def bind(self, read, runtime):
         self.runtime = runtime
         H, I, E = self.hidden_size, self.inter, self.num_experts
-        self.w_router = runtime.matrix(read(self.prefix + self.n["router"] + ".weight"))
+        # the router's product is 32-bit in both precisions: its weights are kept in 32-bit (E x H is small)
+        self.w_router = runtime.vector(read(self.prefix + self.n["router"] + ".weight"))
         self.expert_bias = runtime.vector(read(self.prefix + self.n["bias"])) if self.use_bias else None
         if self.stacked:
             self.w_gate_up = runtime.matrix(read(self.base + ".gate_up_proj"))
@@ -111,12 +112,15 @@ class SigmoidTopKExperts(Part):
                 self.w_gate_up[e, I:].copy_(read(f"{self.base}.{e}.{self.n['up']}.weight"))
                 self.w_down[e].copy_(read(f"{self.base}.{e}.{self.n['down']}.weight"))
 
-    def route(self, x):
-        """(ids int32 [R, k], weights float32 [R, k]) of the rows x."""
-        R = x.shape[0]
-        logits = linear(x, self.w_router, out_dtype=torch.float32)
-        ids = torch.empty(R, self.top_k, dtype=torch.int32, device=x.device)
-        wts = torch.empty(R, self.top_k, dtype=torch.float32, device=x.device)
+    wants_x32 = True        # the block hands the normed rows unrounded as well: router logits are 32-bit end to end
+
+    def route(self, x32):
+        """(ids int32 [R, k], weights float32 [R, k]) of the 32-bit rows x32."""
+        R = x32.shape[0]
+        logits = ops.gemm_simt(x32, self.w_router, None, torch.empty(R, self.num_experts, dtype=torch.float32,
+                                                                      device=x32.device))
+        ids = torch.empty(R, self.top_k, dtype=torch.int32, device=x32.device)
+        wts = torch.empty(R, self.top_k, dtype=torch.float32, device=x32.device)
         ops.router_topk(logits, self.expert_bias, self.top_k, self.normalize, self.norm_floor, self.scale, ids, wts)
         return ids, wts
 
@@ -126,10 +130,10 @@ class SigmoidTopKExperts(Part):
             self._plan = ops.MoePlan(cap, self.num_experts, ops.simt_tile_rows(), device)
         return self._plan
 
-    def forward(self, x, step):
+    def forward(self, x, step, x32=None):
         R, H = x.shape[0], self.hidden_size
-        ids, wts = self.route(x)
-        out = torch.empty(R, H, dtype=x.dtype, device=x.device)
+        ids, wts = self.route(x32 if x32 is not None else x.float())
+        out = torch.empty(R, H, dtype=torch.float32, device=x.device)
         if _expert_impl is not None and x.dtype == torch.bfloat16 and _expert_impl.experts(self, x, ids, wts, out):
             return out
         plan = self.plan_for(R * self.top_k, x.device).build(ids)

@@ -32,8 +32,17 @@ class RMSNorm(Part):
         self.weight = runtime.vector(read(self.name))
 
     def add_norm(self, residual: torch.Tensor, delta: torch.Tensor | None, out: torch.Tensor | None = None,
-                 gather: torch.Tensor | None = None, n_out: int | None = None) -> torch.Tensor:
+                 gather: torch.Tensor | None = None, n_out: int | None = None, want32: bool = False):
+        """residual += delta (both 32-bit); returns the normed rows in the compute dtype, and with `want32` the
+        pair (normed, the same rows unrounded in 32-bit)."""
         rows = residual.shape[0] if gather is None else (n_out if n_out is not None else gather.shape[0])
         if out is None:
             out = torch.empty(rows, self.size, dtype=self.runtime.dtype, device=residual.device)
-        return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather)
+        if not want32:
+            return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather)
+        if out.dtype == torch.float32:
+            ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather)
+            return out, out
+        out32 = torch.empty(rows, self.size, dtype=torch.float32, device=residual.device)
+        ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather, out32)
+        return out, out32

@@ -144,9 +144,23 @@ def expert_mlp(x: torch.Tensor, W: dict, p: str, e: int) -> torch.Tensor:
     return (torch.nn.functional.silu(x @ W[q + "w1.weight"].T) * (x @ W[q + "w3.weight"].T)) @ W[q + "w2.weight"].T
 
 
-def moe(n: torch.Tensor, W: dict, p: str, cfg: dict) -> torch.Tensor:
+def routing_margin(n: torch.Tensor, W: dict, p: str, cfg: dict) -> torch.Tensor:
+    """Per row, the gap between the k-th and the (k+1)-th choice score: how far the row is from another choice
+    of experts (0 when every expert is chosen anyway)."""
+    k = cfg_get(cfg, "num_experts_per_tok", 4)
+    s = (n @ W[p + "gate.weight"].T).sigmoid()
+    choice = s + W[p + "expert_bias"] if cfg_get(cfg, "use_expert_bias", True) else s
+    if k >= choice.shape[-1]:
+        return torch.full((n.shape[0],), float("inf"))
+    top = torch.sort(choice, dim=-1, descending=True).values
+    return top[:, k - 1] - top[:, k]
+
+
+def moe(n: torch.Tensor, W: dict, p: str, cfg: dict, margins: list | None = None) -> torch.Tensor:
     """engine/models/lfm2_moe/ref.py:207-214: each chosen expert's output times its weight, added in ascending
-    expert id."""
+    expert id. `margins`, when given, collects each layer's routing margins."""
+    if margins is not None:
+        margins.append(routing_margin(n, W, p, cfg))
     ids, w = route(n, W, p, cfg)
     out = torch.zeros_like(n)
     for e in sorted(set(ids.reshape(-1).tolist())):
@@ -155,10 +169,12 @@ def moe(n: torch.Tensor, W: dict, p: str, cfg: dict) -> torch.Tensor:
     return out
 
 
-def forward(cfg: dict, W: dict, tokens: list[int] | torch.Tensor, dtype=torch.float32) -> torch.Tensor:
+def forward(cfg: dict, W: dict, tokens: list[int] | torch.Tensor, dtype=torch.float32,
+            margins: list | None = None) -> torch.Tensor:
     """Logits [T, vocab] (32-bit) of a whole sequence (engine/models/lfm2_moe/ref.py:218-241): embed; per layer
     n = norm(h), h += mixer(n), n = norm(h), h += ffn(n); final norm `embedding_norm`; head = lm_head.weight
-    if the model has an untied head, else the embedding."""
+    if the model has an untied head, else the embedding. `margins` collects the routing margins [T] of every
+    MoE layer."""
     W = {k: (v.to(dtype) if v.is_floating_point() and not k.endswith("expert_bias") else v) for k, v in W.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     eps = cfg_get(cfg, "norm_eps", 1e-5)
@@ -174,7 +190,7 @@ def forward(cfg: dict, W: dict, tokens: list[int] | torch.Tensor, dtype=torch.fl
             h = h + short_conv(n, W, p + "conv.", cfg_get(cfg, "conv_L_cache", 3), bool(cfg.get("conv_bias", False)))
         n = rms_norm(h, W[p + "ffn_norm.weight"], eps)
         f = p + "feed_forward."
-        h = h + (moe(n, W, f, cfg) if li >= dense_layers else dense_mlp(n, W, f))
+        h = h + (moe(n, W, f, cfg, margins) if li >= dense_layers else dense_mlp(n, W, f))
     h = rms_norm(h, W["embedding_norm.weight"], eps)
     tied = cfg.get("tie_word_embeddings", cfg.get("tie_embedding", True))
     head = W["embed_tokens.weight"] if tied else W["lm_head.weight"]

@@ -1,0 +1,462 @@
+"""Each kernel alone against a plain torch reference of the same operation, at sizes other than the tiny
+models': widths and vocabularies that are no powers of two, head sizes in steps of 16, odd head counts and
+groups, tails shorter than a tile. Where random inputs would hide a fault (a far key among hundreds, a
+window's edge, a page's edge) the inputs are made so that it shows.
+"""
+
+import math
+
+import pytest
+import torch
+
+from tests import plain_lfm2 as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    from tandemllm_b200.kernels import ops as o
+    o.core()
+    return o
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 2e-2
+
+
+def close(got, want, dtype, what=""):
+    got, want = got.float().cpu(), want.float().cpu()
+    scale = want.abs().max().clamp_min(1e-6)
+    err = float((got - want).abs().max() / scale)
+    assert err <= tol(dtype), f"{what}: error {err:.3g} of the largest value"
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g) * scale
+
+
+# ------------------------------------------------------------------------------------------ rows
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [200, 96, 2048, 5000])
+def test_embed_and_add_rmsnorm(dtype, hidden):
+    o = ops()
+    V, R = 77, 13
+    table = rnd(V, hidden, seed=1).to(dtype)
+    toks = torch.randint(0, V, (R,), generator=torch.Generator().manual_seed(2), dtype=torch.int32)
+    res = torch.empty(R, hidden, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.embed_rows(table.to(DEV), toks.to(DEV), res, status)
+    assert torch.equal(res.cpu(), table[toks.long()].float()) and int(status) == 0
+    w = 1 + rnd(hidden, seed=3, scale=0.2)
+    delta = rnd(R, hidden, seed=4)
+    eps = 3e-4
+    want_res = table[toks.long()].float() + delta
+    want = P.rms_norm(want_res, w, eps)
+    out = torch.empty(R, hidden, dtype=dtype, device=DEV)
+    out32 = torch.empty(R, hidden, dtype=torch.float32, device=DEV)
+    o.add_rmsnorm(res, delta.to(DEV), w.to(DEV), eps, out, None, out32)
+    close(res, want_res, torch.float32, "residual")
+    close(out, want, dtype, "normed")
+    close(out32, want, torch.float32, "normed32")
+    # gathered rows, residual untouched
+    before = res.clone()
+    idx = torch.tensor([5, 0, 12], dtype=torch.int32)
+    out2 = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    o.add_rmsnorm(res, delta.to(DEV), w.to(DEV), eps, out2, idx.to(DEV))
+    close(out2, P.rms_norm(want_res[idx.long()] + delta[idx.long()], w, eps), dtype, "gathered")
+    assert torch.equal(res, before)
+
+
+def test_embed_records_a_bad_token_instead_of_faulting():
+    o = ops()
+    table = rnd(10, 32).to(DEV)
+    res = torch.empty(2, 32, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.embed_rows(table, torch.tensor([3, 10], dtype=torch.int32, device=DEV), res, status)
+    assert int(status) == 1
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    o = ops()
+    gu = rnd(7, 2 * 150, seed=5).to(dtype)
+    out = torch.empty(7, 150, dtype=dtype, device=DEV)
+    o.silu_mul(gu.to(DEV), out)
+    g, u = gu.float()[:, :150], gu.float()[:, 150:]
+    close(out, torch.nn.functional.silu(g) * u, dtype)
+
+
+# ------------------------------------------------------------------------------------------ products
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 130, 77), (3, 64, 64), (8, 257, 100), (9, 130, 77), (70, 96, 200), (200, 33, 17)])
+def test_gemm_simt(dtype, M, N, K):
+    o = ops()
+    x, w, b = rnd(M, K, seed=6).to(dtype), rnd(N, K, seed=7).to(dtype), rnd(N, seed=8)
+    want = x.float() @ w.float().T + b
+    for out_dtype in {dtype, torch.float32}:
+        out = torch.empty(M, N, dtype=out_dtype, device=DEV)
+        o.gemm_simt(x.to(DEV), w.to(DEV), b.to(DEV), out)
+        close(out, want, out_dtype if dtype == torch.float32 else torch.bfloat16, f"{M}x{N}x{K}")
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    o.gemm_simt(x.to(DEV), w.to(DEV), None, out)
+    close(out, x.float() @ w.float().T, dtype, "no bias")
+
+
+def test_gemm_row_does_not_depend_on_the_other_rows():
+    """A row of a tiled call equals the same row in a smaller tiled call bit for bit (the k order is fixed)."""
+    o = ops()
+    x, w = rnd(100, 300, seed=9).to(DEV), rnd(50, 300, seed=10).to(DEV)
+    big = o.gemm_simt(x, w, None, torch.empty(100, 50, device=DEV))
+    small = o.gemm_simt(x[60:75].contiguous(), w, None, torch.empty(15, 50, device=DEV))
+    assert torch.equal(big[60:75], small)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("R,E,k,H,I", [(5, 4, 2, 48, 40), (70, 6, 3, 96, 72), (300, 40, 4, 64, 24), (1, 8, 8, 32, 16)])
+def test_router_plan_experts_and_combine(dtype, R, E, k, H, I):
+    """The expert path end to end against a loop over experts, and its plan against a stable sort."""
+    o = ops()
+    x = rnd(R, H, seed=11)
+    gate, bias = rnd(E, H, seed=12, scale=0.3), rnd(E, seed=13, scale=0.2)
+    w13, w2 = rnd(E, 2 * I, H, seed=14, scale=0.2).to(dtype), rnd(E, H, I, seed=15, scale=0.2).to(dtype)
+    xd = x.to(dtype)
+    logits = x @ gate.T
+    ids = torch.empty(R, k, dtype=torch.int32, device=DEV)
+    wts = torch.empty(R, k, dtype=torch.float32, device=DEV)
+    for normalize, scale, use_bias in ((True, 1.0, True), (False, 2.5, False)):
+        o.router_topk(logits.to(DEV), bias.to(DEV) if use_bias else None, k, normalize, 1e-6, scale, ids, wts)
+        cfg = dict(num_experts_per_tok=k, use_expert_bias=use_bias, norm_topk_prob=normalize, routed_scaling_factor=scale)
+        want_ids, want_w = P.route(x, {"gate.weight": gate, "expert_bias": bias}, "", cfg)
+        assert torch.equal(ids.cpu().long(), want_ids), "chosen experts and their order"
+        close(wts, want_w, torch.float32, "routing weights")
+    plan = o.MoePlan(R * k, E, o.simt_tile_rows(), DEV).build(ids)
+    flat = ids.cpu().reshape(-1).long()
+    order = torch.sort(flat, stable=True).indices
+    assert torch.equal(plan.sorted_pairs[:R * k].cpu().long(), order)
+    assert torch.equal(plan.counts.cpu().long(), torch.bincount(flat, minlength=E))
+    assert torch.equal(plan.pos_of_pair[:R * k].cpu().long()[order], torch.arange(R * k))
+    nt = int(plan.n_tiles)
+    assert nt == sum(-(-int(c) // plan.tile_m) for c in plan.counts.cpu()) and nt <= plan.max_tiles
+    covered = sum(int(r) for r in plan.tile_rows[:nt].cpu())
+    assert covered == R * k
+    act = torch.empty(R * k, I, dtype=dtype, device=DEV)
+    o.gemm_simt_grouped(xd.to(DEV), plan.sorted_pairs, k, w13.to(DEV), act, plan, True)
+    y = torch.empty(R * k, H, dtype=torch.float32, device=DEV)
+    o.gemm_simt_grouped(act, None, 1, w2.to(DEV), y, plan, False)
+    out = torch.empty(R, H, dtype=torch.float32, device=DEV)
+    o.moe_combine(y, plan, ids, wts, out)
+    want = torch.zeros(R, H)
+    xf, w13f, w2f = xd.float(), w13.float(), w2.float()
+    wc = wts.cpu()
+    for e in range(E):
+        rows, slot = torch.where(ids.cpu() == e)
+        if rows.numel():
+            h = torch.nn.functional.silu(xf[rows] @ w13f[e, :I].T) * (xf[rows] @ w13f[e, I:].T)
+            if dtype == torch.bfloat16:
+                h = h.to(dtype).float()
+            want.index_add_(0, rows, (h @ w2f[e].T) * wc[rows, slot, None])
+    close(out, want, dtype, "experts")
+
+
+def test_router_ties_and_many_experts():
+    o = ops()
+    for E, k in ((8, 3), (130, 5), (1000, 32)):
+        logits = torch.zeros(4, E)
+        logits[1, E - 1] = 1.0
+        ids = torch.empty(4, k, dtype=torch.int32, device=DEV)
+        wts = torch.empty(4, k, dtype=torch.float32, device=DEV)
+        o.router_topk(logits.to(DEV), None, k, True, 1e-6, 1.0, ids, wts)
+        assert ids[0].tolist() == list(range(k)), "equal scores: the lower ids, in order"
+        assert ids[1].tolist() == [E - 1] + list(range(k - 1))
+    with pytest.raises(o.KernelError, match="experts"):
+        o.router_topk(torch.zeros(1, 2000, device=DEV), None, 2, True, 1e-6, 1.0, ids, wts)
+
+
+# ------------------------------------------------------------------------------------------ short conv
+def plain_conv_with_state(bcx, taps_w, bias, state, K):
+    """Rows of one request after `state` [K-1, H] (oldest first): (y [n, H], new state)."""
+    H = bcx.shape[1] // 3
+    bx = bcx[:, :H] * bcx[:, 2 * H:]
+    full = torch.cat([state, bx], 0)
+    y = torch.stack([(full[t:t + K] * taps_w.T).sum(0) for t in range(bx.shape[0])])
+    if bias is not None:
+        y = y + bias
+    return bcx[:, H:2 * H] * y, full[-(K - 1):]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("K,H,use_bias", [(3, 200, False), (4, 96, True), (2, 64, False), (7, 300, True)])
+def test_short_conv_mixed_batch_and_state(dtype, K, H, use_bias):
+    """Three requests in one call: a new one with a portion shorter than the taps, one that continues from its
+    slot with a single row, one that continues with a long portion. A stale slot must not leak into a new one."""
+    o = ops()
+    lens, starts = [2, 1, 19], [0, 5, 3]
+    R = sum(lens)
+    bcx = rnd(R, 3 * H, seed=20).to(dtype)
+    taps_w, bias = rnd(H, K, seed=21), (rnd(H, seed=22) if use_bias else None)
+    slots = [2, 0, 3]
+    state = rnd(5, K - 1, H, seed=23)                 # slot 2 holds junk that a sequence starting at 0 must not read
+    row_start = [0, 2, 3, R]
+    req_of_row = sum(([b] * n for b, n in enumerate(lens)), [])
+    positions = sum((list(range(s, s + n)) for s, n in zip(starts, lens)), [])
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    st = state.clone().to(DEV)
+    y = torch.empty(R, H, dtype=dtype, device=DEV)
+    args = (bcx.to(DEV), taps_w.to(DEV), bias.to(DEV) if use_bias else None, st, i32(slots), i32(req_of_row),
+            i32(row_start), i32(positions), y)
+    o.short_conv(*args)
+    o.short_conv_state(bcx.to(DEV), st, i32(slots), i32(row_start), i32(positions), 3, H, K)
+    for b in range(3):
+        old = state[slots[b]].clone()
+        if starts[b] < K - 1:                          # inputs before position 0 are zero
+            old[:K - 1 - starts[b]] = 0
+        rows = slice(row_start[b], row_start[b + 1])
+        want_y, want_state = plain_conv_with_state(bcx[rows].float(), taps_w, bias, old, K)
+        close(y[rows], want_y, dtype, f"request {b}")
+        close(st[slots[b]], want_state, torch.float32, f"state of request {b}")
+    assert torch.equal(st[1].cpu(), state[1]) and torch.equal(st[4].cpu(), state[4]), "other slots are untouched"
+
+
+# ------------------------------------------------------------------------------------------ attention
+def plain_attention(q, k, v, scale, window=None):
+    """q [T, Hq, D] for the last T positions of a sequence whose keys k, v [L, Hk, D] are all given."""
+    T, Hq, D = q.shape
+    L, Hk = k.shape[0], k.shape[1]
+    ks, vs = k.repeat_interleave(Hq // Hk, 1), v.repeat_interleave(Hq // Hk, 1)
+    s = torch.einsum("thd,shd->hts", q, ks) * scale
+    qpos = torch.arange(L - T, L)[:, None]
+    kpos = torch.arange(L)[None, :]
+    hidden = kpos > qpos
+    if window:
+        hidden = hidden | (kpos <= qpos - window)
+    s = s.masked_fill(hidden[None], float("-inf"))
+    return torch.einsum("hts,shd->thd", torch.softmax(s, -1), vs)
+
+
+def paged_setup(seqs, Hk, D, page, dtype, seed):
+    """Random K/V for sequences of the given lengths scattered over shuffled pages: (k_cache, v_cache, table, ks, vs)."""
+    g = torch.Generator().manual_seed(seed)
+    n_pages = sum(-(-L // page) for L in seqs) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kc = torch.zeros(n_pages, Hk, page, D)
+    vc = torch.zeros(n_pages, Hk, page, D)
+    width = max(-(-L // page) for L in seqs) + 1
+    table = torch.full((len(seqs), width), -1, dtype=torch.int32)
+    ks, vs = [], []
+    for b, L in enumerate(seqs):
+        k = (torch.randn(L, Hk, D, generator=g)).to(dtype).float()
+        v = (torch.randn(L, Hk, D, generator=g)).to(dtype).float()
+        for j in range(-(-L // page)):
+            pg = perm.pop()
+            table[b, j] = pg
+            n = min(page, L - j * page)
+            kc[pg, :, :n] = k[j * page:j * page + n].transpose(0, 1)
+            vc[pg, :, :n] = v[j * page:j * page + n].transpose(0, 1)
+        ks.append(k)
+        vs.append(v)
+    return kc.to(dtype), vc.to(dtype), table, ks, vs
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hk,D,page,window", [(6, 2, 48, 16, None), (5, 5, 16, 16, None), (8, 1, 128, 32, None),
+                                                 (4, 2, 64, 16, 37), (3, 1, 256, 64, None), (4, 4, 80, 16, 16)])
+def test_paged_attention_mixed_rows(dtype, Hq, Hk, D, page, window):
+    """A decode row at a long context, a prompt portion in the middle of a sequence, and a sequence's first rows,
+    in one call, against whole-sequence attention."""
+    o = ops()
+    seqs, news = [333, 90, 7], [1, 23, 7]              # context after the step, rows in the step
+    kc, vc, table, ks, vs = paged_setup(seqs, Hk, D, page, dtype, seed=30)
+    R = sum(news)
+    q = rnd(R, Hq, D, seed=31).to(dtype)
+    req_of_row = sum(([b] * n for b, n in enumerate(news)), [])
+    positions = sum((list(range(L - n, L)) for L, n in zip(seqs, news)), [])
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    out = torch.empty(R, Hq, D, dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    scale = 0.7 / math.sqrt(D)
+    o.paged_attention_simt(q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), page, i32(req_of_row), i32(positions),
+                           scale, window, out, status)
+    assert int(status) == 0
+    at = 0
+    for b, (L, n) in enumerate(zip(seqs, news)):
+        want = plain_attention(q[at:at + n].float(), ks[b], vs[b], scale, window)
+        close(out[at:at + n], want, dtype, f"sequence {b}")
+        at += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 15, 16, 17, 255, 256, 300, 511])
+def test_one_far_key_stands_out(dtype, far):
+    """Among 512 keys, one key is made to match the query so strongly that the output must be its value: a key
+    skipped or read from the wrong page (a page's edge, a chunk's edge) shows at once."""
+    o = ops()
+    Hq, Hk, D, page, L = 4, 2, 64, 16, 512
+    kc, vc, table, ks, vs = paged_setup([L], Hk, D, page, dtype, seed=40 + far)
+    q = rnd(1, Hq, D, seed=41).to(dtype).float()
+    # make key `far` of both KV heads equal to 4 x the queries' mean direction
+    direction = q.mean(1)[0]
+    pg, off = int(table[0, far // page]), far % page
+    kc[pg, :, off] = (4 * direction).to(dtype)
+    ks[0][far] = (4 * direction).to(dtype).float()
+    out = torch.empty(1, Hq, D, dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    o.paged_attention_simt(q.to(dtype).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), page, i32([0]), i32([L - 1]),
+                           1.0, None, out, status)
+    want = plain_attention(q, ks[0], vs[0], 1.0)
+    close(out, want, dtype, f"far key {far}")
+    weight = torch.softmax(torch.einsum("hd,shd->hs", q[0], ks[0].repeat_interleave(2, 1)), -1)[:, far]
+    assert float(weight.min()) > 0.5, "the test's key does dominate"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(dtype):
+    """With a window of w the key w positions back is out and the one w-1 back is in; pages wholly behind the
+    window may be gone (-1 in the table)."""
+    o = ops()
+    Hq, Hk, D, page, L, w = 2, 1, 32, 16, 100, 20
+    kc, vc, table, ks, vs = paged_setup([L], Hk, D, page, dtype, seed=50)
+    q = rnd(1, Hq, D, seed=51).to(dtype).float()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    for hot in (L - w, L - w - 1):                      # first position inside the window, last one outside
+        k2 = [ks[0].clone()]
+        k2[0][hot] = (6 * q.mean(1)[0]).to(dtype).float()
+        kc2 = kc.clone()
+        kc2[int(table[0, hot // page]), :, hot % page] = k2[0][hot].to(dtype)
+        t2 = table.clone()
+        t2[0, :(L - w) // page] = -1                     # pages the window has passed
+        out = torch.empty(1, Hq, D, dtype=dtype, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        o.paged_attention_simt(q.to(dtype).to(DEV), kc2.to(DEV), vc.to(DEV), t2.to(DEV), page, i32([0]), i32([L - 1]),
+                               1.0, w, out, status)
+        assert int(status) == 0
+        close(out, plain_attention(q, k2[0], vs[0], 1.0, w), dtype, f"hot key at {hot}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hk,D,rot", [(6, 2, 48, 48), (3, 1, 32, 16), (4, 4, 128, 128)])
+def test_qk_prepare_norm_rotary_and_page_write(dtype, Hq, Hk, D, rot):
+    o = ops()
+    page, seqs, news = 16, [40, 17], [9, 17]
+    R = sum(news)
+    qkv = rnd(R, (Hq + 2 * Hk) * D, seed=60).to(dtype)
+    qw, kw = 1 + rnd(D, seed=61, scale=0.2), 1 + rnd(D, seed=62, scale=0.2)
+    theta, eps = 5e4, 2e-5
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    table = torch.tensor([[4, 1, 6, -1], [0, 5, -1, -1]], dtype=torch.int32)
+    req_of_row = sum(([b] * n for b, n in enumerate(news)), [])
+    positions = sum((list(range(L - n, L)) for L, n in zip(seqs, news)), [])
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    kc = torch.zeros(8, Hk, page, D, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(R, Hq, D, dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o.qk_prepare(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, inv_freq.to(DEV), rot, i32(positions), i32(req_of_row),
+                 table.to(DEV), page, q_out, kc, vc, None, None, Hq, Hk, D, status)
+    assert int(status) == 0
+    x = qkv.float()
+    q = P.rms_norm(x[:, :Hq * D].view(R, Hq, D), qw, eps)
+    k = P.rms_norm(x[:, Hq * D:(Hq + Hk) * D].view(R, Hk, D), kw, eps)
+    v = x[:, (Hq + Hk) * D:].view(R, Hk, D)
+    pos = torch.tensor(positions)
+    f = pos.float()[:, None] * inv_freq[None, :]
+    cos, sin = torch.cat([f, f], -1).cos()[:, None, :], torch.cat([f, f], -1).sin()[:, None, :]
+
+    def rope(t):
+        a, rest = t[..., :rot], t[..., rot:]
+        return torch.cat([a * cos + P.rotate_half(a) * sin, rest], -1)
+    close(q_out, rope(q), dtype, "q")
+    kk, vv = rope(k), v
+    for r in range(R):
+        b, p = req_of_row[r], positions[r]
+        pg = int(table[b, p // page])
+        close(kc[pg, :, p % page], kk[r], dtype, f"k row {r}")
+        close(vc[pg, :, p % page], vv[r], dtype, f"v row {r}")
+    # the unfused pair: plain outputs, then the page write
+    k_out = torch.empty(R, Hk, D, dtype=dtype, device=DEV)
+    v_out = torch.empty(R, Hk, D, dtype=dtype, device=DEV)
+    o.qk_prepare(qkv.to(DEV), qw.to(DEV), kw.to(DEV), eps, None, 0, i32(positions), i32(req_of_row), None, 0, q_out,
+                 None, None, k_out, v_out, Hq, Hk, D, status)
+    close(k_out, k, dtype, "k without rotation")
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    o.kv_store(k_out, v_out, i32(positions), i32(req_of_row), table.to(DEV), page, kc2, vc2, status)
+    r = R - 1
+    pg = int(table[1, positions[r] // page])
+    assert torch.equal(kc2[pg, :, positions[r] % page], k_out[r]) and int(status) == 0
+    # a write to a position without a page is recorded, not performed
+    o.kv_store(k_out[:1], v_out[:1], i32([50]), i32([1]), table.to(DEV), page, kc2, vc2, status)
+    assert int(status) == 2
+
+
+def test_refused_sizes_are_clear_errors():
+    o = ops()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    q = torch.zeros(1, 2, 24, device=DEV)
+    kc = torch.zeros(2, 2, 16, 24, device=DEV)
+    with pytest.raises(o.KernelError, match="head size 24"):
+        o.paged_attention_simt(q, kc, kc, i32([[0]]), 16, i32([0]), i32([0]), 1.0, None, torch.empty_like(q), status)
+    with pytest.raises(o.KernelError, match="taps"):
+        o.short_conv(torch.zeros(1, 96, device=DEV), torch.zeros(32, 17, device=DEV), None, torch.zeros(1, 16, 32, device=DEV),
+                     i32([0]), i32([0]), i32([0, 1]), i32([0]), torch.empty(1, 32, device=DEV))
+    with pytest.raises(o.KernelError, match="CUDA"):
+        o.gemm_simt(torch.zeros(1, 4), torch.zeros(2, 4), None, torch.zeros(1, 2))
+
+
+# ------------------------------------------------------------------------------------------ sampling
+def test_argmax_and_sampling_match_the_plain_draws():
+    o = ops()
+    V, n = 5003, 12
+    logits = rnd(n, V, seed=70, scale=2.5)
+    logits[3, 77] = logits[3, 4000] = logits[3].max() + 1     # a tie: the lower index
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    o.argmax(logits.to(DEV), out)
+    assert out.tolist() == [77 if i == 3 else int(logits[i].argmax()) for i in range(n)]
+    temps = [0.0, 0.7, 1.0, 1.3, 0.7, 0.7, 1.0, 0.5, 2.0, 1.0, 0.9, 0.0]
+    top_k = [0, 0, 50, 0, 5, 0, 20, 1, 0, 0, 3, 7]
+    top_p = [1.0, 1.0, 1.0, 0.9, 1.0, 0.5, 0.95, 1.0, 0.3, 1.0, 0.8, 0.2]
+    min_p = [0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.1, 0.05, 0.0]
+    seeds = [11 * i + 3 for i in range(n)]
+    pos = [5 * i for i in range(n)]
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+    o.sample(logits.to(DEV), f32(temps), torch.tensor(top_k, dtype=torch.int32, device=DEV), f32(top_p), f32(min_p),
+             torch.tensor(seeds, dtype=torch.int64, device=DEV), torch.tensor(pos, dtype=torch.int32, device=DEV), out)
+    got = out.tolist()
+    for i in range(n):
+        want = P.sample(logits[i], temps[i], top_k[i], top_p[i], min_p[i], seeds[i], pos[i])
+        if got[i] != want:
+            # the only allowed difference: a token at a filter's edge, kept by one side and not the other
+            keep = P.kept_tokens(logits[i], temps[i], top_k[i], top_p[i], min_p[i])
+            assert temps[i] > 0 and bool(keep[got[i]]) , (i, got[i], want)
+    assert sum(g == P.sample(logits[i], temps[i], top_k[i], top_p[i], min_p[i], seeds[i], pos[i])
+               for i, g in enumerate(got)) >= n - 1
+
+
+def test_sampling_follows_the_distribution_and_the_filters():
+    o = ops()
+    V, n = 50, 20000
+    row = torch.tensor([math.log(i + 1.0) for i in range(V)])
+    logits = row.repeat(n, 1).to(DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    ones = torch.ones(n, device=DEV)
+    i32z = torch.zeros(n, dtype=torch.int32, device=DEV)
+    seeds = torch.arange(n, dtype=torch.int64, device=DEV) * 7919 + 1
+    o.sample(logits, ones, i32z, ones, ones * 0, seeds, i32z, out)
+    freq = torch.bincount(out.cpu().long(), minlength=V).float() / n
+    p = torch.softmax(row, -1)
+    assert float((freq - p).abs().max()) < 0.01
+    o.sample(logits, ones, i32z + 5, ones, ones * 0, seeds, i32z, out)
+    assert set(out.tolist()) <= set(range(V - 5, V))
+    o.sample(logits, ones, i32z, ones * 0.5, ones * 0, seeds, i32z, out)
+    kept = P.kept_tokens(row, 1.0, 0, 0.5, 0.0)
+    assert set(out.tolist()) <= set(torch.nonzero(kept).reshape(-1).tolist())
+    # same seed and position: the same token whatever else is in the batch; another position: other noise
+    a = out.clone()
+    o.sample(logits[:7], ones[:7], i32z[:7], ones[:7] * 0.5, ones[:7] * 0, seeds[:7], i32z[:7], out[:7])
+    assert torch.equal(a[:7], out[:7])
+    o.sample(logits, ones, i32z, ones, ones * 0, seeds, i32z + 1, out)
+    assert not torch.equal(a, out)
