@@ -1,0 +1,141 @@
+"""Command line: `python -m tandemllm_b200 <command> ...`
+
+  generate        token ids in, token ids out, through the scheduler and the step function
+  random-weights  write a model folder (config.json, model.safetensors) from a config.json and a seed
+  replay          the trace replay program (the same as bin/trace_run)
+
+Option names follow the reference's command lines where it has them: `--model`, `--max-len`, `--tokens`,
+`--graph on|off`, `--json` (tools/lfm_check.py:374-418), `--temperature`, `--top-p`, `--top-k`, `--parallel`
+(server/app.py:12893-12940). No tokenizer is involved: prompts are token ids.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+
+def _engine_options(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--model", help="a folder with config.json and model.safetensors")
+    p.add_argument("--config", help="a config.json to build a random-weights model from (with --random-weights)")
+    p.add_argument("--random-weights", type=int, metavar="SEED", help="random weights from this seed instead of --model")
+    p.add_argument("--std", type=float, default=0.02, help="standard deviation of random matrices")
+    p.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
+    p.add_argument("--max-len", type=int, default=8192, help="the window: prompt plus generated tokens of a request")
+    p.add_argument("--parallel", type=int, default=8, help="requests running at once")
+    p.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
+    p.add_argument("--kv-blocks", type=int, help="cache pages (default: enough for --parallel requests of --max-len)")
+    p.add_argument("--max-batched-tokens", type=int, default=2048, help="token budget of one step")
+    p.add_argument("--chunk-size", type=int, default=512, help="longest prompt portion in one step")
+    p.add_argument("--graph", default="on", choices=("on", "off"), help="CUDA graphs for decode-only steps")
+    p.add_argument("--device", default="cuda:0")
+
+
+def _build_engine(a):
+    from .config import Lfm2MoeConfig, architecture_of
+    from .engine import Engine, EngineArgs
+    args = EngineArgs(dtype=a.dtype, max_len=a.max_len, parallel=a.parallel, block_size=a.block_size,
+                      kv_blocks=a.kv_blocks, max_batched_tokens=a.max_batched_tokens, chunk_size=a.chunk_size,
+                      device=a.device, graph=a.graph == "on")
+    if a.random_weights is not None:
+        if not a.config:
+            raise SystemExit("--random-weights needs --config FILE (a config.json)")
+        with open(a.config) as f:
+            raw = json.load(f)
+        config = architecture_of(raw).read_config(raw, "", None)
+        return Engine.from_config(config, a.random_weights, args, std=a.std)
+    if not a.model:
+        raise SystemExit("give --model DIR, or --config FILE with --random-weights SEED")
+    return Engine.from_folder(a.model, args)
+
+
+def cmd_generate(a) -> int:
+    import torch
+
+    from .sampling import SamplingParams
+    engine = _build_engine(a)
+    vocab = engine.model.vocab_size
+    if a.prompt_ids:
+        prompts = [[int(t) for t in p.replace(",", " ").split()] for p in a.prompt_ids]
+    else:
+        g = torch.Generator().manual_seed(a.prompt_seed)
+        prompts = [torch.randint(0, vocab, (a.prompt_len,), generator=g).tolist() for _ in range(a.prompts)]
+    params = SamplingParams(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, min_p=a.min_p, seed=a.seed,
+                            max_tokens=a.tokens, ignore_eos=a.ignore_eos)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    result = {"outputs": outs, "seconds": round(dt, 4), "generated": sum(len(o) for o in outs),
+              "tok_s": round(sum(len(o) for o in outs) / dt, 2), "stats": engine.stats()}
+    for i, o in enumerate(outs):
+        print(f"[{i}] " + " ".join(str(t) for t in o))
+    print(json.dumps({k: v for k, v in result.items() if k != "outputs"}), file=sys.stderr)
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump({"prompts": prompts, **result}, f)
+    return 0
+
+
+def cmd_random_weights(a) -> int:
+    import torch
+
+    from .config import architecture_of
+    from .weights.random_init import write_model_folder
+    with open(a.config) as f:
+        raw = json.load(f)
+    config = architecture_of(raw).read_config(raw, "", None)
+    dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[a.dtype]
+    print(write_model_folder(config, a.out, a.seed, std=a.std, bias_std=a.bias_std, norm_std=a.norm_std, dtype=dtype))
+    return 0
+
+
+def cmd_replay(a) -> int:
+    import os
+    import runpy
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bin", "trace_run")
+    sys.argv = [path] + a.rest
+    runpy.run_path(path, run_name="__main__")
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m tandemllm_b200", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("generate", help="generate token ids")
+    _engine_options(g)
+    g.add_argument("--prompt-ids", action="append", help="a prompt as token ids separated by spaces or commas (repeatable)")
+    g.add_argument("--prompts", type=int, default=1, help="number of random prompts when no --prompt-ids is given")
+    g.add_argument("--prompt-len", type=int, default=32)
+    g.add_argument("--prompt-seed", type=int, default=0)
+    g.add_argument("--tokens", type=int, default=128, help="new tokens per request at most")
+    g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--top-k", type=int, default=0)
+    g.add_argument("--min-p", type=float, default=0.0)
+    g.add_argument("--seed", type=int, help="sampling seed (default: from the operating system)")
+    g.add_argument("--ignore-eos", action="store_true")
+    g.add_argument("--json", help="write prompts, outputs and timing here")
+    g.set_defaults(fn=cmd_generate)
+    r = sub.add_parser("random-weights", help="write a random model folder")
+    r.add_argument("--config", required=True)
+    r.add_argument("--out", required=True)
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--std", type=float, default=0.02)
+    r.add_argument("--bias-std", type=float, default=0.1)
+    r.add_argument("--norm-std", type=float, default=0.0)
+    r.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
+    r.set_defaults(fn=cmd_random_weights)
+    p = sub.add_parser("replay", help="the trace replay program; options as for bin/trace_run")
+    p.add_argument("rest", nargs=argparse.REMAINDER)
+    p.set_defaults(fn=cmd_replay)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

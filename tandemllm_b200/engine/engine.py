@@ -131,6 +131,21 @@ class Engine:
         self.scheduler.add(req)
         return req
 
+    def add_request_with_context(self, prompt: list[int], params: SamplingParams | None = None, request_id=None) -> Request:
+        """For measurement: a running request whose prompt, except its last token, counts as already computed. Its
+        pages are reserved and hold whatever they held (fill the cache tensors first for realistic values), so a
+        decode step at a long context can be timed without running the prompt. The text it generates is not meaningful."""
+        req = self.add_request(prompt, params, request_id)
+        self.scheduler.waiting.remove(req)
+        self.cache.admit(req.request_id)
+        n = len(req.prompt) - 1
+        self.cache.reserve(req.request_id, n)
+        self.cache.advance(req.request_id, n)
+        req.num_computed = n
+        req.state = "running"
+        self.scheduler.running.append(req)
+        return req
+
     def run_step(self) -> list[Request]:
         """One scheduler step: schedule, run, sample, account. Returns the requests that finished."""
         batch = self.scheduler.schedule()

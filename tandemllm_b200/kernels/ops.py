@@ -81,8 +81,13 @@ def core():
     return _core
 
 
-def check(code: int, what: str, lib=None) -> None:
+launches = 0        # kernels of this package launched so far (a launcher that starts two kernels counts both)
+
+
+def check(code: int, what: str, lib=None, kernels: int = 1) -> None:
+    global launches
     if code == 0:
+        launches += kernels
         return
     lib = lib or core()
     if code == TL_BAD_ARGUMENT:
@@ -254,7 +259,8 @@ class MoePlan:
         self.max_tiles = core().tl_moe_max_tiles(pairs, self.num_experts, self.tile_m)
         check(core().tl_moe_plan(ptr(ids), pairs, self.num_experts, self.tile_m, ptr(self.counts), ptr(self.offsets),
                                  ptr(self.sorted_pairs), ptr(self.pos_of_pair), ptr(self.tile_group),
-                                 ptr(self.tile_row0), ptr(self.tile_rows), ptr(self.n_tiles), stream()), "moe_plan")
+                                 ptr(self.tile_row0), ptr(self.tile_rows), ptr(self.n_tiles), stream()), "moe_plan",
+              kernels=2)
         return self
 
 

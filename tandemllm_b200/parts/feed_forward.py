@@ -75,7 +75,8 @@ class SigmoidTopKExperts(Part):
         self.base = prefix + self.n["experts"]
         self._plan = None
         self.stacked = False
-        self.load_counts = None     # int64 [E]: pairs routed to each expert since the last reset (when recording)
+        self.record_counts = False  # when set, `last_counts` keeps the pairs routed to each expert in the last pass
+        self.last_counts = None
 
     def _stacked(self, present) -> bool:
         return present is not None and (self.base + ".gate_up_proj") in present
@@ -137,8 +138,8 @@ class SigmoidTopKExperts(Part):
         if _expert_impl is not None and x.dtype == torch.bfloat16 and _expert_impl.experts(self, x, ids, wts, out):
             return out
         plan = self.plan_for(R * self.top_k, x.device).build(ids)
-        if self.load_counts is not None:
-            self.load_counts += plan.counts
+        if self.record_counts:
+            self.last_counts = plan.counts.clone()
         act = torch.empty(R * self.top_k, self.inter, dtype=x.dtype, device=x.device)
         ops.gemm_simt_grouped(x, plan.sorted_pairs, self.top_k, self.w_gate_up, act, plan, swiglu=True)
         y = torch.empty(R * self.top_k, H, dtype=torch.float32, device=x.device)
