@@ -13,7 +13,18 @@
 #define TL_FP32 0
 #define TL_BF16 1
 
-extern "C" void tl_set_error(const char* fmt, ...);
+#include <stdarg.h>
+#include <stdio.h>
+
+// The last refusal's message of the calling thread. Each library exports a function that returns it.
+inline thread_local char tl_error_text[512] = "";
+
+inline void tl_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tl_error_text, sizeof(tl_error_text), fmt, ap);
+  va_end(ap);
+}
 
 #define TL_REQUIRE(cond, ...)            \
   do {                                   \

@@ -4,21 +4,9 @@
 // The residual stream is 32-bit in both precisions; norms compute mean(x^2), rsqrt and the scale in
 // 32-bit and round once to the compute type. Formulas: engine/models/lfm2_moe/ref.py:105-109 (norm),
 // :230 (embedding), :180-183 (SwiGLU) of the reference.
-#include <stdarg.h>
-#include <stdio.h>
-
 #include "common.cuh"
 
-static thread_local char g_error[512] = "";
-
-extern "C" void tl_set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_error, sizeof(g_error), fmt, ap);
-  va_end(ap);
-}
-
-extern "C" const char* tl_last_error() { return g_error; }
+extern "C" const char* tl_last_error() { return tl_error_text; }
 
 extern "C" const char* tl_cuda_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
 

@@ -1,0 +1,511 @@
+// bfloat16 matrix products on the 5th-generation tensor cores (tcgen05) for sm_100a:
+//
+//   C[m, n] = sum_k X[m, k] * W[n, k] (+ bias[n])     X: rows (tokens), W: weight rows, both row-major, k contiguous
+//
+// One CTA computes one output tile. Operand tiles of 64 k-elements (128 bytes a row) are brought into shared
+// memory by TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast: every CTA fetches its own tiles) through
+// a ring of stages guarded by mbarriers; one elected thread issues tcgen05.mma (kind::f16, bf16 inputs, f32
+// accumulation) from shared-memory descriptors into an accumulator in tensor memory; tcgen05.commit releases the
+// stage and, after the last k-block, signals the epilogue warps, which read the accumulator with tcgen05.ld,
+// apply the bias or silu(gate) * up, and store.
+//
+// Two orientations share the code. The MMA's M side is always a tile of 128 rows:
+//   SWAP    M side = 128 weight rows, N side = BN token rows (16..256). For decode: few tokens, weights streamed
+//           once at full TMA rate; thread t of the epilogue owns weight row t, so a store of one token is 32
+//           consecutive outputs per warp.
+//   !SWAP   M side = 128 token rows, N side = BN weight rows. For prompts: each thread owns a token row and
+//           stores BN consecutive outputs.
+// SWIGLU: the weight matrix holds gate rows [0, N) and up rows [N, 2N) (per group); the CTA accumulates both for
+// the same columns in two accumulators and stores silu(gate) * up.
+// Grouped (experts): a tile map built on the device names, per token tile, the group (expert) whose weights it
+// multiplies by and the rows of the expert-sorted list it covers; tiles past *n_tiles exit at once.
+// Split-K (SWAP, plain): grid.z CTAs each take a range of k-blocks and write 32-bit partial sums to a workspace
+// [splits, M, N]; `splitk_reduce` adds them in a fixed order, so results do not depend on timing.
+//
+// Every wait on an mbarrier is bounded: when a bound is hit the CTA records status 11, stops issuing work, waits
+// (bounded again) for the copies it already started, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace tl {
+
+constexpr int TILE_M = 128;         // rows of the MMA's M side
+constexpr int TILE_K = 64;          // k-elements per stage: 128 bytes, one swizzle atom
+constexpr int UMMA_K = 16;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+struct TcParams {
+  void* C;
+  const float* bias;
+  float* partial;             // split-K workspace or nullptr
+  long long ldc;
+  int M, N, K;                // tokens, outputs (per group), reduction length
+  int k_blocks_per_split;
+  long long rows_per_group;   // weight rows per group in the weight tensor (grouped), else 0
+  const int* tile_group;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* n_tiles;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Waits for the phase with the given parity to complete; false when the bound ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle: 8-row groups are
+// 1024 bytes apart (stride byte offset), version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major), in 16-byte units
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+  d |= (uint64_t)1 << 46;                 // descriptor version
+  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: f32 accumulate, bf16 A and B, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename TOut> __device__ __forceinline__ void store_out(TOut* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+
+template <int BN, bool SWAP, bool SWIGLU>
+struct Smem {
+  static constexpr int A_BYTES = TILE_M * TILE_K * 2;                  // the M-side tile
+  static constexpr int B_BYTES = BN * TILE_K * 2;                      // the N-side tile
+  // with SWIGLU the weight side is loaded twice (gate rows and up rows)
+  static constexpr int W_TILES = SWIGLU ? 2 : 1;
+  static constexpr int STAGE_BYTES = SWAP ? (W_TILES * A_BYTES + B_BYTES) : (A_BYTES + W_TILES * B_BYTES);
+  static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int TMEM_COLS_RAW = BN * W_TILES;
+  static constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128
+                                   : TMEM_COLS_RAW <= 256 ? 256 : 512;
+};
+
+template <int BN, bool SWAP, bool SWIGLU, typename TOut>
+__global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                      const __grid_constant__ CUtensorMap tmX, TcParams p) {
+  using S = Smem<BN, SWAP, SWIGLU>;
+  // ---- which tile ----
+  int tok0, tok_rows;
+  long long w_base = 0;                 // first weight row of this tile's group in the weight tensor
+  const int tok_tile = SWAP ? BN : TILE_M;
+  if (p.tile_group) {
+    const int t = blockIdx.y;
+    if (t >= *p.n_tiles) return;
+    tok0 = p.tile_row0[t];
+    tok_rows = p.tile_rows[t];
+    w_base = (long long)p.tile_group[t] * p.rows_per_group;
+  } else {
+    tok0 = blockIdx.y * tok_tile;
+    tok_rows = min(tok_tile, p.M - tok0);
+  }
+  const int n0 = blockIdx.x * (SWAP ? TILE_M : BN);        // first output column (weight row within the group)
+  const int total_kb = (p.K + TILE_K - 1) / TILE_K;
+  const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+  const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
+  const int num_kb = kb_end - kb_begin;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + S::STAGES * S::STAGE_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* acc_ready = empty + S::STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+  volatile uint32_t* aborted = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_ready, 1);
+    *aborted = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)S::TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  // A side = M side (128 rows), B side = N side (BN rows). With SWAP the weights are the A side.
+  const CUtensorMap* mapA = SWAP ? &tmW : &tmX;
+  const CUtensorMap* mapB = SWAP ? &tmX : &tmW;
+  const int rowA = SWAP ? (int)(w_base + n0) : tok0;
+  const int rowB = SWAP ? tok0 : (int)(w_base + n0);
+  const int rowW2 = (int)(w_base + p.N + n0);               // the up rows (SWIGLU)
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer ----
+    int issued = 0;
+    for (int i = 0; i < num_kb; ++i) {
+      const int s = i % S::STAGES;
+      if (i >= S::STAGES && !mbar_wait(&empty[s], ((i / S::STAGES) - 1) & 1)) {
+        *aborted = 1;
+        atomicExch(p.status, 11);
+        break;
+      }
+      if (*aborted) break;
+      uint8_t* st = tiles + s * S::STAGE_BYTES;
+      mbar_expect_tx(&full[s], S::STAGE_BYTES);
+      const int kx = (kb_begin + i) * TILE_K;
+      if (SWAP) {
+        tma_load_2d(st, mapA, &full[s], kx, rowA);
+        if (SWIGLU) tma_load_2d(st + S::A_BYTES, mapA, &full[s], kx, rowW2);
+        tma_load_2d(st + S::W_TILES * S::A_BYTES, mapB, &full[s], kx, rowB);
+      } else {
+        tma_load_2d(st, mapA, &full[s], kx, rowA);
+        tma_load_2d(st + S::A_BYTES, mapB, &full[s], kx, rowB);
+        if (SWIGLU) tma_load_2d(st + S::A_BYTES + S::B_BYTES, mapB, &full[s], kx, rowW2);
+      }
+      issued = i + 1;
+    }
+    if (*aborted) {
+      // copies already started must land before the CTA's shared memory goes away
+      for (int i = max(0, issued - S::STAGES); i < issued; ++i) mbar_wait(&full[i % S::STAGES], (i / S::STAGES) & 1);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    constexpr uint32_t idesc = umma_idesc(BN);
+    for (int i = 0; i < num_kb; ++i) {
+      const int s = i % S::STAGES;
+      if (!mbar_wait(&full[s], (i / S::STAGES) & 1)) {
+        *aborted = 1;
+        atomicExch(p.status, 11);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t st = smem_u32(tiles + s * S::STAGE_BYTES);
+      const uint32_t a0 = st;
+      const uint32_t b0 = st + (SWAP ? S::W_TILES * S::A_BYTES : S::A_BYTES);
+#pragma unroll
+      for (int k = 0; k < TILE_K / UMMA_K; ++k) {
+        const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+        const uint32_t koff = k * UMMA_K * 2;
+        umma(tmem_base, umma_desc(a0 + koff), umma_desc(b0 + koff), idesc, acc);
+        if (SWIGLU) {
+          if (SWAP) umma(tmem_base + BN, umma_desc(a0 + S::A_BYTES + koff), umma_desc(b0 + koff), idesc, acc);
+          else umma(tmem_base + BN, umma_desc(a0 + koff), umma_desc(b0 + S::B_BYTES + koff), idesc, acc);
+        }
+      }
+      umma_commit(&empty[s]);
+    }
+    umma_commit(acc_ready);
+  } else if (warp >= 2) {
+    // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31 ----
+    const int quad = warp & 3;
+    const int m_row = quad * 32 + lane;                  // row of the M side this thread owns
+    bool ok = num_kb > 0 ? mbar_wait(acc_ready, 0) : true;
+    if (!ok) {
+      *aborted = 1;
+      atomicExch(p.status, 11);
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && !*aborted) {
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      TOut* C = (TOut*)p.C;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16], u[16];
+        if (num_kb > 0) {
+          tmem_ld16(taddr + c0, v);
+          if (SWIGLU) tmem_ld16(taddr + BN + c0, u);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = u[j] = 0.f;
+        }
+        if (SWAP) {
+          // this thread: output column n0 + m_row; registers: tokens tok0 + c0 + j
+          const int n = n0 + m_row;
+          if (n < p.N) {
+            const float b = (p.bias && blockIdx.z == 0) ? p.bias[n] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = c0 + j;
+              if (t < tok_rows) {
+                const float r = SWIGLU ? silu_mul(v[j], u[j]) : v[j] + b;
+                if (p.partial) p.partial[((long long)blockIdx.z * p.M + tok0 + t) * p.N + n] = r;
+                else store_out<TOut>(C + (long long)(tok0 + t) * p.ldc + n, r);
+              }
+            }
+          }
+        } else {
+          // this thread: token tok0 + m_row; registers: output columns n0 + c0 + j
+          if (m_row < tok_rows) {
+            TOut* row = C + (long long)(tok0 + m_row) * p.ldc;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int n = n0 + c0 + j;
+              if (n < p.N) {
+                const float r = SWIGLU ? silu_mul(v[j], u[j]) : v[j] + (p.bias ? p.bias[n] : 0.f);
+                store_out<TOut>(row + n, r);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS));
+  }
+}
+
+// out[m, n] = sum over splits (in order) of partial[s, m, n] (+ nothing: the bias went into split 0)
+template <typename TOut>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, long long ldc, int M, int N,
+                                     int splits) {
+  const long long total = (long long)M * N;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[(long long)s * total + i];
+    const long long m = i / N;
+    store_out<TOut>(out + m * ldc + (i - m * N), acc);
+  }
+}
+
+// rows[i, :] = x[index[i] / div, :]   (the expert-sorted copy of the token rows)
+__global__ void gather_rows_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ index, int div,
+                                   bf16* __restrict__ out, int width) {
+  const int i = blockIdx.x;
+  const uint4* src = (const uint4*)(x + (long long)(index[i] / div) * ldx);
+  uint4* dst = (uint4*)(out + (long long)i * width);
+  for (int c = threadIdx.x; c < width / 8; c += blockDim.x) dst[c] = src[c];
+}
+
+// ------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, cols, ld;
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr;
+    h ^= (size_t)k.rows * 0x9E3779B97F4A7C15ULL + (size_t)k.cols * 0xBF58476D1CE4E5B9ULL + (size_t)k.ld * 31 + k.box_rows;
+    return h;
+  }
+};
+
+// A 2D bf16 tensor [rows, cols] with row stride ld (elements), box [box_rows, 64 columns], 128-byte swizzle.
+static int tensor_map(const void* ptr, long long rows, long long cols, long long ld, int box_rows, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> g(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  EncodeTiledFn fn = encode_fn();
+  TL_REQUIRE(fn != nullptr, "tensor-core gemm: the driver does not export cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TILE_K, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TL_REQUIRE(r == CUDA_SUCCESS, "tensor-core gemm: cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld ld %lld box %d)",
+             (int)r, rows, cols, ld, box_rows);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+template <int BN, bool SWAP, bool SWIGLU, typename TOut>
+static int launch_one(const CUtensorMap& tmW, const CUtensorMap& tmX, const TcParams& p, dim3 grid, cudaStream_t stream) {
+  using S = Smem<BN, SWAP, SWIGLU>;
+  auto kernel = gemm_tc_kernel<BN, SWAP, SWIGLU, TOut>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kernel<<<grid, 192, S::TOTAL, stream>>>(tmW, tmX, p);
+  return (int)cudaGetLastError();
+}
+
+template <bool SWAP, bool SWIGLU, typename TOut>
+static int launch_bn(int bn, const CUtensorMap& tmW, const CUtensorMap& tmX, const TcParams& p, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16: return launch_one<16, SWAP, SWIGLU, TOut>(tmW, tmX, p, grid, s);
+    case 32: return launch_one<32, SWAP, SWIGLU, TOut>(tmW, tmX, p, grid, s);
+    case 64: return launch_one<64, SWAP, SWIGLU, TOut>(tmW, tmX, p, grid, s);
+    case 128: return launch_one<128, SWAP, SWIGLU, TOut>(tmW, tmX, p, grid, s);
+    case 256: return launch_one<256, SWAP, SWIGLU, TOut>(tmW, tmX, p, grid, s);
+  }
+  tl_set_error("tensor-core gemm: tile of %d rows on the N side; 16, 32, 64, 128 and 256 are built", bn);
+  return TL_BAD_ARGUMENT;
+}
+
+}  // namespace tl
+
+using namespace tl;
+
+extern "C" const char* tl_tc_last_error() { return tl_error_text; }
+
+// The token-tile height the grouped kernel wants for a given orientation (the MoE plan is built with it).
+extern "C" int tl_tc_token_tile(int swap, int bn) { return swap ? bn : TILE_M; }
+
+// X [M, K] (row stride ldx), W [groups * rows_per_group, K] (row stride ldw). Plain: groups = 1, tile_group = nullptr.
+// swiglu: W holds 2 N rows per group (gate then up) and C = silu(gate) * up. out_dtype: TL_BF16 or TL_FP32.
+// splits > 1 (swap, not swiglu, not grouped): `partial` must hold splits * M * N floats.
+extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
+                          long long rows_per_group, const float* bias, void* C, long long ldc, int M, int N, int K, int swap,
+                          int bn, int swiglu, int out_dtype, const int* tile_group, const int* tile_row0,
+                          const int* tile_rows, const int* n_tiles, int max_tiles, int splits, float* partial,
+                          int* status, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  TL_REQUIRE(M > 0 && N > 0 && K > 0, "tensor-core gemm: M %d N %d K %d", M, N, K);
+  TL_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
+             "tensor-core gemm: K %d and the row strides %lld, %lld must be multiples of 8 elements (16 bytes) for TMA", K,
+             ldx, ldw);
+  TL_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "tensor-core gemm: operands must be 16-byte aligned");
+  TL_REQUIRE(out_dtype == TL_BF16 || out_dtype == TL_FP32, "tensor-core gemm: output dtype %d", out_dtype);
+  TL_REQUIRE(splits >= 1 && (splits == 1 || (swap && !swiglu && !tile_group && partial)),
+             "tensor-core gemm: split-K needs the swapped plain kernel and a workspace");
+  TL_REQUIRE(!bias || !swiglu, "tensor-core gemm: a bias with the SwiGLU epilogue is not implemented");
+  CUtensorMap tmW, tmX;
+  const int w_box = swap ? TILE_M : bn, x_box = swap ? bn : TILE_M;
+  if (int e = tensor_map(W, w_rows, K, ldw, w_box, &tmW)) return e;
+  if (int e = tensor_map(X, x_rows, K, ldx, x_box, &tmX)) return e;
+  const int total_kb = ceil_div(K, TILE_K);
+  TcParams p = {};
+  p.C = C; p.bias = bias; p.partial = splits > 1 ? partial : nullptr; p.ldc = ldc; p.M = M; p.N = N; p.K = K;
+  p.k_blocks_per_split = ceil_div(total_kb, splits);
+  p.rows_per_group = rows_per_group;
+  p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles; p.status = status;
+  const int tok_tile = swap ? bn : TILE_M, n_tile = swap ? TILE_M : bn;
+  dim3 grid(ceil_div(N, n_tile), tile_group ? max_tiles : ceil_div(M, tok_tile), ceil_div(total_kb, p.k_blocks_per_split));
+  TL_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "tensor-core gemm: grid %u x %u x %u exceeds the limits", grid.x, grid.y, grid.z);
+  int e;
+  if (swap) {
+    if (swiglu) e = out_dtype == TL_BF16 ? launch_bn<true, true, bf16>(bn, tmW, tmX, p, grid, stream)
+                                         : launch_bn<true, true, float>(bn, tmW, tmX, p, grid, stream);
+    else e = out_dtype == TL_BF16 ? launch_bn<true, false, bf16>(bn, tmW, tmX, p, grid, stream)
+                                  : launch_bn<true, false, float>(bn, tmW, tmX, p, grid, stream);
+  } else {
+    if (swiglu) e = out_dtype == TL_BF16 ? launch_bn<false, true, bf16>(bn, tmW, tmX, p, grid, stream)
+                                         : launch_bn<false, true, float>(bn, tmW, tmX, p, grid, stream);
+    else e = out_dtype == TL_BF16 ? launch_bn<false, false, bf16>(bn, tmW, tmX, p, grid, stream)
+                                  : launch_bn<false, false, float>(bn, tmW, tmX, p, grid, stream);
+  }
+  if (e) return e;
+  if (splits > 1) {
+    const long long total = (long long)M * N;
+    const int blocks = (int)(ceil_div64(total, 256) < 1184 ? ceil_div64(total, 256) : 1184);
+    if (out_dtype == TL_BF16)
+      splitk_reduce_kernel<bf16><<<blocks, 256, 0, stream>>>(partial, (bf16*)C, ldc, M, N, (int)grid.z);
+    else
+      splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(partial, (float*)C, ldc, M, N, (int)grid.z);
+    TL_LAUNCH_CHECK();
+  }
+  return 0;
+}
+
+extern "C" int tl_gather_rows(const void* x, long long ldx, const int* index, int div, void* out, int rows, int width,
+                              cudaStream_t stream) {
+  if (rows == 0) return 0;
+  TL_REQUIRE(width % 8 == 0 && ldx % 8 == 0 && div >= 1, "gather_rows: width %d, stride %lld, div %d", width, ldx, div);
+  gather_rows_kernel<<<rows, 128, 0, stream>>>((const bf16*)x, ldx, index, div, (bf16*)out, width);
+  TL_LAUNCH_CHECK();
+  return 0;
+}

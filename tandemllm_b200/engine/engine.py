@@ -100,7 +100,7 @@ class Engine:
         ops.core()                                  # built and loaded now; a missing library fails here, loudly
         if runtime.dtype == torch.bfloat16 and args.tensorcore:
             from ..kernels import tensorcore
-            tensorcore.enable()
+            tensorcore.enable(runtime)
         build = arch.build_model if arch is not None and arch.build_model else DecoderModel
         with torch.cuda.device(dev):
             model = build(spec).load(weights, runtime)

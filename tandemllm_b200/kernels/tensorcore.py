@@ -1,5 +1,146 @@
-"""Switches the bfloat16 path onto the tcgen05 tensor-core kernels (placeholder until they are built in)."""
+"""The bfloat16 path's tensor-core kernels (tcgen05 + TMA, `csrc/tc_gemm.cu`): when enabled, `parts.linear` and
+the expert feed-forward send their products here.
+
+Choice of kernel by shape:
+  up to 128 token rows   the swapped orientation: 128 weight rows on the MMA's M side, the tokens (padded to 16,
+                         32, 64 or 128) on its N side, so a decode step streams every weight once. When a product
+                         would launch fewer CTAs than the GPU has SMs, its k range is split over several CTAs that
+                         write 32-bit partial sums to a workspace, reduced in a fixed order by a second kernel.
+  more rows              128 token rows on the M side, 128 weight rows on the N side.
+Experts: the token rows are copied into expert-sorted order, the plan's tiles carry the expert, gate/up and
+SwiGLU run in one kernel, the down projection writes 32-bit rows that the combine kernel weighs and adds.
+Anything the kernels do not take (k or a row stride not a multiple of 8 elements, as TMA needs 16-byte strides)
+goes back to the CUDA-core kernels by returning False.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_longlong, c_void_p
+
+import torch
+
+from . import ops
+from .build import load
+
+SM_COUNT = 148
+_lib = None
+_impl = None
 
 
-def enable() -> None:
-    return None
+def lib():
+    global _lib
+    if _lib is None:
+        l = load("tensorcore")
+        l.tl_gemm_tc.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p,
+                                 c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]
+        l.tl_gemm_tc.restype = c_int
+        l.tl_gather_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
+        l.tl_gather_rows.restype = c_int
+        l.tl_tc_token_tile.argtypes = [c_int, c_int]
+        l.tl_tc_token_tile.restype = c_int
+        l.tl_tc_last_error.restype = ctypes.c_char_p
+        _lib = l
+    return _lib
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    if code == 0:
+        ops.launches += kernels
+        return
+    if code == ops.TL_BAD_ARGUMENT:
+        raise ops.KernelError(lib().tl_tc_last_error().decode())
+    raise ops.KernelError(f"{what}: CUDA error {code}: {ops.core().tl_cuda_error_string(code).decode()}")
+
+
+def _pow2_at_least(n: int, lo: int = 16) -> int:
+    b = lo
+    while b < n:
+        b *= 2
+    return b
+
+
+def usable(x: torch.Tensor, w: torch.Tensor) -> bool:
+    K = x.shape[-1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(-1) == 1
+            and w.stride(-1) == 1 and x.stride(0) % 8 == 0 and w.stride(-2) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+class TensorCore:
+    def __init__(self, device, status: torch.Tensor):
+        self.device, self.status = device, status
+        self._workspace = None
+
+    def workspace(self, floats: int) -> torch.Tensor:
+        if self._workspace is None or self._workspace.numel() < floats:
+            self._workspace = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
+        return self._workspace
+
+    # ---- x @ w^T (+ bias) ----
+    def gemm(self, x, w2d, bias, out, *, rows_per_group=0, plan=None, swiglu=False, swap=None, bn=None, n_out=None):
+        M, K = x.shape
+        N = n_out if n_out is not None else w2d.shape[0]
+        if swap is None:
+            swap = M <= 128
+        if bn is None:
+            bn = _pow2_at_least(M) if swap else 128
+        splits, partial = 1, None
+        if swap and plan is None and not swiglu:
+            ctas = -(-N // 128) * -(-M // bn)
+            kb = -(-K // 64)
+            if ctas < SM_COUNT and kb >= 8:
+                splits = max(1, min(kb // 4, -(-SM_COUNT // ctas), 16))
+                if splits > 1:
+                    partial = self.workspace(splits * M * N)
+        tg = tr0 = trs = nt = None
+        max_tiles = 0
+        if plan is not None:
+            tg, tr0, trs, nt, max_tiles = plan.tile_group, plan.tile_row0, plan.tile_rows, plan.n_tiles, plan.max_tiles
+        code = lib().tl_gemm_tc(
+            x.data_ptr(), x.stride(0), x.shape[0], w2d.data_ptr(), w2d.stride(0), w2d.shape[0], rows_per_group,
+            ops.ptr(bias), out.data_ptr(), out.stride(0), M, N, K, int(swap), bn, int(swiglu), ops.dtype_code(out.dtype),
+            ops.ptr(tg), ops.ptr(tr0), ops.ptr(trs), ops.ptr(nt), max_tiles, splits, ops.ptr(partial),
+            self.status.data_ptr(), ops.stream())
+        _check(code, "gemm_tc", kernels=2 if splits > 1 else 1)
+
+    def linear(self, x, w, bias, out) -> bool:
+        if not usable(x, w) or out.stride(-1) != 1:
+            return False
+        self.gemm(x, w, bias, out)
+        return True
+
+    # ---- routed experts ----
+    def experts(self, part, x, ids, wts, out) -> bool:
+        E, I2, H = part.w_gate_up.shape
+        inter = I2 // 2
+        if not usable(x, part.w_gate_up.view(E * I2, H)) or inter % 8 or not part.w_down.is_contiguous():
+            return False
+        R, k = ids.shape
+        P = R * k
+        avg = P / E
+        swap = avg <= 48
+        bn = 16 if avg <= 12 else 32 if avg <= 24 else 64 if swap else 128
+        tile = lib().tl_tc_token_tile(int(swap), bn)
+        plan = part.plan_for(P, x.device, tile).build(ids)
+        if part.record_counts:
+            part.last_counts = plan.counts.clone()
+        xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
+        _check(lib().tl_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k, xs.data_ptr(), P, H,
+                                    ops.stream()), "gather_rows")
+        act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
+        self.gemm(xs, part.w_gate_up.view(E * I2, H), None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=swap,
+                  bn=bn, n_out=inter)
+        y = torch.empty(P, H, dtype=torch.float32, device=x.device)
+        self.gemm(act, part.w_down.view(E * H, inter), None, y, rows_per_group=H, plan=plan, swap=swap, bn=bn, n_out=H)
+        ops.moe_combine(y, plan, ids, wts, out)
+        return True
+
+
+def enable(runtime) -> TensorCore:
+    """Build and load the tensor-core library and give `runtime` its kernels: the runtime's bfloat16 products and
+    expert feed-forwards go through them from now on."""
+    lib()
+    runtime.tensorcore = TensorCore(runtime.device, runtime.status)
+    return runtime.tensorcore

@@ -20,14 +20,6 @@ from ..weights.loader import TensorSpec
 from .base import PagedNeed, Part, make_part, register_part
 from .linear import linear
 
-_attention_impl = None      # set by kernels.tensorcore.enable(): .attention(q, cache, table, step, scale, window, out) -> bool
-
-
-def use_attention_kernel(impl) -> None:
-    global _attention_impl
-    _attention_impl = impl
-
-
 @register_part("mixer", "attention")
 class AttentionMixer(Part):
     def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
@@ -81,7 +73,7 @@ class AttentionMixer(Part):
         R, dt, dev = x.shape[0], x.dtype, x.device
         Hq, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
         status = self.runtime.status
-        qkv = linear(x, self.w_qkv)
+        qkv = linear(self.runtime, x, self.w_qkv)
         q = torch.empty(R, Hq, D, dtype=dt, device=dev)
         table = step.block_tables[cache.group]
         qw = self.q_norm.weight if self.q_norm else None
@@ -103,7 +95,8 @@ class AttentionMixer(Part):
             if writes_cache:
                 ops.kv_store(k, v, step.positions, step.req_of_row, table, cache.page_size, cache.k, cache.v, status)
         o = torch.empty(R, Hq, D, dtype=dt, device=dev)
-        if _attention_impl is None or not _attention_impl.attention(q, cache, table, step, self.scale, self.window, o):
+        fast = self.runtime.attention_kernels
+        if fast is None or not fast.attention(q, cache, table, step, self.scale, self.window, o):
             ops.paged_attention_simt(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions,
                                      self.scale, self.window, o, status)
-        return linear(o.view(R, Hq * D), self.w_out, out_dtype=torch.float32)
+        return linear(self.runtime, o.view(R, Hq * D), self.w_out, out_dtype=torch.float32)

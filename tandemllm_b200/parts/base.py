@@ -67,6 +67,8 @@ class Runtime:
     device: torch.device
     dtype: torch.dtype
     status: torch.Tensor | None = None      # int32[1] on the device: kernels record a bad index here instead of faulting
+    tensorcore: Any = None                  # the bfloat16 tensor-core kernels (kernels.tensorcore.TensorCore) or None
+    attention_kernels: Any = None           # faster attention kernels for bfloat16, or None: the CUDA-core kernel
 
     def __post_init__(self) -> None:
         if self.dtype not in (torch.float32, torch.bfloat16):

@@ -23,14 +23,6 @@ from ..weights.loader import TensorSpec
 from .base import Part, register_part
 from .linear import linear
 
-_expert_impl = None     # set by kernels.tensorcore.enable(): .experts(part, x, ids, wts, out) -> bool
-
-
-def use_expert_kernel(impl) -> None:
-    global _expert_impl
-    _expert_impl = impl
-
-
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
     def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
@@ -50,10 +42,10 @@ class SwiGLU(Part):
         self.w_down = runtime.matrix(read(self.n["down"] + ".weight"))
 
     def forward(self, x, step, x32=None):
-        gu = linear(x, self.w_gate_up)
+        gu = linear(self.runtime, x, self.w_gate_up)
         act = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
         ops.silu_mul(gu, act)
-        return linear(act, self.w_down, out_dtype=torch.float32)
+        return linear(self.runtime, act, self.w_down, out_dtype=torch.float32)
 
 
 @register_part("feed_forward", "sigmoid_topk_experts")
@@ -73,7 +65,7 @@ class SigmoidTopKExperts(Part):
             raise ValueError(f"{self.num_experts} experts top-{self.top_k}: up to 1024 experts and top-32 are implemented")
         self.n = dict(spec["names"])
         self.base = prefix + self.n["experts"]
-        self._plan = None
+        self._plans: dict[int, ops.MoePlan] = {}
         self.stacked = False
         self.record_counts = False  # when set, `last_counts` keeps the pairs routed to each expert in the last pass
         self.last_counts = None
@@ -125,17 +117,21 @@ class SigmoidTopKExperts(Part):
         ops.router_topk(logits, self.expert_bias, self.top_k, self.normalize, self.norm_floor, self.scale, ids, wts)
         return ids, wts
 
-    def plan_for(self, pairs: int, device) -> ops.MoePlan:
-        if self._plan is None or self._plan.max_pairs < pairs:
-            cap = max(pairs, 64) if self._plan is None else max(pairs, 2 * self._plan.max_pairs)
-            self._plan = ops.MoePlan(cap, self.num_experts, ops.simt_tile_rows(), device)
-        return self._plan
+    def plan_for(self, pairs: int, device, tile_rows: int | None = None) -> ops.MoePlan:
+        """The routing-plan buffers for up to `pairs` pairs and token tiles of `tile_rows` rows (kept and reused)."""
+        tile_rows = tile_rows or ops.simt_tile_rows()
+        plan = self._plans.get(tile_rows)
+        if plan is None or plan.max_pairs < pairs:
+            cap = max(pairs, 64) if plan is None else max(pairs, 2 * plan.max_pairs)
+            plan = self._plans[tile_rows] = ops.MoePlan(cap, self.num_experts, tile_rows, device)
+        return plan
 
     def forward(self, x, step, x32=None):
         R, H = x.shape[0], self.hidden_size
         ids, wts = self.route(x32 if x32 is not None else x.float())
         out = torch.empty(R, H, dtype=torch.float32, device=x.device)
-        if _expert_impl is not None and x.dtype == torch.bfloat16 and _expert_impl.experts(self, x, ids, wts, out):
+        tc = self.runtime.tensorcore
+        if tc is not None and x.dtype == torch.bfloat16 and tc.experts(self, x, ids, wts, out):
             return out
         plan = self.plan_for(R * self.top_k, x.device).build(ids)
         if self.record_counts:

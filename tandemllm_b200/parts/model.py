@@ -87,4 +87,4 @@ class DecoderModel:
         if step.n_out == 0:
             return torch.empty(0, self.vocab_size, dtype=torch.float32, device=rt.device)
         n = self.final_norm.add_norm(residual, pending, gather=step.out_rows, n_out=step.n_out)
-        return linear(n, self.head, out_dtype=torch.float32)
+        return linear(rt, n, self.head, out_dtype=torch.float32)

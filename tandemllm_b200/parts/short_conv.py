@@ -57,11 +57,11 @@ class ShortConvMixer(Part):
 
     def forward(self, x, step, cache, writes_cache: bool = True):
         H = self.hidden_size
-        bcx = linear(x, self.w_in, self.b_in)
+        bcx = linear(self.runtime, x, self.w_in, self.b_in)
         y = torch.empty(x.shape[0], H, dtype=x.dtype, device=x.device)
         ops.short_conv(bcx, self.w_taps, self.b_taps, cache.state, step.state_slot, step.req_of_row, step.row_start,
                        step.positions, y)
         if writes_cache:
             ops.short_conv_state(bcx, cache.state, step.state_slot, step.row_start, step.positions, step.n_requests,
                                  H, self.taps)
-        return linear(y, self.w_out, self.b_out, out_dtype=torch.float32)
+        return linear(self.runtime, y, self.w_out, self.b_out, out_dtype=torch.float32)

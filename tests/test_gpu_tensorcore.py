@@ -1,0 +1,111 @@
+"""The tcgen05 / TMA matrix-product kernels alone against torch in 32-bit: both orientations, every token-tile
+size, tails in every dimension, bias, 32-bit and bfloat16 outputs, split-K, and the grouped expert form with the
+SwiGLU epilogue against a loop over experts."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def tc():
+    from tandemllm_b200.kernels import tensorcore
+    from tandemllm_b200.parts import Runtime
+    rt = Runtime(torch.device(DEV), torch.bfloat16)
+    return tensorcore.enable(rt), rt
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale).to(torch.bfloat16)
+
+
+def rel(got, want):
+    return float((got.float().cpu() - want).abs().max() / want.abs().max().clamp_min(1e-6))
+
+
+@pytest.mark.parametrize("M", [1, 8, 17, 64, 100, 128, 129, 300, 1000])
+@pytest.mark.parametrize("N,K", [(128, 64), (200, 200), (3072, 2048), (72, 136)])
+def test_linear_all_shapes(M, N, K):
+    impl, rt = tc()
+    x, w, b = rnd(M, K, seed=1), rnd(N, K, seed=2, scale=0.1), torch.randn(N, generator=torch.Generator().manual_seed(3))
+    want = x.float() @ w.float().T
+    for out_dtype, bias in ((torch.bfloat16, None), (torch.float32, b)):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        assert impl.linear(x.to(DEV), w.to(DEV), None if bias is None else bias.to(DEV), out)
+        torch.cuda.synchronize()
+        assert int(rt.status) == 0
+        ref = want + (0 if bias is None else bias)
+        assert rel(out, ref) < (1e-2 if out_dtype == torch.bfloat16 else 1e-4), (M, N, K, out_dtype)
+
+
+@pytest.mark.parametrize("swap,bn", [(True, 16), (True, 32), (True, 64), (True, 128), (True, 256), (False, 16),
+                                     (False, 64), (False, 128), (False, 256)])
+def test_every_tile_shape_in_both_orientations(swap, bn):
+    impl, rt = tc()
+    M, N, K = 150, 330, 520
+    x, w = rnd(M, K, seed=4), rnd(N, K, seed=5, scale=0.1)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    impl.gemm(x.to(DEV), w.to(DEV), None, out, swap=swap, bn=bn)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    assert rel(out, x.float() @ w.float().T) < 1e-3
+
+
+def test_split_k_is_used_and_repeatable():
+    impl, rt = tc()
+    M, N, K = 8, 256, 4096                      # 2 CTAs without a split: the k range is cut
+    x, w = rnd(M, K, seed=6), rnd(N, K, seed=7, scale=0.05)
+    b = torch.randn(N, generator=torch.Generator().manual_seed(8))
+    outs = []
+    for _ in range(2):
+        out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        impl.linear(x.to(DEV), w.to(DEV), b.to(DEV), out)
+        outs.append(out.clone())
+    assert impl._workspace is not None
+    assert torch.equal(outs[0], outs[1])
+    assert rel(outs[0], x.float() @ w.float().T + b) < 1e-3
+
+
+@pytest.mark.parametrize("R,E,k,H,I", [(4, 8, 2, 128, 64), (8, 32, 4, 256, 192), (64, 8, 3, 136, 72), (700, 6, 2, 128, 96),
+                                       (2048, 4, 2, 64, 128)])
+def test_grouped_experts_with_swiglu(R, E, k, H, I):
+    from tandemllm_b200.config import PartSpec
+    from tandemllm_b200.parts import make_part
+    impl, rt = tc()
+    spec = PartSpec("sigmoid_topk_experts", {"num_experts": E, "top_k": k, "intermediate_size": I, "expert_bias": False,
+                                             "normalize": True, "scale": 1.0,
+                                             "names": {"router": "gate", "bias": "expert_bias", "experts": "experts",
+                                                       "gate": "w1", "up": "w3", "down": "w2"}})
+    part = make_part("feed_forward", spec, prefix="m.", hidden_size=H)
+    W = {"m.gate.weight": rnd(E, H, seed=9, scale=0.5).float()}
+    w13, w2 = rnd(E, 2 * I, H, seed=10, scale=0.2), rnd(E, H, I, seed=11, scale=0.2)
+    for e in range(E):
+        W[f"m.experts.{e}.w1.weight"], W[f"m.experts.{e}.w3.weight"] = w13[e, :I], w13[e, I:]
+        W[f"m.experts.{e}.w2.weight"] = w2[e]
+    part.weight_specs(set(W))
+    part.bind(lambda n: W[n], rt)
+    x = rnd(R, H, seed=12)
+    ids, wts = part.route(x.float().to(DEV))
+    out = torch.full((R, H), float("nan"), dtype=torch.float32, device=DEV)
+    assert impl.experts(part, x.to(DEV), ids, wts, out)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    want = torch.zeros(R, H)
+    xf, idc, wc = x.float(), ids.cpu(), wts.cpu()
+    for e in range(E):
+        rows, slot = torch.where(idc == e)
+        if rows.numel():
+            h = torch.nn.functional.silu(xf[rows] @ w13[e, :I].float().T) * (xf[rows] @ w13[e, I:].float().T)
+            want.index_add_(0, rows, (h.to(torch.bfloat16).float() @ w2[e].float().T) * wc[rows, slot, None])
+    assert rel(out, want) < 2e-2
+
+
+def test_shapes_tma_cannot_take_fall_back():
+    impl, rt = tc()
+    x, w = rnd(4, 100, seed=13), rnd(8, 100, seed=14)          # k = 100 is not a multiple of 8
+    out = torch.empty(4, 8, dtype=torch.bfloat16, device=DEV)
+    assert not impl.linear(x.to(DEV), w.to(DEV), None, out)
+    from tandemllm_b200.parts.linear import linear
+    got = linear(rt, x.to(DEV), w.to(DEV))
+    assert rel(got, x.float() @ w.float().T) < 1e-2
