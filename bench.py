@@ -169,6 +169,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
     ap.add_argument("--graph", default="on", choices=("on", "off"))
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--profile", action="store_true",
+                    help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
@@ -231,11 +233,15 @@ def main() -> int:
         torch.cuda.synchronize()
         before = ops.launches
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if a.profile:
+            torch.cuda.profiler.start()
         e0.record()
         for i in range(warmup, warmup + steps):
             one(i)
         e1.record()
         torch.cuda.synchronize()
+        if a.profile:
+            torch.cuda.profiler.stop()
         ms = e0.elapsed_time(e1)
         launched = ops.launches - before
         fn.check_status = True

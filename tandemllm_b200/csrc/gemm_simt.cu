@@ -159,9 +159,45 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmParams p) {
   }
 }
 
+// Few rows and few output columns (a router's E x H product): one CTA per output column, its 256 threads stride
+// over k and their sums are joined in a fixed order (lanes by shuffles, then the 8 warps in order).
+template <typename TIn, typename TOut, int MAXM>
+__global__ void __launch_bounds__(256) gemm_skinny_narrow_kernel(GemmParams p) {
+  __shared__ float part[8][MAXM];
+  const int n = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const TIn* A = (const TIn*)p.A;
+  const TIn* w = (const TIn*)p.W + (long long)n * p.ldw;
+  float acc[MAXM];
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m) acc[m] = 0.f;
+  for (int k = tid; k < p.K; k += 256) {
+    const float wv = to_f32(w[k]);
+#pragma unroll
+    for (int m = 0; m < MAXM; ++m)
+      if (m < p.M) acc[m] = fmaf(to_f32(A[(long long)m * p.lda + k]), wv, acc[m]);
+  }
+#pragma unroll
+  for (int m = 0; m < MAXM; ++m) {
+    const float v = warp_sum(acc[m]);
+    if (lane == 0) part[warp][m] = v;
+  }
+  __syncthreads();
+  if (tid < p.M) {
+    float v = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 8; ++wi) v += part[wi][tid];
+    if (p.bias) v += p.bias[n];
+    ((TOut*)p.C)[(long long)tid * p.ldc + n] = from_f32<TOut>(v);
+  }
+}
+
 template <typename TIn, typename TOut>
 static int launch(const GemmParams& p, int max_tiles, cudaStream_t stream) {
   if (!p.tile_group && !p.swiglu && p.M <= 8) {
+    if (p.N <= 512 && p.K >= 512) {
+      gemm_skinny_narrow_kernel<TIn, TOut, 8><<<p.N, 256, 0, stream>>>(p);
+      return 0;
+    }
     const int blocks = ceil_div(p.N, 8);
     gemm_skinny_kernel<TIn, TOut, 8><<<blocks, 256, 0, stream>>>(p);
     return 0;

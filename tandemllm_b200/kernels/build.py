@@ -32,7 +32,8 @@ NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 
 LIBRARIES: dict[str, list[str]] = {
     # every kernel of the 32-bit path, and the plain bfloat16 variants of the same kernels
-    "core": ["rows.cu", "gemm_simt.cu", "conv.cu", "attention_simt.cu", "moe_route.cu", "sampling.cu"],
+    "core": ["rows.cu", "gemm_simt.cu", "conv.cu", "attention_simt.cu", "attention_split.cu", "moe_route.cu",
+             "sampling.cu"],
     # the tcgen05 / TMA kernels of the bfloat16 path; a 32-bit run never builds or loads them
     "tensorcore": ["tc_gemm.cu"],
 }

@@ -51,6 +51,9 @@ _SIGNATURES = {
                     c_int, c_int, c_void_p, c_void_p],
     "tl_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tl_attention_spans": [c_int],
+    "tl_paged_attention_split": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "tl_router_topk": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p,
                        c_void_p],
     "tl_moe_max_tiles": [c_int, c_int, c_int],
@@ -222,6 +225,33 @@ def paged_attention_simt(q, k_cache, v_cache, block_table, page_size, req_of_row
                                          int(page_size), ptr(req_of_row), ptr(positions), float(scale),
                                          int(window or 0), ptr(out), rows, Hq, Hk, D, dtype_code(q.dtype), ptr(status),
                                          stream()), "paged_attention")
+    return out
+
+
+def attention_spans(max_context: int) -> int:
+    """Key spans the split kernel cuts a context of `max_context` positions into."""
+    return core().tl_attention_spans(int(max_context))
+
+
+def attention_scratch_floats(rows: int, num_heads: int, head_dim: int, n_spans: int) -> int:
+    return rows * num_heads * n_spans * (head_dim + 2)
+
+
+def paged_attention_split(q, k_cache, v_cache, block_table, page_size, req_of_row, positions, scale, window, out,
+                          scratch, n_spans: int, status) -> torch.Tensor:
+    """Attention of every row over its request's cached keys, split along the keys; `scratch` is float32 with at
+    least attention_scratch_floats(rows, Hq, D, n_spans) elements and n_spans covers the longest context."""
+    _need(q, k_cache.dtype, "q"); _need(out, q.dtype, "out"); _need(scratch, torch.float32, "scratch")
+    rows, Hq, D = q.shape
+    Hk = k_cache.shape[1]
+    if scratch.numel() < attention_scratch_floats(rows, Hq, D, n_spans):
+        raise KernelError(f"attention scratch of {scratch.numel()} floats, "
+                          f"{attention_scratch_floats(rows, Hq, D, n_spans)} needed")
+    check(core().tl_paged_attention_split(ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.shape[1],
+                                          int(page_size), ptr(req_of_row), ptr(positions), float(scale),
+                                          int(window or 0), ptr(out), ptr(scratch), rows, Hq, Hk, D, int(n_spans),
+                                          dtype_code(q.dtype), ptr(status), stream()), "paged_attention_split",
+          kernels=2 if n_spans > 1 else 1)
     return out
 
 

@@ -97,6 +97,8 @@ class AttentionMixer(Part):
         o = torch.empty(R, Hq, D, dtype=dt, device=dev)
         fast = self.runtime.attention_kernels
         if fast is None or not fast.attention(q, cache, table, step, self.scale, self.window, o):
-            ops.paged_attention_simt(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions,
-                                     self.scale, self.window, o, status)
+            spans = ops.attention_spans(step.max_context)
+            scratch = self.runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans))
+            ops.paged_attention_split(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions,
+                                      self.scale, self.window, o, scratch, spans, status)
         return linear(self.runtime, o.view(R, Hq * D), self.w_out, out_dtype=torch.float32)

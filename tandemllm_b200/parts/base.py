@@ -76,6 +76,15 @@ class Runtime:
         if self.status is None and self.device.type == "cuda":
             self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
+    def scratch(self, name: str, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """A kept device buffer of at least `numel` elements for a kernel's intermediate results. Kernels on one
+        stream run in order, so parts that run one after another may share a name."""
+        pool = self.__dict__.setdefault("_scratch", {})
+        buf = pool.get((name, dtype))
+        if buf is None or buf.numel() < numel:
+            buf = pool[(name, dtype)] = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+        return buf
+
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(device=self.device, dtype=self.dtype).contiguous()
 

@@ -92,7 +92,8 @@ def test_silu_mul(dtype):
 
 # ------------------------------------------------------------------------------------------ products
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("M,N,K", [(1, 130, 77), (3, 64, 64), (8, 257, 100), (9, 130, 77), (70, 96, 200), (200, 33, 17)])
+@pytest.mark.parametrize("M,N,K", [(1, 130, 77), (3, 64, 64), (8, 257, 100), (9, 130, 77), (70, 96, 200), (200, 33, 17),
+                                   (5, 40, 600), (8, 32, 2048)])
 def test_gemm_simt(dtype, M, N, K):
     o = ops()
     x, w, b = rnd(M, K, seed=6).to(dtype), rnd(N, K, seed=7).to(dtype), rnd(N, seed=8)
@@ -261,10 +262,25 @@ def paged_setup(seqs, Hk, D, page, dtype, seed):
     return kc.to(dtype), vc.to(dtype), table, ks, vs
 
 
+KERNELS = ["simt", "split"]
+
+
+def attend(o, kind, q, kc, vc, table, page, req_of_row, positions, scale, window, out, status):
+    """The plain CUDA-core kernel or the split (flash-decoding) kernel, the latter with scratch sized for the call."""
+    if kind == "simt":
+        return o.paged_attention_simt(q, kc, vc, table, page, req_of_row, positions, scale, window, out, status)
+    spans = o.attention_spans(int(positions.max()) + 1)
+    R, Hq, D = q.shape
+    scratch = torch.full((o.attention_scratch_floats(R, Hq, D, spans),), float("nan"), device=DEV)
+    return o.paged_attention_split(q, kc, vc, table, page, req_of_row, positions, scale, window, out, scratch, spans, status)
+
+
+@pytest.mark.parametrize("kind", KERNELS)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("Hq,Hk,D,page,window", [(6, 2, 48, 16, None), (5, 5, 16, 16, None), (8, 1, 128, 32, None),
-                                                 (4, 2, 64, 16, 37), (3, 1, 256, 64, None), (4, 4, 80, 16, 16)])
-def test_paged_attention_mixed_rows(dtype, Hq, Hk, D, page, window):
+                                                 (4, 2, 64, 16, 37), (3, 1, 256, 64, None), (4, 4, 80, 16, 16),
+                                                 (24, 2, 32, 16, None)])
+def test_paged_attention_mixed_rows(kind, dtype, Hq, Hk, D, page, window):
     """A decode row at a long context, a prompt portion in the middle of a sequence, and a sequence's first rows,
     in one call, against whole-sequence attention."""
     o = ops()
@@ -278,8 +294,8 @@ def test_paged_attention_mixed_rows(dtype, Hq, Hk, D, page, window):
     out = torch.empty(R, Hq, D, dtype=dtype, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     scale = 0.7 / math.sqrt(D)
-    o.paged_attention_simt(q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), page, i32(req_of_row), i32(positions),
-                           scale, window, out, status)
+    attend(o, kind, q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), page, i32(req_of_row), i32(positions), scale,
+           window, out, status)
     assert int(status) == 0
     at = 0
     for b, (L, n) in enumerate(zip(seqs, news)):
@@ -288,9 +304,10 @@ def test_paged_attention_mixed_rows(dtype, Hq, Hk, D, page, window):
         at += n
 
 
+@pytest.mark.parametrize("kind", KERNELS)
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("far", [0, 15, 16, 17, 255, 256, 300, 511])
-def test_one_far_key_stands_out(dtype, far):
+def test_one_far_key_stands_out(kind, dtype, far):
     """Among 512 keys, one key is made to match the query so strongly that the output must be its value: a key
     skipped or read from the wrong page (a page's edge, a chunk's edge) shows at once."""
     o = ops()
@@ -305,8 +322,8 @@ def test_one_far_key_stands_out(dtype, far):
     out = torch.empty(1, Hq, D, dtype=dtype, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    o.paged_attention_simt(q.to(dtype).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), page, i32([0]), i32([L - 1]),
-                           1.0, None, out, status)
+    attend(o, kind, q.to(dtype).to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), page, i32([0]), i32([L - 1]), 1.0, None,
+           out, status)
     want = plain_attention(q, ks[0], vs[0], 1.0)
     close(out, want, dtype, f"far key {far}")
     weight = torch.softmax(torch.einsum("hd,shd->hs", q[0], ks[0].repeat_interleave(2, 1)), -1)[:, far]
@@ -314,7 +331,33 @@ def test_one_far_key_stands_out(dtype, far):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_window_edge(dtype):
+@pytest.mark.parametrize("window", [None, 700, 256, 257])
+def test_split_kernel_over_many_spans(dtype, window):
+    """Contexts of several 256-key spans, with and without a window whose edge falls inside a span, and rows of
+    one call that need different numbers of spans."""
+    o = ops()
+    Hq, Hk, D, page = 8, 2, 64, 16
+    seqs, news = [1500, 300, 1024], [2, 1, 3]
+    kc, vc, table, ks, vs = paged_setup(seqs, Hk, D, page, dtype, seed=45)
+    R = sum(news)
+    q = rnd(R, Hq, D, seed=46).to(dtype)
+    req_of_row = sum(([b] * n for b, n in enumerate(news)), [])
+    positions = sum((list(range(L - n, L)) for L, n in zip(seqs, news)), [])
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    out = torch.full((R, Hq, D), float("nan"), dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    attend(o, "split", q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), page, i32(req_of_row), i32(positions), 0.125,
+           window, out, status)
+    assert int(status) == 0
+    at = 0
+    for b, (L, n) in enumerate(zip(seqs, news)):
+        close(out[at:at + n], plain_attention(q[at:at + n].float(), ks[b], vs[b], 0.125, window), dtype, f"sequence {b}")
+        at += n
+
+
+@pytest.mark.parametrize("kind", KERNELS)
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(kind, dtype):
     """With a window of w the key w positions back is out and the one w-1 back is in; pages wholly behind the
     window may be gone (-1 in the table)."""
     o = ops()
@@ -331,8 +374,8 @@ def test_window_edge(dtype):
         t2[0, :(L - w) // page] = -1                     # pages the window has passed
         out = torch.empty(1, Hq, D, dtype=dtype, device=DEV)
         status = torch.zeros(1, dtype=torch.int32, device=DEV)
-        o.paged_attention_simt(q.to(dtype).to(DEV), kc2.to(DEV), vc.to(DEV), t2.to(DEV), page, i32([0]), i32([L - 1]),
-                               1.0, w, out, status)
+        attend(o, kind, q.to(dtype).to(DEV), kc2.to(DEV), vc.to(DEV), t2.to(DEV), page, i32([0]), i32([L - 1]), 1.0, w,
+               out, status)
         assert int(status) == 0
         close(out, plain_attention(q, k2[0], vs[0], 1.0, w), dtype, f"hot key at {hot}")
 
