@@ -61,7 +61,8 @@ class Engine:
             pages = args.parallel * (-(-args.max_len // args.block_size))
         self.cache = CacheManager(model.cache_needs(), num_pages=pages, max_requests=args.parallel,
                                   page_size=args.block_size, dtype=model.runtime.dtype, device=self.device)
-        self.step_function = StepFunction(model, self.cache)
+        self.step_function = StepFunction(model, self.cache, use_graphs=args.graph and model.graph_safe,
+                                          max_graph_batch=args.parallel)
         self.sampler = Sampler(self.device)
         self.scheduler = Scheduler(self.cache, max_num_seqs=args.parallel, max_num_batched_tokens=args.max_batched_tokens,
                                    chunk_size=args.chunk_size, max_model_len=args.max_len,

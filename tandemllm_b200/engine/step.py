@@ -9,6 +9,11 @@ request's length has moved by its tokens and windowed groups have given back wha
 
 The reference never mixes prompt chunks and decode rows in one pass (engine.py:353-365, :602); here they
 are the same case, because every kernel takes rows with explicit request, position and tables.
+
+Decode-only steps (every request brings one token and wants its logits) can run from CUDA graphs, as the
+reference replays one graph per decode token (engine.py:745-794): a graph is captured per batch size,
+block-table width and context bucket the first time that shape has run eagerly, and replayed afterwards
+from the same staged integers. The kernels and their order are the eager step's own.
 """
 
 from __future__ import annotations
@@ -17,7 +22,8 @@ from dataclasses import dataclass
 
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, OutOfPages
+from ..kernels import ops
 from ..parts.base import StepContext
 
 
@@ -31,45 +37,70 @@ class StepEntry:
 
 
 class KernelFault(RuntimeError):
-    """A kernel recorded an index outside what it was given (and skipped the access)."""
+    """A kernel recorded an index outside what it was given (and skipped the access), or gave up a bounded wait."""
 
 
 _STATUS = {1: "a token id outside the vocabulary", 2: "a key/value write to a position without a page",
-           3: "a visible key without a page"}
+           3: "a visible key without a page", 11: "a pipeline wait that ran out in a tensor-core kernel"}
+
+CONTEXT_BUCKET = 1024       # a decode graph serves contexts up to the next multiple of this
+
+
+class _Staging:
+    """Three pinned buffers that take turns, so that a buffer is rewritten only after the copy that read it."""
+
+    def __init__(self, cap: int):
+        self.cap = cap
+        self.buffers = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+        self.events = [None, None, None]
+        self.turn = 0
+
+    def next(self) -> torch.Tensor:
+        self.turn = (self.turn + 1) % 3
+        if self.events[self.turn] is not None:
+            self.events[self.turn].synchronize()
+        return self.buffers[self.turn]
+
+    def copied(self) -> None:
+        ev = self.events[self.turn] or torch.cuda.Event()
+        ev.record()
+        self.events[self.turn] = ev
+
+
+class _DecodeGraph:
+    """One captured decode step: its device integers, its context, the graph and the logits it writes."""
+
+    def __init__(self, dev: torch.Tensor, step: StepContext):
+        self.dev, self.step = dev, step
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.kernels = 0
+        self.logits: torch.Tensor | None = None
 
 
 class StepFunction:
-    def __init__(self, model, cache: CacheManager, check_status: bool = True):
+    def __init__(self, model, cache: CacheManager, check_status: bool = True, use_graphs: bool = False,
+                 max_graph_batch: int = 64):
         self.model, self.cache = model, cache
         self.device = model.runtime.device
         self.check_status = check_status
-        self._pinned = None
+        self.use_graphs = use_graphs
+        self.max_graph_batch = max_graph_batch
+        self._staging: _Staging | None = None
         self._device_ints = None
+        self._graphs: dict[tuple, _DecodeGraph] = {}
+        self._graph_pool = None
         self.steps = 0
         self.rows_run = 0
+        self.graph_replays = 0
 
-    def _buffers(self, n: int):
-        """A pinned staging buffer that no copy in flight still reads, and the device buffer it is copied to.
-        Three pinned buffers take turns; each waits for the event recorded after its last copy."""
-        if self._pinned is None or self._pinned[0].numel() < n:
-            cap = max(4096, 2 * n)
+    # ---- laying a batch out ----
+    def _pinned(self, n: int) -> torch.Tensor:
+        if self._staging is None or self._staging.cap < n:
             torch.cuda.current_stream().synchronize()
-            self._pinned = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(3)]
-            self._events = [None, None, None]
-            self._turn = 0
-            self._device_ints = torch.empty(cap, dtype=torch.int32, device=self.device)
-        self._turn = (self._turn + 1) % 3
-        if self._events[self._turn] is not None:
-            self._events[self._turn].synchronize()
-        return self._pinned[self._turn], self._device_ints
+            self._staging = _Staging(max(4096, 2 * n))
+        return self._staging.next()
 
-    def _copied(self) -> None:
-        ev = self._events[self._turn] or torch.cuda.Event()
-        ev.record()
-        self._events[self._turn] = ev
-
-    def build(self, entries: list[StepEntry]) -> StepContext:
-        """Reserve pages for the batch and stage its integers on the device (one host-to-device copy)."""
+    def _reserve(self, entries: list[StepEntry]) -> None:
         cache = self.cache
         wants = []
         for e in entries:
@@ -82,71 +113,139 @@ class StepFunction:
         if len({e.request for e in entries}) != len(entries):
             raise ValueError("a request appears twice in one step")
         if not cache.can_reserve(wants):
-            from ..cache.manager import OutOfPages
             raise OutOfPages(f"the step's {sum(len(e.tokens) for e in entries)} tokens need more pages than are free")
         for req, new_len in wants:
             cache.reserve(req, new_len)
 
-        B = len(entries)
-        R = sum(len(e.tokens) for e in entries)
-        n_out = sum(len(e.want) for e in entries)
-        G = len(cache.groups)
-        max_pages = max(1, cache.max_table_len([e.request for e in entries]))
-        total = 3 * R + (B + 1) + B + n_out + G * B * max_pages
-        pinned, dev = self._buffers(total)
-        host = pinned.numpy()
-        o_tok, o_pos, o_req = 0, R, 2 * R
-        o_start = 3 * R
-        o_slot = o_start + B + 1
-        o_out = o_slot + B
-        o_tab = o_out + n_out
-        r = 0
-        k = 0
-        max_rows = max_ctx = 0
+    @staticmethod
+    def _layout(B: int, R: int, n_out: int, G: int, max_pages: int) -> dict:
+        o = {"tok": 0, "pos": R, "req": 2 * R, "start": 3 * R}
+        o["slot"] = o["start"] + B + 1
+        o["out"] = o["slot"] + B
+        o["tab"] = o["out"] + n_out
+        o["total"] = o["tab"] + G * B * max_pages
+        return o
+
+    def _fill(self, host, o: dict, entries: list[StepEntry], max_pages: int) -> tuple[int, int]:
+        """Write the batch's integers into `host` (a numpy view) at layout `o`; returns (most rows of a request,
+        longest context after the step)."""
+        cache = self.cache
+        B, G = len(entries), len(cache.groups)
+        r = k = max_rows = max_ctx = 0
         for b, e in enumerate(entries):
             n = len(e.tokens)
             start = cache.length_of(e.request)
-            host[o_tok + r:o_tok + r + n] = e.tokens
-            host[o_pos + r:o_pos + r + n] = range(start, start + n)
-            host[o_req + r:o_req + r + n] = b
-            host[o_start + b] = r
-            host[o_slot + b] = cache.slot_of(e.request)
+            host[o["tok"] + r:o["tok"] + r + n] = e.tokens
+            host[o["pos"] + r:o["pos"] + r + n] = range(start, start + n)
+            host[o["req"] + r:o["req"] + r + n] = b
+            host[o["start"] + b] = r
+            host[o["slot"] + b] = cache.slot_of(e.request)
             for w in e.want:
-                host[o_out + k] = r + w
+                host[o["out"] + k] = r + w
                 k += 1
             for g in range(G):
                 t = cache.table(g, e.request)
-                base = o_tab + (g * B + b) * max_pages
+                base = o["tab"] + (g * B + b) * max_pages
                 host[base:base + len(t)] = t
                 host[base + len(t):base + max_pages] = -1
             r += n
             max_rows = max(max_rows, n)
             max_ctx = max(max_ctx, start + n)
-        host[o_start + B] = R
-        dev[:total].copy_(pinned[:total], non_blocking=True)
-        self._copied()
-        tables = [dev[o_tab + g * B * max_pages:o_tab + (g + 1) * B * max_pages].view(B, max_pages) for g in range(G)]
-        return StepContext(
-            n_rows=R, n_requests=B, token_ids=dev[o_tok:o_tok + R], positions=dev[o_pos:o_pos + R],
-            req_of_row=dev[o_req:o_req + R], row_start=dev[o_start:o_start + B + 1], state_slot=dev[o_slot:o_slot + B],
-            block_tables=tables, out_rows=dev[o_out:o_out + n_out], n_out=n_out, max_rows_per_request=max_rows,
-            max_context=max_ctx,
-            host={"row_start": [int(x) for x in host[o_start:o_start + B + 1]],
-                  "start_pos": [cache.length_of(e.request) for e in entries],
-                  "slots": [cache.slot_of(e.request) for e in entries]})
+        host[o["start"] + B] = r
+        return max_rows, max_ctx
 
+    def _context(self, dev: torch.Tensor, o: dict, B: int, R: int, n_out: int, max_pages: int, max_rows: int,
+                 max_ctx: int, host_lists: dict) -> StepContext:
+        G = len(self.cache.groups)
+        tables = [dev[o["tab"] + g * B * max_pages:o["tab"] + (g + 1) * B * max_pages].view(B, max_pages) for g in range(G)]
+        return StepContext(
+            n_rows=R, n_requests=B, token_ids=dev[o["tok"]:o["tok"] + R], positions=dev[o["pos"]:o["pos"] + R],
+            req_of_row=dev[o["req"]:o["req"] + R], row_start=dev[o["start"]:o["start"] + B + 1],
+            state_slot=dev[o["slot"]:o["slot"] + B], block_tables=tables, out_rows=dev[o["out"]:o["out"] + n_out],
+            n_out=n_out, max_rows_per_request=max_rows, max_context=max_ctx, host=host_lists)
+
+    def build(self, entries: list[StepEntry]) -> StepContext:
+        """Reserve pages for the batch and stage its integers on the device (one host-to-device copy)."""
+        self._reserve(entries)
+        cache = self.cache
+        B = len(entries)
+        R = sum(len(e.tokens) for e in entries)
+        n_out = sum(len(e.want) for e in entries)
+        max_pages = max(1, cache.max_table_len([e.request for e in entries]))
+        o = self._layout(B, R, n_out, len(cache.groups), max_pages)
+        pinned = self._pinned(o["total"])
+        if self._device_ints is None or self._device_ints.numel() < o["total"]:
+            self._device_ints = torch.empty(max(4096, 2 * o["total"]), dtype=torch.int32, device=self.device)
+        dev = self._device_ints
+        host = pinned.numpy()
+        max_rows, max_ctx = self._fill(host, o, entries, max_pages)
+        dev[:o["total"]].copy_(pinned[:o["total"]], non_blocking=True)
+        self._staging.copied()
+        lists = {"row_start": [int(x) for x in host[o["start"]:o["start"] + B + 1]],
+                 "start_pos": [cache.length_of(e.request) for e in entries],
+                 "slots": [cache.slot_of(e.request) for e in entries]}
+        return self._context(dev, o, B, R, n_out, max_pages, max_rows, max_ctx, lists)
+
+    # ---- running ----
     def run(self, entries: list[StepEntry]) -> torch.Tensor:
         """Logits float32 [wanted, vocab] in the order of the entries and of their `want`."""
         if not entries:
             return torch.empty(0, self.model.vocab_size, dtype=torch.float32, device=self.device)
-        step = self.build(entries)
-        logits = self.model.forward(step, self.cache.site_cache)
+        if (self.use_graphs and len(entries) <= self.max_graph_batch
+                and all(len(e.tokens) == 1 and e.want == [0] for e in entries)):
+            logits = self._run_decode_graph(entries)
+        else:
+            step = self.build(entries)
+            logits = self.model.forward(step, self.cache.site_cache)
         for e in entries:
             self.cache.advance(e.request, self.cache.length_of(e.request) + len(e.tokens))
         self.steps += 1
-        self.rows_run += step.n_rows
+        self.rows_run += sum(len(e.tokens) for e in entries)
         if self.check_status:
             self.raise_on_fault()
+        return logits
+
+    def _run_decode_graph(self, entries: list[StepEntry]) -> torch.Tensor:
+        """A decode-only step: eager the first time its shape is seen (and then captured), a graph replay after."""
+        self._reserve(entries)
+        cache = self.cache
+        B = len(entries)
+        pages = max(1, cache.max_table_len([e.request for e in entries]))
+        width = 8
+        while width < pages:
+            width *= 2
+        longest = max(cache.length_of(e.request) for e in entries) + 1
+        ctx = -(-longest // CONTEXT_BUCKET) * CONTEXT_BUCKET
+        key = (B, width, ctx)
+        o = self._layout(B, B, B, len(cache.groups), width)
+        slot = self._graphs.get(key)
+        fresh = slot is None
+        if fresh:
+            dev = torch.empty(o["total"], dtype=torch.int32, device=self.device)
+            lists = {"row_start": list(range(B + 1)), "start_pos": None, "slots": None}
+            slot = self._graphs[key] = _DecodeGraph(dev, self._context(dev, o, B, B, B, width, 1, ctx, lists))
+        pinned = self._pinned(o["total"])
+        self._fill(pinned.numpy(), o, entries, width)
+        slot.dev.copy_(pinned[:o["total"]], non_blocking=True)
+        self._staging.copied()
+        if slot.graph is not None:
+            slot.graph.replay()
+            self.graph_replays += 1
+            ops.launches += slot.kernels
+            return slot.logits
+        # the first step of this shape runs eagerly (it also sizes every kept buffer); then the same calls are
+        # captured for the steps that follow. Capturing launches nothing.
+        logits = self.model.forward(slot.step, cache.site_cache)
+        torch.cuda.current_stream().synchronize()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launches
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            slot.logits = self.model.forward(slot.step, cache.site_cache)
+        slot.kernels = ops.launches - before        # kernels one replay runs; capturing ran none
+        ops.launches = before
+        slot.graph = graph
         return logits
 
     def raise_on_fault(self) -> None:

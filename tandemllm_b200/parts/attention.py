@@ -22,6 +22,10 @@ from .linear import linear
 
 @register_part("mixer", "attention")
 class AttentionMixer(Part):
+    @property
+    def graph_safe(self) -> bool:
+        return self.position.graph_safe
+
     def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
         super().__init__(spec, prefix, hidden_size)
         self.num_heads = int(spec["num_heads"])

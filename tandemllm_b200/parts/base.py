@@ -140,7 +140,13 @@ class StepContext:
 
 
 class Part:
-    """Shared plumbing: a part keeps its spec and names its tensors under a prefix."""
+    """Shared plumbing: a part keeps its spec and names its tensors under a prefix.
+
+    `graph_safe`: the part's forward only launches work on the current stream, with shapes that depend on the
+    batch's sizes alone (no host reads of device data, no Python branches on values), so a decode step that
+    runs it may be captured in a CUDA graph. A part says so itself; the default is no."""
+
+    graph_safe = False
 
     def __init__(self, spec: PartSpec, prefix: str = "", hidden_size: int = 0, **_):
         self.spec = spec

@@ -25,6 +25,8 @@ from .linear import linear
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
+    graph_safe = True
+
     def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
         super().__init__(spec, prefix, hidden_size)
         self.inter = int(spec["intermediate_size"])
@@ -50,6 +52,8 @@ class SwiGLU(Part):
 
 @register_part("feed_forward", "sigmoid_topk_experts")
 class SigmoidTopKExperts(Part):
+    graph_safe = True
+
     def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
         super().__init__(spec, prefix, hidden_size)
         self.num_experts = int(spec["num_experts"])

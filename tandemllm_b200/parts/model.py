@@ -68,6 +68,12 @@ class DecoderModel:
                         stack.append(v)
         return total
 
+    @property
+    def graph_safe(self) -> bool:
+        """Every part of every layer says its forward may be captured in a CUDA graph."""
+        return all(getattr(p, "graph_safe", False) for layer in self.layers for p in layer.parts) and \
+            getattr(self.final_norm, "graph_safe", False)
+
     # ---- caches ----
     def cache_needs(self) -> list:
         """Per site of the schedule: the need of its mixer, or None when the site reads another site's cache."""

@@ -17,6 +17,8 @@ from .base import Part, register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
+    graph_safe = True
+
     def __init__(self, spec, prefix: str = "", size: int = 0, **_):
         super().__init__(spec, prefix)
         self.size = size

@@ -20,6 +20,8 @@ from .base import Part, register_part
 
 @register_part("position_encoding", "rope_neox")
 class RotaryNeox(Part):
+    graph_safe = True
+
     def __init__(self, spec, head_dim: int = 0, **_):
         super().__init__(spec)
         self.theta = float(spec["theta"])
@@ -43,6 +45,8 @@ class RotaryNeox(Part):
 
 @register_part("position_encoding", "none")
 class NoPosition(Part):
+    graph_safe = True
+
     def __init__(self, spec, head_dim: int = 0, **_):
         super().__init__(spec)
 

@@ -22,6 +22,8 @@ from .linear import linear
 
 @register_part("mixer", "short_conv")
 class ShortConvMixer(Part):
+    graph_safe = True
+
     def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
         super().__init__(spec, prefix, hidden_size)
         self.taps = int(spec["taps"])

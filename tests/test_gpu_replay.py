@@ -167,6 +167,25 @@ def test_long_decoding(case):
     case.compare(case.replay(eng, trace), "long decoding")
 
 
+def test_decode_graph_equals_eager_bit_for_bit(case):
+    """Decode steps replayed from CUDA graphs give the eager step's bits (the reference holds its decode graph to
+    the same, tests/gpu/test_lfm2_moe_gpu.py:158-186), alone and with two requests decoding together."""
+    reqs = {"q1": case.requests["q1"], "q5": case.requests["q5"]}
+    trace = traces.decoded_tail({"q1": reqs["q1"]}, 40)
+    both = [{"step": 0, "entries": [{"id": r, "tokens": t[:20], "want": []} for r, t in reqs.items()], "end": []}]
+    both += [{"step": 1 + i, "entries": [{"id": r, "tokens": [t[20 + i]], "want": [0]} for r, t in reqs.items()], "end": []}
+             for i in range(25)]
+    for tr in (trace, both):
+        with_graph = case.engine(max_tokens=256, graph=True)
+        eager = case.engine(max_tokens=256, graph=False)
+        a, b = case.replay(with_graph, tr), case.replay(eager, tr)
+        assert with_graph.step_function.graph_replays > 10 and eager.step_function.graph_replays == 0
+        assert a.keys() == b.keys()
+        for key in a:
+            assert torch.equal(a[key], b[key]), key
+        case.compare(a, "decode from graphs")
+
+
 def test_first_tokens_of_a_sequence(case):
     """A sequence shorter than the conv taps and than a page; and a first portion of one token."""
     eng = case.engine(max_tokens=128)
