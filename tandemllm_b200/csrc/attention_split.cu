@@ -15,7 +15,7 @@
 namespace tl {
 
 constexpr int SPAN = 256;        // key positions per CTA
-constexpr int MAX_GROUP = 8;     // query heads per KV head handled in one pass
+// GM (a template parameter, 4 or 8): query heads of a KV head handled in one pass; larger groups take more passes
 constexpr int MAX_D = 256;
 
 template <typename T> struct Vec;
@@ -40,7 +40,7 @@ template <> struct Vec<bf16> {
 };
 
 // grid (rows, Hk, spans), 128 threads
-template <typename T>
+template <typename T, int GM>
 __global__ void __launch_bounds__(128) attention_span_kernel(
     const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ req_of_row,
@@ -59,10 +59,10 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
   const int* table = block_table + (long long)req_of_row[r] * max_pages;
   const int nch = D / VEC;                        // 16-byte chunks per key row
   const int nkl = 128 / nch;                      // key lanes of the value phase
-  float* qs = smem;                               // [MAX_GROUP][D]
-  float* sc = qs + MAX_GROUP * D;                 // [MAX_GROUP][SPAN]
-  long long* offs = (long long*)(sc + MAX_GROUP * SPAN);   // [SPAN] element offset of each key row, -1: no page
-  float* red = (float*)(offs + SPAN);             // [128 * VEC * MAX_GROUP] value-phase partials; also reductions
+  float* qs = smem;                               // [GM][D]
+  float* sc = qs + GM * D;                 // [GM][SPAN]
+  long long* offs = (long long*)(sc + GM * SPAN);   // [SPAN] element offset of each key row, -1: no page
+  float* red = (float*)(offs + SPAN);             // [128 * VEC * GM] value-phase partials; also reductions
 
   for (int i = tid; i < n_keys; i += 128) {
     const int kp = k_begin + i;
@@ -76,21 +76,70 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
   }
   const bool single = (lo / SPAN) == (pos / SPAN);     // the row has one span: write the result directly
 
-  for (int h0 = 0; h0 < G; h0 += MAX_GROUP) {
-    const int gc = min(MAX_GROUP, G - h0);            // heads in this pass
+  for (int h0 = 0; h0 < G; h0 += GM) {
+    const int gc = min(GM, G - h0);            // heads in this pass
     const int head0 = g * G + h0;
     __syncthreads();
     for (int i = tid; i < gc * D; i += 128)
       qs[i] = to_f32(q[((long long)r * Hq + head0 + i / D) * D + i % D]) * scale;
     __syncthreads();
+    float mx[GM];
+#pragma unroll
+    for (int j = 0; j < GM; ++j) mx[j] = -INFINITY;
+    const bool pow2 = (nch & (nch - 1)) == 0 && nch <= 32;
+    if (pow2) {
+      // ---- scores, coalesced: thread (key lane, chunk) multiplies its 16 bytes of each key row by the matching
+      // part of q; the chunks of a key sit in neighbouring lanes and are added by shuffles in a fixed order ----
+      const int c = tid % nch, kl = tid / nch;
+      float qreg[GM][VEC];
+#pragma unroll
+      for (int j = 0; j < GM; ++j)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) qreg[j][e] = j < gc ? qs[j * D + c * VEC + e] : 0.f;
+      const int rounds = (n_keys + nkl - 1) / nkl;          // every lane runs every round: the shuffles are warp-wide
+      for (int t = 0; t < rounds; t += 2) {
+        long long off[2];
+        float kv[2][VEC];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int i = (t + u) * nkl + kl;
+          off[u] = (t + u < rounds && i < n_keys) ? offs[i] : -1;
+          if (off[u] >= 0) Vec<T>::load(k_cache + off[u] + c * VEC, kv[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (t + u >= rounds) break;
+          const int i = (t + u) * nkl + kl;
+          float dot[GM];
+#pragma unroll
+          for (int j = 0; j < GM; ++j) {
+            dot[j] = 0.f;
+            if (off[u] >= 0)
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) dot[j] = fmaf(qreg[j][e], kv[u][e], dot[j]);
+          }
+          for (int w = nch >> 1; w > 0; w >>= 1)
+#pragma unroll
+            for (int j = 0; j < GM; ++j)
+              if (j < gc) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], w);
+          if (c == 0 && i < n_keys) {
+#pragma unroll
+            for (int j = 0; j < GM; ++j) {
+              if (j < gc) {
+                const float s = off[u] >= 0 ? dot[j] : -INFINITY;
+                sc[j * SPAN + i] = s;
+                mx[j] = fmaxf(mx[j], s);
+              }
+            }
+          }
+        }
+      }
+    } else
     // ---- scores: one thread per key ----
-    float mx[MAX_GROUP];
-#pragma unroll
-    for (int j = 0; j < MAX_GROUP; ++j) mx[j] = -INFINITY;
     for (int i = tid; i < n_keys; i += 128) {
-      float dot[MAX_GROUP];
+      float dot[GM];
 #pragma unroll
-      for (int j = 0; j < MAX_GROUP; ++j) dot[j] = 0.f;
+      for (int j = 0; j < GM; ++j) dot[j] = 0.f;
       const long long off = offs[i];
       if (off >= 0) {
         const T* kr = k_cache + off;
@@ -98,7 +147,7 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
           float kv[VEC];
           Vec<T>::load(kr + c * VEC, kv);
 #pragma unroll
-          for (int j = 0; j < MAX_GROUP; ++j) {
+          for (int j = 0; j < GM; ++j) {
             if (j < gc) {
               const float* qj = qs + j * D + c * VEC;
 #pragma unroll
@@ -108,7 +157,7 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
         }
       }
 #pragma unroll
-      for (int j = 0; j < MAX_GROUP; ++j) {
+      for (int j = 0; j < GM; ++j) {
         if (j < gc) {
           const float s = off >= 0 ? dot[j] : -INFINITY;
           sc[j * SPAN + i] = s;
@@ -118,23 +167,23 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
     }
     // ---- per-head maximum over the span ----
 #pragma unroll
-    for (int j = 0; j < MAX_GROUP; ++j) mx[j] = warp_max(mx[j]);
+    for (int j = 0; j < GM; ++j) mx[j] = warp_max(mx[j]);
     __syncthreads();
     if ((tid & 31) == 0)
 #pragma unroll
-      for (int j = 0; j < MAX_GROUP; ++j) red[(tid >> 5) * MAX_GROUP + j] = mx[j];
+      for (int j = 0; j < GM; ++j) red[(tid >> 5) * GM + j] = mx[j];
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < MAX_GROUP; ++j)
-      mx[j] = fmaxf(fmaxf(red[j], red[MAX_GROUP + j]), fmaxf(red[2 * MAX_GROUP + j], red[3 * MAX_GROUP + j]));
+    for (int j = 0; j < GM; ++j)
+      mx[j] = fmaxf(fmaxf(red[j], red[GM + j]), fmaxf(red[2 * GM + j], red[3 * GM + j]));
     __syncthreads();
     // ---- exponentials and their sums ----
-    float sum[MAX_GROUP];
+    float sum[GM];
 #pragma unroll
-    for (int j = 0; j < MAX_GROUP; ++j) sum[j] = 0.f;
+    for (int j = 0; j < GM; ++j) sum[j] = 0.f;
     for (int i = tid; i < n_keys; i += 128) {
 #pragma unroll
-      for (int j = 0; j < MAX_GROUP; ++j) {
+      for (int j = 0; j < GM; ++j) {
         if (j < gc) {
           const float s = sc[j * SPAN + i];
           const float p = (s == -INFINITY) ? 0.f : expf(s - mx[j]);
@@ -144,49 +193,58 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
       }
     }
 #pragma unroll
-    for (int j = 0; j < MAX_GROUP; ++j) sum[j] = warp_sum(sum[j]);
+    for (int j = 0; j < GM; ++j) sum[j] = warp_sum(sum[j]);
     if ((tid & 31) == 0)
 #pragma unroll
-      for (int j = 0; j < MAX_GROUP; ++j) red[(tid >> 5) * MAX_GROUP + j] = sum[j];
+      for (int j = 0; j < GM; ++j) red[(tid >> 5) * GM + j] = sum[j];
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < MAX_GROUP; ++j)
-      sum[j] = (red[j] + red[MAX_GROUP + j]) + (red[2 * MAX_GROUP + j] + red[3 * MAX_GROUP + j]);
+    for (int j = 0; j < GM; ++j)
+      sum[j] = (red[j] + red[GM + j]) + (red[2 * GM + j] + red[3 * GM + j]);
     __syncthreads();
     // ---- values: thread (key lane kl, chunk c) adds p * v over keys kl, kl + nkl, ... ----
     const int c = tid % nch, kl = tid / nch;
-    float acc[MAX_GROUP][VEC];
+    float acc[GM][VEC];
 #pragma unroll
-    for (int j = 0; j < MAX_GROUP; ++j)
+    for (int j = 0; j < GM; ++j)
 #pragma unroll
       for (int e = 0; e < VEC; ++e) acc[j][e] = 0.f;
     if (kl < nkl) {
-      for (int i = kl; i < n_keys; i += nkl) {
-        const long long off = offs[i];
-        if (off < 0) continue;
-        float vv[VEC];
-        Vec<T>::load(v_cache + off + c * VEC, vv);
+      for (int i0 = kl; i0 < n_keys; i0 += 4 * nkl) {
+        long long off[4];
+        float vv[4][VEC];
 #pragma unroll
-        for (int j = 0; j < MAX_GROUP; ++j) {
-          if (j < gc) {
-            const float p = sc[j * SPAN + i];
+        for (int u = 0; u < 4; ++u) {           // four loads in flight before any is used
+          const int i = i0 + u * nkl;
+          off[u] = i < n_keys ? offs[i] : -1;
+          if (off[u] >= 0) Vec<T>::load(v_cache + off[u] + c * VEC, vv[u]);
+        }
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) acc[j][e] = fmaf(p, vv[e], acc[j][e]);
+        for (int u = 0; u < 4; ++u) {
+          if (off[u] < 0) continue;
+          const int i = i0 + u * nkl;
+#pragma unroll
+          for (int j = 0; j < GM; ++j) {
+            if (j < gc) {
+              const float p = sc[j * SPAN + i];
+#pragma unroll
+              for (int e = 0; e < VEC; ++e) acc[j][e] = fmaf(p, vv[u][e], acc[j][e]);
+            }
           }
         }
       }
 #pragma unroll
-      for (int j = 0; j < MAX_GROUP; ++j)
+      for (int j = 0; j < GM; ++j)
         if (j < gc)
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) red[((long long)kl * MAX_GROUP + j) * D + c * VEC + e] = acc[j][e];
+          for (int e = 0; e < VEC; ++e) red[((long long)kl * GM + j) * D + c * VEC + e] = acc[j][e];
     }
     __syncthreads();
     // ---- join the key lanes in order and store ----
     for (int i = tid; i < gc * D; i += 128) {
       const int j = i / D, d = i % D;
       float o = 0.f;
-      for (int l = 0; l < nkl; ++l) o += red[((long long)l * MAX_GROUP + j) * D + d];
+      for (int l = 0; l < nkl; ++l) o += red[((long long)l * GM + j) * D + d];
       const int head = head0 + j;
       if (single) {
         out[((long long)r * Hq + head) * D + d] = from_f32<T>(sum[j] > 0.f ? o / sum[j] : 0.f);
@@ -199,7 +257,7 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
       // the loop above left mx[], sum[] identical in every thread
       float m_t = 0.f, s_t = 0.f;
 #pragma unroll
-      for (int j = 0; j < MAX_GROUP; ++j)
+      for (int j = 0; j < GM; ++j)
         if (j == tid) {
           m_t = mx[j];
           s_t = sum[j];
@@ -233,10 +291,37 @@ __global__ void attention_join_kernel(const float* __restrict__ part_o, const fl
   }
 }
 
-template <typename T>
+template <typename T, int GM>
 static size_t span_smem(int D) {
-  return (size_t)(MAX_GROUP * D + MAX_GROUP * SPAN) * sizeof(float) + SPAN * sizeof(long long) +
-         (size_t)128 * Vec<T>::N * MAX_GROUP * sizeof(float);
+  return (size_t)(GM * D + GM * SPAN) * sizeof(float) + SPAN * sizeof(long long) +
+         (size_t)128 * Vec<T>::N * GM * sizeof(float);
+}
+
+template <typename T, int GM>
+static int launch_spans(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int max_pages,
+                        int page_size, const int* req_of_row, const int* positions, float scale, int window, void* out,
+                        float* part_o, float* part_ml, int rows, int Hq, int Hk, int D, int n_spans, int* status,
+                        cudaStream_t stream) {
+  static bool set = false;
+  if (!set) {
+    cudaError_t e = cudaFuncSetAttribute(attention_span_kernel<T, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)span_smem<T, GM>(MAX_D));
+    if (e != cudaSuccess) return (int)e;
+    set = true;
+  }
+  dim3 grid(rows, Hk, n_spans);
+  attention_span_kernel<T, GM><<<grid, 128, span_smem<T, GM>(D), stream>>>(
+      (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, max_pages, page_size, req_of_row, positions, scale,
+      window, part_o, part_ml, (T*)out, Hq, Hk, D, n_spans, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  if (n_spans > 1) {
+    dim3 join(rows, Hq);
+    attention_join_kernel<T><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (T*)out, Hq, D,
+                                                                    n_spans);
+    e = cudaGetLastError();
+  }
+  return (int)e;
 }
 
 }  // namespace tl
@@ -264,36 +349,10 @@ extern "C" int tl_paged_attention_split(const void* q, const void* k_cache, cons
   TL_REQUIRE(scratch != nullptr, "paged_attention: no scratch memory given");
   float* part_o = scratch;
   float* part_ml = scratch + (long long)rows * Hq * n_spans * D;
-  dim3 grid(rows, Hk, n_spans), join(rows, Hq);
-  if (dtype == TL_FP32) {
-    const size_t smem = span_smem<float>(D);
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(attention_span_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)span_smem<float>(MAX_D));
-      set = true;
-    }
-    attention_span_kernel<float><<<grid, 128, smem, stream>>>(
-        (const float*)q, (const float*)k_cache, (const float*)v_cache, block_table, max_pages, page_size, req_of_row,
-        positions, scale, window, part_o, part_ml, (float*)out, Hq, Hk, D, n_spans, status);
-    TL_LAUNCH_CHECK();
-    if (n_spans > 1)
-      attention_join_kernel<float><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (float*)out,
-                                                                          Hq, D, n_spans);
-  } else {
-    const size_t smem = span_smem<bf16>(D);
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(attention_span_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)span_smem<bf16>(MAX_D));
-      set = true;
-    }
-    attention_span_kernel<bf16><<<grid, 128, smem, stream>>>(
-        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size, req_of_row,
-        positions, scale, window, part_o, part_ml, (bf16*)out, Hq, Hk, D, n_spans, status);
-    TL_LAUNCH_CHECK();
-    if (n_spans > 1)
-      attention_join_kernel<bf16><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (bf16*)out, Hq,
-                                                                         D, n_spans);
-  }
-  TL_LAUNCH_CHECK();
-  return 0;
+  const bool small = Hq / Hk <= 4;
+#define TL_SPANS(T, GM) launch_spans<T, GM>(q, k_cache, v_cache, block_table, max_pages, page_size, req_of_row, positions, \
+                                            scale, window, out, part_o, part_ml, rows, Hq, Hk, D, n_spans, status, stream)
+  if (dtype == TL_FP32) return small ? TL_SPANS(float, 4) : TL_SPANS(float, 8);
+  return small ? TL_SPANS(bf16, 4) : TL_SPANS(bf16, 8);
+#undef TL_SPANS
 }

@@ -7,95 +7,22 @@
 //   out[r] = sum over the row's experts in ascending expert id of w * expert(x[r])    ref.py:207-214
 //
 // The plan is a stable counting sort: pairs keep their row order inside an expert, so the order of every
-// sum is fixed by the inputs alone (no atomics).
-#include "common.cuh"
+// sum is fixed by the inputs alone (no atomics). Two forms build the same plan: three small kernels for any
+// number of pairs, and one kernel for up to 4096 pairs (a decode step) that also copies the token rows into
+// expert-sorted order for the tensor-core kernels.
+#include "route.cuh"
 
 namespace tl {
-
-constexpr int MAX_EXPERTS = 1024;
-constexpr int MAX_TOP_K = 32;
 
 // one warp per row
 __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, long long ld,
                                                           const float* __restrict__ bias, int rows, int E, int k,
                                                           int normalize, float floor_, float scale,
                                                           int* __restrict__ ids, float* __restrict__ wts) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (warp >= rows) return;
-  const float* lg = logits + (long long)warp * ld;
-  constexpr int PER = MAX_EXPERTS / 32;
-  float score[PER], choice[PER];
-#pragma unroll
-  for (int t = 0; t < PER; ++t) {
-    const int e = lane + 32 * t;
-    if (e < E) {
-      const float s = 1.f / (1.f + expf(-lg[e]));
-      score[t] = s;
-      choice[t] = bias ? s + bias[e] : s;
-      if (!(choice[t] == choice[t])) choice[t] = -INFINITY;   // a NaN score is never chosen before a number
-    } else {
-      score[t] = 0.f;
-      choice[t] = -INFINITY;
-    }
-  }
-  float sum = 0.f, my_w = 0.f;
-  int my_id = 0;
-  for (int j = 0; j < k; ++j) {
-    float best = -INFINITY;
-    int best_e = 0x7fffffff;
-    float best_s = 0.f;
-#pragma unroll
-    for (int t = 0; t < PER; ++t) {
-      const int e = lane + 32 * t;
-      if (e < E && choice[t] != -INFINITY && (choice[t] > best || (choice[t] == best && e < best_e))) {
-        best = choice[t];
-        best_e = e;
-        best_s = score[t];
-      }
-    }
-    // when everything left is -inf (only with NaN scores) fall back to the lowest untaken id
-    if (best_e == 0x7fffffff) {
-#pragma unroll
-      for (int t = 0; t < PER; ++t) {
-        const int e = lane + 32 * t;
-        if (e < E && score[t] != -1.f && e < best_e) {
-          best_e = e;
-          best_s = score[t];
-        }
-      }
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
-      if (ob > best || (ob == best && oe < best_e)) {
-        best = ob;
-        best_e = oe;
-        best_s = os;
-      }
-    }
-    // the owner retires the winner
-    if ((best_e & 31) == lane) {
-#pragma unroll
-      for (int t = 0; t < PER; ++t)
-        if (lane + 32 * t == best_e) {
-          choice[t] = -INFINITY;
-          score[t] = -1.f;
-        }
-    }
-    sum += best_s;
-    if (lane == j) {
-      my_id = best_e;
-      my_w = best_s;
-    }
-  }
-  if (lane < k) {
-    float w = my_w;
-    if (normalize) w = w / (sum + floor_);
-    ids[(long long)warp * k + lane] = my_id;
-    wts[(long long)warp * k + lane] = w * scale;
-  }
+  warp_route(logits + (long long)warp * ld, bias, E, k, normalize, floor_, scale, ids + (long long)warp * k,
+             wts + (long long)warp * k);
 }
 
 // grid E: block e counts the pairs routed to expert e
@@ -162,6 +89,63 @@ __global__ void __launch_bounds__(256) moe_place_kernel(const int* __restrict__ 
   }
 }
 
+constexpr int SMALL_PLAN_PAIRS = 4096;
+
+// grid P (one block per pair), 128 threads: block p finds where pair p lands in the expert-sorted order (pairs of
+// lower experts first, then earlier pairs of its own expert), records it, and copies the pair's token row there.
+// Block 0 also writes the counts, offsets and row tiles.
+__global__ void __launch_bounds__(128) moe_plan_small_kernel(const int* __restrict__ ids, int P, int E, int tile_m, int top_k,
+                                                             int* __restrict__ counts, int* __restrict__ offsets,
+                                                             int* __restrict__ sorted_pairs, int* __restrict__ pos_of_pair,
+                                                             int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                                                             int* __restrict__ tile_rows, int* __restrict__ n_tiles,
+                                                             const bf16* __restrict__ x, long long ldx,
+                                                             bf16* __restrict__ x_sorted, int width) {
+  __shared__ int s_ids[SMALL_PLAN_PAIRS];
+  __shared__ float scratch[33];
+  __shared__ int s_counts[MAX_EXPERTS];
+  const int p = blockIdx.x, tid = threadIdx.x;
+  for (int i = tid; i < P; i += 128) s_ids[i] = ids[i];
+  __syncthreads();
+  const int e = s_ids[p];
+  int n = 0;
+  for (int i = tid; i < P; i += 128) n += (s_ids[i] < e) || (s_ids[i] == e && i < p);
+  const int at = (int)(block_sum((float)n, scratch) + 0.5f);
+  if (tid == 0) {
+    sorted_pairs[at] = p;
+    pos_of_pair[p] = at;
+  }
+  if (x) {
+    const uint4* src = (const uint4*)(x + (long long)(p / top_k) * ldx);
+    uint4* dst = (uint4*)(x_sorted + (long long)at * width);
+    for (int c = tid; c < width / 8; c += 128) dst[c] = src[c];
+  }
+  if (p != 0) return;
+  for (int ex = tid; ex < E; ex += 128) {
+    int cnt = 0;
+    for (int i = 0; i < P; ++i) cnt += s_ids[i] == ex;
+    s_counts[ex] = cnt;
+    counts[ex] = cnt;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int off = 0, tiles = 0;
+    for (int ex = 0; ex < E; ++ex) {
+      offsets[ex] = off;
+      const int cnt = s_counts[ex];
+      for (int t = 0; t * tile_m < cnt; ++t) {
+        tile_group[tiles] = ex;
+        tile_row0[tiles] = off + t * tile_m;
+        tile_rows[tiles] = min(tile_m, cnt - t * tile_m);
+        ++tiles;
+      }
+      off += cnt;
+    }
+    offsets[E] = off;
+    *n_tiles = tiles;
+  }
+}
+
 // one block per row: out[r, :] = sum over the row's slots in ascending expert id of wts * y[pos_of_pair]  (32-bit)
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                                           const int* __restrict__ ids, const float* __restrict__ wts,
@@ -216,16 +200,31 @@ extern "C" int tl_moe_max_tiles(int pairs, int E, int tile_m) {
   return by_rows < pairs ? by_rows : (pairs > 0 ? pairs : 1);
 }
 
-extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int* counts, int* offsets, int* sorted_pairs,
-                           int* pos_of_pair, int* tile_group, int* tile_row0, int* tile_rows, int* n_tiles,
+// Builds the plan of `pairs` (row, slot) pairs. With `x` (bfloat16 rows [pairs / top_k, width], stride ldx) it also
+// writes x_sorted[i] = x[sorted_pairs[i] / top_k]. Returns the number of kernels it launched through *launched.
+extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int top_k, int* counts, int* offsets,
+                           int* sorted_pairs, int* pos_of_pair, int* tile_group, int* tile_row0, int* tile_rows,
+                           int* n_tiles, const void* x, long long ldx, void* x_sorted, int width, int* launched,
                            cudaStream_t stream) {
-  TL_REQUIRE(E > 0 && E <= 65535 && tile_m > 0, "moe plan: %d experts, tile of %d rows", E, tile_m);
+  TL_REQUIRE(E > 0 && E <= 65535 && tile_m > 0 && top_k > 0, "moe plan: %d experts, tile of %d rows, top-%d", E, tile_m, top_k);
   TL_REQUIRE(pairs >= 0 && pairs < (1 << 24), "moe plan: %d pairs; fewer than 2^24 are implemented", pairs);
+  TL_REQUIRE(!x || (width % 8 == 0 && ldx % 8 == 0 && x_sorted), "moe plan: row copy of width %d, stride %lld", width, ldx);
+  if (launched) *launched = 0;
+  if (pairs == 0) return 0;
+  if (pairs <= SMALL_PLAN_PAIRS && E <= MAX_EXPERTS) {
+    moe_plan_small_kernel<<<pairs, 128, 0, stream>>>(ids, pairs, E, tile_m, top_k, counts, offsets, sorted_pairs, pos_of_pair,
+                                                     tile_group, tile_row0, tile_rows, n_tiles, (const bf16*)x, ldx,
+                                                     (bf16*)x_sorted, width);
+    TL_LAUNCH_CHECK();
+    if (launched) *launched = 1;
+    return 0;
+  }
   moe_count_kernel<<<E, 256, 0, stream>>>(ids, pairs, counts);
   TL_LAUNCH_CHECK();
   moe_place_kernel<<<E, 256, 0, stream>>>(ids, pairs, E, tile_m, counts, offsets, sorted_pairs, pos_of_pair, tile_group,
                                           tile_row0, tile_rows, n_tiles);
   TL_LAUNCH_CHECK();
+  if (launched) *launched = 2;
   return 0;
 }
 

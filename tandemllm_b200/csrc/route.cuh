@@ -1,0 +1,92 @@
+// The router's choice for one row, run by one full warp: sigmoid scores, the top-k of score + bias (the bias for
+// the choice only), weights = chosen scores, divided by (their sum + floor) when normalised, times scale.
+// Ties go to the lower expert id; a NaN score is chosen only when nothing else is left.
+// (engine/models/lfm2_moe/ref.py:185-197, engine/models/lfm2_moe/kernels.py:265-287 of the reference)
+#pragma once
+
+#include "common.cuh"
+
+namespace tl {
+
+constexpr int MAX_EXPERTS = 1024;
+constexpr int MAX_TOP_K = 32;
+
+// `lg`: the row's E logits (global or shared memory). Lanes 0..k-1 write ids[lane] and wts[lane], in the order
+// of the choice (best first).
+__device__ __forceinline__ void warp_route(const float* lg, const float* __restrict__ bias, int E, int k, int normalize,
+                                           float floor_, float scale, int* ids, float* wts) {
+  const int lane = threadIdx.x & 31;
+  constexpr int PER = MAX_EXPERTS / 32;
+  float score[PER], choice[PER];
+#pragma unroll
+  for (int t = 0; t < PER; ++t) {
+    const int e = lane + 32 * t;
+    if (e < E) {
+      const float s = 1.f / (1.f + expf(-lg[e]));
+      score[t] = s;
+      choice[t] = bias ? s + bias[e] : s;
+      if (!(choice[t] == choice[t])) choice[t] = -INFINITY;
+    } else {
+      score[t] = 0.f;
+      choice[t] = -INFINITY;
+    }
+  }
+  float sum = 0.f, my_w = 0.f;
+  int my_id = 0;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    float best_s = 0.f;
+#pragma unroll
+    for (int t = 0; t < PER; ++t) {
+      const int e = lane + 32 * t;
+      if (e < E && choice[t] != -INFINITY && (choice[t] > best || (choice[t] == best && e < best_e))) {
+        best = choice[t];
+        best_e = e;
+        best_s = score[t];
+      }
+    }
+    if (best_e == 0x7fffffff) {     // nothing but -inf left in this lane: offer its lowest untaken id
+#pragma unroll
+      for (int t = 0; t < PER; ++t) {
+        const int e = lane + 32 * t;
+        if (e < E && score[t] != -1.f && e < best_e) {
+          best_e = e;
+          best_s = score[t];
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+        best_s = os;
+      }
+    }
+    if ((best_e & 31) == lane) {    // the owner retires the winner
+#pragma unroll
+      for (int t = 0; t < PER; ++t)
+        if (lane + 32 * t == best_e) {
+          choice[t] = -INFINITY;
+          score[t] = -1.f;
+        }
+    }
+    sum += best_s;
+    if (lane == j) {
+      my_id = best_e;
+      my_w = best_s;
+    }
+  }
+  if (lane < k) {
+    float w = my_w;
+    if (normalize) w = w / (sum + floor_);
+    ids[lane] = my_id;
+    wts[lane] = w * scale;
+  }
+}
+
+}  // namespace tl

@@ -1,10 +1,11 @@
-// Row-wise kernels: embedding gather, residual add fused with RMS norm, SwiGLU gating, and the last
-// error message of the library.
+// Row-wise kernels: embedding gather, residual add fused with RMS norm (and, for the rows of an expert layer, with
+// the router), SwiGLU gating, and the last error message of the library.
 //
 // The residual stream is 32-bit in both precisions; norms compute mean(x^2), rsqrt and the scale in
 // 32-bit and round once to the compute type. Formulas: engine/models/lfm2_moe/ref.py:105-109 (norm),
-// :230 (embedding), :180-183 (SwiGLU) of the reference.
-#include "common.cuh"
+// :230 (embedding), :180-183 (SwiGLU), :185-197 (router) of the reference, which fuses the add and the norm too
+// (`add_rms`, engine/models/lfm2_moe/kernels.py:90-107).
+#include "route.cuh"
 
 extern "C" const char* tl_last_error() { return tl_error_text; }
 
@@ -27,39 +28,119 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]);
 }
 
-// One block per output row. The branch output `delta` is 32-bit in both precisions.
-//   gather == nullptr: row r:  residual[r] += delta[r] (when delta);  normed[r] = w * residual[r] * rsqrt(mean + eps)
-//   gather != nullptr: output row i reads row gather[i]: x = residual[g] + delta[g]; normed[i] = norm(x);
-//                      the residual is left as it is (used for the final norm at the wanted rows only)
-// normed32 (optional) receives the same normalised row unrounded, for consumers that compute in 32-bit (the router).
+// What is added to the residual before the norm. The previous branch's output comes in one of three forms, so
+// that the kernel which would only have summed it can be left out:
+//   delta, parts = 1          a plain 32-bit tensor [rows, hidden]
+//   delta, parts = S          S partial sums [S, rows, hidden] of a product split along k, added in order 0..S-1
+//   expert_rows               the rows a routed expert layer computed, [pairs, hidden] in expert-sorted order:
+//                             row r adds sum_j wts[r, j] * expert_rows[pos_of_pair[r k + j]] over its slots in
+//                             ascending expert id (engine/models/lfm2_moe/ref.py:207-214)
+struct NormParams {
+  float* residual;
+  const float* delta;
+  int parts;
+  long long part_stride;
+  const float* expert_rows;
+  const int* pos_of_pair;
+  const int* ids;
+  const float* wts;
+  int top_k;
+  const float* weight;
+  float eps;
+  void* normed;
+  float* normed32;
+  const int* gather;
+  int hidden;
+  // the router of the layer that reads the normed rows (optional)
+  const float* router_w;     // [E, hidden] 32-bit
+  const float* router_bias;  // [E] or nullptr
+  int E, route_k, normalize;
+  float floor_, scale;
+  int* route_ids;            // [rows, route_k]
+  float* route_wts;
+};
+
+// One block per output row.
+//   gather == nullptr: row r:  residual[r] += added[r];  normed[r] = w * residual[r] * rsqrt(mean + eps)
+//   gather != nullptr: output row i reads row gather[i] and leaves the residual as it is (the final norm of the
+//                      wanted rows only)
+// normed32 (optional) receives the normalised row unrounded. With a router, the row's logits are computed from
+// the unrounded row in 32-bit, and the choice and weights are written as well.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta,
-                                   const float* __restrict__ weight, T* __restrict__ normed,
-                                   float* __restrict__ normed32, const int* __restrict__ gather, int hidden, float eps) {
-  extern __shared__ float row[];       // hidden floats, then 33 for the reduction
-  float* scratch = row + hidden;
+__global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
+  extern __shared__ float row[];       // hidden floats, 33 for the reduction, then E logits
+  float* scratch = row + p.hidden;
+  float* logits = scratch + 33;
+  __shared__ int s_src[MAX_TOP_K];
+  __shared__ float s_w[MAX_TOP_K];
   const int out_r = blockIdx.x;
-  const int r = gather ? gather[out_r] : out_r;
-  float* res = residual + (size_t)r * hidden;
-  const float* del = delta ? delta + (size_t)r * hidden : nullptr;
+  const int r = p.gather ? p.gather[out_r] : out_r;
+  const int hidden = p.hidden;
+  if (p.expert_rows) {
+    if (threadIdx.x == 0) {
+      const int k = p.top_k;
+      int order[MAX_TOP_K];
+      for (int j = 0; j < k; ++j) {     // insertion sort of the slots by expert id (slot index breaks ties)
+        int i = j;
+        const int e = p.ids[(long long)r * k + j];
+        while (i > 0 && p.ids[(long long)r * k + order[i - 1]] > e) {
+          order[i] = order[i - 1];
+          --i;
+        }
+        order[i] = j;
+      }
+      for (int j = 0; j < k; ++j) {
+        s_src[j] = p.pos_of_pair[(long long)r * k + order[j]];
+        s_w[j] = p.wts[(long long)r * k + order[j]];
+      }
+    }
+    __syncthreads();
+  }
+  float* res = p.residual + (size_t)r * hidden;
+  const bool adds = p.delta || p.expert_rows;
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float x = res[c];
-    if (del) x += del[c];
+    if (p.delta) {
+      float d = 0.f;
+      for (int s = 0; s < p.parts; ++s) d += p.delta[(long long)s * p.part_stride + (size_t)r * hidden + c];
+      x += d;
+    }
+    if (p.expert_rows) {
+      float d = 0.f;
+      for (int j = 0; j < p.top_k; ++j) d = fmaf(s_w[j], p.expert_rows[(long long)s_src[j] * hidden + c], d);
+      x += d;
+    }
     row[c] = x;
     ss += x * x;
   }
   ss = block_sum(ss, scratch);
-  const float inv = rsqrtf(ss / (float)hidden + eps);
-  T* out = normed + (size_t)out_r * hidden;
-  float* out32 = normed32 ? normed32 + (size_t)out_r * hidden : nullptr;
+  const float inv = rsqrtf(ss / (float)hidden + p.eps);
+  T* out = (T*)p.normed + (size_t)out_r * hidden;
+  float* out32 = p.normed32 ? p.normed32 + (size_t)out_r * hidden : nullptr;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     const float x = row[c];
-    if (!gather && del) res[c] = x;
-    const float y = weight[c] * (x * inv);
+    if (!p.gather && adds) res[c] = x;
+    const float y = p.weight[c] * (x * inv);
     out[c] = from_f32<T>(y);
     if (out32) out32[c] = y;
+    row[c] = y;
   }
+  if (!p.router_w) return;
+  __syncthreads();
+  // logits[e] = row . router_w[e]: each warp takes experts warp, warp + nwarps, ...; lanes stride over the row
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < p.E; e += nwarps) {
+    const float* w = p.router_w + (size_t)e * hidden;
+    float acc = 0.f;
+    for (int c = lane; c < hidden; c += 32) acc = fmaf(row[c], w[c], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) logits[e] = acc;
+  }
+  __syncthreads();
+  if (warp == 0)
+    warp_route(logits, p.router_bias, p.E, p.route_k, p.normalize, p.floor_, p.scale,
+               p.route_ids + (size_t)out_r * p.route_k, p.route_wts + (size_t)out_r * p.route_k);
 }
 
 // out[r, i] = silu(gate_up[r, i]) * gate_up[r, inter + i]
@@ -92,24 +173,41 @@ extern "C" int tl_embed_rows(const void* table, const int* tokens, float* residu
   return 0;
 }
 
-extern "C" int tl_add_rmsnorm(float* residual, const float* delta, const float* weight, void* normed, float* normed32,
-                              const int* gather, int out_rows, int hidden, float eps, int dtype, cudaStream_t stream) {
+// See NormParams for the forms of what is added. Null pointers switch a form or the router off.
+extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, long long part_stride,
+                              const float* expert_rows, const int* pos_of_pair, const int* ids, const float* wts, int top_k,
+                              const float* weight, void* normed, float* normed32, const int* gather, int out_rows,
+                              int hidden, float eps, int dtype, const float* router_w, const float* router_bias, int E,
+                              int route_k, int normalize, float floor_, float scale, int* route_ids, float* route_wts,
+                              cudaStream_t stream) {
   if (out_rows == 0) return 0;
   TL_REQUIRE(out_rows > 0 && hidden > 0, "add_rmsnorm: rows %d hidden %d", out_rows, hidden);
-  const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  TL_REQUIRE(!delta || parts >= 1, "add_rmsnorm: %d parts", parts);
+  TL_REQUIRE(!expert_rows || (top_k > 0 && top_k <= MAX_TOP_K && pos_of_pair && ids && wts),
+             "add_rmsnorm: expert rows with top-%d", top_k);
+  if (router_w) {
+    TL_REQUIRE(E > 0 && E <= MAX_EXPERTS, "router: %d experts; up to %d are implemented", E, MAX_EXPERTS);
+    TL_REQUIRE(route_k > 0 && route_k <= E && route_k <= MAX_TOP_K && route_ids && route_wts,
+               "router: top-%d of %d experts; up to top-%d is implemented", route_k, E, MAX_TOP_K);
+  }
+  const size_t smem = (size_t)(hidden + 33 + (router_w ? E : 0)) * sizeof(float);
   TL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory, the limit is 204800",
              hidden, smem);
+  NormParams p = {};
+  p.residual = residual; p.delta = delta; p.parts = parts; p.part_stride = part_stride; p.expert_rows = expert_rows;
+  p.pos_of_pair = pos_of_pair; p.ids = ids; p.wts = wts; p.top_k = top_k; p.weight = weight; p.eps = eps;
+  p.normed = normed; p.normed32 = normed32; p.gather = gather; p.hidden = hidden; p.router_w = router_w;
+  p.router_bias = router_bias; p.E = E; p.route_k = route_k; p.normalize = normalize; p.floor_ = floor_; p.scale = scale;
+  p.route_ids = route_ids; p.route_wts = route_wts;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (dtype == TL_FP32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<float><<<out_rows, threads, smem, stream>>>(residual, delta, weight, (float*)normed, normed32,
-                                                                  gather, hidden, eps);
+    add_rmsnorm_kernel<float><<<out_rows, threads, smem, stream>>>(p);
   } else {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<bf16><<<out_rows, threads, smem, stream>>>(residual, delta, weight, (bf16*)normed, normed32,
-                                                                 gather, hidden, eps);
+    add_rmsnorm_kernel<bf16><<<out_rows, threads, smem, stream>>>(p);
   }
   TL_LAUNCH_CHECK();
   return 0;

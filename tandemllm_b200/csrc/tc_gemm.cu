@@ -452,7 +452,7 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
                           long long rows_per_group, const float* bias, void* C, long long ldc, int M, int N, int K, int swap,
                           int bn, int swiglu, int out_dtype, const int* tile_group, const int* tile_row0,
                           const int* tile_rows, const int* n_tiles, int max_tiles, int splits, float* partial,
-                          int* status, cudaStream_t stream) {
+                          int reduce, int* status, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   TL_REQUIRE(M > 0 && N > 0 && K > 0, "tensor-core gemm: M %d N %d K %d", M, N, K);
   TL_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
@@ -489,7 +489,7 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
                                   : launch_bn<false, false, float>(bn, tmW, tmX, p, grid, stream);
   }
   if (e) return e;
-  if (splits > 1) {
+  if (splits > 1 && reduce) {     // without `reduce` the caller adds the partial sums itself (fused into its next kernel)
     const long long total = (long long)M * N;
     const int blocks = (int)(ceil_div64(total, 256) < 1184 ? ceil_div64(total, 256) : 1184);
     if (out_dtype == TL_BF16)

@@ -32,8 +32,9 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 _SIGNATURES = {
     "tl_embed_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "tl_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int,
-                       c_void_p],
+    "tl_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                       c_float, c_float, c_void_p, c_void_p, c_void_p],
     "tl_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_gemm_simt": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
                      c_int, c_int, c_void_p],
@@ -57,8 +58,8 @@ _SIGNATURES = {
     "tl_router_topk": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p,
                        c_void_p],
     "tl_moe_max_tiles": [c_int, c_int, c_int],
-    "tl_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                    c_void_p, c_void_p],
+    "tl_moe_plan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                    c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -123,20 +124,67 @@ def embed_rows(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor
                                dtype_code(table.dtype), ptr(status), stream()), "embed_rows")
 
 
-def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
-                out: torch.Tensor, gather: torch.Tensor | None = None, out32: torch.Tensor | None = None) -> torch.Tensor:
-    """residual += delta (32-bit); out = weight * rms_normalised(residual). With `gather` (int32 row indices) the
-    output row i is computed from row gather[i] and the residual is left unchanged. `out32` also receives the
-    normalised rows unrounded."""
+class PartialSums:
+    """A branch output still in `parts` partial sums [parts, rows, hidden] (32-bit), to be added in order."""
+
+    def __init__(self, data: torch.Tensor, parts: int, rows: int, hidden: int):
+        self.data, self.parts, self.rows, self.hidden = data, parts, rows, hidden
+
+    def materialize(self) -> torch.Tensor:
+        return self.data[:self.parts * self.rows * self.hidden].view(self.parts, self.rows, self.hidden).sum(0)
+
+
+class ExpertRows:
+    """A routed expert layer's output still as one row per (row, slot) pair in expert-sorted order [pairs, hidden]
+    (32-bit), with what is needed to weigh and add them per row."""
+
+    def __init__(self, rows: torch.Tensor, pos_of_pair: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor):
+        self.rows, self.pos_of_pair, self.ids, self.wts = rows, pos_of_pair, ids, wts
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.empty(self.ids.shape[0], self.rows.shape[1], dtype=torch.float32, device=self.rows.device)
+        check(core().tl_moe_combine(ptr(self.rows), ptr(self.pos_of_pair), ptr(self.ids), ptr(self.wts), ptr(out),
+                                    out.shape[0], out.shape[1], self.ids.shape[1], stream()), "moe_combine")
+        return out
+
+
+def materialize(branch):
+    """A branch output as a plain tensor, whatever form a part returned it in."""
+    return branch.materialize() if isinstance(branch, (PartialSums, ExpertRows)) else branch
+
+
+def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                gather: torch.Tensor | None = None, out32: torch.Tensor | None = None, route: dict | None = None
+                ) -> torch.Tensor:
+    """residual += delta (32-bit); out = weight * rms_normalised(residual). `delta` is None, a float32 tensor, a
+    `PartialSums` or an `ExpertRows`. With `gather` (int32 row indices) the output row i is computed from row
+    gather[i] and the residual is left unchanged. `out32` also receives the normalised rows unrounded. `route`
+    (router weights float32 [E, hidden], bias, k, normalize, floor, scale, ids, wts) also runs the router on the
+    unrounded rows and fills ids int32 [rows, k] and wts float32 [rows, k]."""
     _need(residual, torch.float32, "residual"); _need(weight, torch.float32, "norm weight"); _need(out, None, "normed")
-    if delta is not None:
-        _need(delta, torch.float32, "delta")
     if out32 is not None:
         _need(out32, torch.float32, "normed32")
+    dense = parts = stride = 0
+    rows_ptr = pos = ids = wts = None
+    top_k = 0
+    if isinstance(delta, PartialSums):
+        dense, parts, stride = delta.data.data_ptr(), delta.parts, delta.rows * delta.hidden
+    elif isinstance(delta, ExpertRows):
+        rows_ptr, pos, ids, wts, top_k = delta.rows, delta.pos_of_pair, delta.ids, delta.wts, delta.ids.shape[1]
+    elif delta is not None:
+        _need(delta, torch.float32, "delta")
+        dense, parts = delta.data_ptr(), 1
     hidden = residual.shape[-1]
     n_out = out.shape[0]
-    check(core().tl_add_rmsnorm(ptr(residual), ptr(delta), ptr(weight), ptr(out), ptr(out32), ptr(gather), n_out,
-                                hidden, float(eps), dtype_code(out.dtype), stream()), "add_rmsnorm")
+    r = route or {}
+    if route:
+        _need(r["weight"], torch.float32, "router weight"); _need(r["ids"], torch.int32, "ids"); _need(r["wts"], torch.float32, "wts")
+    check(core().tl_add_rmsnorm(
+        ptr(residual), dense or None, parts, stride, ptr(rows_ptr), ptr(pos), ptr(ids), ptr(wts), top_k, ptr(weight),
+        ptr(out), ptr(out32), ptr(gather), n_out, hidden, float(eps), dtype_code(out.dtype), ptr(r.get("weight")),
+        ptr(r.get("bias")), r["weight"].shape[0] if route else 0, int(r.get("k", 0)), int(r.get("normalize", 0)),
+        float(r.get("floor", 0.0)), float(r.get("scale", 1.0)), ptr(r.get("ids")), ptr(r.get("wts")), stream()),
+        "add_rmsnorm")
     return out
 
 
@@ -281,16 +329,24 @@ class MoePlan:
         self.pairs = 0
         self.max_tiles = 1
 
-    def build(self, ids: torch.Tensor) -> "MoePlan":
+    def build(self, ids: torch.Tensor, x: torch.Tensor | None = None, x_sorted: torch.Tensor | None = None) -> "MoePlan":
+        """Build the plan for `ids` [rows, k]. With `x` [rows, width] (bfloat16) and `x_sorted` [pairs, width], the
+        token rows are copied into expert-sorted order as well when the one-kernel form applies; `self.copied`
+        says whether they were."""
         pairs = ids.numel()
         if pairs > self.max_pairs:
             raise KernelError(f"routing plan sized for {self.max_pairs} pairs, got {pairs}")
         self.pairs = pairs
         self.max_tiles = core().tl_moe_max_tiles(pairs, self.num_experts, self.tile_m)
-        check(core().tl_moe_plan(ptr(ids), pairs, self.num_experts, self.tile_m, ptr(self.counts), ptr(self.offsets),
-                                 ptr(self.sorted_pairs), ptr(self.pos_of_pair), ptr(self.tile_group),
-                                 ptr(self.tile_row0), ptr(self.tile_rows), ptr(self.n_tiles), stream()), "moe_plan",
-              kernels=2)
+        launched = ctypes.c_int(0)
+        check(core().tl_moe_plan(ptr(ids), pairs, self.num_experts, self.tile_m, ids.shape[-1], ptr(self.counts),
+                                 ptr(self.offsets), ptr(self.sorted_pairs), ptr(self.pos_of_pair), ptr(self.tile_group),
+                                 ptr(self.tile_row0), ptr(self.tile_rows), ptr(self.n_tiles), ptr(x),
+                                 x.stride(0) if x is not None else 0, ptr(x_sorted), x.shape[1] if x is not None else 0,
+                                 ctypes.addressof(launched), stream()), "moe_plan", kernels=0)
+        global launches
+        launches += launched.value
+        self.copied = x is not None and launched.value == 1
         return self
 
 

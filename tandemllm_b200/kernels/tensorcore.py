@@ -1,16 +1,19 @@
-"""The bfloat16 path's tensor-core kernels (tcgen05 + TMA, `csrc/tc_gemm.cu`): when enabled, `parts.linear` and
-the expert feed-forward send their products here.
+"""The bfloat16 path's tensor-core kernels (tcgen05 + TMA, `csrc/tc_gemm.cu`): when a runtime has them,
+`parts.linear` and the expert feed-forward send their products here.
 
 Choice of kernel by shape:
   up to 128 token rows   the swapped orientation: 128 weight rows on the MMA's M side, the tokens (padded to 16,
                          32, 64 or 128) on its N side, so a decode step streams every weight once. When a product
                          would launch fewer CTAs than the GPU has SMs, its k range is split over several CTAs that
-                         write 32-bit partial sums to a workspace, reduced in a fixed order by a second kernel.
+                         write 32-bit partial sums to a workspace; they are added in a fixed order by a second
+                         kernel, or, for a branch's last product, by the norm kernel that consumes the branch
+                         (`ops.PartialSums`).
   more rows              128 token rows on the M side, 128 weight rows on the N side.
-Experts: the token rows are copied into expert-sorted order, the plan's tiles carry the expert, gate/up and
-SwiGLU run in one kernel, the down projection writes 32-bit rows that the combine kernel weighs and adds.
+Experts: the token rows are copied into expert-sorted order (by the plan kernel itself for a decode step), the
+plan's tiles carry the expert, gate/up and SwiGLU run in one kernel, the down projection writes 32-bit rows that
+the next norm kernel weighs and adds (`ops.ExpertRows`).
 Anything the kernels do not take (k or a row stride not a multiple of 8 elements, as TMA needs 16-byte strides)
-goes back to the CUDA-core kernels by returning False.
+goes back to the CUDA-core kernels by returning None.
 """
 
 from __future__ import annotations
@@ -25,7 +28,6 @@ from .build import load
 
 SM_COUNT = 148
 _lib = None
-_impl = None
 
 
 def lib():
@@ -34,7 +36,7 @@ def lib():
         l = load("tensorcore")
         l.tl_gemm_tc.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p,
                                  c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                 c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]
+                                 c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
         l.tl_gemm_tc.restype = c_int
         l.tl_gather_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         l.tl_gather_rows.restype = c_int
@@ -79,7 +81,10 @@ class TensorCore:
         return self._workspace
 
     # ---- x @ w^T (+ bias) ----
-    def gemm(self, x, w2d, bias, out, *, rows_per_group=0, plan=None, swiglu=False, swap=None, bn=None, n_out=None):
+    def gemm(self, x, w2d, bias, out, *, rows_per_group=0, plan=None, swiglu=False, swap=None, bn=None, n_out=None,
+             defer: bool = False):
+        """Runs the product into `out`. With `defer`, a product that was split along k is left as partial sums and
+        returned as `ops.PartialSums` (nothing is written to `out`); otherwise returns None."""
         M, K = x.shape
         N = n_out if n_out is not None else w2d.shape[0]
         if swap is None:
@@ -94,6 +99,7 @@ class TensorCore:
                 splits = max(1, min(kb // 4, -(-SM_COUNT // ctas), 16))
                 if splits > 1:
                     partial = self.workspace(splits * M * N)
+        deferred = defer and splits > 1 and out.dtype == torch.float32
         tg = tr0 = trs = nt = None
         max_tiles = 0
         if plan is not None:
@@ -101,41 +107,44 @@ class TensorCore:
         code = lib().tl_gemm_tc(
             x.data_ptr(), x.stride(0), x.shape[0], w2d.data_ptr(), w2d.stride(0), w2d.shape[0], rows_per_group,
             ops.ptr(bias), out.data_ptr(), out.stride(0), M, N, K, int(swap), bn, int(swiglu), ops.dtype_code(out.dtype),
-            ops.ptr(tg), ops.ptr(tr0), ops.ptr(trs), ops.ptr(nt), max_tiles, splits, ops.ptr(partial),
+            ops.ptr(tg), ops.ptr(tr0), ops.ptr(trs), ops.ptr(nt), max_tiles, splits, ops.ptr(partial), int(not deferred),
             self.status.data_ptr(), ops.stream())
-        _check(code, "gemm_tc", kernels=2 if splits > 1 else 1)
+        _check(code, "gemm_tc", kernels=2 if splits > 1 and not deferred else 1)
+        return ops.PartialSums(partial, splits, M, N) if deferred else None
 
-    def linear(self, x, w, bias, out) -> bool:
+    def linear(self, x, w, bias, out, defer: bool = False):
+        """False when the kernels do not take these operands; else True, or the deferred partial sums."""
         if not usable(x, w) or out.stride(-1) != 1:
             return False
-        self.gemm(x, w, bias, out)
-        return True
+        return self.gemm(x, w, bias, out, defer=defer) or True
 
     # ---- routed experts ----
-    def experts(self, part, x, ids, wts, out) -> bool:
+    def experts(self, part, x, ids, wts):
+        """The routed experts of `part` on rows x: an `ops.ExpertRows` (to be weighed and added per row), or None
+        when the kernels do not take the shapes."""
         E, I2, H = part.w_gate_up.shape
         inter = I2 // 2
         if not usable(x, part.w_gate_up.view(E * I2, H)) or inter % 8 or not part.w_down.is_contiguous():
-            return False
+            return None
         R, k = ids.shape
         P = R * k
         avg = P / E
         swap = avg <= 48
         bn = 16 if avg <= 12 else 32 if avg <= 24 else 64 if swap else 128
         tile = lib().tl_tc_token_tile(int(swap), bn)
-        plan = part.plan_for(P, x.device, tile).build(ids)
+        xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
+        plan = part.plan_for(P, x.device, tile).build(ids, x, xs)
+        if not plan.copied:
+            _check(lib().tl_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k, xs.data_ptr(), P, H,
+                                        ops.stream()), "gather_rows")
         if part.record_counts:
             part.last_counts = plan.counts.clone()
-        xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
-        _check(lib().tl_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k, xs.data_ptr(), P, H,
-                                    ops.stream()), "gather_rows")
         act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
         self.gemm(xs, part.w_gate_up.view(E * I2, H), None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=swap,
                   bn=bn, n_out=inter)
         y = torch.empty(P, H, dtype=torch.float32, device=x.device)
         self.gemm(act, part.w_down.view(E * H, inter), None, y, rows_per_group=H, plan=plan, swap=swap, bn=bn, n_out=H)
-        ops.moe_combine(y, plan, ids, wts, out)
-        return True
+        return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)
 
 
 def enable(runtime) -> TensorCore:

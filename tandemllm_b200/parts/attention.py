@@ -105,4 +105,4 @@ class AttentionMixer(Part):
             scratch = self.runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans))
             ops.paged_attention_split(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions,
                                       self.scale, self.window, o, scratch, spans, status)
-        return linear(self.runtime, o.view(R, Hq * D), self.w_out, out_dtype=torch.float32)
+        return linear(self.runtime, o.view(R, Hq * D), self.w_out, out_dtype=torch.float32, defer=True)

@@ -43,11 +43,11 @@ class SwiGLU(Part):
                                     runtime.matrix(read(self.n["up"] + ".weight"))]).contiguous()
         self.w_down = runtime.matrix(read(self.n["down"] + ".weight"))
 
-    def forward(self, x, step, x32=None):
+    def forward(self, x, step, x32=None, routing=None):
         gu = linear(self.runtime, x, self.w_gate_up)
         act = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
         ops.silu_mul(gu, act)
-        return linear(self.runtime, act, self.w_down, out_dtype=torch.float32)
+        return linear(self.runtime, act, self.w_down, out_dtype=torch.float32, defer=True)
 
 
 @register_part("feed_forward", "sigmoid_topk_experts")
@@ -110,6 +110,17 @@ class SigmoidTopKExperts(Part):
                 self.w_down[e].copy_(read(f"{self.base}.{e}.{self.n['down']}.weight"))
 
     wants_x32 = True        # the block hands the normed rows unrounded as well: router logits are 32-bit end to end
+    FUSED_ROUTE_ROWS = 64   # up to this many rows, the norm kernel in front of the layer runs the router itself
+
+    def router_args(self, rows: int, device):
+        """What the norm kernel needs to run this layer's router on its `rows` output rows, or None when the
+        router runs on its own (many rows: a tiled product reads the router weights once, not once per row)."""
+        if rows > self.FUSED_ROUTE_ROWS:
+            return None
+        return {"weight": self.w_router, "bias": self.expert_bias, "k": self.top_k, "normalize": self.normalize,
+                "floor": self.norm_floor, "scale": self.scale,
+                "ids": torch.empty(rows, self.top_k, dtype=torch.int32, device=device),
+                "wts": torch.empty(rows, self.top_k, dtype=torch.float32, device=device)}
 
     def route(self, x32):
         """(ids int32 [R, k], weights float32 [R, k]) of the 32-bit rows x32."""
@@ -130,13 +141,17 @@ class SigmoidTopKExperts(Part):
             plan = self._plans[tile_rows] = ops.MoePlan(cap, self.num_experts, tile_rows, device)
         return plan
 
-    def forward(self, x, step, x32=None):
+    def forward(self, x, step, x32=None, routing=None):
+        """The layer's output as `ops.ExpertRows`: one 32-bit row per (row, slot) pair, which the consuming norm
+        kernel weighs and adds in ascending expert id. `routing` = (ids, wts) when the norm in front already ran
+        the router; else it runs here, on `x32` (the unrounded normed rows) where given."""
         R, H = x.shape[0], self.hidden_size
-        ids, wts = self.route(x32 if x32 is not None else x.float())
-        out = torch.empty(R, H, dtype=torch.float32, device=x.device)
+        ids, wts = routing if routing is not None else self.route(x32 if x32 is not None else x.float())
         tc = self.runtime.tensorcore
-        if tc is not None and x.dtype == torch.bfloat16 and tc.experts(self, x, ids, wts, out):
-            return out
+        if tc is not None and x.dtype == torch.bfloat16:
+            rows = tc.experts(self, x, ids, wts)
+            if rows is not None:
+                return rows
         plan = self.plan_for(R * self.top_k, x.device).build(ids)
         if self.record_counts:
             self.last_counts = plan.counts.clone()
@@ -144,4 +159,4 @@ class SigmoidTopKExperts(Part):
         ops.gemm_simt_grouped(x, plan.sorted_pairs, self.top_k, self.w_gate_up, act, plan, swiglu=True)
         y = torch.empty(R * self.top_k, H, dtype=torch.float32, device=x.device)
         ops.gemm_simt_grouped(act, None, 1, self.w_down, y, plan, swiglu=False)
-        return ops.moe_combine(y, plan, ids, wts, out)
+        return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)

@@ -33,18 +33,20 @@ class RMSNorm(Part):
         self.runtime = runtime
         self.weight = runtime.vector(read(self.name))
 
-    def add_norm(self, residual: torch.Tensor, delta: torch.Tensor | None, out: torch.Tensor | None = None,
-                 gather: torch.Tensor | None = None, n_out: int | None = None, want32: bool = False):
-        """residual += delta (both 32-bit); returns the normed rows in the compute dtype, and with `want32` the
-        pair (normed, the same rows unrounded in 32-bit)."""
+    def add_norm(self, residual: torch.Tensor, delta, out: torch.Tensor | None = None,
+                 gather: torch.Tensor | None = None, n_out: int | None = None, want32: bool = False,
+                 route: dict | None = None):
+        """residual += delta (32-bit; a tensor or a branch output in one of the deferred forms of `kernels.ops`);
+        returns the normed rows in the compute dtype, and with `want32` the pair (normed, the same rows unrounded
+        in 32-bit). `route` (see `ops.add_rmsnorm`) also runs a router on the unrounded rows in the same kernel."""
         rows = residual.shape[0] if gather is None else (n_out if n_out is not None else gather.shape[0])
         if out is None:
             out = torch.empty(rows, self.size, dtype=self.runtime.dtype, device=residual.device)
         if not want32:
-            return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather)
+            return ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather, None, route)
         if out.dtype == torch.float32:
-            ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather)
+            ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather, None, route)
             return out, out
         out32 = torch.empty(rows, self.size, dtype=torch.float32, device=residual.device)
-        ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather, out32)
+        ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather, out32, route)
         return out, out32

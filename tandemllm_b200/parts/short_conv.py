@@ -66,4 +66,4 @@ class ShortConvMixer(Part):
         if writes_cache:
             ops.short_conv_state(bcx, cache.state, step.state_slot, step.row_start, step.positions, step.n_requests,
                                  H, self.taps)
-        return linear(self.runtime, y, self.w_out, self.b_out, out_dtype=torch.float32)
+        return linear(self.runtime, y, self.w_out, self.b_out, out_dtype=torch.float32, defer=True)

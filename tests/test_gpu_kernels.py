@@ -71,6 +71,70 @@ def test_embed_and_add_rmsnorm(dtype, hidden):
     assert torch.equal(res, before)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_add_rmsnorm_adds_deferred_branch_outputs_and_routes(dtype):
+    """The forms a branch output may arrive in (partial sums of a split product; the rows of an expert layer with
+    their weights) give what adding the plain tensor gives, and the fused router gives the separate router's choice."""
+    o = ops()
+    R, H, S, E, k = 7, 136, 3, 12, 4
+    res0, w = rnd(R, H, seed=1), 1 + rnd(H, seed=2, scale=0.2)
+    parts = rnd(S, R, H, seed=3)
+    want = P.rms_norm(res0 + parts.sum(0), w, 1e-5)
+    res = res0.clone().to(DEV)
+    out = torch.empty(R, H, dtype=dtype, device=DEV)
+    o.add_rmsnorm(res, o.PartialSums(parts.to(DEV).reshape(-1), S, R, H), w.to(DEV), 1e-5, out)
+    close(out, want, dtype, "partial sums")
+    close(res, res0 + parts.sum(0), torch.float32, "residual after partial sums")
+    # expert rows: each row adds its k slots in ascending expert id
+    ids = torch.stack([torch.randperm(E, generator=torch.Generator().manual_seed(10 + r))[:k] for r in range(R)]).int()
+    wts = torch.rand(R, k, generator=torch.Generator().manual_seed(4))
+    y = rnd(R * k, H, seed=5)
+    pos = torch.randperm(R * k, generator=torch.Generator().manual_seed(6)).int()
+    added = torch.zeros(R, H)
+    for r in range(R):
+        for j in sorted(range(k), key=lambda j: int(ids[r, j])):
+            added[r] += wts[r, j] * y[pos[r * k + j]]
+    res = res0.clone().to(DEV)
+    rows = o.ExpertRows(y.to(DEV), pos.to(DEV), ids.to(DEV), wts.to(DEV))
+    o.add_rmsnorm(res, rows, w.to(DEV), 1e-5, out)
+    close(out, P.rms_norm(res0 + added, w, 1e-5), dtype, "expert rows")
+    close(rows.materialize(), added, torch.float32, "materialised expert rows")
+    # the router inside the norm kernel
+    gate, bias = rnd(E, H, seed=7, scale=0.3), rnd(E, seed=8, scale=0.2)
+    route = {"weight": gate.to(DEV), "bias": bias.to(DEV), "k": k, "normalize": True, "floor": 1e-6, "scale": 1.5,
+             "ids": torch.empty(R, k, dtype=torch.int32, device=DEV), "wts": torch.empty(R, k, dtype=torch.float32, device=DEV)}
+    res = res0.clone().to(DEV)
+    o.add_rmsnorm(res, None, w.to(DEV), 1e-5, out, None, None, route)
+    n32 = P.rms_norm(res0, w, 1e-5)
+    cfg = dict(num_experts_per_tok=k, use_expert_bias=True, norm_topk_prob=True, routed_scaling_factor=1.5)
+    want_ids, want_w = P.route(n32, {"gate.weight": gate, "expert_bias": bias}, "", cfg)
+    assert torch.equal(route["ids"].cpu().long(), want_ids)
+    close(route["wts"], want_w, torch.float32, "fused routing weights")
+    close(out, n32, dtype, "normed rows beside the router")
+
+
+@pytest.mark.parametrize("P_rows,E,k", [(8, 32, 4), (64, 6, 3), (1500, 8, 4)])
+def test_plan_forms_agree_and_copy_rows(P_rows, E, k):
+    """The one-kernel plan (a decode step) and the three-kernel plan (many pairs) are the same stable sort; the
+    one-kernel form also copies the token rows into expert-sorted order."""
+    o = ops()
+    g = torch.Generator().manual_seed(9)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(P_rows)]).int().to(DEV)
+    x = rnd(P_rows, 64, seed=10).to(torch.bfloat16).to(DEV)
+    xs = torch.zeros(P_rows * k, 64, dtype=torch.bfloat16, device=DEV)
+    plan = o.MoePlan(P_rows * k, E, 16, DEV).build(ids, x, xs)
+    flat = ids.cpu().reshape(-1).long()
+    order = torch.sort(flat, stable=True).indices
+    assert torch.equal(plan.sorted_pairs[:P_rows * k].cpu().long(), order)
+    assert torch.equal(plan.counts.cpu().long(), torch.bincount(flat, minlength=E))
+    assert torch.equal(plan.offsets.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), torch.bincount(flat, minlength=E).cumsum(0)]))
+    nt = int(plan.n_tiles)
+    assert sum(int(r) for r in plan.tile_rows[:nt].cpu()) == P_rows * k
+    assert plan.copied == (P_rows * k <= 4096)
+    if plan.copied:
+        assert torch.equal(xs.cpu(), x.cpu()[order // k])
+
+
 def test_embed_records_a_bad_token_instead_of_faulting():
     o = ops()
     table = rnd(10, 32).to(DEV)

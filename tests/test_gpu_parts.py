@@ -44,6 +44,12 @@ def rnd(*shape, seed=0, scale=1.0):
     return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
 
 
+def plain(branch) -> torch.Tensor:
+    """A part's output on the CPU as a plain tensor, whatever form the part returned it in."""
+    from tandemllm_b200.kernels import ops
+    return ops.materialize(branch).cpu()
+
+
 def reader(W):
     return lambda name: W[name]
 
@@ -73,7 +79,7 @@ def test_attention_part_alone(dtype, tol):
     outs = []
     for lo, hi in ((0, 17), (17, 18), (18, T)):
         ctx = step([("r", hi - lo)])
-        outs.append(part.forward(x[lo:hi].to(DEV), ctx, cache.site_cache[0]).cpu())
+        outs.append(plain(part.forward(x[lo:hi].to(DEV), ctx, cache.site_cache[0])))
     assert max_rel(torch.cat(outs), want) < tol
 
 
@@ -100,7 +106,7 @@ def test_short_conv_part_alone(dtype, tol, bias):
     outs = []
     for lo, hi in ((0, 2), (2, 3), (3, 4), (4, 21), (21, T)):
         ctx = step([("r", hi - lo)])
-        outs.append(part.forward(x[lo:hi].to(DEV), ctx, cache.site_cache[0]).cpu())
+        outs.append(plain(part.forward(x[lo:hi].to(DEV), ctx, cache.site_cache[0])))
     assert max_rel(torch.cat(outs), want) < tol
 
 
@@ -117,7 +123,7 @@ def test_feed_forward_parts_alone(dtype, tol):
                       prefix="f.", hidden_size=H)
     dense.bind(reader(W), rt)
     x = rnd(T, H, seed=4).to(dtype)
-    assert max_rel(dense.forward(x.to(DEV), None).cpu(), P.dense_mlp(x.float(), W, "f.")) < tol
+    assert max_rel(plain(dense.forward(x.to(DEV), None)), P.dense_mlp(x.float(), W, "f.")) < tol
     for use_bias, normalize, scale in ((True, True, 1.0), (False, False, 2.0)):
         M = {"m.gate.weight": rnd(E, H, seed=5, scale=0.5), "m.expert_bias": rnd(E, seed=6, scale=0.3)}
         for e in range(E):
@@ -136,7 +142,7 @@ def test_feed_forward_parts_alone(dtype, tol):
         part.bind(reader(M), rt)
         cfg = dict(num_experts_per_tok=k, use_expert_bias=use_bias, norm_topk_prob=normalize, routed_scaling_factor=scale)
         margins = P.routing_margin(x.float(), M, "m.", cfg)
-        got = part.forward(x.to(DEV), None, x32=x.float().to(DEV)).cpu()
+        got = plain(part.forward(x.to(DEV), None, x32=x.float().to(DEV)))
         want = P.moe(x.float(), M, "m.", cfg)
         stable = margins > 1e-4
         assert int(stable.sum()) > T // 2
