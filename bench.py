@@ -169,6 +169,7 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
     ap.add_argument("--graph", default="on", choices=("on", "off"))
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--only", choices=("prefill",), help="measure only this part and print it (a profiling aid)")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     a = ap.parse_args()
@@ -298,10 +299,14 @@ def main() -> int:
             prompt = torch.randint(0, V, (tokens,), generator=g).tolist()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if a.profile and i == reps:
+                torch.cuda.profiler.start()
             e0.record()
             engine.step([StepEntry("prefill", prompt, [tokens - 1])])
             e1.record()
             torch.cuda.synchronize()
+            if a.profile and i == reps:
+                torch.cuda.profiler.stop()
             engine.release("prefill")
             if i:
                 times.append(e0.elapsed_time(e1))
@@ -310,6 +315,9 @@ def main() -> int:
         return {"value": round(tokens / (ms / 1e3), 1), "tokens": tokens, "ms": round(ms, 3),
                 "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(flops / ms / 1e9, 1)}
 
+    if a.only == "prefill":          # a profiling aid: the prefill alone, its last repetition between profiler marks
+        print(json.dumps({"prefill": prefill(PREFILL_TOKENS, reps=2)}))
+        return 0
     clocks = Clocks().start()
     main_run = device_decode(a.batch, a.context, a.steps, a.warmup)
     e2e = e2e_decode(a.batch, a.context, a.steps, a.warmup)

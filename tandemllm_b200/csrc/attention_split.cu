@@ -356,3 +356,21 @@ extern "C" int tl_paged_attention_split(const void* q, const void* k_cache, cons
   return small ? TL_SPANS(bf16, 4) : TL_SPANS(bf16, 8);
 #undef TL_SPANS
 }
+
+// Joins the spans that another kernel left in `scratch` (same layout as above) into `out`, in ascending order.
+extern "C" int tl_attention_join(const float* scratch, const int* positions, int window, void* out, int rows, int Hq, int D,
+                                 int n_spans, int dtype, cudaStream_t stream) {
+  if (rows == 0 || n_spans <= 1) return 0;
+  TL_REQUIRE(scratch != nullptr && Hq > 0 && Hq <= 65535 && D > 0, "attention join: %d heads of size %d", Hq, D);
+  const float* part_o = scratch;
+  const float* part_ml = scratch + (long long)rows * Hq * n_spans * D;
+  dim3 join(rows, Hq);
+  if (dtype == TL_FP32)
+    attention_join_kernel<float><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (float*)out, Hq, D,
+                                                                        n_spans);
+  else
+    attention_join_kernel<bf16><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (bf16*)out, Hq, D,
+                                                                       n_spans);
+  TL_LAUNCH_CHECK();
+  return 0;
+}

@@ -43,6 +43,14 @@ def lib():
         l.tl_tc_token_tile.argtypes = [c_int, c_int]
         l.tl_tc_token_tile.restype = c_int
         l.tl_tc_last_error.restype = ctypes.c_char_p
+        l.tl_paged_attention_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                                             ctypes.c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                             c_int, c_void_p, c_void_p]
+        l.tl_paged_attention_mma.restype = c_int
+        l.tl_attention_mma_tile_rows.argtypes = [c_int, c_int]
+        l.tl_attention_mma_tile_rows.restype = c_int
+        l.tl_attention_mma_supported.argtypes = [c_int, c_int, c_int]
+        l.tl_attention_mma_supported.restype = c_int
         _lib = l
     return _lib
 
@@ -147,9 +155,51 @@ class TensorCore:
         return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)
 
 
+    # ---- attention ----
+    def query_tiles(self, step, tile_rows: int) -> torch.Tensor:
+        """int32 [tiles, 3] = (request, first row, rows) cutting every request's rows of this step into tiles of at
+        most `tile_rows` query rows. A decode-only step (one row a request) is laid out by device code alone, so
+        that it can be captured in a graph; anything else comes from the step's host lists. Kept on the step."""
+        key = ("query_tiles", tile_rows)
+        if key not in step.host:
+            B = step.n_requests
+            if step.max_rows_per_request == 1:
+                ar = torch.arange(B, dtype=torch.int32, device=self.device)
+                step.host[key] = torch.stack([ar, ar, torch.ones_like(ar)], 1).contiguous()
+            else:
+                starts = step.host["row_start"]
+                rows = [(b, r0, min(tile_rows, starts[b + 1] - r0)) for b in range(B)
+                        for r0 in range(starts[b], starts[b + 1], tile_rows)]
+                step.host[key] = torch.tensor(rows, dtype=torch.int32).to(self.device, non_blocking=True)
+        return step.host[key]
+
+    def attention(self, q, cache, table, step, scale, window, out, runtime) -> bool:
+        """Attention of every row over its request's cached keys on the tensor cores; False when the sizes are not
+        the kernel's (head sizes 64 and 128, groups up to 64): the caller then uses the CUDA-core kernel."""
+        R, Hq, D = q.shape
+        Hk = cache.k.shape[1]
+        if q.dtype != torch.bfloat16 or not lib().tl_attention_mma_supported(Hq, Hk, D):
+            return False
+        tiles = self.query_tiles(step, lib().tl_attention_mma_tile_rows(Hq, Hk))
+        n_tiles = tiles.shape[0]
+        # few tiles and long contexts (decoding): split the keys over CTAs as well
+        split = n_tiles * Hk < 2 * SM_COUNT and step.max_context > 512
+        spans = ops.attention_spans(step.max_context) if split else 1
+        scratch = runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans)) if split else None
+        code = lib().tl_paged_attention_mma(
+            q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
+            tiles.data_ptr(), n_tiles, step.positions.data_ptr(), float(scale), int(window or 0), out.data_ptr(),
+            ops.ptr(scratch), R, Hq, Hk, D, spans, int(split), self.status.data_ptr(), ops.stream())
+        _check(code, "attention_mma")
+        if split:
+            ops.attention_join(scratch, step.positions, window, out, spans)
+        return True
+
+
 def enable(runtime) -> TensorCore:
-    """Build and load the tensor-core library and give `runtime` its kernels: the runtime's bfloat16 products and
-    expert feed-forwards go through them from now on."""
+    """Build and load the tensor-core library and give `runtime` its kernels: the runtime's bfloat16 products,
+    expert feed-forwards and attention go through them from now on."""
     lib()
     runtime.tensorcore = TensorCore(runtime.device, runtime.status)
+    runtime.attention_kernels = runtime.tensorcore
     return runtime.tensorcore

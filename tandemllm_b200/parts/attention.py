@@ -100,7 +100,7 @@ class AttentionMixer(Part):
                 ops.kv_store(k, v, step.positions, step.req_of_row, table, cache.page_size, cache.k, cache.v, status)
         o = torch.empty(R, Hq, D, dtype=dt, device=dev)
         fast = self.runtime.attention_kernels
-        if fast is None or not fast.attention(q, cache, table, step, self.scale, self.window, o):
+        if fast is None or not fast.attention(q, cache, table, step, self.scale, self.window, o, self.runtime):
             spans = ops.attention_spans(step.max_context)
             scratch = self.runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans))
             ops.paged_attention_split(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions,

@@ -2,12 +2,16 @@
 whole; most of it in one step and the last 32 tokens one by one; in portions of changing size; mixed with
 other requests on so few pages that they are used again; through `bin/trace_run` itself; long decoding; the
 first tokens of a sequence; greedy and sampled generation through the Python entry point. In 32-bit and in
-bfloat16, on two tiny models that differ in every size and option.
+bfloat16, on tiny models that differ in every size and option (A and B; C has the head size and widths the
+tensor-core kernels of the bfloat16 path take).
 
-Tolerances. 32-bit: every logit within 1e-4 of the row's largest magnitude. bfloat16: within 3e-2. A position
-whose routing is a near tie in the plain implementation (the k-th and (k+1)-th expert scores closer than the
-precision's noise: 1e-5 in 32-bit, 2e-3 in bfloat16) may route differently and is not compared, as the
-reference excludes near ties when it compares engines (tools/lfm_check.py:100-125); most positions must remain.
+Tolerances. 32-bit: every logit within 1e-4 of the row's largest magnitude. bfloat16: within 3e-2. The one
+allowed exception is a position whose routing is a near tie in the plain implementation: when the k-th and the
+(k+1)-th expert score of some layer are closer than the precision's noise in those scores (1e-5 in 32-bit; 3e-2
+in bfloat16, where activations carry errors of about a hundredth of their size), the engine may choose the other
+expert, and that token's logits then differ by much more than rounding. The reference sets near ties aside the
+same way when it compares engines (tools/lfm_check.py:100-125). Such positions must be few (a tenth at most),
+and a position with a clear routing margin must be within the tolerance whatever the others do.
 """
 
 import json
@@ -28,7 +32,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 TOL = {"float32": 1e-4, "bfloat16": 3e-2}
-NEAR_TIE = {"float32": 1e-5, "bfloat16": 2e-3}
+NEAR_TIE = {"float32": 1e-5, "bfloat16": 3e-2}
 LENGTHS = (150, 97, 33, 64, 129, 48, 16, 81)
 
 
@@ -37,17 +41,17 @@ class Case:
 
     def __init__(self, name: str, dtype: str, tmp):
         self.name, self.dtype = name, dtype
-        self.cfg = T.TINY_A if name == "a" else T.TINY_B
+        self.cfg = T.CONFIGS[name]
         exact = dtype == "bfloat16"
         self.W = random_model_weights(self.cfg, T.SEEDS[name], T.STD[name], bf16_exact=exact)
         self.folder = write_folder(str(tmp / f"{name}-{dtype}"), self.cfg, self.W,
                                    torch.bfloat16 if exact else torch.float32)
         self.requests = {f"q{i}": T.long_tokens(name, n, seed=20 + i) for i, n in enumerate(LENGTHS)}
-        self.ref, self.stable = {}, {}
+        self.ref, self.margin = {}, {}
         for rid, toks in self.requests.items():
             margins = []
             self.ref[rid] = P.forward(self.cfg, self.W, toks, margins=margins)
-            self.stable[rid] = torch.stack(margins).min(0).values >= NEAR_TIE[dtype]
+            self.margin[rid] = torch.stack(margins).min(0).values      # per position, the tightest routing margin
 
     def engine(self, max_tokens: int, parallel: int = 4, block_size: int = 16, **kw):
         from tandemllm_b200.engine import Engine, EngineArgs
@@ -80,23 +84,21 @@ class Case:
         return got
 
     def compare(self, got: dict, what: str) -> None:
-        worst, compared, skipped, first_bad = 0.0, 0, 0, None
+        worst, rerouted, first_bad = 0.0, [], None
         for (rid, pos), row in sorted(got.items()):
             ref = self.ref[rid][pos]
-            if not bool(self.stable[rid][pos]):
-                skipped += 1
-                continue
             err = float((row - ref).abs().max() / ref.abs().max())
-            compared += 1
-            if err > worst:
-                worst = err
-            if err > TOL[self.dtype] and first_bad is None:
-                first_bad = (rid, pos, err)
-        if compared + skipped >= 20:
-            assert compared > 2 * skipped, f"{what}: {skipped} of {compared + skipped} positions are routing near-ties"
+            if err <= TOL[self.dtype]:
+                worst = max(worst, err)
+            elif float(self.margin[rid][pos]) < NEAR_TIE[self.dtype]:
+                rerouted.append((rid, pos, round(err, 3)))          # a routing near tie went the other way
+            elif first_bad is None:
+                first_bad = (rid, pos, err, float(self.margin[rid][pos]))
         assert first_bad is None, (f"{what} [{self.name} {self.dtype}]: first wrong token is {first_bad[0]} position "
-                                   f"{first_bad[1]} (page offset {first_bad[1] % 16}) with error {first_bad[2]:.3g}; "
-                                   f"worst {worst:.3g}, tolerance {TOL[self.dtype]:.1g}")
+                                   f"{first_bad[1]} (page offset {first_bad[1] % 16}) with error {first_bad[2]:.3g} and "
+                                   f"routing margin {first_bad[3]:.3g}; tolerance {TOL[self.dtype]:.1g}")
+        assert len(rerouted) <= max(1, len(got) // 10), (f"{what} [{self.name} {self.dtype}]: {len(rerouted)} of {len(got)} "
+                                                         f"positions differ as routing near ties: {rerouted[:8]}")
 
 
 def greedy_like_plain(case, prompt, out) -> None:
@@ -113,7 +115,8 @@ def greedy_like_plain(case, prompt, out) -> None:
         seq.append(tok)
 
 
-@pytest.fixture(scope="module", params=[("a", "float32"), ("b", "float32"), ("a", "bfloat16"), ("b", "bfloat16")],
+@pytest.fixture(scope="module", params=[("a", "float32"), ("b", "float32"), ("c", "float32"), ("a", "bfloat16"),
+                                        ("b", "bfloat16"), ("c", "bfloat16")],
                 ids=lambda p: f"{p[0]}-{p[1]}")
 def case(request, tmp_path_factory):
     return Case(request.param[0], request.param[1], tmp_path_factory.mktemp("models"))

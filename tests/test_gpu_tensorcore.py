@@ -102,6 +102,61 @@ def test_grouped_experts_with_swiglu(R, E, k, H, I):
     assert rel(out, want) < 2e-2
 
 
+@pytest.mark.parametrize("split", [False, True])
+@pytest.mark.parametrize("Hq,Hk,D,page,window", [(8, 2, 64, 16, None), (4, 4, 64, 16, None), (6, 2, 128, 32, None),
+                                                 (8, 1, 64, 16, 100), (32, 8, 64, 16, None), (3, 1, 64, 64, None),
+                                                 (5, 1, 128, 16, 300)])
+def test_attention_on_tensor_cores(split, Hq, Hk, D, page, window):
+    """Prompt portions of several lengths, a sequence's first rows and decode rows at short and long contexts in
+    one call, unsplit and split over key spans, against whole-sequence attention."""
+    import types
+
+    from tandemllm_b200.kernels import ops, tensorcore
+    from tests.test_gpu_kernels import paged_setup, plain_attention
+    impl, rt = tc()
+    seqs, news = [700, 90, 7, 300, 513], [1, 23, 7, 150, 1]
+    kc, vc, table, ks, vs = paged_setup(seqs, Hk, D, page, torch.bfloat16, seed=60)
+    R = sum(news)
+    q = rnd(R, Hq, D, seed=61)
+    positions = sum((list(range(L - n, L)) for L, n in zip(seqs, news)), [])
+    starts = [0]
+    for n in news:
+        starts.append(starts[-1] + n)
+    pos_dev = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    step = types.SimpleNamespace(n_requests=len(seqs), max_rows_per_request=max(news), max_context=max(seqs),
+                                 positions=pos_dev, host={"row_start": starts})
+    lib = tensorcore.lib()
+    tile_rows = lib.tl_attention_mma_tile_rows(Hq, Hk)
+    tiles = impl.query_tiles(step, tile_rows)
+    assert int(tiles[:, 2].sum()) == R and int(tiles[:, 2].max()) <= tile_rows
+    spans = ops.attention_spans(max(seqs)) if split else 1
+    scratch = torch.full((ops.attention_scratch_floats(R, Hq, D, spans),), float("nan"), device=DEV) if split else None
+    out = torch.full((R, Hq, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scale = 0.9 / D ** 0.5
+    qd, kd, vd, td = q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV)      # kept alive until the kernel has run
+    code = lib.tl_paged_attention_mma(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(),
+                                      table.shape[1], page, tiles.data_ptr(), tiles.shape[0], pos_dev.data_ptr(), scale,
+                                      window or 0, out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, int(split),
+                                      rt.status.data_ptr(), ops.stream())
+    assert code == 0
+    if split:
+        ops.attention_join(scratch, pos_dev, window, out, spans)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    at = 0
+    for b, (L, n) in enumerate(zip(seqs, news)):
+        want = plain_attention(q[at:at + n].float(), ks[b], vs[b], scale, window)
+        assert rel(out[at:at + n], want) < 2e-2, f"sequence {b}"
+        at += n
+
+
+def test_decode_tiles_are_built_on_the_device():
+    import types
+    impl, rt = tc()
+    step = types.SimpleNamespace(n_requests=5, max_rows_per_request=1, host={})
+    assert impl.query_tiles(step, 16).tolist() == [[b, b, 1] for b in range(5)]
+
+
 def test_shapes_tma_cannot_take_fall_back():
     impl, rt = tc()
     x, w = rnd(4, 100, seed=13), rnd(8, 100, seed=14)          # k = 100 is not a multiple of 8

@@ -30,21 +30,34 @@ TINY_B = dict(
     rope_parameters={"rope_type": "default", "rope_theta": 1000000.0}, eos_token_id=3, bos_token_id=1, pad_token_id=0,
 )
 
+# A third model with the head size (64) and the widths (multiples of 8) that the tensor-core kernels of the bfloat16
+# path take, so that the replay tests run those kernels too; it starts with an attention layer and ends with a conv.
+TINY_C = dict(
+    model_type="lfm2_moe", architectures=["Lfm2MoeForCausalLM"], vocab_size=320, hidden_size=128,
+    intermediate_size=192, moe_intermediate_size=64, num_hidden_layers=4, num_attention_heads=4,
+    num_key_value_heads=1, head_dim=64, norm_eps=1e-5, max_position_embeddings=4096, conv_bias=False,
+    conv_L_cache=3, num_dense_layers=1, num_experts=6, num_experts_per_tok=2, use_expert_bias=True,
+    routed_scaling_factor=1.0, norm_topk_prob=True, tie_word_embeddings=True,
+    layer_types=["full_attention", "conv", "full_attention", "conv"],
+    rope_parameters={"rope_type": "default", "rope_theta": 1000000.0}, eos_token_id=2, bos_token_id=1, pad_token_id=0,
+)
+
 # B without the three options the reference refuses, so the reference itself can run it
 TINY_B_REFERENCE = {**TINY_B, "conv_bias": False, "norm_topk_prob": True}
 
-SEEDS = {"a": 0, "b": 1}
-STD = {"a": 0.02, "b": 0.05}
+SEEDS = {"a": 0, "b": 1, "c": 2}
+STD = {"a": 0.02, "b": 0.05, "c": 0.02}
+CONFIGS = {"a": TINY_A, "b": TINY_B, "c": TINY_C}
 
 
 def prompts(name: str) -> list[list[int]]:
-    """Seeded uniform-random token ids: A has prompts of 16 and 9 tokens, B of 33, 5 and 20."""
-    cfg, lens, seed = (TINY_A, (16, 9), 100) if name == "a" else (TINY_B, (33, 5, 20), 101)
+    """Seeded uniform-random token ids: A has prompts of 16 and 9 tokens, B of 33, 5 and 20, C of 70 and 12."""
+    lens, seed = {"a": ((16, 9), 100), "b": ((33, 5, 20), 101), "c": ((70, 12), 102)}[name]
     g = torch.Generator().manual_seed(seed)
-    return [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    return [torch.randint(0, CONFIGS[name]["vocab_size"], (n,), generator=g).tolist() for n in lens]
 
 
 def long_tokens(name: str, n: int, seed: int = 7) -> list[int]:
-    cfg = TINY_A if name == "a" else TINY_B
+    cfg = CONFIGS[name]
     g = torch.Generator().manual_seed(seed * 1000 + n)
     return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
