@@ -108,8 +108,9 @@ class Clocks:
 
 def reference_arm() -> int:
     print(json.dumps({"impl": "reference", "unavailable":
-                      "the reference's installable package holds its proxy and dashboard only; its engine is not "
-                      "installed by pip, has no sm_100 kernel path and builds its CUDA parts for sm_121a"}))
+                      "pip installs the reference's proxy, server and chatd packages only (pyproject.toml lists no "
+                      "engine package): `import server.app` from baseline/_ref fails with No module named 'engine', "
+                      "so no stock code path of the install generates tokens; its kernels also target sm_121a only"}))
     return 0
 
 

@@ -8,14 +8,21 @@ it is in, or knows which other parts surround it.
 Interfaces (duck-typed; the base classes below document them and hold the shared plumbing):
 
   Norm            weight_specs() -> [TensorSpec];  bind(read, runtime);
-                  add_norm(residual, delta, out, gather=None) -> out      residual += delta, out = norm(residual)
+                  add_norm(residual, delta, out=None, gather=None, n_out=None, want32=False, route=None) -> out
+                                                                         residual += delta, out = norm(residual)
   PositionEncoding  fused_rotary() -> (inv_freq, rotary_dim) | None      what the fused q/k kernel can apply itself
                   apply(q, k, positions) -> None                         in place on [R, heads, D], else
   Mixer           weight_specs(present) -> [TensorSpec];  bind(read, runtime);
                   cache_need() -> PagedNeed | SlotNeed | None
-                  forward(x, step, cache) -> [R, hidden] in the compute dtype
-  FeedForward     weight_specs(present);  bind(read, runtime);  forward(x, step) -> [R, hidden]
-  Arrangement     run(layer, residual, pending, step, cache) -> pending  (the not-yet-added branch output)
+                  forward(x, step, cache, writes_cache=True) -> branch output
+  FeedForward     weight_specs(present);  bind(read, runtime);
+                  forward(x, step, x32=None, routing=None) -> branch output
+                  optional: wants_x32 (also gets the normed rows unrounded), router_args(rows, device)
+  Arrangement     run(layer, residual, pending, step, cache, writes_cache) -> pending  (the not-yet-added branch output)
+
+A branch output is what a mixer or feed-forward adds to the residual stream: a float32 tensor [R, hidden], or one of
+the deferred forms of `kernels.ops` (`PartialSums`, `ExpertRows`) that the next norm kernel adds itself;
+`kernels.ops.materialize` turns any of them into a tensor.
 
 `step` is the `StepContext` of the running batch: rows of several requests flattened, with each row's
 request, position and the request's tables and slots. `cache` is what the cache manager made for the
