@@ -374,3 +374,52 @@ extern "C" int tl_attention_join(const float* scratch, const int* positions, int
   TL_LAUNCH_CHECK();
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// The split kernel with its scratch inside the library, for callers that cannot allocate device memory.
+// attention_noalloc.h says who they are, what the array costs and the rules that come with sharing it.
+#include <mutex>
+
+#include "attention_noalloc.h"
+
+// The scratch itself: device memory that exists on every GPU the library is loaded on, until the process ends.
+// In host code this name is only a handle for cudaGetSymbolAddress; kernels must be given the address it returns.
+static __device__ __align__(256) float tl_static_scratch[TL_STATIC_SCRATCH_FLOATS];
+
+static const int TL_MAX_DEVICES = 64;
+static float* tl_static_scratch_address[TL_MAX_DEVICES];     // per device, looked up at the first call there
+static std::mutex tl_static_scratch_mutex;
+
+extern "C" int tl_paged_attention_split_static(const void* q, const void* k_cache, const void* v_cache,
+                                               const int* block_table, int max_pages, int page_size,
+                                               const int* req_of_row, const int* positions, float scale, int window,
+                                               void* out, int rows, int Hq, int Hk, int D, int n_spans, int dtype,
+                                               int* status, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  TL_REQUIRE(rows > 0 && Hq > 0 && D > 0 && n_spans > 0, "paged_attention (static scratch): rows %d, heads %d, head size %d, spans %d",
+             rows, Hq, D, n_spans);
+  const long long need = tl_attention_scratch_floats(rows, Hq, D, n_spans);
+  TL_REQUIRE(need <= (long long)TL_STATIC_SCRATCH_FLOATS,
+             "paged_attention (static scratch): %d rows x %d heads x %d spans x (%d + 2) = %lld floats of scratch, the "
+             "library's fixed array holds %d; bring your own scratch to tl_paged_attention_split for sizes like this",
+             rows, Hq, n_spans, D, need, (int)TL_STATIC_SCRATCH_FLOATS);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  TL_REQUIRE(device >= 0 && device < TL_MAX_DEVICES, "paged_attention (static scratch): device index %d", device);
+  float* scratch;
+  {
+    // set-up, once per device, with that device current: the array's address on this device
+    std::lock_guard<std::mutex> guard(tl_static_scratch_mutex);
+    if (tl_static_scratch_address[device] == nullptr) {
+      float* address = nullptr;
+      e = cudaGetSymbolAddress((void**)&address, tl_static_scratch);
+      if (e != cudaSuccess) return (int)e;
+      tl_static_scratch_address[device] = address;
+    }
+    scratch = tl_static_scratch_address[device];
+  }
+  // from here on it is the ordinary entry point, which launches the two kernels and allocates nothing
+  return tl_paged_attention_split(q, k_cache, v_cache, block_table, max_pages, page_size, req_of_row, positions, scale,
+                                  window, out, scratch, rows, Hq, Hk, D, n_spans, dtype, status, stream);
+}
