@@ -191,8 +191,52 @@ __global__ void __launch_bounds__(256) gemm_skinny_narrow_kernel(GemmParams p) {
   }
 }
 
+// Many rows and few output columns (a router over a prompt portion): a CTA takes 16 rows and all of up to 64
+// columns, so that the grid has M / 16 CTAs instead of one column of 64-row tiles. k is walked in order.
+template <typename TIn, typename TOut>
+__global__ void __launch_bounds__(256) gemm_tall_narrow_kernel(GemmParams p) {
+  constexpr int RM = 16, RN = 64, RK = 32;
+  __shared__ float As[RK][RM + 1];
+  __shared__ float Ws[RK][RN + 1];
+  const int tid = threadIdx.x;
+  const int row0 = blockIdx.x * RM;
+  const int r = tid >> 4, cg = (tid & 15) * 4;
+  const TIn* A = (const TIn*)p.A;
+  const TIn* W = (const TIn*)p.W;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < p.K; k0 += RK) {
+    for (int i = tid; i < RM * RK; i += 256) {
+      const int rr = i / RK, kk = i % RK;
+      As[kk][rr] = (row0 + rr < p.M && k0 + kk < p.K) ? to_f32(A[(long long)(row0 + rr) * p.lda + k0 + kk]) : 0.f;
+    }
+    for (int i = tid; i < RN * RK; i += 256) {
+      const int nn = i / RK, kk = i % RK;
+      Ws[kk][nn] = (nn < p.N && k0 + kk < p.K) ? to_f32(W[(long long)nn * p.ldw + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < RK; ++kk) {
+      const float a = As[kk][r];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j] = fmaf(a, Ws[kk][cg + j], acc[j]);
+    }
+    __syncthreads();
+  }
+  if (row0 + r < p.M) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = cg + j;
+      if (n < p.N) ((TOut*)p.C)[(long long)(row0 + r) * p.ldc + n] = from_f32<TOut>(acc[j] + (p.bias ? p.bias[n] : 0.f));
+    }
+  }
+}
+
 template <typename TIn, typename TOut>
 static int launch(const GemmParams& p, int max_tiles, cudaStream_t stream) {
+  if (!p.tile_group && !p.swiglu && p.N <= 64 && p.M > 64) {
+    gemm_tall_narrow_kernel<TIn, TOut><<<ceil_div(p.M, 16), 256, 0, stream>>>(p);
+    return 0;
+  }
   if (!p.tile_group && !p.swiglu && p.M <= 8) {
     if (p.N <= 512 && p.K >= 512) {
       gemm_skinny_narrow_kernel<TIn, TOut, 8><<<p.N, 256, 0, stream>>>(p);

@@ -68,7 +68,7 @@ struct NormParams {
 // the unrounded row in 32-bit, and the choice and weights are written as well.
 template <typename T>
 __global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
-  extern __shared__ float row[];       // hidden floats, 33 for the reduction, then E logits
+  extern __shared__ __align__(16) float row[];       // hidden floats, 33 for the reduction, then E logits
   float* scratch = row + p.hidden;
   float* logits = scratch + 33;
   __shared__ int s_src[MAX_TOP_K];
@@ -98,33 +98,82 @@ __global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
   }
   float* res = p.residual + (size_t)r * hidden;
   const bool adds = p.delta || p.expert_rows;
+  const bool vec = (hidden & 3) == 0;           // rows are then 16-byte aligned: four elements a step
   float ss = 0.f;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-    float x = res[c];
-    if (p.delta) {
-      float d = 0.f;
-      for (int s = 0; s < p.parts; ++s) d += p.delta[(long long)s * p.part_stride + (size_t)r * hidden + c];
-      x += d;
+  if (vec) {
+    const int h4 = hidden >> 2;
+    const float4* res4 = reinterpret_cast<const float4*>(res);
+    for (int c = threadIdx.x; c < h4; c += blockDim.x) {
+      float4 x = res4[c];
+      if (p.delta) {
+        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < p.parts; ++s) {
+          const float4 t = reinterpret_cast<const float4*>(p.delta + (long long)s * p.part_stride + (size_t)r * hidden)[c];
+          d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w;
+        }
+        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+      }
+      if (p.expert_rows) {
+        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < p.top_k; ++j) {
+          const float4 t = reinterpret_cast<const float4*>(p.expert_rows + (long long)s_src[j] * hidden)[c];
+          const float w = s_w[j];
+          d.x = fmaf(w, t.x, d.x); d.y = fmaf(w, t.y, d.y); d.z = fmaf(w, t.z, d.z); d.w = fmaf(w, t.w, d.w);
+        }
+        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+      }
+      reinterpret_cast<float4*>(row)[c] = x;
+      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
     }
-    if (p.expert_rows) {
-      float d = 0.f;
-      for (int j = 0; j < p.top_k; ++j) d = fmaf(s_w[j], p.expert_rows[(long long)s_src[j] * hidden + c], d);
-      x += d;
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      float x = res[c];
+      if (p.delta) {
+        float d = 0.f;
+        for (int s = 0; s < p.parts; ++s) d += p.delta[(long long)s * p.part_stride + (size_t)r * hidden + c];
+        x += d;
+      }
+      if (p.expert_rows) {
+        float d = 0.f;
+        for (int j = 0; j < p.top_k; ++j) d = fmaf(s_w[j], p.expert_rows[(long long)s_src[j] * hidden + c], d);
+        x += d;
+      }
+      row[c] = x;
+      ss += x * x;
     }
-    row[c] = x;
-    ss += x * x;
   }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + p.eps);
   T* out = (T*)p.normed + (size_t)out_r * hidden;
   float* out32 = p.normed32 ? p.normed32 + (size_t)out_r * hidden : nullptr;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-    const float x = row[c];
-    if (!p.gather && adds) res[c] = x;
-    const float y = p.weight[c] * (x * inv);
-    out[c] = from_f32<T>(y);
-    if (out32) out32[c] = y;
-    row[c] = y;
+  if (vec) {
+    const int h4 = hidden >> 2;
+    for (int c = threadIdx.x; c < h4; c += blockDim.x) {
+      const float4 x = reinterpret_cast<const float4*>(row)[c];
+      if (!p.gather && adds) reinterpret_cast<float4*>(res)[c] = x;
+      const float4 w = reinterpret_cast<const float4*>(p.weight)[c];
+      const float4 y = make_float4(w.x * (x.x * inv), w.y * (x.y * inv), w.z * (x.z * inv), w.w * (x.w * inv));
+      if constexpr (sizeof(T) == 2) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(out)[c] = packed;
+      } else {
+        reinterpret_cast<float4*>(out)[c] = y;
+      }
+      if (out32) reinterpret_cast<float4*>(out32)[c] = y;
+      reinterpret_cast<float4*>(row)[c] = y;
+    }
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      const float x = row[c];
+      if (!p.gather && adds) res[c] = x;
+      const float y = p.weight[c] * (x * inv);
+      out[c] = from_f32<T>(y);
+      if (out32) out32[c] = y;
+      row[c] = y;
+    }
   }
   if (!p.router_w) return;
   __syncthreads();

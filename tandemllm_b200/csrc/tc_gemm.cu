@@ -142,7 +142,11 @@ struct Smem {
   // with SWIGLU the weight side is loaded twice (gate rows and up rows)
   static constexpr int W_TILES = SWIGLU ? 2 : 1;
   static constexpr int STAGE_BYTES = SWAP ? (W_TILES * A_BYTES + B_BYTES) : (A_BYTES + W_TILES * B_BYTES);
-  static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+  // The swapped (weight-streaming) form takes the whole SM's shared memory for a deep ring. The plain form keeps to
+  // about half of it, so that two CTAs share an SM and one's epilogue runs under the other's main loop.
+  static constexpr int BUDGET = SWAP ? 200 * 1024 : 100 * 1024;
+  static constexpr int FIT = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = FIT > 8 ? 8 : (FIT < 2 ? 2 : FIT);
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
   static constexpr int TMEM_COLS_RAW = BN * W_TILES;
   static constexpr int TMEM_COLS = TMEM_COLS_RAW <= 32 ? 32 : TMEM_COLS_RAW <= 64 ? 64 : TMEM_COLS_RAW <= 128 ? 128
@@ -306,13 +310,34 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
           // this thread: token tok0 + m_row; registers: output columns n0 + c0 + j
           if (m_row < tok_rows) {
             TOut* row = C + (long long)(tok0 + m_row) * p.ldc;
+            float r[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int n = n0 + c0 + j;
-              if (n < p.N) {
-                const float r = SWIGLU ? silu_mul(v[j], u[j]) : v[j] + (p.bias ? p.bias[n] : 0.f);
-                store_out<TOut>(row + n, r);
+              r[j] = SWIGLU ? silu_mul(v[j], u[j]) : v[j] + ((p.bias && n < p.N) ? p.bias[n] : 0.f);
+            }
+            // 16 consecutive outputs of one row: 16-byte stores when they are all there and aligned
+            const bool whole = n0 + c0 + 16 <= p.N && (((uintptr_t)(row + n0 + c0)) & 15) == 0;
+            if (whole) {
+              if constexpr (sizeof(TOut) == 2) {
+                uint4 lo, hi;
+                __nv_bfloat162 t;
+#define TL_PACK(dst, a, b) t = __floats2bfloat162_rn(a, b); dst = *reinterpret_cast<uint32_t*>(&t)
+                TL_PACK(lo.x, r[0], r[1]); TL_PACK(lo.y, r[2], r[3]); TL_PACK(lo.z, r[4], r[5]); TL_PACK(lo.w, r[6], r[7]);
+                TL_PACK(hi.x, r[8], r[9]); TL_PACK(hi.y, r[10], r[11]); TL_PACK(hi.z, r[12], r[13]); TL_PACK(hi.w, r[14], r[15]);
+#undef TL_PACK
+                uint4* dst = reinterpret_cast<uint4*>(row + n0 + c0);
+                dst[0] = lo;
+                dst[1] = hi;
+              } else {
+                float4* dst = reinterpret_cast<float4*>(row + n0 + c0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst[j] = make_float4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
               }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (n0 + c0 + j < p.N) store_out<TOut>(row + n0 + c0 + j, r[j]);
             }
           }
         }

@@ -131,6 +131,12 @@ def build(name: str, force: bool = False) -> str:
             if r.returncode != 0:
                 raise ExtensionError(f"linking {out} failed:\n{r.stdout}\n{r.stderr}")
             os.replace(tmp, out)
+            for old in os.listdir(folder):          # builds of earlier source texts are of no use any more
+                if old.startswith(f"lib{name}-") and old.endswith(".so") and os.path.join(folder, old) != out:
+                    try:
+                        os.remove(os.path.join(folder, old))
+                    except OSError:
+                        pass
             for o in objs:
                 try:
                     os.remove(o)

@@ -157,7 +157,7 @@ def test_silu_mul(dtype):
 # ------------------------------------------------------------------------------------------ products
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,N,K", [(1, 130, 77), (3, 64, 64), (8, 257, 100), (9, 130, 77), (70, 96, 200), (200, 33, 17),
-                                   (5, 40, 600), (8, 32, 2048)])
+                                   (5, 40, 600), (8, 32, 2048), (300, 64, 130), (2048, 32, 256)])
 def test_gemm_simt(dtype, M, N, K):
     o = ops()
     x, w, b = rnd(M, K, seed=6).to(dtype), rnd(N, K, seed=7).to(dtype), rnd(N, seed=8)
