@@ -171,6 +171,8 @@ def main() -> int:
     ap.add_argument("--graph", default="on", choices=("on", "off"))
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--only", choices=("prefill",), help="measure only this part and print it (a profiling aid)")
+    ap.add_argument("--chain", default="off", choices=("on", "off"),
+                    help="programmatic dependent launch between the kernels (for comparison; ordinary launches by default)")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     a = ap.parse_args()
@@ -203,6 +205,11 @@ def main() -> int:
         max_batched_tokens=max(PREFILL_TOKENS, max_batch), chunk_size=PREFILL_TOKENS, graph=a.graph == "on"))
     torch.cuda.synchronize()
     load_s = time.time() - t0
+    if a.chain == "on":
+        from tandemllm_b200.kernels import tensorcore
+        ops.core().tl_set_chained_launches(1)
+        if a.dtype == "bfloat16":
+            tensorcore.lib().tl_tc_set_chained_launches(1)
     for sc in engine.cache.site_cache:            # a synthetic context: random keys and values
         if hasattr(sc, "k"):
             sc.k.normal_(0, 0.5)

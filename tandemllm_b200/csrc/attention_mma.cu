@@ -10,16 +10,16 @@
 // Keys and values come page by page through cp.async into swizzled shared memory, two stages deep; scores and
 // the running maximum, sum and output stay in registers (the online softmax of flash attention).
 //   split = 0   the CTA walks all visible keys of its tile and writes the output (prompt portions)
-//   split = 1   grid.z spans of 256 key positions, aligned to absolute positions; a row whose keys lie in one
-//               span is written directly, else the span's (max, sum, weighted values) go to scratch and the join
-//               kernel of attention_split.cu adds the spans in order (decoding at long contexts)
+//   split = S   grid.z spans of S key positions (a multiple of 64), aligned to absolute positions; a row whose keys
+//               lie in one span is written directly, else the span's (max, sum, weighted values) go to scratch and
+//               the join kernel of attention_split.cu adds the spans in order (decoding at long contexts). The
+//               caller picks S so that the grid fills the GPU: short spans for one request, long ones for many.
 // The tile table (request, first row, rows) comes from the host with the step's other integers.
 #include "common.cuh"
 
 namespace tl {
 
-constexpr int MMA_SPAN = 256;     // must equal SPAN of attention_split.cu (the join kernel reads the same layout)
-constexpr int KT = 64;            // keys per tile
+constexpr int KT = 64;            // keys per tile; a span's length is a multiple of it
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
   uint8_t* sk = sq + TILE_BYTES;             // [2][64][D]
   uint8_t* sv = sk + 2 * TILE_BYTES;         // [2][64][D]
 
+  chain_next();
+  chain_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t = blockIdx.x, g = blockIdx.y, span = blockIdx.z;
   const int b = tiles[3 * t], row0 = tiles[3 * t + 1], nq = tiles[3 * t + 2];
@@ -73,9 +75,10 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
   // keys any row of the tile may see
   int k_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
   int k_hi = pos0 + nq - 1;
+  const int span_keys = split > 0 ? split : 1;     // `split` carries the span's length in key positions (0: no split)
   if (split) {
-    k_lo = max(k_lo, span * MMA_SPAN);
-    k_hi = min(k_hi, (span + 1) * MMA_SPAN - 1);
+    k_lo = max(k_lo, span * span_keys);
+    k_hi = min(k_hi, (span + 1) * span_keys - 1);
   }
   if (k_lo > k_hi) return;
   const int kt_first = k_lo / KT, kt_last = k_hi / KT;
@@ -234,17 +237,17 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
     const float l = half ? l_hi : l_lo, mrow = half ? m_hi : m_lo;
     const int pos = pos0 + qi;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const bool direct = !split || (lo / MMA_SPAN == pos / MMA_SPAN);
+    const bool direct = !split || (lo / span_keys == pos / span_keys);
     if (direct) {
-      if (split && span != pos / MMA_SPAN) continue;      // only the CTA of the row's own span holds its keys
+      if (split && span != pos / span_keys) continue;      // only the CTA of the row's own span holds its keys
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = out + (row * Hq + head) * D + (lane & 3) * 2;
 #pragma unroll
       for (int n = 0; n < D / 8; ++n)
         *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
     } else {
-      // a span that holds none of the row's keys writes nothing: the join kernel reads only spans lo/256 .. pos/256
-      if (span < lo / MMA_SPAN || span > pos / MMA_SPAN) continue;
+      // a span that holds none of the row's keys writes nothing: the join kernel reads only the spans of lo .. pos
+      if (span < lo / span_keys || span > pos / span_keys) continue;
       float* dst = part_o + ((row * Hq + head) * n_spans + span) * D + (lane & 3) * 2;
 #pragma unroll
       for (int n = 0; n < D / 8; ++n) {
@@ -273,10 +276,9 @@ static int launch_mma(const void* q, const void* k_cache, const void* v_cache, c
     set = true;
   }
   dim3 grid(n_tiles, Hk, split ? n_spans : 1);
-  attention_mma_kernel<D><<<grid, 128, SMEM, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                                                       block_table, max_pages, page_size, tiles, positions, scale, window,
-                                                       (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status);
-  return (int)cudaGetLastError();
+  return (int)launch_chained(attention_mma_kernel<D>, grid, dim3(128), SMEM, stream, (const bf16*)q, (const bf16*)k_cache,
+                             (const bf16*)v_cache, block_table, max_pages, page_size, tiles, positions, scale, window,
+                             (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status);
 }
 
 }  // namespace tl
@@ -304,7 +306,8 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_cache, const 
   TL_REQUIRE(tl_attention_mma_supported(Hq, Hk, D), "attention (tensor cores): %d heads over %d KV heads of size %d", Hq, Hk, D);
   TL_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "attention: page size %d, table width %d, window %d", page_size,
              max_pages, window);
-  TL_REQUIRE(!split || (scratch && n_spans >= 1 && n_spans <= 65535), "attention: split over %d spans without scratch", n_spans);
+  TL_REQUIRE(!split || (scratch && n_spans >= 1 && n_spans <= 65535 && split % KT == 0),
+             "attention: split over %d spans of %d keys (a multiple of %d) needs scratch", n_spans, split, KT);
   TL_REQUIRE(Hk <= 65535, "attention: %d KV heads exceed the grid limit", Hk);
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (long long)rows * Hq * n_spans * D : nullptr;

@@ -29,6 +29,8 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, T* __restrict__ k_out,
     T* __restrict__ v_out, int Hq, int Hk, int D, int* __restrict__ status) {
   __shared__ float vec[4][MAX_HEAD_DIM];
+  chain_next();
+  chain_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x;
   const int head = blockIdx.y * 4 + warp;
@@ -202,18 +204,16 @@ extern "C" int tl_qk_prepare(const void* qkv, long long ld_qkv, const float* q_w
              "qk_prepare: neither cache pages nor plain outputs for k and v");
   dim3 grid(rows, ceil_div(Hq + 2 * Hk, 4));
   TL_REQUIRE(grid.y <= 65535, "qk_prepare: %d heads exceed the grid limit", Hq + 2 * Hk);
+  cudaError_t e;
   if (dtype == TL_FP32)
-    qk_prepare_kernel<float><<<grid, 128, 0, stream>>>(
-        (const float*)qkv, ld_qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions, req_of_row, block_table,
-        max_pages, page_size, (float*)q_out, (float*)k_cache, (float*)v_cache, (float*)k_out, (float*)v_out, Hq, Hk, D,
-        status);
+    e = launch_chained(qk_prepare_kernel<float>, grid, dim3(128), 0, stream, (const float*)qkv, ld_qkv, q_weight, k_weight, eps,
+                       inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, (float*)q_out,
+                       (float*)k_cache, (float*)v_cache, (float*)k_out, (float*)v_out, Hq, Hk, D, status);
   else
-    qk_prepare_kernel<bf16><<<grid, 128, 0, stream>>>(
-        (const bf16*)qkv, ld_qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions, req_of_row, block_table,
-        max_pages, page_size, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, (bf16*)k_out, (bf16*)v_out, Hq, Hk, D,
-        status);
-  TL_LAUNCH_CHECK();
-  return 0;
+    e = launch_chained(qk_prepare_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)qkv, ld_qkv, q_weight, k_weight, eps,
+                       inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, (bf16*)q_out,
+                       (bf16*)k_cache, (bf16*)v_cache, (bf16*)k_out, (bf16*)v_out, Hq, Hk, D, status);
+  return (int)e;
 }
 
 extern "C" int tl_kv_store(const void* k, const void* v, const int* positions, const int* req_of_row,

@@ -272,11 +272,13 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
 template <typename T>
 __global__ void attention_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       const int* __restrict__ positions, int window, T* __restrict__ out, int Hq, int D,
-                                      int n_spans) {
+                                      int n_spans, int span_keys) {
+  chain_next();
+  chain_wait();
   const int r = blockIdx.x, h = blockIdx.y;
   const int pos = positions[r];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int s0 = lo / SPAN, s1 = pos / SPAN;
+  const int s0 = lo / span_keys, s1 = pos / span_keys;
   if (s0 == s1) return;                                 // written directly by the span kernel
   const long long base = ((long long)r * Hq + h) * n_spans;
   float m = -INFINITY;
@@ -318,7 +320,7 @@ static int launch_spans(const void* q, const void* k_cache, const void* v_cache,
   if (n_spans > 1) {
     dim3 join(rows, Hq);
     attention_join_kernel<T><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (T*)out, Hq, D,
-                                                                    n_spans);
+                                                                    n_spans, SPAN);
     e = cudaGetLastError();
   }
   return (int)e;
@@ -358,21 +360,23 @@ extern "C" int tl_paged_attention_split(const void* q, const void* k_cache, cons
 }
 
 // Joins the spans that another kernel left in `scratch` (same layout as above) into `out`, in ascending order.
+// `span_keys`: the key positions a span covers (the kernel that wrote the spans chose it).
 extern "C" int tl_attention_join(const float* scratch, const int* positions, int window, void* out, int rows, int Hq, int D,
-                                 int n_spans, int dtype, cudaStream_t stream) {
+                                 int n_spans, int span_keys, int dtype, cudaStream_t stream) {
   if (rows == 0 || n_spans <= 1) return 0;
-  TL_REQUIRE(scratch != nullptr && Hq > 0 && Hq <= 65535 && D > 0, "attention join: %d heads of size %d", Hq, D);
+  TL_REQUIRE(scratch != nullptr && Hq > 0 && Hq <= 65535 && D > 0 && span_keys > 0,
+             "attention join: %d heads of size %d, spans of %d keys", Hq, D, span_keys);
   const float* part_o = scratch;
   const float* part_ml = scratch + (long long)rows * Hq * n_spans * D;
   dim3 join(rows, Hq);
+  cudaError_t e;
   if (dtype == TL_FP32)
-    attention_join_kernel<float><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (float*)out, Hq, D,
-                                                                        n_spans);
+    e = launch_chained(attention_join_kernel<float>, join, dim3(D <= 64 ? 64 : 128), 0, stream, part_o, part_ml, positions,
+                       window, (float*)out, Hq, D, n_spans, span_keys);
   else
-    attention_join_kernel<bf16><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (bf16*)out, Hq, D,
-                                                                       n_spans);
-  TL_LAUNCH_CHECK();
-  return 0;
+    e = launch_chained(attention_join_kernel<bf16>, join, dim3(D <= 64 ? 64 : 128), 0, stream, part_o, part_ml, positions,
+                       window, (bf16*)out, Hq, D, n_spans, span_keys);
+  return (int)e;
 }
 
 // ------------------------------------------------------------------------------------------------------------------

@@ -22,6 +22,8 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __rest
                                   const int* __restrict__ state_slot, const int* __restrict__ req_of_row,
                                   const int* __restrict__ row_start, const int* __restrict__ positions,
                                   T* __restrict__ y, int hidden, int K) {
+  chain_next();
+  chain_wait();
   const int r = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= hidden) return;
@@ -55,6 +57,8 @@ template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __restrict__ state,
                                         const int* __restrict__ state_slot, const int* __restrict__ row_start,
                                         const int* __restrict__ positions, int hidden, int K) {
+  chain_next();
+  chain_wait();
   const int b = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= hidden) return;
@@ -95,14 +99,14 @@ extern "C" int tl_short_conv(const void* bcx, const float* taps, const float* bi
   TL_REQUIRE(K >= 2 && K <= MAX_TAPS, "short_conv: %d taps; 2..%d are implemented", K, MAX_TAPS);
   dim3 grid(rows, ceil_div(hidden, 256));
   TL_REQUIRE(grid.y <= 65535, "short_conv: hidden size %d exceeds the grid limit", hidden);
+  cudaError_t e;
   if (dtype == TL_FP32)
-    short_conv_kernel<float><<<grid, 256, 0, stream>>>((const float*)bcx, taps, bias, state, state_slot, req_of_row,
-                                                       row_start, positions, (float*)y, hidden, K);
+    e = launch_chained(short_conv_kernel<float>, grid, dim3(256), 0, stream, (const float*)bcx, taps, bias, state, state_slot,
+                       req_of_row, row_start, positions, (float*)y, hidden, K);
   else
-    short_conv_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)bcx, taps, bias, state, state_slot, req_of_row,
-                                                      row_start, positions, (bf16*)y, hidden, K);
-  TL_LAUNCH_CHECK();
-  return 0;
+    e = launch_chained(short_conv_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)bcx, taps, bias, state, state_slot,
+                       req_of_row, row_start, positions, (bf16*)y, hidden, K);
+  return (int)e;
 }
 
 extern "C" int tl_short_conv_state(const void* bcx, float* state, const int* state_slot, const int* row_start,
@@ -112,12 +116,12 @@ extern "C" int tl_short_conv_state(const void* bcx, float* state, const int* sta
   TL_REQUIRE(requests > 0 && hidden > 0, "short_conv_state: requests %d hidden %d", requests, hidden);
   TL_REQUIRE(K >= 2 && K <= MAX_TAPS, "short_conv_state: %d taps; 2..%d are implemented", K, MAX_TAPS);
   dim3 grid(requests, ceil_div(hidden, 256));
+  cudaError_t e;
   if (dtype == TL_FP32)
-    short_conv_state_kernel<float><<<grid, 256, 0, stream>>>((const float*)bcx, state, state_slot, row_start, positions,
-                                                             hidden, K);
+    e = launch_chained(short_conv_state_kernel<float>, grid, dim3(256), 0, stream, (const float*)bcx, state, state_slot,
+                       row_start, positions, hidden, K);
   else
-    short_conv_state_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)bcx, state, state_slot, row_start, positions,
-                                                            hidden, K);
-  TL_LAUNCH_CHECK();
-  return 0;
+    e = launch_chained(short_conv_state_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)bcx, state, state_slot,
+                       row_start, positions, hidden, K);
+  return (int)e;
 }

@@ -104,6 +104,8 @@ __global__ void __launch_bounds__(128) moe_plan_small_kernel(const int* __restri
   __shared__ int s_ids[SMALL_PLAN_PAIRS];
   __shared__ float scratch[33];
   __shared__ int s_counts[MAX_EXPERTS];
+  chain_next();
+  chain_wait();
   const int p = blockIdx.x, tid = threadIdx.x;
   for (int i = tid; i < P; i += 128) s_ids[i] = ids[i];
   __syncthreads();
@@ -212,10 +214,10 @@ extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int top
   if (launched) *launched = 0;
   if (pairs == 0) return 0;
   if (pairs <= SMALL_PLAN_PAIRS && E <= MAX_EXPERTS) {
-    moe_plan_small_kernel<<<pairs, 128, 0, stream>>>(ids, pairs, E, tile_m, top_k, counts, offsets, sorted_pairs, pos_of_pair,
-                                                     tile_group, tile_row0, tile_rows, n_tiles, (const bf16*)x, ldx,
-                                                     (bf16*)x_sorted, width);
-    TL_LAUNCH_CHECK();
+    cudaError_t e = launch_chained(moe_plan_small_kernel, dim3(pairs), dim3(128), 0, stream, ids, pairs, E, tile_m, top_k,
+                                   counts, offsets, sorted_pairs, pos_of_pair, tile_group, tile_row0, tile_rows, n_tiles,
+                                   (const bf16*)x, ldx, (bf16*)x_sorted, width);
+    if (e != cudaSuccess) return (int)e;
     if (launched) *launched = 1;
     return 0;
   }

@@ -17,6 +17,8 @@ namespace tl {
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                                   float* __restrict__ residual, int hidden, int vocab, int* __restrict__ status) {
+  chain_next();
+  chain_wait();
   const int r = blockIdx.x;
   int tok = tokens[r];
   if (tok < 0 || tok >= vocab) {
@@ -58,7 +60,12 @@ struct NormParams {
   float floor_, scale;
   int* route_ids;            // [rows, route_k]
   float* route_wts;
+  int rows_per_block, out_rows;
 };
+
+// With a router and many rows, a block norms this many rows before it multiplies them by the router's weights,
+// so that the weights are read once per block and not once per row.
+constexpr int MAX_ROWS_PER_BLOCK = 8;
 
 // One block per output row.
 //   gather == nullptr: row r:  residual[r] += added[r];  normed[r] = w * residual[r] * rsqrt(mean + eps)
@@ -68,14 +75,22 @@ struct NormParams {
 // the unrounded row in 32-bit, and the choice and weights are written as well.
 template <typename T>
 __global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
-  extern __shared__ __align__(16) float row[];       // hidden floats, 33 for the reduction, then E logits
-  float* scratch = row + p.hidden;
+  // rows_per_block rows of `hidden` floats, 33 for the reduction, then rows_per_block x E logits
+  extern __shared__ __align__(16) float rows_buf[];
+  float* scratch = rows_buf + (size_t)p.rows_per_block * p.hidden;
   float* logits = scratch + 33;
   __shared__ int s_src[MAX_TOP_K];
   __shared__ float s_w[MAX_TOP_K];
-  const int out_r = blockIdx.x;
-  const int r = p.gather ? p.gather[out_r] : out_r;
+  chain_next();
+  chain_wait();
   const int hidden = p.hidden;
+  const int first_row = blockIdx.x * p.rows_per_block;
+  const int n_rows = min(p.rows_per_block, p.out_rows - first_row);
+  for (int rr = 0; rr < n_rows; ++rr) {
+  const int out_r = first_row + rr;
+  float* row = rows_buf + (size_t)rr * hidden;
+  const int r = p.gather ? p.gather[out_r] : out_r;
+  __syncthreads();            // the row before this one is done with the slot table and the reduction scratch
   if (p.expert_rows) {
     if (threadIdx.x == 0) {
       const int k = p.top_k;
@@ -175,26 +190,42 @@ __global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
       row[c] = y;
     }
   }
+  }   // rows of this block
   if (!p.router_w) return;
   __syncthreads();
-  // logits[e] = row . router_w[e]: each warp takes experts warp, warp + nwarps, ...; lanes stride over the row
+  // logits[row, e] = row . router_w[e]: each warp takes experts warp, warp + nwarps, ...; lanes stride over the
+  // columns; an expert's weights are read once for all rows of the block
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int e = warp; e < p.E; e += nwarps) {
     const float* w = p.router_w + (size_t)e * hidden;
-    float acc = 0.f;
-    for (int c = lane; c < hidden; c += 32) acc = fmaf(row[c], w[c], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) logits[e] = acc;
+    float acc[MAX_ROWS_PER_BLOCK];
+#pragma unroll
+    for (int rr = 0; rr < MAX_ROWS_PER_BLOCK; ++rr) acc[rr] = 0.f;
+    for (int c = lane; c < hidden; c += 32) {
+      const float wv = w[c];
+#pragma unroll
+      for (int rr = 0; rr < MAX_ROWS_PER_BLOCK; ++rr)
+        if (rr < n_rows) acc[rr] = fmaf(rows_buf[(size_t)rr * hidden + c], wv, acc[rr]);
+    }
+#pragma unroll
+    for (int rr = 0; rr < MAX_ROWS_PER_BLOCK; ++rr) {
+      if (rr < n_rows) {
+        const float v = warp_sum(acc[rr]);
+        if (lane == 0) logits[rr * p.E + e] = v;
+      }
+    }
   }
   __syncthreads();
-  if (warp == 0)
-    warp_route(logits, p.router_bias, p.E, p.route_k, p.normalize, p.floor_, p.scale,
-               p.route_ids + (size_t)out_r * p.route_k, p.route_wts + (size_t)out_r * p.route_k);
+  for (int rr = warp; rr < n_rows; rr += nwarps)
+    warp_route(logits + rr * p.E, p.router_bias, p.E, p.route_k, p.normalize, p.floor_, p.scale,
+               p.route_ids + (size_t)(first_row + rr) * p.route_k, p.route_wts + (size_t)(first_row + rr) * p.route_k);
 }
 
 // out[r, i] = silu(gate_up[r, i]) * gate_up[r, inter + i]
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows, int inter) {
+  chain_next();
+  chain_wait();
   const long long n = rows * inter;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / inter;
@@ -214,13 +245,17 @@ extern "C" int tl_embed_rows(const void* table, const int* tokens, float* residu
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && hidden > 0 && vocab > 0, "embed_rows: rows %d hidden %d vocab %d", rows, hidden, vocab);
   const int threads = hidden >= 1024 ? 256 : 128;
+  cudaError_t e;
   if (dtype == TL_FP32)
-    embed_rows_kernel<float><<<rows, threads, 0, stream>>>((const float*)table, tokens, residual, hidden, vocab, status);
+    e = launch_chained(embed_rows_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)table, tokens, residual,
+                       hidden, vocab, status);
   else
-    embed_rows_kernel<bf16><<<rows, threads, 0, stream>>>((const bf16*)table, tokens, residual, hidden, vocab, status);
-  TL_LAUNCH_CHECK();
-  return 0;
+    e = launch_chained(embed_rows_kernel<bf16>, dim3(rows), dim3(threads), 0, stream, (const bf16*)table, tokens, residual,
+                       hidden, vocab, status);
+  return (int)e;
 }
+
+extern "C" void tl_set_chained_launches(int enabled) { chained_launches() = enabled; }
 
 // See NormParams for the forms of what is added. Null pointers switch a form or the router off.
 extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, long long part_stride,
@@ -239,7 +274,9 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
     TL_REQUIRE(route_k > 0 && route_k <= E && route_k <= MAX_TOP_K && route_ids && route_wts,
                "router: top-%d of %d experts; up to top-%d is implemented", route_k, E, MAX_TOP_K);
   }
-  const size_t smem = (size_t)(hidden + 33 + (router_w ? E : 0)) * sizeof(float);
+  int rows_per_block = (router_w && out_rows > 64) ? MAX_ROWS_PER_BLOCK : 1;
+  while (rows_per_block > 1 && (size_t)rows_per_block * (hidden + E) * sizeof(float) > 96 * 1024) rows_per_block /= 2;
+  const size_t smem = ((size_t)rows_per_block * hidden + 33 + (router_w ? (size_t)rows_per_block * E : 0)) * sizeof(float);
   TL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory, the limit is 204800",
              hidden, smem);
   NormParams p = {};
@@ -248,18 +285,20 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
   p.normed = normed; p.normed32 = normed32; p.gather = gather; p.hidden = hidden; p.router_w = router_w;
   p.router_bias = router_bias; p.E = E; p.route_k = route_k; p.normalize = normalize; p.floor_ = floor_; p.scale = scale;
   p.route_ids = route_ids; p.route_wts = route_wts;
+  p.rows_per_block = rows_per_block; p.out_rows = out_rows;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  const dim3 grid(ceil_div(out_rows, rows_per_block));
+  cudaError_t e;
   if (dtype == TL_FP32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<float><<<out_rows, threads, smem, stream>>>(p);
+    e = launch_chained(add_rmsnorm_kernel<float>, grid, dim3(threads), smem, stream, p);
   } else {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_rmsnorm_kernel<bf16><<<out_rows, threads, smem, stream>>>(p);
+    e = launch_chained(add_rmsnorm_kernel<bf16>, grid, dim3(threads), smem, stream, p);
   }
-  TL_LAUNCH_CHECK();
-  return 0;
+  return (int)e;
 }
 
 extern "C" int tl_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
@@ -267,10 +306,12 @@ extern "C" int tl_silu_mul(const void* gate_up, void* out, int rows, int inter, 
   TL_REQUIRE(rows > 0 && inter > 0, "silu_mul: rows %d width %d", rows, inter);
   const long long n = (long long)rows * inter;
   const int blocks = (int)(ceil_div64(n, 256) < 148 * 16 ? ceil_div64(n, 256) : 148 * 16);
+  cudaError_t e;
   if (dtype == TL_FP32)
-    silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, rows, inter);
+    e = launch_chained(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out,
+                       (long long)rows, inter);
   else
-    silu_mul_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, rows, inter);
-  TL_LAUNCH_CHECK();
-  return 0;
+    e = launch_chained(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out,
+                       (long long)rows, inter);
+  return (int)e;
 }

@@ -157,6 +157,8 @@ template <int BN, bool SWAP, bool SWIGLU, typename TOut>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW,
                                                       const __grid_constant__ CUtensorMap tmX, TcParams p) {
   using S = Smem<BN, SWAP, SWIGLU>;
+  chain_next();
+  chain_wait();       // the tile map and the operands are written by the kernels before this one
   // ---- which tile ----
   int tok0, tok_rows;
   long long w_base = 0;                 // first weight row of this tile's group in the weight tensor
@@ -355,6 +357,8 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 template <typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, long long ldc, int M, int N,
                                      int splits) {
+  chain_next();
+  chain_wait();
   const long long total = (long long)M * N;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     float acc = 0.f;
@@ -444,8 +448,7 @@ static int launch_one(const CUtensorMap& tmW, const CUtensorMap& tmX, const TcPa
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kernel<<<grid, 192, S::TOTAL, stream>>>(tmW, tmX, p);
-  return (int)cudaGetLastError();
+  return (int)launch_chained(kernel, grid, dim3(192), S::TOTAL, stream, tmW, tmX, p);
 }
 
 template <bool SWAP, bool SWIGLU, typename TOut>
@@ -517,14 +520,19 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   if (splits > 1 && reduce) {     // without `reduce` the caller adds the partial sums itself (fused into its next kernel)
     const long long total = (long long)M * N;
     const int blocks = (int)(ceil_div64(total, 256) < 1184 ? ceil_div64(total, 256) : 1184);
+    cudaError_t r;
     if (out_dtype == TL_BF16)
-      splitk_reduce_kernel<bf16><<<blocks, 256, 0, stream>>>(partial, (bf16*)C, ldc, M, N, (int)grid.z);
+      r = launch_chained(splitk_reduce_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const float*)partial, (bf16*)C, ldc,
+                         M, N, (int)grid.z);
     else
-      splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(partial, (float*)C, ldc, M, N, (int)grid.z);
-    TL_LAUNCH_CHECK();
+      r = launch_chained(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)partial, (float*)C,
+                         ldc, M, N, (int)grid.z);
+    if (r != cudaSuccess) return (int)r;
   }
   return 0;
 }
+
+extern "C" void tl_tc_set_chained_launches(int enabled) { chained_launches() = enabled; }
 
 extern "C" int tl_gather_rows(const void* x, long long ldx, const int* index, int div, void* out, int rows, int width,
                               cudaStream_t stream) {

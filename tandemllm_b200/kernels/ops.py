@@ -55,7 +55,7 @@ _SIGNATURES = {
     "tl_attention_spans": [c_int],
     "tl_paged_attention_split": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "tl_attention_join": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tl_attention_join": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tl_router_topk": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p,
                        c_void_p],
     "tl_moe_max_tiles": [c_int, c_int, c_int],
@@ -304,11 +304,16 @@ def paged_attention_split(q, k_cache, v_cache, block_table, page_size, req_of_ro
     return out
 
 
-def attention_join(scratch, positions, window, out, n_spans: int) -> None:
-    """Adds the key spans another kernel left in `scratch` (layout of `paged_attention_split`) into `out`."""
+SPAN_KEYS = 256     # key positions per span of `paged_attention_split`
+
+
+def attention_join(scratch, positions, window, out, n_spans: int, span_keys: int = SPAN_KEYS) -> None:
+    """Adds the key spans (of `span_keys` positions each) another kernel left in `scratch` (layout of
+    `paged_attention_split`) into `out`."""
     rows, Hq, D = out.shape
     check(core().tl_attention_join(ptr(scratch), ptr(positions), int(window or 0), ptr(out), rows, Hq, D, int(n_spans),
-                                   dtype_code(out.dtype), stream()), "attention_join", kernels=1 if n_spans > 1 else 0)
+                                   int(span_keys), dtype_code(out.dtype), stream()), "attention_join",
+          kernels=1 if n_spans > 1 else 0)
 
 
 # ------------------------------------------------------------------------------------------ experts

@@ -182,17 +182,24 @@ class TensorCore:
             return False
         tiles = self.query_tiles(step, lib().tl_attention_mma_tile_rows(Hq, Hk))
         n_tiles = tiles.shape[0]
-        # few tiles and long contexts (decoding): split the keys over CTAs as well
-        split = n_tiles * Hk < 2 * SM_COUNT and step.max_context > 512
-        spans = ops.attention_spans(step.max_context) if split else 1
-        scratch = runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans)) if split else None
+        # Few tiles and long contexts (decoding): split the keys over CTAs as well, in spans long enough that a CTA's
+        # start-up is a small part of its work and short enough that the grid still has a few CTAs per SM.
+        span_keys = 0
+        if step.max_context > 512 and n_tiles * Hk < 8 * SM_COUNT:
+            span_keys = 256
+            while span_keys < 2048 and n_tiles * Hk * -(-step.max_context // (2 * span_keys)) >= 4 * SM_COUNT:
+                span_keys *= 2
+        spans = -(-step.max_context // span_keys) if span_keys else 1
+        if spans <= 1:
+            span_keys, spans = 0, 1
+        scratch = runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans)) if span_keys else None
         code = lib().tl_paged_attention_mma(
             q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
             tiles.data_ptr(), n_tiles, step.positions.data_ptr(), float(scale), int(window or 0), out.data_ptr(),
-            ops.ptr(scratch), R, Hq, Hk, D, spans, int(split), self.status.data_ptr(), ops.stream())
+            ops.ptr(scratch), R, Hq, Hk, D, spans, span_keys, self.status.data_ptr(), ops.stream())
         _check(code, "attention_mma")
-        if split:
-            ops.attention_join(scratch, step.positions, window, out, spans)
+        if span_keys:
+            ops.attention_join(scratch, step.positions, window, out, spans, span_keys)
         return True
 
 

@@ -110,13 +110,9 @@ class SigmoidTopKExperts(Part):
                 self.w_down[e].copy_(read(f"{self.base}.{e}.{self.n['down']}.weight"))
 
     wants_x32 = True        # the block hands the normed rows unrounded as well: router logits are 32-bit end to end
-    FUSED_ROUTE_ROWS = 64   # up to this many rows, the norm kernel in front of the layer runs the router itself
-
     def router_args(self, rows: int, device):
-        """What the norm kernel needs to run this layer's router on its `rows` output rows, or None when the
-        router runs on its own (many rows: a tiled product reads the router weights once, not once per row)."""
-        if rows > self.FUSED_ROUTE_ROWS:
-            return None
+        """What the norm kernel in front of the layer needs to run this layer's router on its `rows` output rows
+        (for many rows the kernel norms several rows per block, so the router's weights are read once per block)."""
         return {"weight": self.w_router, "bias": self.expert_bias, "k": self.top_k, "normalize": self.normalize,
                 "floor": self.norm_floor, "scale": self.scale,
                 "ids": torch.empty(rows, self.top_k, dtype=torch.int32, device=device),

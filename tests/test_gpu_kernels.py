@@ -72,11 +72,13 @@ def test_embed_and_add_rmsnorm(dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_add_rmsnorm_adds_deferred_branch_outputs_and_routes(dtype):
+@pytest.mark.parametrize("R", [7, 100])
+def test_add_rmsnorm_adds_deferred_branch_outputs_and_routes(dtype, R):
     """The forms a branch output may arrive in (partial sums of a split product; the rows of an expert layer with
-    their weights) give what adding the plain tensor gives, and the fused router gives the separate router's choice."""
+    their weights) give what adding the plain tensor gives, and the fused router gives the separate router's choice
+    (with many rows a block norms and routes several rows; 100 rows leave a partly filled last block)."""
     o = ops()
-    R, H, S, E, k = 7, 136, 3, 12, 4
+    H, S, E, k = 136, 3, 12, 4
     res0, w = rnd(R, H, seed=1), 1 + rnd(H, seed=2, scale=0.2)
     parts = rnd(S, R, H, seed=3)
     want = P.rms_norm(res0 + parts.sum(0), w, 1e-5)

@@ -102,7 +102,7 @@ def test_grouped_experts_with_swiglu(R, E, k, H, I):
     assert rel(out, want) < 2e-2
 
 
-@pytest.mark.parametrize("split", [False, True])
+@pytest.mark.parametrize("split", [0, 256, 512])
 @pytest.mark.parametrize("Hq,Hk,D,page,window", [(8, 2, 64, 16, None), (4, 4, 64, 16, None), (6, 2, 128, 32, None),
                                                  (8, 1, 64, 16, 100), (32, 8, 64, 16, None), (3, 1, 64, 64, None),
                                                  (5, 1, 128, 16, 300)])
@@ -129,7 +129,7 @@ def test_attention_on_tensor_cores(split, Hq, Hk, D, page, window):
     tile_rows = lib.tl_attention_mma_tile_rows(Hq, Hk)
     tiles = impl.query_tiles(step, tile_rows)
     assert int(tiles[:, 2].sum()) == R and int(tiles[:, 2].max()) <= tile_rows
-    spans = ops.attention_spans(max(seqs)) if split else 1
+    spans = -(-max(seqs) // split) if split else 1          # `split`: key positions per span, 0 for one pass
     scratch = torch.full((ops.attention_scratch_floats(R, Hq, D, spans),), float("nan"), device=DEV) if split else None
     out = torch.full((R, Hq, D), float("nan"), dtype=torch.bfloat16, device=DEV)
     scale = 0.9 / D ** 0.5
@@ -140,7 +140,7 @@ def test_attention_on_tensor_cores(split, Hq, Hk, D, page, window):
                                       rt.status.data_ptr(), ops.stream())
     assert code == 0
     if split:
-        ops.attention_join(scratch, pos_dev, window, out, spans)
+        ops.attention_join(scratch, pos_dev, window, out, spans, split)
     torch.cuda.synchronize()
     assert int(rt.status) == 0
     at = 0
