@@ -51,18 +51,24 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // row so that the eight rows an ldmatrix reads fall into different banks.
 template <int D> __device__ __forceinline__ int swz(int row, int chunk) { return row * (D * 2) + ((chunk ^ (row & 7)) << 4); }
 
-template <int D>
-__global__ void __launch_bounds__(128) attention_mma_kernel(
+// KEYSPLIT: every tile of the launch has at most 16 M rows in use (decoding: one query row of up to 16 heads). The
+// four warps then share those rows and split each 64-key tile among themselves, 16 keys a warp, each with its own
+// running (max, sum, output); they are merged in warp order through shared memory at the end. Otherwise each warp
+// owns 16 of the tile's 64 M rows and walks all keys. STAGES is the depth of the cp.async ring of key/value tiles.
+template <int D, bool KEYSPLIT, int STAGES>
+__global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-    const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ tiles,
+    const int* __restrict__ block_table, int max_pages, int page_size, int page_shift, const int* __restrict__ tiles,
     const int* __restrict__ positions, float scale, int window, bf16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, int n_spans, int split, int Hq, int Hk, int* __restrict__ status) {
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int TILE_BYTES = 64 * D * 2;
+  constexpr int QROWS = KEYSPLIT ? 16 : 64;
+  constexpr int NS = KEYSPLIT ? 2 : 8;      // 8-key score tiles a warp computes per key tile
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* sq = smem;                        // [64][D]
-  uint8_t* sk = sq + TILE_BYTES;             // [2][64][D]
-  uint8_t* sv = sk + 2 * TILE_BYTES;         // [2][64][D]
+  uint8_t* sq = smem;                            // [QROWS][D]
+  uint8_t* sk = sq + QROWS * D * 2;              // [STAGES][64][D]
+  uint8_t* sv = sk + STAGES * TILE_BYTES;        // [STAGES][64][D]
 
   chain_next();
   chain_wait();
@@ -70,6 +76,10 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
   const int t = blockIdx.x, g = blockIdx.y, span = blockIdx.z;
   const int b = tiles[3 * t], row0 = tiles[3 * t + 1], nq = tiles[3 * t + 2];
   const int G = Hq / Hk;
+  if (KEYSPLIT && nq * G > 16) {                 // the caller promised small tiles
+    if (tid == 0) atomicExch(status, 4);
+    return;
+  }
   const int pos0 = positions[row0];
   const int* table = block_table + (long long)b * max_pages;
   // keys any row of the tile may see
@@ -84,43 +94,56 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
   const int kt_first = k_lo / KT, kt_last = k_hi / KT;
 
   // ---- Q tile: M row m = (query row m / G, head m % G); rows past the tile's queries are zero ----
-  for (int i = tid; i < 64 * CH; i += 128) {
+  for (int i = tid; i < QROWS * CH; i += 128) {
     const int m = i / CH, c = i % CH;
     const int qi = m / G, hj = m % G;
     const bool valid = qi < nq;
     const bf16* src = q + ((long long)(row0 + (valid ? qi : 0)) * Hq + g * G + hj) * D + c * 8;
     cp_async16(sq + swz<D>(m, c), src, valid);
   }
+  // Two threads copy one key's row: one page lookup a thread and tile, and each pair of threads fills whole 32-byte
+  // sectors with every copy.
+  const int my_key = tid >> 1;
   auto load_kv = [&](int kt, int stage) {
-    for (int i = tid; i < 64 * CH; i += 128) {
-      const int key = i / CH, c = i % CH;
-      const int kp = kt * KT + key;
-      bool valid = kp >= k_lo && kp <= k_hi;
-      long long off = 0;
-      if (valid) {
-        const int page = table[kp / page_size];
-        if (page < 0) {
-          atomicExch(status, 3);
-          valid = false;
-        } else {
-          off = (((long long)page * Hk + g) * page_size + kp % page_size) * D + c * 8;
-        }
+    const int kp = kt * KT + my_key;
+    bool valid = kp >= k_lo && kp <= k_hi;
+    long long off = 0;
+    if (valid) {
+      const int pg = page_shift >= 0 ? kp >> page_shift : kp / page_size;
+      const int page = table[pg];
+      if (page < 0) {
+        atomicExch(status, 3);
+        valid = false;
+      } else {
+        off = (((long long)page * Hk + g) * page_size + (kp - pg * page_size)) * D;
       }
-      cp_async16(sk + stage * TILE_BYTES + swz<D>(key, c), k_cache + off, valid);
-      cp_async16(sv + stage * TILE_BYTES + swz<D>(key, c), v_cache + off, valid);
+    }
+    uint8_t* dk = sk + stage * TILE_BYTES;
+    uint8_t* dv = sv + stage * TILE_BYTES;
+#pragma unroll
+    for (int j = 0; j < CH / 2; ++j) {
+      const int c = (tid & 1) + 2 * j;
+      cp_async16(dk + swz<D>(my_key, c), k_cache + off + c * 8, valid);
+      cp_async16(dv + swz<D>(my_key, c), v_cache + off + c * 8, valid);
     }
   };
-  load_kv(kt_first, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int s0 = 0; s0 < STAGES - 1; ++s0) {
+    if (kt_first + s0 <= kt_last) load_kv(kt_first + s0, s0);
+    cp_async_commit();
+  }
 
   // this thread's two M rows and their query positions
-  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+  const int wrow = KEYSPLIT ? 0 : warp * 16;
+  const int r_lo = wrow + (lane >> 2), r_hi = r_lo + 8;
   const int q_lo = r_lo / G, q_hi = r_hi / G;
   const bool v_lo = q_lo < nq, v_hi = q_hi < nq;
   const int p_lo = pos0 + q_lo, p_hi = pos0 + q_hi;
   const int w_lo = window > 0 ? max(0, p_lo - window + 1) : 0, w_hi = window > 0 ? max(0, p_hi - window + 1) : 0;
+  const int n_base = KEYSPLIT ? warp * 2 : 0;      // first 8-key score tile of this warp
+  const float scale2 = scale * 1.4426950408889634f;   // scores are kept in units of log 2: exponentials are exp2
 
-  const bool active = warp * 16 < nq * G;
+  const bool active = wrow < nq * G;
   float o[D / 8][4];
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -128,50 +151,48 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
   uint32_t qf[D / 16][4];
 
   for (int kt = kt_first; kt <= kt_last; ++kt) {
-    const int stage = (kt - kt_first) & 1;
-    if (kt < kt_last) load_kv(kt + 1, stage ^ 1);
+    const int it = kt - kt_first;
+    const int stage = it % STAGES;
+    cp_async_wait<STAGES - 2>();      // this thread's copies of tile kt have landed
+    __syncthreads();                  // everybody's have, and everybody is done with the tile before
+    if (kt + STAGES - 1 <= kt_last) load_kv(kt + STAGES - 1, (it + STAGES - 1) % STAGES);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-    if (!active) {                // a warp whose 16 M rows lie past the tile's queries only helps with the loads
-      __syncthreads();
-      continue;
-    }
+    if (!active) continue;            // a warp whose 16 M rows lie past the tile's queries only helps with the loads
     if (kt == kt_first) {
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
-        const int row = warp * 16 + (lane & 15), c = kk * 2 + (lane >> 4);
+        const int row = wrow + (lane & 15), c = kk * 2 + (lane >> 4);
         ldmatrix_x4(smem_addr(sq + swz<D>(row, c)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
       }
     }
     const uint8_t* ks = sk + stage * TILE_BYTES;
     const uint8_t* vs = sv + stage * TILE_BYTES;
-    // ---- scores of this warp's 16 rows against 64 keys ----
-    float s[8][4];
+    // ---- scores of this warp's 16 rows against its keys of the tile ----
+    float s[NS][4];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int n = 0; n < NS; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
 #pragma unroll
-      for (int n = 0; n < 8; n += 2) {
+      for (int n = 0; n < NS; n += 2) {
         uint32_t b0, b1, b2, b3;
-        const int row = (n + (lane >> 4)) * 8 + (lane & 7), c = kk * 2 + ((lane >> 3) & 1);
+        const int row = (n_base + n + (lane >> 4)) * 8 + (lane & 7), c = kk * 2 + ((lane >> 3) & 1);
         ldmatrix_x4(smem_addr(ks + swz<D>(row, c)), b0, b1, b2, b3);
         mma_bf16(s[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
         mma_bf16(s[n + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
       }
     }
     // ---- mask, running maximum ----
-    const int key0 = kt * KT + (lane & 3) * 2;
+    const int key0 = kt * KT + n_base * 8 + (lane & 3) * 2;
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
+    for (int n = 0; n < NS; ++n) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int kp = key0 + n * 8 + e;
         const bool in = kp >= k_lo && kp <= k_hi;
-        s[n][e] = (in && v_lo && kp <= p_lo && kp >= w_lo) ? s[n][e] * scale : -INFINITY;
-        s[n][2 + e] = (in && v_hi && kp <= p_hi && kp >= w_hi) ? s[n][2 + e] * scale : -INFINITY;
+        s[n][e] = (in && v_lo && kp <= p_lo && kp >= w_lo) ? s[n][e] * scale2 : -INFINITY;
+        s[n][2 + e] = (in && v_hi && kp <= p_hi && kp >= w_hi) ? s[n][2 + e] * scale2 : -INFINITY;
         mx_lo = fmaxf(mx_lo, s[n][e]);
         mx_hi = fmaxf(mx_hi, s[n][2 + e]);
       }
@@ -181,17 +202,17 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
     const float n_lo = fmaxf(m_lo, mx_lo), n_hi = fmaxf(m_hi, mx_hi);
-    const float a_lo = n_lo == -INFINITY ? 1.f : expf(m_lo - n_lo), a_hi = n_hi == -INFINITY ? 1.f : expf(m_hi - n_hi);
+    // a row that has seen no key yet keeps 0 as its reference, so that exp2(-inf - reference) is 0, not NaN
+    const float c_lo = n_lo == -INFINITY ? 0.f : n_lo, c_hi = n_hi == -INFINITY ? 0.f : n_hi;
+    const float a_lo = exp2f(m_lo - c_lo), a_hi = exp2f(m_hi - c_hi);      // 0 where the row had no key before
     m_lo = n_lo;
     m_hi = n_hi;
     float sum_lo = 0.f, sum_hi = 0.f;
-    uint32_t pf[4][4];                        // P as A fragments: k-step j covers keys 16 j .. 16 j + 15
+    uint32_t pf[NS / 2][4];                   // P as A fragments: k-step j covers 16 of the warp's keys
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const float p0 = s[n][0] == -INFINITY ? 0.f : expf(s[n][0] - n_lo);
-      const float p1 = s[n][1] == -INFINITY ? 0.f : expf(s[n][1] - n_lo);
-      const float p2 = s[n][2] == -INFINITY ? 0.f : expf(s[n][2] - n_hi);
-      const float p3 = s[n][3] == -INFINITY ? 0.f : expf(s[n][3] - n_hi);
+    for (int n = 0; n < NS; ++n) {
+      const float p0 = exp2f(s[n][0] - c_lo), p1 = exp2f(s[n][1] - c_lo);
+      const float p2 = exp2f(s[n][2] - c_hi), p3 = exp2f(s[n][3] - c_hi);
       sum_lo += p0 + p1;
       sum_hi += p2 + p3;
       pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
@@ -199,26 +220,27 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
     }
     l_lo = l_lo * a_lo + sum_lo;
     l_hi = l_hi * a_hi + sum_hi;
+    if (__any_sync(0xffffffffu, a_lo != 1.f || a_hi != 1.f)) {      // most tiles leave the maxima as they are
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-      o[n][0] *= a_lo;
-      o[n][1] *= a_lo;
-      o[n][2] *= a_hi;
-      o[n][3] *= a_hi;
+      for (int n = 0; n < D / 8; ++n) {
+        o[n][0] *= a_lo;
+        o[n][1] *= a_lo;
+        o[n][2] *= a_hi;
+        o[n][3] *= a_hi;
+      }
     }
     // ---- o += P V ----
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < NS / 2; ++j) {
 #pragma unroll
       for (int n = 0; n < D / 8; n += 2) {
         uint32_t b0, b1, b2, b3;
-        const int row = j * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = n + (lane >> 4);
+        const int row = (n_base / 2 + j) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = n + (lane >> 4);
         ldmatrix_x4_trans(smem_addr(vs + swz<D>(row, c)), b0, b1, b2, b3);
         mma_bf16(o[n], pf[j][0], pf[j][1], pf[j][2], pf[j][3], b0, b1);
         mma_bf16(o[n + 1], pf[j][0], pf[j][1], pf[j][2], pf[j][3], b2, b3);
       }
     }
-    __syncthreads();            // the stage read here is the one the next iteration's prefetch overwrites
   }
   cp_async_wait<0>();
   // the row sums live in the four lanes of a quad
@@ -227,58 +249,102 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
 
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const bool valid = half ? v_hi : v_lo;
-    if (!valid) continue;
-    const int r = half ? r_hi : r_lo;
+  // One finished pair of columns of a row goes to the output, or, when the row's keys lie in several spans, to scratch.
+  auto emit = [&](int r, int col, float o0, float o1, float mrow, float l, bool first) {
     const int qi = r / G, head = g * G + r % G;
     const long long row = row0 + qi;
-    const float l = half ? l_hi : l_lo, mrow = half ? m_hi : m_lo;
     const int pos = pos0 + qi;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const bool direct = !split || (lo / span_keys == pos / span_keys);
     if (direct) {
-      if (split && span != pos / span_keys) continue;      // only the CTA of the row's own span holds its keys
+      if (split && span != pos / span_keys) return;        // only the CTA of the row's own span holds its keys
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = out + (row * Hq + head) * D + (lane & 3) * 2;
-#pragma unroll
-      for (int n = 0; n < D / 8; ++n)
-        *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+      *reinterpret_cast<uint32_t*>(out + (row * Hq + head) * D + col) = pack_bf16(o0 * inv, o1 * inv);
     } else {
       // a span that holds none of the row's keys writes nothing: the join kernel reads only the spans of lo .. pos
-      if (span < lo / span_keys || span > pos / span_keys) continue;
-      float* dst = part_o + ((row * Hq + head) * n_spans + span) * D + (lane & 3) * 2;
+      if (span < lo / span_keys || span > pos / span_keys) return;
+      float* dst = part_o + ((row * Hq + head) * n_spans + span) * D + col;
+      dst[0] = o0;
+      dst[1] = o1;
+      if (first) {
+        float* ml = part_ml + ((row * Hq + head) * n_spans + span) * 2;
+        ml[0] = mrow * 0.6931471805599453f;             // the join kernel works in natural units
+        ml[1] = l;
+      }
+    }
+  };
+
+  if constexpr (!KEYSPLIT) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      if (!(half ? v_hi : v_lo)) continue;
+      const int r = half ? r_hi : r_lo;
+      const float l = half ? l_hi : l_lo, mrow = half ? m_hi : m_lo;
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n)
+        emit(r, n * 8 + (lane & 3) * 2, o[n][half * 2], o[n][half * 2 + 1], mrow, l, n == 0 && (lane & 3) == 0);
+    }
+  } else {
+    // ---- merge the four warps' shares of the keys, in warp order ----
+    float* mo = reinterpret_cast<float*>(sk);              // [4][16][D]
+    float* mml = mo + 4 * 16 * D;                          // [4][16][2]
+    __syncthreads();                                       // every warp is done with the key/value stages
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = (lane >> 2) + half * 8;
+      float* dst = mo + (warp * 16 + r) * D + (lane & 3) * 2;
 #pragma unroll
       for (int n = 0; n < D / 8; ++n) {
         dst[n * 8] = o[n][half * 2];
         dst[n * 8 + 1] = o[n][half * 2 + 1];
       }
       if ((lane & 3) == 0) {
-        float* ml = part_ml + ((row * Hq + head) * n_spans + span) * 2;
-        ml[0] = mrow;
-        ml[1] = l;
+        mml[(warp * 16 + r) * 2] = half ? m_hi : m_lo;
+        mml[(warp * 16 + r) * 2 + 1] = half ? l_hi : l_lo;
       }
+    }
+    __syncthreads();
+    for (int i = tid; i < 16 * (D / 2); i += 128) {
+      const int r = i / (D / 2), col = (i % (D / 2)) * 2;
+      if (r >= nq * G) continue;
+      float mrow = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mrow = fmaxf(mrow, mml[(w * 16 + r) * 2]);
+      float l = 0.f, o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = mml[(w * 16 + r) * 2];
+        const float f = mw == -INFINITY ? 0.f : exp2f(mw - mrow);
+        l += f * mml[(w * 16 + r) * 2 + 1];
+        o0 += f * mo[(w * 16 + r) * D + col];
+        o1 += f * mo[(w * 16 + r) * D + col + 1];
+      }
+      emit(r, col, o0, o1, mrow, l, col == 0);
     }
   }
 }
 
-template <int D>
+template <int D, bool KEYSPLIT, int STAGES>
 static int launch_mma(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int max_pages,
                       int page_size, const int* tiles, int n_tiles, const int* positions, float scale, int window,
                       void* out, float* part_o, float* part_ml, int n_spans, int split, int Hq, int Hk, int* status,
                       cudaStream_t stream) {
-  constexpr int SMEM = 5 * 64 * D * 2;
+  constexpr int SMEM = ((KEYSPLIT ? 16 : 64) + 2 * STAGES * 64) * D * 2;
+  static_assert(!KEYSPLIT || 4 * 16 * (D + 2) * 4 <= 2 * STAGES * 64 * D * 2, "the merge buffer reuses the stages");
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D, KEYSPLIT, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     set = true;
   }
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size;) ++page_shift;
   dim3 grid(n_tiles, Hk, split ? n_spans : 1);
-  return (int)launch_chained(attention_mma_kernel<D>, grid, dim3(128), SMEM, stream, (const bf16*)q, (const bf16*)k_cache,
-                             (const bf16*)v_cache, block_table, max_pages, page_size, tiles, positions, scale, window,
-                             (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status);
+  return (int)launch_chained(attention_mma_kernel<D, KEYSPLIT, STAGES>, grid, dim3(128), SMEM, stream, (const bf16*)q,
+                             (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size, page_shift,
+                             tiles, positions, scale, window, (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status);
 }
 
 }  // namespace tl
@@ -296,12 +362,13 @@ extern "C" int tl_attention_mma_supported(int Hq, int Hk, int D) {
 }
 
 // tiles: int32 [n_tiles, 3] = (request index, first row, query rows <= tile_rows), rows of a tile consecutive in position.
-// With split, scratch holds rows * Hq * n_spans * (D + 2) floats and the caller runs the join afterwards
-// (tl_attention_join) when n_spans > 1.
+// max_tile_rows: the most query rows any tile holds; when they and their heads fit 16 M rows (decoding), the kernel
+// form that splits the keys among the warps runs. With split, scratch holds rows * Hq * n_spans * (D + 2) floats and
+// the caller runs the join afterwards (tl_attention_join) when n_spans > 1.
 extern "C" int tl_paged_attention_mma(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                      int max_pages, int page_size, const int* tiles, int n_tiles, const int* positions,
-                                      float scale, int window, void* out, float* scratch, int rows, int Hq, int Hk, int D,
-                                      int n_spans, int split, int* status, cudaStream_t stream) {
+                                      int max_pages, int page_size, const int* tiles, int n_tiles, int max_tile_rows,
+                                      const int* positions, float scale, int window, void* out, float* scratch, int rows,
+                                      int Hq, int Hk, int D, int n_spans, int split, int* status, cudaStream_t stream) {
   if (rows == 0 || n_tiles == 0) return 0;
   TL_REQUIRE(tl_attention_mma_supported(Hq, Hk, D), "attention (tensor cores): %d heads over %d KV heads of size %d", Hq, Hk, D);
   TL_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "attention: page size %d, table width %d, window %d", page_size,
@@ -309,11 +376,15 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_cache, const 
   TL_REQUIRE(!split || (scratch && n_spans >= 1 && n_spans <= 65535 && split % KT == 0),
              "attention: split over %d spans of %d keys (a multiple of %d) needs scratch", n_spans, split, KT);
   TL_REQUIRE(Hk <= 65535, "attention: %d KV heads exceed the grid limit", Hk);
+  TL_REQUIRE(max_tile_rows >= 1 && max_tile_rows <= tl_attention_mma_tile_rows(Hq, Hk),
+             "attention: tiles of %d query rows, at most %d fit", max_tile_rows, tl_attention_mma_tile_rows(Hq, Hk));
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (long long)rows * Hq * n_spans * D : nullptr;
-  int e = D == 64 ? launch_mma<64>(q, k_cache, v_cache, block_table, max_pages, page_size, tiles, n_tiles, positions, scale,
-                                   window, out, part_o, part_ml, n_spans, split, Hq, Hk, status, stream)
-                  : launch_mma<128>(q, k_cache, v_cache, block_table, max_pages, page_size, tiles, n_tiles, positions, scale,
-                                    window, out, part_o, part_ml, n_spans, split, Hq, Hk, status, stream);
-  return e;
+  const bool keysplit = max_tile_rows * (Hq / Hk) <= 16;
+#define TL_MMA(D_, KS_, ST_)                                                                                               \
+  launch_mma<D_, KS_, ST_>(q, k_cache, v_cache, block_table, max_pages, page_size, tiles, n_tiles, positions, scale, window, \
+                           out, part_o, part_ml, n_spans, split, Hq, Hk, status, stream)
+  if (D == 64) return keysplit ? TL_MMA(64, true, 4) : TL_MMA(64, false, 2);
+  return keysplit ? TL_MMA(128, true, 3) : TL_MMA(128, false, 2);
+#undef TL_MMA
 }

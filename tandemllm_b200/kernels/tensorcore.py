@@ -43,8 +43,8 @@ def lib():
         l.tl_tc_token_tile.argtypes = [c_int, c_int]
         l.tl_tc_token_tile.restype = c_int
         l.tl_tc_last_error.restype = ctypes.c_char_p
-        l.tl_paged_attention_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
-                                             ctypes.c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+        l.tl_paged_attention_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                                             c_void_p, ctypes.c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                              c_int, c_void_p, c_void_p]
         l.tl_paged_attention_mma.restype = c_int
         l.tl_attention_mma_tile_rows.argtypes = [c_int, c_int]
@@ -180,7 +180,8 @@ class TensorCore:
         Hk = cache.k.shape[1]
         if q.dtype != torch.bfloat16 or not lib().tl_attention_mma_supported(Hq, Hk, D):
             return False
-        tiles = self.query_tiles(step, lib().tl_attention_mma_tile_rows(Hq, Hk))
+        tile_rows = lib().tl_attention_mma_tile_rows(Hq, Hk)
+        tiles = self.query_tiles(step, tile_rows)
         n_tiles = tiles.shape[0]
         # Few tiles and long contexts (decoding): split the keys over CTAs as well, in spans long enough that a CTA's
         # start-up is a small part of its work and short enough that the grid still has a few CTAs per SM.
@@ -195,8 +196,8 @@ class TensorCore:
         scratch = runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans)) if span_keys else None
         code = lib().tl_paged_attention_mma(
             q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
-            tiles.data_ptr(), n_tiles, step.positions.data_ptr(), float(scale), int(window or 0), out.data_ptr(),
-            ops.ptr(scratch), R, Hq, Hk, D, spans, span_keys, self.status.data_ptr(), ops.stream())
+            tiles.data_ptr(), n_tiles, min(tile_rows, step.max_rows_per_request), step.positions.data_ptr(),
+            float(scale), int(window or 0), out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, span_keys, self.status.data_ptr(), ops.stream())
         _check(code, "attention_mma")
         if span_keys:
             ops.attention_join(scratch, step.positions, window, out, spans, span_keys)

@@ -109,12 +109,28 @@ def test_grouped_experts_with_swiglu(R, E, k, H, I):
 def test_attention_on_tensor_cores(split, Hq, Hk, D, page, window):
     """Prompt portions of several lengths, a sequence's first rows and decode rows at short and long contexts in
     one call, unsplit and split over key spans, against whole-sequence attention."""
+    attention_against_plain([700, 90, 7, 300, 513], [1, 23, 7, 150, 1], split, Hq, Hk, D, page, window)
+
+
+@pytest.mark.parametrize("split", [0, 64, 256])
+@pytest.mark.parametrize("Hq,Hk,D,page,window,news", [
+    (8, 2, 64, 16, None, [1, 1, 1, 1, 1, 1, 1]), (32, 8, 64, 16, None, [1, 1, 1, 1, 1, 1, 1]),
+    (16, 1, 64, 16, 100, [1, 1, 1, 1, 1, 1, 1]), (6, 2, 128, 32, None, [1, 1, 1, 1, 1, 1, 1]),
+    (8, 2, 64, 24, 70, [4, 2, 3, 1, 4, 1, 2]), (3, 3, 128, 16, None, [16, 5, 7, 1, 9, 2, 16]),
+    (5, 1, 64, 64, 300, [3, 1, 2, 3, 1, 1, 3])])
+def test_attention_of_small_tiles_splits_the_keys_among_warps(split, Hq, Hk, D, page, window, news):
+    """Tiles whose rows and heads fit 16 M rows (decoding, and portions of a few rows) run the kernel form in which
+    each warp takes a quarter of every key tile: contexts that end inside a warp's quarter, at a tile's edge, a
+    sequence's first rows, page sizes that are no power of two."""
+    attention_against_plain([700, 90, 16, 300, 513, 64, 65], news, split, Hq, Hk, D, page, window)
+
+
+def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window):
     import types
 
     from tandemllm_b200.kernels import ops, tensorcore
     from tests.test_gpu_kernels import paged_setup, plain_attention
     impl, rt = tc()
-    seqs, news = [700, 90, 7, 300, 513], [1, 23, 7, 150, 1]
     kc, vc, table, ks, vs = paged_setup(seqs, Hk, D, page, torch.bfloat16, seed=60)
     R = sum(news)
     q = rnd(R, Hq, D, seed=61)
@@ -135,7 +151,8 @@ def test_attention_on_tensor_cores(split, Hq, Hk, D, page, window):
     scale = 0.9 / D ** 0.5
     qd, kd, vd, td = q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV)      # kept alive until the kernel has run
     code = lib.tl_paged_attention_mma(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(),
-                                      table.shape[1], page, tiles.data_ptr(), tiles.shape[0], pos_dev.data_ptr(), scale,
+                                      table.shape[1], page, tiles.data_ptr(), tiles.shape[0], int(tiles[:, 2].max()),
+                                      pos_dev.data_ptr(), scale,
                                       window or 0, out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, int(split),
                                       rt.status.data_ptr(), ops.stream())
     assert code == 0
