@@ -11,12 +11,12 @@ namespace tl {
 constexpr int MAX_EXPERTS = 1024;
 constexpr int MAX_TOP_K = 32;
 
-// `lg`: the row's E logits (global or shared memory). Lanes 0..k-1 write ids[lane] and wts[lane], in the order
-// of the choice (best first).
-__device__ __forceinline__ void warp_route(const float* lg, const float* __restrict__ bias, int E, int k, int normalize,
-                                           float floor_, float scale, int* ids, float* wts) {
+// `lg`: the row's E <= 32 PER logits (global or shared memory). Lanes 0..k-1 write ids[lane] and wts[lane], in the
+// order of the choice (best first). PER: experts a lane holds.
+template <int PER>
+__device__ __forceinline__ void warp_route_sized(const float* lg, const float* __restrict__ bias, int E, int k,
+                                                 int normalize, float floor_, float scale, int* ids, float* wts) {
   const int lane = threadIdx.x & 31;
-  constexpr int PER = MAX_EXPERTS / 32;
   float score[PER], choice[PER];
 #pragma unroll
   for (int t = 0; t < PER; ++t) {
@@ -87,6 +87,13 @@ __device__ __forceinline__ void warp_route(const float* lg, const float* __restr
     ids[lane] = my_id;
     wts[lane] = w * scale;
   }
+}
+
+__device__ __forceinline__ void warp_route(const float* lg, const float* __restrict__ bias, int E, int k, int normalize,
+                                           float floor_, float scale, int* ids, float* wts) {
+  if (E <= 32) warp_route_sized<1>(lg, bias, E, k, normalize, floor_, scale, ids, wts);
+  else if (E <= 128) warp_route_sized<4>(lg, bias, E, k, normalize, floor_, scale, ids, wts);
+  else warp_route_sized<MAX_EXPERTS / 32>(lg, bias, E, k, normalize, floor_, scale, ids, wts);
 }
 
 }  // namespace tl

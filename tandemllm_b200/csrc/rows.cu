@@ -67,6 +67,49 @@ struct NormParams {
 // so that the weights are read once per block and not once per row.
 constexpr int MAX_ROWS_PER_BLOCK = 8;
 
+// logits[rr, e] = rows[rr] . router_w[e] for the block's n_rows <= ROWS rows (in shared memory). Sixteen-byte loads,
+// eight of them in flight a lane, when the width allows.
+template <int ROWS>
+__device__ __forceinline__ void router_logits(const NormParams& p, const float* rows, float* logits, int n_rows, int lane,
+                                              int warp, int nwarps) {
+  const int hidden = p.hidden;
+  for (int e = warp; e < p.E; e += nwarps) {
+    const float* w = p.router_w + (size_t)e * hidden;
+    float acc[ROWS];
+#pragma unroll
+    for (int rr = 0; rr < ROWS; ++rr) acc[rr] = 0.f;
+    if ((hidden & 3) == 0) {
+      const int h4 = hidden >> 2;
+      const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll 8
+      for (int c = lane; c < h4; c += 32) {
+        const float4 wv = __ldg(w4 + c);
+#pragma unroll
+        for (int rr = 0; rr < ROWS; ++rr)
+          if (rr < n_rows) {
+            const float4 x = reinterpret_cast<const float4*>(rows + (size_t)rr * hidden)[c];
+            acc[rr] = fmaf(x.w, wv.w, fmaf(x.z, wv.z, fmaf(x.y, wv.y, fmaf(x.x, wv.x, acc[rr]))));
+          }
+      }
+    } else {
+#pragma unroll 4
+      for (int c = lane; c < hidden; c += 32) {
+        const float wv = __ldg(w + c);
+#pragma unroll
+        for (int rr = 0; rr < ROWS; ++rr)
+          if (rr < n_rows) acc[rr] = fmaf(rows[(size_t)rr * hidden + c], wv, acc[rr]);
+      }
+    }
+#pragma unroll
+    for (int rr = 0; rr < ROWS; ++rr) {
+      if (rr < n_rows) {
+        const float v = warp_sum(acc[rr]);
+        if (lane == 0) logits[rr * p.E + e] = v;
+      }
+    }
+  }
+}
+
 // One block per output row.
 //   gather == nullptr: row r:  residual[r] += added[r];  normed[r] = w * residual[r] * rsqrt(mean + eps)
 //   gather != nullptr: output row i reads row gather[i] and leaves the residual as it is (the final norm of the
@@ -194,27 +237,11 @@ __global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
   if (!p.router_w) return;
   __syncthreads();
   // logits[row, e] = row . router_w[e]: each warp takes experts warp, warp + nwarps, ...; lanes stride over the
-  // columns; an expert's weights are read once for all rows of the block
+  // columns; an expert's weights are read once for all rows of the block. A row's sum is built in the same order
+  // whether the block holds one row or several.
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int e = warp; e < p.E; e += nwarps) {
-    const float* w = p.router_w + (size_t)e * hidden;
-    float acc[MAX_ROWS_PER_BLOCK];
-#pragma unroll
-    for (int rr = 0; rr < MAX_ROWS_PER_BLOCK; ++rr) acc[rr] = 0.f;
-    for (int c = lane; c < hidden; c += 32) {
-      const float wv = w[c];
-#pragma unroll
-      for (int rr = 0; rr < MAX_ROWS_PER_BLOCK; ++rr)
-        if (rr < n_rows) acc[rr] = fmaf(rows_buf[(size_t)rr * hidden + c], wv, acc[rr]);
-    }
-#pragma unroll
-    for (int rr = 0; rr < MAX_ROWS_PER_BLOCK; ++rr) {
-      if (rr < n_rows) {
-        const float v = warp_sum(acc[rr]);
-        if (lane == 0) logits[rr * p.E + e] = v;
-      }
-    }
-  }
+  if (n_rows == 1) router_logits<1>(p, rows_buf, logits, 1, lane, warp, nwarps);
+  else router_logits<MAX_ROWS_PER_BLOCK>(p, rows_buf, logits, n_rows, lane, warp, nwarps);
   __syncthreads();
   for (int rr = warp; rr < n_rows; rr += nwarps)
     warp_route(logits + rr * p.E, p.router_bias, p.E, p.route_k, p.normalize, p.floor_, p.scale,

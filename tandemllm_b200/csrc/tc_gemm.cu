@@ -142,9 +142,11 @@ struct Smem {
   // with SWIGLU the weight side is loaded twice (gate rows and up rows)
   static constexpr int W_TILES = SWIGLU ? 2 : 1;
   static constexpr int STAGE_BYTES = SWAP ? (W_TILES * A_BYTES + B_BYTES) : (A_BYTES + W_TILES * B_BYTES);
-  // The swapped (weight-streaming) form takes the whole SM's shared memory for a deep ring. The plain form keeps to
-  // about half of it, so that two CTAs share an SM and one's epilogue runs under the other's main loop.
-  static constexpr int BUDGET = SWAP ? 200 * 1024 : 100 * 1024;
+  // Every form but the experts' gate/up product keeps to about half of an SM's shared memory, so that two CTAs share
+  // an SM: one's epilogue runs under the other's main loop, and with chained launches the next product's CTA sits
+  // beside the running one with its first weight tiles already on the way. The gate/up product streams two weight
+  // tiles a stage and takes the whole SM for a ring that is deep enough.
+  static constexpr int BUDGET = (SWAP && SWIGLU) ? 200 * 1024 : 100 * 1024;
   static constexpr int FIT = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = FIT > 8 ? 8 : (FIT < 2 ? 2 : FIT);
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -157,8 +159,11 @@ template <int BN, bool SWAP, bool SWIGLU, typename TOut>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW,
                                                       const __grid_constant__ CUtensorMap tmX, TcParams p) {
   using S = Smem<BN, SWAP, SWIGLU>;
+  // Chained launches: the weights are written by no kernel, so a product without a tile map sets itself up and
+  // requests its first weight tiles before it waits for the kernels in front of it; only the token rows, and
+  // everything a grouped product reads through the tile map, have to wait.
   chain_next();
-  chain_wait();       // the tile map and the operands are written by the kernels before this one
+  if (p.tile_group) chain_wait();
   // ---- which tile ----
   int tok0, tok_rows;
   long long w_base = 0;                 // first weight row of this tile's group in the weight tensor
@@ -217,7 +222,32 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   if (warp == 0 && lane == 0) {
     // ---- producer ----
     int issued = 0;
-    for (int i = 0; i < num_kb; ++i) {
+    auto load_weights = [&](int i) {
+      const int s = i % S::STAGES;
+      uint8_t* st = tiles + s * S::STAGE_BYTES;
+      mbar_expect_tx(&full[s], S::STAGE_BYTES);
+      const int kx = (kb_begin + i) * TILE_K;
+      if (SWAP) {
+        tma_load_2d(st, mapA, &full[s], kx, rowA);
+        if (SWIGLU) tma_load_2d(st + S::A_BYTES, mapA, &full[s], kx, rowW2);
+      } else {
+        tma_load_2d(st + S::A_BYTES, mapB, &full[s], kx, rowB);
+        if (SWIGLU) tma_load_2d(st + S::A_BYTES + S::B_BYTES, mapB, &full[s], kx, rowW2);
+      }
+    };
+    auto load_tokens = [&](int i) {
+      const int s = i % S::STAGES;
+      uint8_t* st = tiles + s * S::STAGE_BYTES;
+      const int kx = (kb_begin + i) * TILE_K;
+      if (SWAP) tma_load_2d(st + S::W_TILES * S::A_BYTES, mapB, &full[s], kx, rowB);
+      else tma_load_2d(st, mapA, &full[s], kx, rowA);
+    };
+    const int ahead = p.tile_group ? 0 : min(num_kb, S::STAGES);      // the ring's first fill: weights first
+    for (int i = 0; i < ahead; ++i) load_weights(i);
+    if (!p.tile_group) chain_wait();
+    for (int i = 0; i < ahead; ++i) load_tokens(i);
+    issued = ahead;
+    for (int i = ahead; i < num_kb; ++i) {
       const int s = i % S::STAGES;
       if (i >= S::STAGES && !mbar_wait(&empty[s], ((i / S::STAGES) - 1) & 1)) {
         *aborted = 1;
@@ -225,18 +255,8 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
         break;
       }
       if (*aborted) break;
-      uint8_t* st = tiles + s * S::STAGE_BYTES;
-      mbar_expect_tx(&full[s], S::STAGE_BYTES);
-      const int kx = (kb_begin + i) * TILE_K;
-      if (SWAP) {
-        tma_load_2d(st, mapA, &full[s], kx, rowA);
-        if (SWIGLU) tma_load_2d(st + S::A_BYTES, mapA, &full[s], kx, rowW2);
-        tma_load_2d(st + S::W_TILES * S::A_BYTES, mapB, &full[s], kx, rowB);
-      } else {
-        tma_load_2d(st, mapA, &full[s], kx, rowA);
-        tma_load_2d(st + S::A_BYTES, mapB, &full[s], kx, rowB);
-        if (SWIGLU) tma_load_2d(st + S::A_BYTES + S::B_BYTES, mapB, &full[s], kx, rowW2);
-      }
+      load_weights(i);
+      load_tokens(i);
       issued = i + 1;
     }
     if (*aborted) {
@@ -275,6 +295,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     const int quad = warp & 3;
     const int m_row = quad * 32 + lane;                  // row of the M side this thread owns
     bool ok = num_kb > 0 ? mbar_wait(acc_ready, 0) : true;
+    if (num_kb == 0) chain_wait();      // an empty k range writes zeros, and nothing else has ordered them behind the kernels in front
     if (!ok) {
       *aborted = 1;
       atomicExch(p.status, 11);
