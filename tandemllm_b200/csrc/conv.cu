@@ -9,7 +9,8 @@
 // from the request's state slot (the K-1 inputs before the step, oldest first, 32-bit); an input before
 // position 0 of the sequence is zero whatever the slot holds. bx is formed in 32-bit from the stored
 // bcx in both cases, so a row's result does not depend on where the prompt was cut.
-// The state is rewritten by a second kernel after every row has read it.
+// The state is rewritten by a second kernel after every row has read it. A step of single rows (decoding) runs one
+// kernel that does both.
 #include "common.cuh"
 
 namespace tl {
@@ -87,6 +88,60 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, float* __rest
   for (int s = 0; s < S; ++s) st[(long long)s * hidden + c] = keep[s];
 }
 
+// A step in which every request has one row (decoding): the convolution and the state's shift in one kernel, one
+// thread a (request, channel). The projection's output may come as `parts` 32-bit partial sums [parts, rows, 3H]
+// (a product split along k): they are added in order and rounded to T first, as the separate reduction would have.
+// Results equal those of the two kernels above bit for bit.
+template <typename T>
+__global__ void short_conv_decode_kernel(const T* __restrict__ bcx, const float* __restrict__ partial, int parts,
+                                         long long part_stride, const float* __restrict__ taps,
+                                         const float* __restrict__ bias, float* __restrict__ state,
+                                         const int* __restrict__ state_slot, const int* __restrict__ req_of_row,
+                                         const int* __restrict__ positions, T* __restrict__ y, int hidden, int K,
+                                         int write_state) {
+  chain_next();
+  chain_wait();
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= hidden) return;
+  const int b = req_of_row[r];
+  const int pos = positions[r];
+  const long long ld = 3LL * hidden;
+  float in[3];                                   // B, C, x of this row and channel
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    const long long at = (long long)r * ld + (long long)j * hidden + c;
+    if (partial) {
+      float acc = 0.f;
+      for (int s = 0; s < parts; ++s) acc += partial[(long long)s * part_stride + at];
+      in[j] = to_f32(from_f32<T>(acc));
+    } else {
+      in[j] = to_f32(bcx[at]);
+    }
+  }
+  const float bx = in[0] * in[2];
+  const int S = K - 1;
+  float* st = state + ((long long)state_slot[b] * S) * hidden;
+  float old[MAX_TAPS];
+#pragma unroll 1
+  for (int s = 0; s < S; ++s) old[s] = st[(long long)s * hidden + c];
+  float acc = bias ? bias[c] : 0.f;
+#pragma unroll 1
+  for (int j = 0; j < K; ++j) {
+    const int back = K - 1 - j;
+    if (pos - back < 0) continue;                // before the sequence's first token: zero
+    const float v = back == 0 ? bx : old[S - back];
+    acc = fmaf(taps[(long long)c * K + j], v, acc);
+  }
+  y[(long long)r * hidden + c] = from_f32<T>(in[1] * acc);
+  if (write_state) {
+#pragma unroll 1
+    for (int s = 0; s + 1 < S; ++s)              // old entry s + 1 sits S - (s + 1) inputs before this row
+      st[(long long)s * hidden + c] = (pos - (S - (s + 1)) >= 0) ? old[s + 1] : 0.f;
+    st[(long long)(S - 1) * hidden + c] = bx;
+  }
+}
+
 }  // namespace tl
 
 using namespace tl;
@@ -123,5 +178,26 @@ extern "C" int tl_short_conv_state(const void* bcx, float* state, const int* sta
   else
     e = launch_chained(short_conv_state_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)bcx, state, state_slot,
                        row_start, positions, hidden, K);
+  return (int)e;
+}
+
+// One row a request. `partial` (or null) holds the projection's output as `parts` partial sums, `part_stride` floats
+// apart; else `bcx` holds it.
+extern "C" int tl_short_conv_decode(const void* bcx, const float* partial, int parts, long long part_stride,
+                                    const float* taps, const float* bias, float* state, const int* state_slot,
+                                    const int* req_of_row, const int* positions, void* y, int rows, int hidden, int K,
+                                    int dtype, int write_state, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  TL_REQUIRE(rows > 0 && hidden > 0 && (bcx || (partial && parts >= 1)), "short_conv_decode: rows %d hidden %d", rows, hidden);
+  TL_REQUIRE(K >= 2 && K <= MAX_TAPS, "short_conv_decode: %d taps; 2..%d are implemented", K, MAX_TAPS);
+  dim3 grid(rows, ceil_div(hidden, 128));
+  TL_REQUIRE(grid.y <= 65535, "short_conv_decode: hidden size %d exceeds the grid limit", hidden);
+  cudaError_t e;
+  if (dtype == TL_FP32)
+    e = launch_chained(short_conv_decode_kernel<float>, grid, dim3(128), 0, stream, (const float*)bcx, partial, parts,
+                       part_stride, taps, bias, state, state_slot, req_of_row, positions, (float*)y, hidden, K, write_state);
+  else
+    e = launch_chained(short_conv_decode_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)bcx, partial, parts,
+                       part_stride, taps, bias, state, state_slot, req_of_row, positions, (bf16*)y, hidden, K, write_state);
   return (int)e;
 }

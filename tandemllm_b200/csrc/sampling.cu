@@ -72,20 +72,43 @@ __device__ __forceinline__ Best block_best(Best x, Best* scratch) {
   return scratch[32];
 }
 
+// This thread's best of a row it strides over: 16-byte loads, eight in flight, when the row allows
+__device__ __forceinline__ Best row_best(const float* __restrict__ row, int V) {
+  Best b;
+  b.v = -INFINITY;
+  b.i = 0x7fffffff;
+  if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 8
+    for (int i = threadIdx.x; i < (V >> 2); i += blockDim.x) {
+      const float4 x = row4[i];
+      const float v[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        Best c;
+        c.v = v[j];
+        c.i = 4 * i + j;
+        if (c.v == c.v) b = better(b, c);
+      }
+    }
+  } else {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      Best c;
+      c.v = row[i];
+      c.i = i;
+      if (c.v == c.v) b = better(b, c);
+    }
+  }
+  return b;
+}
+
 // one block per row; the lowest index wins a tie; NaN is never the maximum
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, long long ld, int V,
                                                       int* __restrict__ out) {
   __shared__ Best scratch[33];
   const float* row = logits + (long long)blockIdx.x * ld;
-  Best b;
-  b.v = -INFINITY;
-  b.i = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    Best c;
-    c.v = row[i];
-    c.i = i;
-    if (c.v == c.v) b = better(b, c);
-  }
+  Best b = row_best(row, V);
   b = block_best(b, scratch);
   if (threadIdx.x == 0) out[blockIdx.x] = b.i == 0x7fffffff ? 0 : b.i;
 }
@@ -105,12 +128,7 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
   b.v = -INFINITY;
   b.i = 0x7fffffff;
   if (!(T > 0.f)) {
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      Best c;
-      c.v = row[i];
-      c.i = i;
-      if (c.v == c.v) b = better(b, c);
-    }
+    b = row_best(row, V);
     b = block_best(b, best_scratch);
     if (threadIdx.x == 0) out[n] = b.i == 0x7fffffff ? 0 : b.i;
     return;

@@ -142,11 +142,11 @@ struct Smem {
   // with SWIGLU the weight side is loaded twice (gate rows and up rows)
   static constexpr int W_TILES = SWIGLU ? 2 : 1;
   static constexpr int STAGE_BYTES = SWAP ? (W_TILES * A_BYTES + B_BYTES) : (A_BYTES + W_TILES * B_BYTES);
-  // Every form but the experts' gate/up product keeps to about half of an SM's shared memory, so that two CTAs share
-  // an SM: one's epilogue runs under the other's main loop, and with chained launches the next product's CTA sits
-  // beside the running one with its first weight tiles already on the way. The gate/up product streams two weight
-  // tiles a stage and takes the whole SM for a ring that is deep enough.
-  static constexpr int BUDGET = (SWAP && SWIGLU) ? 200 * 1024 : 100 * 1024;
+  // Every form keeps to about half of an SM's shared memory (the swapped gate/up product, with two weight tiles a
+  // stage, a little more for a third stage), so that two CTAs share an SM: one's epilogue runs under the other's main loop, and with chained launches the next product's CTA sits
+  // beside the running one with its first weight tiles already on the way. Two CTAs an SM also put a decode step's
+  // expert tiles (a few hundred CTAs) into one wave.
+  static constexpr int BUDGET = (SWAP && SWIGLU) ? 110 * 1024 : 100 * 1024;
   static constexpr int FIT = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = FIT > 8 ? 8 : (FIT < 2 ? 2 : FIT);
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;

@@ -44,6 +44,8 @@ _SIGNATURES = {
     "tl_gemm_simt_tile_rows": [],
     "tl_short_conv": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_int, c_int, c_void_p],
+    "tl_short_conv_decode": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tl_short_conv_state": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "tl_qk_prepare": [c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                       c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -126,13 +128,18 @@ def embed_rows(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tensor
 
 
 class PartialSums:
-    """A branch output still in `parts` partial sums [parts, rows, hidden] (32-bit), to be added in order."""
+    """A product's output still in `parts` partial sums [parts, rows, hidden] (32-bit), to be added in order and, when
+    `dtype` is given, rounded to it (what the product's own reduction would have stored)."""
 
-    def __init__(self, data: torch.Tensor, parts: int, rows: int, hidden: int):
-        self.data, self.parts, self.rows, self.hidden = data, parts, rows, hidden
+    def __init__(self, data: torch.Tensor, parts: int, rows: int, hidden: int, dtype: torch.dtype | None = None):
+        self.data, self.parts, self.rows, self.hidden, self.dtype = data, parts, rows, hidden, dtype
 
     def materialize(self) -> torch.Tensor:
-        return self.data[:self.parts * self.rows * self.hidden].view(self.parts, self.rows, self.hidden).sum(0)
+        parts = self.data[:self.parts * self.rows * self.hidden].view(self.parts, self.rows, self.hidden)
+        total = torch.zeros_like(parts[0])
+        for part in parts:
+            total += part
+        return total if self.dtype is None else total.to(self.dtype)
 
 
 class ExpertRows:
@@ -235,6 +242,25 @@ def short_conv(bcx, taps, bias, state, state_slot, req_of_row, row_start, positi
     check(core().tl_short_conv(ptr(bcx), ptr(taps), ptr(bias), ptr(state), ptr(state_slot), ptr(req_of_row),
                                ptr(row_start), ptr(positions), ptr(out), rows, hidden, K, dtype_code(out.dtype),
                                stream()), "short_conv")
+    return out
+
+
+def short_conv_decode(bcx, taps, bias, state, state_slot, req_of_row, positions, out, write_state: bool = True):
+    """The convolution and the state's shift for a step of one row a request; `bcx` a tensor or `PartialSums`."""
+    _need(taps, torch.float32, "taps"); _need(state, torch.float32, "conv state")
+    rows, hidden = out.shape
+    partial, parts, stride, data = None, 0, 0, None
+    if isinstance(bcx, PartialSums):
+        if bcx.dtype not in (None, out.dtype) or bcx.hidden != 3 * hidden or bcx.rows != rows:
+            raise KernelError("short_conv_decode: partial sums of another shape or precision")
+        partial, parts, stride = bcx.data, bcx.parts, bcx.rows * bcx.hidden
+    else:
+        _need(bcx, out.dtype, "bcx")
+        data = bcx
+    check(core().tl_short_conv_decode(ptr(data), ptr(partial), parts, stride, ptr(taps), ptr(bias), ptr(state),
+                                      ptr(state_slot), ptr(req_of_row), ptr(positions), ptr(out), rows, hidden,
+                                      taps.shape[1], dtype_code(out.dtype), int(write_state), stream()),
+          "short_conv_decode")
     return out
 
 

@@ -107,7 +107,9 @@ class TensorCore:
                 splits = max(1, min(kb // 4, -(-SM_COUNT // ctas), 16))
                 if splits > 1:
                     partial = self.workspace(splits * M * N)
-        deferred = defer and splits > 1 and out.dtype == torch.float32
+        # `defer` True: a 32-bit result may stay in partial sums; "rounded": so may one of any precision, and its
+        # consumer rounds the sum to the output's precision
+        deferred = bool(defer) and splits > 1 and (out.dtype == torch.float32 or defer == "rounded")
         tg = tr0 = trs = nt = None
         max_tiles = 0
         if plan is not None:
@@ -118,7 +120,9 @@ class TensorCore:
             ops.ptr(tg), ops.ptr(tr0), ops.ptr(trs), ops.ptr(nt), max_tiles, splits, ops.ptr(partial), int(not deferred),
             self.status.data_ptr(), ops.stream())
         _check(code, "gemm_tc", kernels=2 if splits > 1 and not deferred else 1)
-        return ops.PartialSums(partial, splits, M, N) if deferred else None
+        if not deferred:
+            return None
+        return ops.PartialSums(partial, splits, M, N, None if out.dtype == torch.float32 else out.dtype)
 
     def linear(self, x, w, bias, out, defer: bool = False):
         """False when the kernels do not take these operands; else True, or the deferred partial sums."""

@@ -6,8 +6,9 @@ with 32-bit accumulation. The reference routes every product through one functio
 (`lin`, engine/models/lfm2_moe/ref.py:99-103; engine.py:184-197).
 
 With `defer` (a branch's last product, whose result only goes into the residual) the result may come back as
-`ops.PartialSums` instead of a tensor: partial sums that the consuming norm kernel adds itself.
-`ops.materialize` turns any such result into a plain tensor.
+`ops.PartialSums` instead of a tensor: partial sums that the consuming norm kernel adds itself. `defer="rounded"`
+allows the same for a result of any precision, whose consumer adds the sums and rounds them as the product would
+have. `ops.materialize` turns any such result into a plain tensor.
 """
 
 from __future__ import annotations

@@ -59,8 +59,14 @@ class ShortConvMixer(Part):
 
     def forward(self, x, step, cache, writes_cache: bool = True):
         H = self.hidden_size
-        bcx = linear(self.runtime, x, self.w_in, self.b_in)
         y = torch.empty(x.shape[0], H, dtype=x.dtype, device=x.device)
+        if step.max_rows_per_request == 1:
+            # decoding: one kernel convolves and shifts the state, and adds the projection's partial sums itself
+            bcx = linear(self.runtime, x, self.w_in, self.b_in, defer="rounded")
+            ops.short_conv_decode(bcx, self.w_taps, self.b_taps, cache.state, step.state_slot, step.req_of_row,
+                                  step.positions, y, write_state=writes_cache)
+            return linear(self.runtime, y, self.w_out, self.b_out, out_dtype=torch.float32, defer=True)
+        bcx = linear(self.runtime, x, self.w_in, self.b_in)
         ops.short_conv(bcx, self.w_taps, self.b_taps, cache.state, step.state_slot, step.req_of_row, step.row_start,
                        step.positions, y)
         if writes_cache:

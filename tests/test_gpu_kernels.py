@@ -288,6 +288,41 @@ def test_short_conv_mixed_batch_and_state(dtype, K, H, use_bias):
     assert torch.equal(st[1].cpu(), state[1]) and torch.equal(st[4].cpu(), state[4]), "other slots are untouched"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("K,H,use_bias", [(3, 200, False), (4, 96, True), (2, 64, False), (7, 300, True)])
+def test_short_conv_of_single_rows_in_one_kernel(dtype, K, H, use_bias):
+    """A step of one row a request (decoding) runs one kernel for the convolution and the state's shift: the same
+    numbers, bit for bit, as the two general kernels, from a stored projection and from its partial sums; sequences
+    at their first positions (inputs before position 0 are zero whatever the slot holds) beside later ones."""
+    o = ops()
+    starts, slots = [0, 1, 2, 5, 40], [2, 0, 3, 4, 6]
+    R = len(starts)
+    parts = torch.stack([rnd(R, 3 * H, seed=24 + i) for i in range(3)])           # [3, R, 3H] partial sums
+    total = torch.zeros(R, 3 * H)
+    for part in parts:
+        total += part
+    bcx = total.to(dtype)
+    taps_w, bias = rnd(H, K, seed=21), (rnd(H, seed=22) if use_bias else None)
+    state = rnd(7, K - 1, H, seed=23)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    dev = lambda t: None if t is None else t.to(DEV)
+    st_two, y_two = state.clone().to(DEV), torch.empty(R, H, dtype=dtype, device=DEV)
+    o.short_conv(bcx.to(DEV), dev(taps_w), dev(bias), st_two, i32(slots), i32(list(range(R))), i32(list(range(R + 1))),
+                 i32(starts), y_two)
+    o.short_conv_state(bcx.to(DEV), st_two, i32(slots), i32(list(range(R + 1))), i32(starts), R, H, K)
+    for source in ("stored", "partial sums"):
+        given = bcx.to(DEV) if source == "stored" else o.PartialSums(parts.to(DEV).contiguous(), 3, R, 3 * H,
+                                                                      None if dtype == torch.float32 else dtype)
+        st, y = state.clone().to(DEV), torch.empty(R, H, dtype=dtype, device=DEV)
+        o.short_conv_decode(given, dev(taps_w), dev(bias), st, i32(slots), i32(list(range(R))), i32(starts), y)
+        assert torch.equal(y, y_two), source
+        assert torch.equal(st, st_two), source
+        kept = state.clone().to(DEV)
+        o.short_conv_decode(given, dev(taps_w), dev(bias), kept, i32(slots), i32(list(range(R))), i32(starts), y,
+                            write_state=False)
+        assert torch.equal(y, y_two) and torch.equal(kept.cpu(), state), "a site that reads another's state leaves it"
+
+
 # ------------------------------------------------------------------------------------------ attention
 def plain_attention(q, k, v, scale, window=None):
     """q [T, Hq, D] for the last T positions of a sequence whose keys k, v [L, Hk, D] are all given."""
@@ -525,6 +560,11 @@ def test_argmax_and_sampling_match_the_plain_draws():
     out = torch.empty(n, dtype=torch.int32, device=DEV)
     o.argmax(logits.to(DEV), out)
     assert out.tolist() == [77 if i == 3 else int(logits[i].argmax()) for i in range(n)]
+    wide = rnd(3, 40000, seed=71)                              # a width that 16-byte loads take
+    wide[1, 39999] = wide[1, 5] = wide[1].max() + 1
+    wide[2, 7] = float("nan")
+    o.argmax(wide.to(DEV), out[:3])
+    assert out[:3].tolist() == [int(wide[0].argmax()), 5, int(torch.nan_to_num(wide[2], nan=-1e30).argmax())]
     temps = [0.0, 0.7, 1.0, 1.3, 0.7, 0.7, 1.0, 0.5, 2.0, 1.0, 0.9, 0.0]
     top_k = [0, 0, 50, 0, 5, 0, 20, 1, 0, 0, 3, 7]
     top_p = [1.0, 1.0, 1.0, 0.9, 1.0, 0.5, 0.95, 1.0, 0.3, 1.0, 0.8, 0.2]
