@@ -17,7 +17,44 @@ namespace tl {
 
 constexpr int MAX_TAPS = 16;
 
-template <typename T>
+// V consecutive elements as 32-bit values, with 16-byte accesses for V = 8
+template <typename T, int V> __device__ __forceinline__ void load_run(const T* __restrict__ p, float* out) {
+  if constexpr (V == 8 && sizeof(T) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      out[2 * i] = f.x;
+      out[2 * i + 1] = f.y;
+    }
+  } else if constexpr (V == 8) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) out[i] = to_f32(p[i]);
+  }
+}
+
+template <typename T, int V> __device__ __forceinline__ void store_run(T* __restrict__ p, const float* v) {
+  if constexpr (V == 8 && sizeof(T) == 2) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  } else if constexpr (V == 8) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < V; ++i) p[i] = from_f32<T>(v[i]);
+  }
+}
+
+// One thread: one row and V consecutive channels (V = 8 when the width is a multiple of 8, else 1).
+template <typename T, int V>
 __global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
                                   const float* __restrict__ bias, const float* __restrict__ state,
                                   const int* __restrict__ state_slot, const int* __restrict__ req_of_row,
@@ -26,30 +63,41 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __rest
   chain_next();
   chain_wait();
   const int r = blockIdx.x;
-  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
   if (c >= hidden) return;
   const int b = req_of_row[r];
   const int first = row_start[b];          // first row of this request in the step
   const int pos = positions[r];            // absolute position of row r
   const long long ld = 3LL * hidden;
   const float* st = state + ((long long)state_slot[b] * (K - 1)) * hidden;
-  float acc = bias ? bias[c] : 0.f;
+  float acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = bias ? bias[c + i] : 0.f;
   // tap j multiplies the input K-1-j rows back; tap K-1 the row itself
   for (int j = 0; j < K; ++j) {
     const int back = K - 1 - j;
     if (pos - back < 0) continue;            // before the sequence's first token: zero
     const int rr = r - back;
-    float v;
+    float v[V];
     if (rr >= first) {
       const T* row = bcx + (long long)rr * ld;
-      v = to_f32(row[c]) * to_f32(row[2 * hidden + c]);
+      float bv[V], xv[V];
+      load_run<T, V>(row + c, bv);
+      load_run<T, V>(row + 2 * hidden + c, xv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) v[i] = bv[i] * xv[i];
     } else {
       // (first - rr) rows before the step's first row: state index K-1 - (first - rr)
-      v = st[(long long)(K - 1 - (first - rr)) * hidden + c];
+      load_run<float, V>(st + (long long)(K - 1 - (first - rr)) * hidden + c, v);
     }
-    acc = fmaf(taps[(long long)c * K + j], v, acc);
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = fmaf(taps[(long long)(c + i) * K + j], v[i], acc[i]);
   }
-  y[(long long)r * hidden + c] = from_f32<T>(to_f32(bcx[(long long)r * ld + hidden + c]) * acc);
+  float cv[V];
+  load_run<T, V>(bcx + (long long)r * ld + hidden + c, cv);
+#pragma unroll
+  for (int i = 0; i < V; ++i) cv[i] *= acc[i];
+  store_run<T, V>(y + (long long)r * hidden + c, cv);
 }
 
 // new state = last K-1 of [old state ; this step's bx rows], per request and channel; one thread does both
@@ -152,16 +200,20 @@ extern "C" int tl_short_conv(const void* bcx, const float* taps, const float* bi
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && hidden > 0, "short_conv: rows %d hidden %d", rows, hidden);
   TL_REQUIRE(K >= 2 && K <= MAX_TAPS, "short_conv: %d taps; 2..%d are implemented", K, MAX_TAPS);
-  dim3 grid(rows, ceil_div(hidden, 256));
+  // 16-byte accesses when every row, of the projection, the state and the output, starts on a 16-byte boundary
+  const bool wide = hidden % 8 == 0 && ((uintptr_t)bcx % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)state % 16) == 0;
+  dim3 grid(rows, ceil_div(hidden, 128 * (wide ? 8 : 1)));
   TL_REQUIRE(grid.y <= 65535, "short_conv: hidden size %d exceeds the grid limit", hidden);
-  cudaError_t e;
-  if (dtype == TL_FP32)
-    e = launch_chained(short_conv_kernel<float>, grid, dim3(256), 0, stream, (const float*)bcx, taps, bias, state, state_slot,
-                       req_of_row, row_start, positions, (float*)y, hidden, K);
-  else
-    e = launch_chained(short_conv_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)bcx, taps, bias, state, state_slot,
-                       req_of_row, row_start, positions, (bf16*)y, hidden, K);
-  return (int)e;
+#define TL_CONV(T_, V_)                                                                                                   \
+  return (int)launch_chained(short_conv_kernel<T_, V_>, grid, dim3(128), 0, stream, (const T_*)bcx, taps, bias, state,    \
+                             state_slot, req_of_row, row_start, positions, (T_*)y, hidden, K)
+  if (dtype == TL_FP32) {
+    if (wide) TL_CONV(float, 8);
+    TL_CONV(float, 1);
+  }
+  if (wide) TL_CONV(bf16, 8);
+  TL_CONV(bf16, 1);
+#undef TL_CONV
 }
 
 extern "C" int tl_short_conv_state(const void* bcx, float* state, const int* state_slot, const int* row_start,

@@ -7,9 +7,10 @@
 //   out[r] = sum over the row's experts in ascending expert id of w * expert(x[r])    ref.py:207-214
 //
 // The plan is a stable counting sort: pairs keep their row order inside an expert, so the order of every
-// sum is fixed by the inputs alone (no atomics). Two forms build the same plan: three small kernels for any
-// number of pairs, and one kernel for up to 4096 pairs (a decode step) that also copies the token rows into
-// expert-sorted order for the tensor-core kernels.
+// sum is fixed by the inputs alone (the only atomics count integers). Two forms build the same plan: for any
+// number of pairs, a kernel that counts each chunk of 1024 pairs per expert and one that places them; and one
+// kernel for up to 4096 pairs (a decode step) that also copies the token rows into expert-sorted order for the
+// tensor-core kernels.
 #include "route.cuh"
 
 namespace tl {
@@ -25,66 +26,95 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
              wts + (long long)warp * k);
 }
 
-// grid E: block e counts the pairs routed to expert e
-__global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ ids, int P, int* __restrict__ counts) {
-  __shared__ float scratch[33];
-  const int e = blockIdx.x;
-  int n = 0;
-  for (int p = threadIdx.x; p < P; p += blockDim.x) n += ids[p] == e;
-  const float total = block_sum((float)n, scratch);   // exact below 2^24 pairs
-  if (threadIdx.x == 0) counts[e] = (int)(total + 0.5f);
+constexpr int PLAN_CHUNK = 1024;     // pairs a block of the two-kernel plan takes
+
+// grid ceil(P / PLAN_CHUNK): block b counts its chunk's pairs per expert into block_hist[b, :]
+__global__ void __launch_bounds__(PLAN_CHUNK) moe_hist_kernel(const int* __restrict__ ids, int P, int E,
+                                                              int* __restrict__ block_hist) {
+  __shared__ int hist[MAX_EXPERTS];
+  chain_next();
+  chain_wait();
+  for (int e = threadIdx.x; e < E; e += PLAN_CHUNK) hist[e] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * PLAN_CHUNK + threadIdx.x;
+  if (p < P) {
+    const int e = ids[p];
+    if ((unsigned)e < (unsigned)E) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += PLAN_CHUNK) block_hist[(long long)blockIdx.x * E + e] = hist[e];
 }
 
-// grid E: block e places its pairs, in pair order, at offsets[e].. of the sorted list and writes its row tiles
-__global__ void __launch_bounds__(256) moe_place_kernel(const int* __restrict__ ids, int P, int E, int tile_m,
-                                                        const int* __restrict__ counts, int* __restrict__ offsets,
-                                                        int* __restrict__ sorted_pairs, int* __restrict__ pos_of_pair,
-                                                        int* __restrict__ tile_group, int* __restrict__ tile_row0,
-                                                        int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
-  __shared__ int warp_total[8];
-  __shared__ int s_base[2];
-  const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) {
-    int off = 0, tiles = 0;
-    for (int i = 0; i < e; ++i) {
-      off += counts[i];
-      tiles += ceil_div(counts[i], tile_m);
+// grid ceil(P / PLAN_CHUNK): block b places its chunk's pairs: a pair of expert e lands behind all pairs of lower
+// experts, behind the pairs of e in earlier chunks, and behind the earlier pairs of e in its own chunk, so the
+// sorted list keeps pair order within an expert. Block 0 also writes counts, offsets and the row tiles.
+__global__ void __launch_bounds__(PLAN_CHUNK) moe_place_kernel(const int* __restrict__ ids, int P, int E, int tile_m,
+                                                               const int* __restrict__ block_hist, int* __restrict__ counts,
+                                                               int* __restrict__ offsets, int* __restrict__ sorted_pairs,
+                                                               int* __restrict__ pos_of_pair, int* __restrict__ tile_group,
+                                                               int* __restrict__ tile_row0, int* __restrict__ tile_rows,
+                                                               int* __restrict__ n_tiles) {
+  __shared__ int total[MAX_EXPERTS];      // pairs of each expert in all chunks
+  __shared__ int base[MAX_EXPERTS];       // where this chunk's first pair of each expert lands
+  __shared__ int run[MAX_EXPERTS];        // pairs of each expert placed so far by this block's earlier warps
+  chain_next();
+  chain_wait();
+  const int b = blockIdx.x, nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int e = tid; e < E; e += PLAN_CHUNK) {
+    int all = 0, before = 0;
+    for (int i = 0; i < nb; ++i) {
+      const int v = block_hist[(long long)i * E + e];
+      all += v;
+      if (i < b) before += v;
     }
-    s_base[0] = off;
-    s_base[1] = tiles;
-    offsets[e] = off;
-    const int cnt = counts[e];
-    const int mine = ceil_div(cnt, tile_m);
-    for (int t = 0; t < mine; ++t) {
-      tile_group[tiles + t] = e;
-      tile_row0[tiles + t] = off + t * tile_m;
-      tile_rows[tiles + t] = min(tile_m, cnt - t * tile_m);
-    }
-    if (e == E - 1) {
-      offsets[E] = off + cnt;
-      *n_tiles = tiles + mine;
+    total[e] = all;
+    run[e] = before;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += PLAN_CHUNK) {
+    int lower = 0;
+    for (int i = 0; i < e; ++i) lower += total[i];
+    base[e] = lower + run[e];
+    if (b == 0) {
+      counts[e] = total[e];
+      offsets[e] = lower;
+      if (e == E - 1) offsets[E] = lower + total[e];
     }
   }
   __syncthreads();
-  int running = s_base[0];
-  for (int p0 = 0; p0 < P; p0 += 256) {
-    const int p = p0 + tid;
-    const bool hit = p < P && ids[p] == e;
-    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) warp_total[warp] = __popc(ballot);
-    __syncthreads();
-    int before = 0, all = 0;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) {
-      if (w < warp) before += warp_total[w];
-      all += warp_total[w];
+  for (int e = tid; e < E; e += PLAN_CHUNK) run[e] = 0;
+  if (b == 0 && tid == 0) {
+    int off = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      const int cnt = total[e];
+      for (int t = 0; t * tile_m < cnt; ++t) {
+        tile_group[tiles] = e;
+        tile_row0[tiles] = off + t * tile_m;
+        tile_rows[tiles] = min(tile_m, cnt - t * tile_m);
+        ++tiles;
+      }
+      off += cnt;
     }
-    if (hit) {
-      const int at = running + before + __popc(ballot & ((1u << lane) - 1u));
-      sorted_pairs[at] = p;
-      pos_of_pair[p] = at;
+    *n_tiles = tiles;
+  }
+  __syncthreads();
+  const int p = b * PLAN_CHUNK + tid;
+  int e = p < P ? ids[p] : -1;
+  if ((unsigned)e >= (unsigned)E) e = -1;
+  const bool hit = e >= 0;
+  for (int w = 0; w < PLAN_CHUNK / 32; ++w) {     // warp after warp, so that earlier pairs land first
+    if (warp == w) {
+      const unsigned hits = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const unsigned same = __match_any_sync(hits, e);
+        const int placed = run[e];
+        __syncwarp(hits);
+        const int at = base[e] + placed + __popc(same & ((1u << lane) - 1u));
+        sorted_pairs[at] = p;
+        pos_of_pair[p] = at;
+        if (lane == __ffs(same) - 1) run[e] = placed + __popc(same);
+      }
     }
-    running += all;
     __syncthreads();
   }
 }
@@ -206,8 +236,8 @@ extern "C" int tl_moe_max_tiles(int pairs, int E, int tile_m) {
 // writes x_sorted[i] = x[sorted_pairs[i] / top_k]. Returns the number of kernels it launched through *launched.
 extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int top_k, int* counts, int* offsets,
                            int* sorted_pairs, int* pos_of_pair, int* tile_group, int* tile_row0, int* tile_rows,
-                           int* n_tiles, const void* x, long long ldx, void* x_sorted, int width, int* launched,
-                           cudaStream_t stream) {
+                           int* n_tiles, int* block_hist, const void* x, long long ldx, void* x_sorted, int width,
+                           int* launched, cudaStream_t stream) {
   TL_REQUIRE(E > 0 && E <= 65535 && tile_m > 0 && top_k > 0, "moe plan: %d experts, tile of %d rows, top-%d", E, tile_m, top_k);
   TL_REQUIRE(pairs >= 0 && pairs < (1 << 24), "moe plan: %d pairs; fewer than 2^24 are implemented", pairs);
   TL_REQUIRE(!x || (width % 8 == 0 && ldx % 8 == 0 && x_sorted), "moe plan: row copy of width %d, stride %lld", width, ldx);
@@ -221,11 +251,14 @@ extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int top
     if (launched) *launched = 1;
     return 0;
   }
-  moe_count_kernel<<<E, 256, 0, stream>>>(ids, pairs, counts);
-  TL_LAUNCH_CHECK();
-  moe_place_kernel<<<E, 256, 0, stream>>>(ids, pairs, E, tile_m, counts, offsets, sorted_pairs, pos_of_pair, tile_group,
-                                          tile_row0, tile_rows, n_tiles);
-  TL_LAUNCH_CHECK();
+  TL_REQUIRE(E <= MAX_EXPERTS && block_hist, "moe plan: %d experts; up to %d are implemented", E, MAX_EXPERTS);
+  const int chunks = ceil_div(pairs, PLAN_CHUNK);
+  cudaError_t e = launch_chained(moe_hist_kernel, dim3(chunks), dim3(PLAN_CHUNK), 0, stream, ids, pairs, E, block_hist);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_chained(moe_place_kernel, dim3(chunks), dim3(PLAN_CHUNK), 0, stream, ids, pairs, E, tile_m,
+                     (const int*)block_hist, counts, offsets, sorted_pairs, pos_of_pair, tile_group, tile_row0, tile_rows,
+                     n_tiles);
+  if (e != cudaSuccess) return (int)e;
   if (launched) *launched = 2;
   return 0;
 }

@@ -116,8 +116,9 @@ __device__ __forceinline__ void router_logits(const NormParams& p, const float* 
 //                      wanted rows only)
 // normed32 (optional) receives the normalised row unrounded. With a router, the row's logits are computed from
 // the unrounded row in 32-bit, and the choice and weights are written as well.
-template <typename T>
-__global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
+// ROUTE_PER: 0 without a router (a small kernel, three blocks an SM), else the experts a lane of the choosing warp holds.
+template <typename T, int ROUTE_PER>
+__global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 : 1)) add_rmsnorm_kernel(NormParams p) {
   // rows_per_block rows of `hidden` floats, 33 for the reduction, then rows_per_block x E logits
   extern __shared__ __align__(16) float rows_buf[];
   float* scratch = rows_buf + (size_t)p.rows_per_block * p.hidden;
@@ -135,21 +136,21 @@ __global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
   const int r = p.gather ? p.gather[out_r] : out_r;
   __syncthreads();            // the row before this one is done with the slot table and the reduction scratch
   if (p.expert_rows) {
-    if (threadIdx.x == 0) {
-      const int k = p.top_k;
-      int order[MAX_TOP_K];
-      for (int j = 0; j < k; ++j) {     // insertion sort of the slots by expert id (slot index breaks ties)
-        int i = j;
-        const int e = p.ids[(long long)r * k + j];
-        while (i > 0 && p.ids[(long long)r * k + order[i - 1]] > e) {
-          order[i] = order[i - 1];
-          --i;
-        }
-        order[i] = j;
+    if (threadIdx.x < 32) {
+      // the row's slots in ascending expert id (the slot index breaks ties): lane j ranks slot j among the others
+      const int k = p.top_k, j = threadIdx.x;
+      const bool mine = j < k;
+      const int e = mine ? p.ids[(long long)r * k + j] : 0x7fffffff;
+      const int src = mine ? p.pos_of_pair[(long long)r * k + j] : 0;
+      const float w = mine ? p.wts[(long long)r * k + j] : 0.f;
+      int rank = 0;
+      for (int i = 0; i < k; ++i) {
+        const int ei = __shfl_sync(0xffffffffu, e, i);
+        rank += (ei < e) || (ei == e && i < j);
       }
-      for (int j = 0; j < k; ++j) {
-        s_src[j] = p.pos_of_pair[(long long)r * k + order[j]];
-        s_w[j] = p.wts[(long long)r * k + order[j]];
+      if (mine) {
+        s_src[rank] = src;
+        s_w[rank] = w;
       }
     }
     __syncthreads();
@@ -234,18 +235,20 @@ __global__ void __launch_bounds__(512) add_rmsnorm_kernel(NormParams p) {
     }
   }
   }   // rows of this block
-  if (!p.router_w) return;
-  __syncthreads();
-  // logits[row, e] = row . router_w[e]: each warp takes experts warp, warp + nwarps, ...; lanes stride over the
-  // columns; an expert's weights are read once for all rows of the block. A row's sum is built in the same order
-  // whether the block holds one row or several.
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  if (n_rows == 1) router_logits<1>(p, rows_buf, logits, 1, lane, warp, nwarps);
-  else router_logits<MAX_ROWS_PER_BLOCK>(p, rows_buf, logits, n_rows, lane, warp, nwarps);
-  __syncthreads();
-  for (int rr = warp; rr < n_rows; rr += nwarps)
-    warp_route(logits + rr * p.E, p.router_bias, p.E, p.route_k, p.normalize, p.floor_, p.scale,
-               p.route_ids + (size_t)(first_row + rr) * p.route_k, p.route_wts + (size_t)(first_row + rr) * p.route_k);
+  if constexpr (ROUTE_PER > 0) {
+    __syncthreads();
+    // logits[row, e] = row . router_w[e]: each warp takes experts warp, warp + nwarps, ...; lanes stride over the
+    // columns; an expert's weights are read once for all rows of the block. A row's sum is built in the same order
+    // whether the block holds one row or several.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    if (n_rows == 1) router_logits<1>(p, rows_buf, logits, 1, lane, warp, nwarps);
+    else router_logits<MAX_ROWS_PER_BLOCK>(p, rows_buf, logits, n_rows, lane, warp, nwarps);
+    __syncthreads();
+    for (int rr = warp; rr < n_rows; rr += nwarps)
+      warp_route_sized<ROUTE_PER>(logits + rr * p.E, p.router_bias, p.E, p.route_k, p.normalize, p.floor_, p.scale,
+                                  p.route_ids + (size_t)(first_row + rr) * p.route_k,
+                                  p.route_wts + (size_t)(first_row + rr) * p.route_k);
+  }
 }
 
 // out[r, i] = silu(gate_up[r, i]) * gate_up[r, inter + i]
@@ -315,17 +318,24 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
   p.rows_per_block = rows_per_block; p.out_rows = out_rows;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const dim3 grid(ceil_div(out_rows, rows_per_block));
-  cudaError_t e;
+  const int per = !router_w ? 0 : (E <= 32 ? 1 : (E <= 128 ? 4 : MAX_EXPERTS / 32));
+#define TL_NORM(T_, PER_)                                                                                         \
+  do {                                                                                                            \
+    if (smem > 48 * 1024)                                                                                         \
+      cudaFuncSetAttribute(add_rmsnorm_kernel<T_, PER_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    return (int)launch_chained(add_rmsnorm_kernel<T_, PER_>, grid, dim3(threads), smem, stream, p);               \
+  } while (0)
   if (dtype == TL_FP32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(add_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = launch_chained(add_rmsnorm_kernel<float>, grid, dim3(threads), smem, stream, p);
-  } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(add_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    e = launch_chained(add_rmsnorm_kernel<bf16>, grid, dim3(threads), smem, stream, p);
+    if (per == 0) TL_NORM(float, 0);
+    if (per == 1) TL_NORM(float, 1);
+    if (per == 4) TL_NORM(float, 4);
+    TL_NORM(float, MAX_EXPERTS / 32);
   }
-  return (int)e;
+  if (per == 0) TL_NORM(bf16, 0);
+  if (per == 1) TL_NORM(bf16, 1);
+  if (per == 4) TL_NORM(bf16, 4);
+  TL_NORM(bf16, MAX_EXPERTS / 32);
+#undef TL_NORM
 }
 
 extern "C" int tl_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, cudaStream_t stream) {

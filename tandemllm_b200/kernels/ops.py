@@ -62,7 +62,7 @@ _SIGNATURES = {
                        c_void_p],
     "tl_moe_max_tiles": [c_int, c_int, c_int],
     "tl_moe_plan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                    c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p],
+                    c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -365,6 +365,7 @@ class MoePlan:
         self.tile_row0 = torch.zeros(self.max_tiles_cap, **i32)
         self.tile_rows = torch.zeros(self.max_tiles_cap, **i32)
         self.n_tiles = torch.zeros(1, **i32)
+        self.block_hist = torch.zeros(-(-max(max_pairs, 1) // 1024) * num_experts, **i32)   # per-chunk counts
         self.pairs = 0
         self.max_tiles = 1
 
@@ -380,7 +381,7 @@ class MoePlan:
         launched = ctypes.c_int(0)
         check(core().tl_moe_plan(ptr(ids), pairs, self.num_experts, self.tile_m, ids.shape[-1], ptr(self.counts),
                                  ptr(self.offsets), ptr(self.sorted_pairs), ptr(self.pos_of_pair), ptr(self.tile_group),
-                                 ptr(self.tile_row0), ptr(self.tile_rows), ptr(self.n_tiles), ptr(x),
+                                 ptr(self.tile_row0), ptr(self.tile_rows), ptr(self.n_tiles), ptr(self.block_hist), ptr(x),
                                  x.stride(0) if x is not None else 0, ptr(x_sorted), x.shape[1] if x is not None else 0,
                                  ctypes.addressof(launched), stream()), "moe_plan", kernels=0)
         global launches

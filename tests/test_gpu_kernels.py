@@ -115,10 +115,11 @@ def test_add_rmsnorm_adds_deferred_branch_outputs_and_routes(dtype, R):
     close(out, n32, dtype, "normed rows beside the router")
 
 
-@pytest.mark.parametrize("P_rows,E,k", [(8, 32, 4), (64, 6, 3), (1500, 8, 4)])
+@pytest.mark.parametrize("P_rows,E,k", [(8, 32, 4), (64, 6, 3), (1500, 8, 4), (3000, 200, 3), (1025, 1000, 5)])
 def test_plan_forms_agree_and_copy_rows(P_rows, E, k):
-    """The one-kernel plan (a decode step) and the three-kernel plan (many pairs) are the same stable sort; the
-    one-kernel form also copies the token rows into expert-sorted order."""
+    """The one-kernel plan (a decode step) and the chunked plan (many pairs: pairs of one expert spread over
+    several chunks and warps) are the same stable sort; the one-kernel form also copies the token rows into
+    expert-sorted order."""
     o = ops()
     g = torch.Generator().manual_seed(9)
     ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(P_rows)]).int().to(DEV)
@@ -130,8 +131,12 @@ def test_plan_forms_agree_and_copy_rows(P_rows, E, k):
     assert torch.equal(plan.sorted_pairs[:P_rows * k].cpu().long(), order)
     assert torch.equal(plan.counts.cpu().long(), torch.bincount(flat, minlength=E))
     assert torch.equal(plan.offsets.cpu().long(), torch.cat([torch.zeros(1, dtype=torch.long), torch.bincount(flat, minlength=E).cumsum(0)]))
+    assert torch.equal(plan.pos_of_pair[:P_rows * k].cpu().long()[order], torch.arange(P_rows * k))
     nt = int(plan.n_tiles)
+    assert nt == sum(-(-int(c) // 16) for c in plan.counts.cpu())
     assert sum(int(r) for r in plan.tile_rows[:nt].cpu()) == P_rows * k
+    groups, row0 = plan.tile_group[:nt].cpu().tolist(), plan.tile_row0[:nt].cpu().tolist()
+    assert groups == sorted(groups) and all(int(plan.offsets[g]) <= r < int(plan.offsets[g + 1]) for g, r in zip(groups, row0))
     assert plan.copied == (P_rows * k <= 4096)
     if plan.copied:
         assert torch.equal(xs.cpu(), x.cpu()[order // k])
