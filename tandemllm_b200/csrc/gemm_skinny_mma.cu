@@ -1,0 +1,137 @@
+// bfloat16 products of a few token rows with a weight matrix of moderate size, for decode steps:
+//
+//   C[m, n] = sum_k X[m, k] * W[n, k] (+ bias[n])       m < 32 tokens; X, W row-major with k contiguous
+//
+// At these sizes (a mixer's projections: some MB of weights, a handful of tokens) a product's time is the length
+// of its chain of dependent steps, not its bytes, so this kernel has the shortest chain there is: no shared-memory
+// staging, no barriers, no tensor memory. A CTA of eight warps owns 16 weight rows. Every lane loads 16 bytes of
+// two of those rows and 16 bytes of one token row straight from global memory into the registers that
+// mma.sync m16n8k16 wants (the weights as the A operand, the tokens as B), many loads in flight, and the eight
+// warps split k between them, chunk by chunk of 32. Because a dot product does not care about the order of k,
+// the 8 consecutive elements a lane holds feed two MMAs whose k slots are mapped to those elements the same way
+// for both operands. The warps' 32-bit partial tiles are added in warp order through shared memory, so the result
+// does not depend on timing. (The reference sends every product through one `lin`,
+// engine/models/lfm2_moe/ref.py:99-103; this is the decode-step form of it.)
+#include "common.cuh"
+
+namespace tl {
+
+constexpr int SKINNY_WARPS = 8;
+constexpr int SKINNY_MAX_TOKENS = 32;
+
+__device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 load16(const bf16* p, bool valid) {
+  return valid ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// NT: token tiles of 8 (M <= 8 NT). UNROLL chunks of 32 k-elements are in flight a warp: with eight, a k of 2048
+// is one round of loads, all issued before the first is used.
+template <int NT, typename TOut>
+__global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_mma_kernel(
+    const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ w, long long ldw, const float* __restrict__ bias,
+    TOut* __restrict__ out, long long ldc, int M, int N, int K) {
+  constexpr int UNROLL = NT == 1 ? 8 : (NT == 2 ? 4 : 2);
+  __shared__ float part[SKINNY_WARPS][NT][16][8 + 1];
+  chain_next();
+  chain_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int r_lo = n0 + g, r_hi = n0 + g + 8;                     // this lane's two weight rows
+  const bool v_lo = r_lo < N, v_hi = r_hi < N;
+  const bf16* w_lo = w + (long long)(v_lo ? r_lo : 0) * ldw + t * 8;
+  const bf16* w_hi = w + (long long)(v_hi ? r_hi : 0) * ldw + t * 8;
+  const bf16* x_row[NT];
+  bool x_ok[NT];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int m = j * 8 + g;                                      // this lane's token of tile j
+    x_ok[j] = m < M;
+    x_row[j] = x + (long long)(x_ok[j] ? m : 0) * ldx + t * 8;
+  }
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+  const int chunks = (K + 31) / 32;
+  // chunk c belongs to warp c % 8; a lane's 8 elements of a chunk start at k = 32 c + 8 t
+  for (int c0 = warp; c0 < chunks; c0 += SKINNY_WARPS * UNROLL) {
+    uint4 a_lo[UNROLL], a_hi[UNROLL], b[UNROLL][NT];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = c0 + u * SKINNY_WARPS;
+      const int k = c * 32 + t * 8;
+      const bool in = c < chunks && k < K;                        // K is a multiple of 8: 8 elements are in or out
+      a_lo[u] = load16(w_lo + c * 32, in && v_lo);
+      a_hi[u] = load16(w_hi + c * 32, in && v_hi);
+#pragma unroll
+      for (int j = 0; j < NT; ++j) b[u][j] = load16(x_row[j] + c * 32, in && x_ok[j]);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        mma_16816(acc[j], a_lo[u].x, a_hi[u].x, a_lo[u].y, a_hi[u].y, b[u][j].x, b[u][j].y);
+        mma_16816(acc[j], a_lo[u].z, a_hi[u].z, a_lo[u].w, a_hi[u].w, b[u][j].z, b[u][j].w);
+      }
+    }
+  }
+  // acc[j]: (row g, tokens 8 j + 2 t, + 1), (row g + 8, the same tokens)
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    part[warp][j][g][2 * t] = acc[j][0];
+    part[warp][j][g][2 * t + 1] = acc[j][1];
+    part[warp][j][g + 8][2 * t] = acc[j][2];
+    part[warp][j][g + 8][2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+  // 16 rows x 8 NT tokens: a thread takes one row of one token, consecutive threads consecutive rows
+  for (int i = threadIdx.x; i < 16 * 8 * NT; i += SKINNY_WARPS * 32) {
+    const int row = i & 15, m = i >> 4;
+    const int n = n0 + row;
+    if (m >= M || n >= N) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int s = 0; s < SKINNY_WARPS; ++s) v += part[s][m >> 3][row][m & 7];
+    if (bias) v += bias[n];
+    out[(long long)m * ldc + n] = from_f32<TOut>(v);
+  }
+}
+
+}  // namespace tl
+
+using namespace tl;
+
+extern "C" int tl_gemm_skinny_supported(int M, int N, int K, long long ldx, long long ldw) {
+  return M >= 1 && M <= SKINNY_MAX_TOKENS && N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
+}
+
+// x [M, K] bfloat16 (row stride ldx), w [N, K] bfloat16 (row stride ldw), bias [N] 32-bit or null,
+// out [M, N] (row stride ldc) in bfloat16 (out_dtype TL_BF16) or 32-bit. Pointers 16-byte aligned.
+extern "C" int tl_gemm_skinny_mma(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
+                                  long long ldc, int M, int N, int K, int out_dtype, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  TL_REQUIRE(tl_gemm_skinny_supported(M, N, K, ldx, ldw), "skinny product: %d tokens x (%d x %d), strides %lld and %lld", M, N,
+             K, ldx, ldw);
+  TL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0, "skinny product: operands must be 16-byte aligned (%d)", 0);
+  const dim3 grid(ceil_div(N, 16)), block(SKINNY_WARPS * 32);
+  const int nt = ceil_div(M, 8);
+#define TL_SKINNY(NT_)                                                                                                  \
+  do {                                                                                                                  \
+    if (out_dtype == TL_FP32)                                                                                           \
+      return (int)launch_chained(gemm_skinny_mma_kernel<NT_, float>, grid, block, 0, stream, (const bf16*)x, ldx,       \
+                                 (const bf16*)w, ldw, bias, (float*)out, ldc, M, N, K);                                 \
+    return (int)launch_chained(gemm_skinny_mma_kernel<NT_, bf16>, grid, block, 0, stream, (const bf16*)x, ldx,          \
+                               (const bf16*)w, ldw, bias, (bf16*)out, ldc, M, N, K);                                    \
+  } while (0)
+  if (nt == 1) TL_SKINNY(1);
+  if (nt == 2) TL_SKINNY(2);
+  if (nt == 3) TL_SKINNY(3);
+  TL_SKINNY(4);
+#undef TL_SKINNY
+}

@@ -2,6 +2,9 @@
 `parts.linear` and the expert feed-forward send their products here.
 
 Choice of kernel by shape:
+  up to 32 token rows and 64 MB of weights (a decode step's projections): `csrc/gemm_skinny_mma.cu`, which loads
+                         both operands straight into mma.sync registers; such a product's time is the length of its
+                         chain of dependent steps, and this chain is the shortest.
   up to 128 token rows   the swapped orientation: 128 weight rows on the MMA's M side, the tokens (padded to 16,
                          32, 64 or 128) on its N side, so a decode step streams every weight once. When a product
                          would launch fewer CTAs than the GPU has SMs, its k range is split over several CTAs that
@@ -27,6 +30,9 @@ from . import ops
 from .build import load
 
 SM_COUNT = 148
+SKINNY_TOKENS = 32              # up to this many token rows ...
+SKINNY_K = 2048                 # ... of at most this many elements (one round of loads a warp) ...
+SKINNY_BYTES = 64 << 20         # ... against at most this many bytes of weights go to the register-only kernel
 _lib = None
 
 
@@ -51,6 +57,11 @@ def lib():
         l.tl_attention_mma_tile_rows.restype = c_int
         l.tl_attention_mma_supported.argtypes = [c_int, c_int, c_int]
         l.tl_attention_mma_supported.restype = c_int
+        l.tl_gemm_skinny_supported.argtypes = [c_int, c_int, c_int, c_longlong, c_longlong]
+        l.tl_gemm_skinny_supported.restype = c_int
+        l.tl_gemm_skinny_mma.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int,
+                                         c_int, c_int, c_int, c_void_p]
+        l.tl_gemm_skinny_mma.restype = c_int
         _lib = l
     return _lib
 
@@ -128,6 +139,15 @@ class TensorCore:
         """False when the kernels do not take these operands; else True, or the deferred partial sums."""
         if not usable(x, w) or out.stride(-1) != 1:
             return False
+        M, K = x.shape
+        N = w.shape[0]
+        if (M <= SKINNY_TOKENS and K <= SKINNY_K and N * K * 2 <= SKINNY_BYTES
+                and lib().tl_gemm_skinny_supported(M, N, K, x.stride(0), w.stride(0))):
+            # a few tokens against some MB of weights: the kernel with the shortest chain of dependent steps
+            _check(lib().tl_gemm_skinny_mma(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), ops.ptr(bias),
+                                            out.data_ptr(), out.stride(0), M, N, K, ops.dtype_code(out.dtype),
+                                            ops.stream()), "gemm_skinny_mma")
+            return True
         return self.gemm(x, w, bias, out, defer=defer) or True
 
     # ---- routed experts ----

@@ -39,6 +39,37 @@ def test_linear_all_shapes(M, N, K):
         assert rel(out, ref) < (1e-2 if out_dtype == torch.bfloat16 else 1e-4), (M, N, K, out_dtype)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16, 23, 32])
+@pytest.mark.parametrize("N,K", [(128, 64), (200, 200), (72, 136), (2048, 2048), (100, 40), (17, 8), (4096, 1024)])
+def test_few_tokens_through_registers_alone(M, N, K):
+    """The decode-step product that loads both operands straight into mma.sync registers: every count of token
+    tiles, widths with tails in rows and in k (a last chunk of 8, 16 or 24 elements), bias, both output types,
+    strided token rows; run twice, the same bits."""
+    from tandemllm_b200.kernels import ops, tensorcore
+    impl, rt = tc()
+    lib = tensorcore.lib()
+    xw = rnd(M, K + 8, seed=21).to(DEV)
+    x = xw[:, :K]                                                   # row stride K + 8
+    w, b = rnd(N, K, seed=22, scale=0.1), torch.randn(N, generator=torch.Generator().manual_seed(23))
+    assert lib.tl_gemm_skinny_supported(M, N, K, x.stride(0), K)
+    want = x.float().cpu() @ w.float().T
+    wd, bd = w.to(DEV), b.to(DEV)
+    for out_dtype, bias in ((torch.bfloat16, None), (torch.float32, bd)):
+        outs = []
+        for _ in range(2):
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+            assert lib.tl_gemm_skinny_mma(x.data_ptr(), x.stride(0), wd.data_ptr(), K, ops.ptr(bias), out.data_ptr(), N,
+                                          M, N, K, ops.dtype_code(out_dtype), ops.stream()) == 0
+            outs.append(out)
+        torch.cuda.synchronize()
+        assert torch.equal(outs[0], outs[1])
+        ref = want + (0 if bias is None else b)
+        assert rel(outs[0], ref) < (1e-2 if out_dtype == torch.bfloat16 else 1e-4), (M, N, K, out_dtype)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    assert impl.linear(x, wd, None, out) is True and impl._workspace is None, "linear() takes this kernel for such shapes"
+    assert not lib.tl_gemm_skinny_supported(33, N, K, K, K) and not lib.tl_gemm_skinny_supported(M, N, K + 4, K + 4, K + 4)
+
+
 @pytest.mark.parametrize("swap,bn", [(True, 16), (True, 32), (True, 64), (True, 128), (True, 256), (False, 16),
                                      (False, 64), (False, 128), (False, 256)])
 def test_every_tile_shape_in_both_orientations(swap, bn):
@@ -60,7 +91,7 @@ def test_split_k_is_used_and_repeatable():
     outs = []
     for _ in range(2):
         out = torch.empty(M, N, dtype=torch.float32, device=DEV)
-        impl.linear(x.to(DEV), w.to(DEV), b.to(DEV), out)
+        impl.gemm(x.to(DEV), w.to(DEV), b.to(DEV), out)
         outs.append(out.clone())
     assert impl._workspace is not None
     assert torch.equal(outs[0], outs[1])
