@@ -50,6 +50,8 @@ struct TcParams {
   const int* tile_row0;
   const int* tile_rows;
   const int* n_tiles;
+  const int* row_index;       // grouped, swapped: token row of sorted position i is row_index[i] / row_div of X (or nullptr:
+  int row_div;                // X is already in sorted order)
   int* status;
 };
 
@@ -222,10 +224,14 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   if (warp == 0 && lane == 0) {
     // ---- producer ----
     int issued = 0;
+    // With a row index the token rows are fetched one by one from where they lie (a decode step's tiles hold a row
+    // or two each); the tile's other rows keep whatever the stage held, and only feed output columns nobody stores.
+    const bool gathers = SWAP && p.row_index != nullptr;
+    const uint32_t stage_tx = gathers ? (uint32_t)(S::W_TILES * S::A_BYTES + tok_rows * TILE_K * 2) : (uint32_t)S::STAGE_BYTES;
     auto load_weights = [&](int i) {
       const int s = i % S::STAGES;
       uint8_t* st = tiles + s * S::STAGE_BYTES;
-      mbar_expect_tx(&full[s], S::STAGE_BYTES);
+      mbar_expect_tx(&full[s], stage_tx);
       const int kx = (kb_begin + i) * TILE_K;
       if (SWAP) {
         tma_load_2d(st, mapA, &full[s], kx, rowA);
@@ -239,8 +245,15 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       const int s = i % S::STAGES;
       uint8_t* st = tiles + s * S::STAGE_BYTES;
       const int kx = (kb_begin + i) * TILE_K;
-      if (SWAP) tma_load_2d(st + S::W_TILES * S::A_BYTES, mapB, &full[s], kx, rowB);
-      else tma_load_2d(st, mapA, &full[s], kx, rowA);
+      if (gathers) {
+        uint8_t* dst = st + S::W_TILES * S::A_BYTES;
+        for (int t = 0; t < tok_rows; ++t)
+          tma_load_2d(dst + t * (TILE_K * 2), mapB, &full[s], kx, p.row_index[tok0 + t] / p.row_div);
+      } else if (SWAP) {
+        tma_load_2d(st + S::W_TILES * S::A_BYTES, mapB, &full[s], kx, rowB);
+      } else {
+        tma_load_2d(st, mapA, &full[s], kx, rowA);
+      }
     };
     const int ahead = p.tile_group ? 0 : min(num_kb, S::STAGES);      // the ring's first fill: weights first
     for (int i = 0; i < ahead; ++i) load_weights(i);
@@ -497,11 +510,13 @@ extern "C" int tl_tc_token_tile(int swap, int bn) { return swap ? bn : TILE_M; }
 // X [M, K] (row stride ldx), W [groups * rows_per_group, K] (row stride ldw). Plain: groups = 1, tile_group = nullptr.
 // swiglu: W holds 2 N rows per group (gate then up) and C = silu(gate) * up. out_dtype: TL_BF16 or TL_FP32.
 // splits > 1 (swap, not swiglu, not grouped): `partial` must hold splits * M * N floats.
+// row_index (swap, grouped; or null): the tile map's rows are positions of this list, and position i stands for row
+// row_index[i] / row_div of X; without it X itself is in the tile map's order.
 extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
                           long long rows_per_group, const float* bias, void* C, long long ldc, int M, int N, int K, int swap,
                           int bn, int swiglu, int out_dtype, const int* tile_group, const int* tile_row0,
-                          const int* tile_rows, const int* n_tiles, int max_tiles, int splits, float* partial,
-                          int reduce, int* status, cudaStream_t stream) {
+                          const int* tile_rows, const int* n_tiles, int max_tiles, const int* row_index, int row_div,
+                          int splits, float* partial, int reduce, int* status, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   TL_REQUIRE(M > 0 && N > 0 && K > 0, "tensor-core gemm: M %d N %d K %d", M, N, K);
   TL_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
@@ -512,8 +527,10 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   TL_REQUIRE(splits >= 1 && (splits == 1 || (swap && !swiglu && !tile_group && partial)),
              "tensor-core gemm: split-K needs the swapped plain kernel and a workspace");
   TL_REQUIRE(!bias || !swiglu, "tensor-core gemm: a bias with the SwiGLU epilogue is not implemented");
+  TL_REQUIRE(!row_index || (swap && tile_group && row_div >= 1),
+             "tensor-core gemm: a row index needs the swapped grouped kernel (divisor %d)", row_div);
   CUtensorMap tmW, tmX;
-  const int w_box = swap ? TILE_M : bn, x_box = swap ? bn : TILE_M;
+  const int w_box = swap ? TILE_M : bn, x_box = row_index ? 1 : (swap ? bn : TILE_M);
   if (int e = tensor_map(W, w_rows, K, ldw, w_box, &tmW)) return e;
   if (int e = tensor_map(X, x_rows, K, ldx, x_box, &tmX)) return e;
   const int total_kb = ceil_div(K, TILE_K);
@@ -522,6 +539,7 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   p.k_blocks_per_split = ceil_div(total_kb, splits);
   p.rows_per_group = rows_per_group;
   p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles; p.status = status;
+  p.row_index = row_index; p.row_div = row_index ? row_div : 1;
   const int tok_tile = swap ? bn : TILE_M, n_tile = swap ? TILE_M : bn;
   dim3 grid(ceil_div(N, n_tile), tile_group ? max_tiles : ceil_div(M, tok_tile), ceil_div(total_kb, p.k_blocks_per_split));
   TL_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "tensor-core gemm: grid %u x %u x %u exceeds the limits", grid.x, grid.y, grid.z);

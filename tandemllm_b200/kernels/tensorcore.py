@@ -42,7 +42,7 @@ def lib():
         l = load("tensorcore")
         l.tl_gemm_tc.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p,
                                  c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                 c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
+                                 c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p]
         l.tl_gemm_tc.restype = c_int
         l.tl_gather_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         l.tl_gather_rows.restype = c_int
@@ -101,10 +101,12 @@ class TensorCore:
 
     # ---- x @ w^T (+ bias) ----
     def gemm(self, x, w2d, bias, out, *, rows_per_group=0, plan=None, swiglu=False, swap=None, bn=None, n_out=None,
-             defer: bool = False):
+             defer: bool = False, row_index=None, row_div: int = 1, rows: int | None = None):
         """Runs the product into `out`. With `defer`, a product that was split along k is left as partial sums and
-        returned as `ops.PartialSums` (nothing is written to `out`); otherwise returns None."""
-        M, K = x.shape
+        returned as `ops.PartialSums` (nothing is written to `out`); otherwise returns None. With `row_index` (grouped,
+        swapped) the plan's position i stands for row row_index[i] // row_div of x, and `rows` is the number of
+        positions."""
+        M, K = (rows if rows is not None else x.shape[0]), x.shape[1]
         N = n_out if n_out is not None else w2d.shape[0]
         if swap is None:
             swap = M <= 128
@@ -128,7 +130,8 @@ class TensorCore:
         code = lib().tl_gemm_tc(
             x.data_ptr(), x.stride(0), x.shape[0], w2d.data_ptr(), w2d.stride(0), w2d.shape[0], rows_per_group,
             ops.ptr(bias), out.data_ptr(), out.stride(0), M, N, K, int(swap), bn, int(swiglu), ops.dtype_code(out.dtype),
-            ops.ptr(tg), ops.ptr(tr0), ops.ptr(trs), ops.ptr(nt), max_tiles, splits, ops.ptr(partial), int(not deferred),
+            ops.ptr(tg), ops.ptr(tr0), ops.ptr(trs), ops.ptr(nt), max_tiles, ops.ptr(row_index), int(row_div), splits,
+            ops.ptr(partial), int(not deferred),
             self.status.data_ptr(), ops.stream())
         _check(code, "gemm_tc", kernels=2 if splits > 1 and not deferred else 1)
         if not deferred:
@@ -151,29 +154,38 @@ class TensorCore:
         return self.gemm(x, w, bias, out, defer=defer) or True
 
     # ---- routed experts ----
-    def experts(self, part, x, ids, wts):
+    def expert_tile(self, pairs: int, experts: int) -> tuple[bool, int, int]:
+        """(swapped?, token tile of the MMA's N side, rows of a plan tile) for `pairs` pairs over `experts` experts."""
+        avg = pairs / experts
+        swap = avg <= 48
+        bn = 16 if avg <= 12 else 32 if avg <= 24 else 64 if swap else 128
+        return swap, bn, lib().tl_tc_token_tile(int(swap), bn)
+
+    def experts(self, part, x, ids, wts, plan=None):
         """The routed experts of `part` on rows x: an `ops.ExpertRows` (to be weighed and added per row), or None
-        when the kernels do not take the shapes."""
+        when the kernels do not take the shapes. `plan`: the routing plan when something built it already."""
         E, I2, H = part.w_gate_up.shape
         inter = I2 // 2
         if not usable(x, part.w_gate_up.view(E * I2, H)) or inter % 8 or not part.w_down.is_contiguous():
             return None
         R, k = ids.shape
         P = R * k
-        avg = P / E
-        swap = avg <= 48
-        bn = 16 if avg <= 12 else 32 if avg <= 24 else 64 if swap else 128
-        tile = lib().tl_tc_token_tile(int(swap), bn)
-        xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
-        plan = part.plan_for(P, x.device, tile).build(ids, x, xs)
-        if not plan.copied:
-            _check(lib().tl_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k, xs.data_ptr(), P, H,
-                                        ops.stream()), "gather_rows")
+        swap, bn, tile = self.expert_tile(P, E)
+        if plan is None or plan.tile_m != tile:
+            plan = part.plan_for(P, x.device, tile).build(ids)
         if part.record_counts:
             part.last_counts = plan.counts.clone()
         act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
-        self.gemm(xs, part.w_gate_up.view(E * I2, H), None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=swap,
-                  bn=bn, n_out=inter)
+        if swap:
+            # few rows an expert: the gate/up product fetches each token row from where it lies
+            self.gemm(x, part.w_gate_up.view(E * I2, H), None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=True,
+                      bn=bn, n_out=inter, row_index=plan.sorted_pairs, row_div=k, rows=P)
+        else:
+            xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
+            _check(lib().tl_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k, xs.data_ptr(), P, H,
+                                        ops.stream()), "gather_rows")
+            self.gemm(xs, part.w_gate_up.view(E * I2, H), None, act, rows_per_group=I2, plan=plan, swiglu=True,
+                      swap=False, bn=bn, n_out=inter)
         y = torch.empty(P, H, dtype=torch.float32, device=x.device)
         self.gemm(act, part.w_down.view(E * H, inter), None, y, rows_per_group=H, plan=plan, swap=swap, bn=bn, n_out=H)
         return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)
