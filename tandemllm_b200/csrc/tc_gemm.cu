@@ -387,6 +387,221 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The prompt-sized product as a persistent kernel: one CTA an SM walks over output tiles of 128 token rows by 256
+// weight rows (SWIGLU: 128 gate rows and the 128 up rows of the same outputs, stacked into one 256-row operand, so
+// one MMA of N = 256 fills gate in accumulator columns 0..127 and up in 128..255). Three roles run side by side:
+//   warp 0      one thread keeps the ring of four 48 KB stages full, across tile borders
+//   warp 1      one thread issues the MMAs of a tile into one of two 256-column accumulators in tensor memory
+//   warps 2..5  read the finished accumulator (tcgen05.ld), apply bias or silu(gate) * up and store, while the MMAs
+//               of the next tile fill the other accumulator
+// A 128 x 256 tile reads 48 KB of operands per 2 M multiply-adds, half of what 128 x 128 tiles read, which is what
+// the path from L2 can feed. Every wait is bounded as in the kernel above.
+struct PersistentSmem {
+  static constexpr int A_BYTES = TILE_M * TILE_K * 2;          // 128 token rows
+  static constexpr int B_BYTES = 256 * TILE_K * 2;             // 256 weight rows
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 4;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <bool SWIGLU, typename TOut>
+__global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                                 const __grid_constant__ CUtensorMap tmX, TcParams p) {
+  using S = PersistentSmem;
+  constexpr int OUT_N = SWIGLU ? 128 : 256;            // output columns of a tile
+  chain_next();
+  chain_wait();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(tiles + S::STAGES * S::STAGE_BYTES);
+  uint64_t* empty = full + S::STAGES;
+  uint64_t* acc_full = empty + S::STAGES;              // [2] the accumulator holds a finished tile
+  uint64_t* acc_empty = acc_full + 2;                  // [2] the epilogue has read it
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  volatile uint32_t* aborted = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);                     // one arrival an epilogue warp
+    }
+    *aborted = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_n = (p.N + OUT_N - 1) / OUT_N;
+  const int tiles_m = p.tile_group ? *p.n_tiles : (p.M + TILE_M - 1) / TILE_M;
+  const int work = tiles_m * tiles_n;
+  const int num_kb = (p.K + TILE_K - 1) / TILE_K;
+
+  // work item w: token tile w / tiles_n, weight tile w % tiles_n (neighbouring CTAs share token rows)
+  auto tile_of = [&](int w, int& tok0, int& tok_rows, long long& w_base, int& n0) {
+    const int tm = w / tiles_n;
+    n0 = (w - tm * tiles_n) * OUT_N;
+    if (p.tile_group) {
+      tok0 = p.tile_row0[tm];
+      tok_rows = p.tile_rows[tm];
+      w_base = (long long)p.tile_group[tm] * p.rows_per_group;
+    } else {
+      tok0 = tm * TILE_M;
+      tok_rows = min(TILE_M, p.M - tok0);
+      w_base = 0;
+    }
+  };
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer ----
+    int it = 0, issued = 0;                            // k-blocks requested so far, over all tiles
+    for (int w = blockIdx.x; w < work && !*aborted; w += gridDim.x) {
+      int tok0, tok_rows, n0;
+      long long w_base;
+      tile_of(w, tok0, tok_rows, w_base, n0);
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % S::STAGES;
+        if (it >= S::STAGES && !mbar_wait(&empty[s], ((it / S::STAGES) - 1) & 1)) {
+          *aborted = 1;
+          atomicExch(p.status, 11);
+        }
+        if (*aborted) break;
+        uint8_t* st = tiles + s * S::STAGE_BYTES;
+        mbar_expect_tx(&full[s], S::STAGE_BYTES);
+        const int kx = kb * TILE_K;
+        tma_load_2d(st, &tmX, &full[s], kx, tok0);
+        if (SWIGLU) {
+          tma_load_2d(st + S::A_BYTES, &tmW, &full[s], kx, (int)(w_base + n0));
+          tma_load_2d(st + S::A_BYTES + S::B_BYTES / 2, &tmW, &full[s], kx, (int)(w_base + p.N + n0));
+        } else {
+          tma_load_2d(st + S::A_BYTES, &tmW, &full[s], kx, (int)(w_base + n0));
+          tma_load_2d(st + S::A_BYTES + S::B_BYTES / 2, &tmW, &full[s], kx, (int)(w_base + n0 + 128));
+        }
+        issued = it + 1;
+      }
+    }
+    if (*aborted) {
+      // copies already started must land before the CTA's shared memory goes away
+      for (int i = max(0, issued - S::STAGES); i < issued; ++i) mbar_wait(&full[i % S::STAGES], (i / S::STAGES) & 1);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    constexpr uint32_t idesc = umma_idesc(256);
+    int it = 0, n = 0;                                 // k-blocks and tiles so far
+    for (int w = blockIdx.x; w < work && !*aborted; w += gridDim.x, ++n) {
+      const int buf = n & 1;
+      if (n >= 2 && !mbar_wait(&acc_empty[buf], ((n >> 1) - 1) & 1)) {
+        *aborted = 1;
+        atomicExch(p.status, 11);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t acc = tmem_base + buf * 256;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % S::STAGES;
+        if (!mbar_wait(&full[s], (it / S::STAGES) & 1)) {
+          *aborted = 1;
+          atomicExch(p.status, 11);
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(tiles + s * S::STAGE_BYTES), b0 = a0 + S::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < TILE_K / UMMA_K; ++k)
+          umma(acc, umma_desc(a0 + k * UMMA_K * 2), umma_desc(b0 + k * UMMA_K * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&empty[s]);
+      }
+      if (*aborted) break;
+      umma_commit(&acc_full[buf]);
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue: warp w reads tensor-memory lanes 32 (w % 4) .. + 31, one token row a thread ----
+    const int quad = warp & 3;
+    const int m_row = quad * 32 + lane;
+    TOut* C = (TOut*)p.C;
+    int n = 0;
+    for (int w = blockIdx.x; w < work && !*aborted; w += gridDim.x, ++n) {
+      int tok0, tok_rows, n0;
+      long long w_base;
+      tile_of(w, tok0, tok_rows, w_base, n0);
+      const int buf = n & 1;
+      if (num_kb > 0 && !mbar_wait(&acc_full[buf], (n >> 1) & 1)) {
+        *aborted = 1;
+        atomicExch(p.status, 11);
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * 256;
+      TOut* row = C + (long long)(tok0 + m_row) * p.ldc;
+#pragma unroll 1
+      for (int c0 = 0; c0 < OUT_N; c0 += 16) {
+        float v[16], u[16];
+        if (num_kb > 0) {
+          tmem_ld16(taddr + c0, v);
+          if (SWIGLU) tmem_ld16(taddr + 128 + c0, u);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = u[j] = 0.f;
+        }
+        if (m_row < tok_rows && n0 + c0 < p.N) {
+          float r[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int col = n0 + c0 + j;
+            r[j] = SWIGLU ? silu_mul(v[j], u[j]) : v[j] + ((p.bias && col < p.N) ? p.bias[col] : 0.f);
+          }
+          const bool whole = n0 + c0 + 16 <= p.N && (((uintptr_t)(row + n0 + c0)) & 15) == 0;
+          if (whole) {
+            if constexpr (sizeof(TOut) == 2) {
+              uint4 lo, hi;
+              __nv_bfloat162 t;
+#define TL_PACK(dst, a, b) t = __floats2bfloat162_rn(a, b); dst = *reinterpret_cast<uint32_t*>(&t)
+              TL_PACK(lo.x, r[0], r[1]); TL_PACK(lo.y, r[2], r[3]); TL_PACK(lo.z, r[4], r[5]); TL_PACK(lo.w, r[6], r[7]);
+              TL_PACK(hi.x, r[8], r[9]); TL_PACK(hi.y, r[10], r[11]); TL_PACK(hi.z, r[12], r[13]); TL_PACK(hi.w, r[14], r[15]);
+#undef TL_PACK
+              uint4* dst = reinterpret_cast<uint4*>(row + n0 + c0);
+              dst[0] = lo;
+              dst[1] = hi;
+            } else {
+              float4* dst = reinterpret_cast<float4*>(row + n0 + c0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dst[j] = make_float4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (n0 + c0 + j < p.N) store_out<TOut>(row + n0 + c0 + j, r[j]);
+          }
+        }
+      }
+      // the accumulator may be overwritten once all four warps have read it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u));
+  }
+}
+
 // out[m, n] = sum over splits (in order) of partial[s, m, n] (+ nothing: the bias went into split 0)
 template <typename TOut>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __restrict__ out, long long ldc, int M, int N,
@@ -485,6 +700,18 @@ static int launch_one(const CUtensorMap& tmW, const CUtensorMap& tmX, const TcPa
   return (int)launch_chained(kernel, grid, dim3(192), S::TOTAL, stream, tmW, tmX, p);
 }
 
+template <bool SWIGLU, typename TOut>
+static int launch_persistent(const CUtensorMap& tmW, const CUtensorMap& tmX, const TcParams& p, dim3 grid, cudaStream_t stream) {
+  auto kernel = gemm_tc_persistent_kernel<SWIGLU, TOut>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PersistentSmem::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return (int)launch_chained(kernel, grid, dim3(192), PersistentSmem::TOTAL, stream, tmW, tmX, p);
+}
+
 template <bool SWAP, bool SWIGLU, typename TOut>
 static int launch_bn(int bn, const CUtensorMap& tmW, const CUtensorMap& tmX, const TcParams& p, dim3 grid, cudaStream_t s) {
   switch (bn) {
@@ -506,6 +733,9 @@ extern "C" const char* tl_tc_last_error() { return tl_error_text; }
 
 // The token-tile height the grouped kernel wants for a given orientation (the MoE plan is built with it).
 extern "C" int tl_tc_token_tile(int swap, int bn) { return swap ? bn : TILE_M; }
+
+// bn = 256 without swap selects the persistent kernel (tiles of 128 token rows by 256 weight rows, or by 128 gate and
+// 128 up rows with swiglu).
 
 // X [M, K] (row stride ldx), W [groups * rows_per_group, K] (row stride ldw). Plain: groups = 1, tile_group = nullptr.
 // swiglu: W holds 2 N rows per group (gate then up) and C = silu(gate) * up. out_dtype: TL_BF16 or TL_FP32.
@@ -530,7 +760,8 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   TL_REQUIRE(!row_index || (swap && tile_group && row_div >= 1),
              "tensor-core gemm: a row index needs the swapped grouped kernel (divisor %d)", row_div);
   CUtensorMap tmW, tmX;
-  const int w_box = swap ? TILE_M : bn, x_box = row_index ? 1 : (swap ? bn : TILE_M);
+  const bool persistent = !swap && bn == 256;          // the prompt-sized kernel: its weight tiles come as two boxes of 128 rows
+  const int w_box = (swap || persistent) ? TILE_M : bn, x_box = row_index ? 1 : (swap ? bn : TILE_M);
   if (int e = tensor_map(W, w_rows, K, ldw, w_box, &tmW)) return e;
   if (int e = tensor_map(X, x_rows, K, ldx, x_box, &tmX)) return e;
   const int total_kb = ceil_div(K, TILE_K);
@@ -544,6 +775,16 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   dim3 grid(ceil_div(N, n_tile), tile_group ? max_tiles : ceil_div(M, tok_tile), ceil_div(total_kb, p.k_blocks_per_split));
   TL_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "tensor-core gemm: grid %u x %u x %u exceeds the limits", grid.x, grid.y, grid.z);
   int e;
+  if (persistent) {
+    const int out_n = swiglu ? 128 : 256;
+    const long long work = (long long)ceil_div(N, out_n) * (tile_group ? max_tiles : ceil_div(M, TILE_M));
+    const dim3 pgrid((unsigned)(work < 148 ? work : 148));
+    if (swiglu) e = out_dtype == TL_BF16 ? launch_persistent<true, bf16>(tmW, tmX, p, pgrid, stream)
+                                         : launch_persistent<true, float>(tmW, tmX, p, pgrid, stream);
+    else e = out_dtype == TL_BF16 ? launch_persistent<false, bf16>(tmW, tmX, p, pgrid, stream)
+                                  : launch_persistent<false, float>(tmW, tmX, p, pgrid, stream);
+    return e;
+  }
   if (swap) {
     if (swiglu) e = out_dtype == TL_BF16 ? launch_bn<true, true, bf16>(bn, tmW, tmX, p, grid, stream)
                                          : launch_bn<true, true, float>(bn, tmW, tmX, p, grid, stream);

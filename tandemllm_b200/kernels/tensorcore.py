@@ -11,10 +11,12 @@ Choice of kernel by shape:
                          write 32-bit partial sums to a workspace; they are added in a fixed order by a second
                          kernel, or, for a branch's last product, by the norm kernel that consumes the branch
                          (`ops.PartialSums`).
-  more rows              128 token rows on the M side, 128 weight rows on the N side.
-Experts: the token rows are copied into expert-sorted order (by the plan kernel itself for a decode step), the
-plan's tiles carry the expert, gate/up and SwiGLU run in one kernel, the down projection writes 32-bit rows that
-the next norm kernel weighs and adds (`ops.ExpertRows`).
+  more rows              the persistent kernel: one CTA an SM walks over tiles of 128 token rows by 256 weight rows,
+                         its loads, its MMAs and its epilogue running side by side on two accumulators.
+Experts: the plan's tiles carry the expert, gate/up and SwiGLU run in one kernel, the down projection writes 32-bit
+rows that the next norm kernel weighs and adds (`ops.ExpertRows`). With a row or two an expert the gate/up product
+fetches each token row by its index; with more, the rows are copied into expert-sorted order first (by the plan
+kernel itself for a small step).
 Anything the kernels do not take (k or a row stride not a multiple of 8 elements, as TMA needs 16-byte strides)
 goes back to the CUDA-core kernels by returning None.
 """
@@ -111,7 +113,7 @@ class TensorCore:
         if swap is None:
             swap = M <= 128
         if bn is None:
-            bn = _pow2_at_least(M) if swap else 128
+            bn = _pow2_at_least(M) if swap else 256        # 256 without swap: the persistent kernel
         splits, partial = 1, None
         if swap and plan is None and not swiglu:
             ctas = -(-N // 128) * -(-M // bn)
@@ -158,7 +160,7 @@ class TensorCore:
         """(swapped?, token tile of the MMA's N side, rows of a plan tile) for `pairs` pairs over `experts` experts."""
         avg = pairs / experts
         swap = avg <= 48
-        bn = 16 if avg <= 12 else 32 if avg <= 24 else 64 if swap else 128
+        bn = 16 if avg <= 12 else 32 if avg <= 24 else 64 if swap else 256
         return swap, bn, lib().tl_tc_token_tile(int(swap), bn)
 
     def experts(self, part, x, ids, wts, plan=None):
@@ -171,21 +173,30 @@ class TensorCore:
         R, k = ids.shape
         P = R * k
         swap, bn, tile = self.expert_tile(P, E)
+        fetch = swap and P <= 2 * E           # a row or two a tile: the gate/up product fetches each token row by its index
+        xs = None
         if plan is None or plan.tile_m != tile:
-            plan = part.plan_for(P, x.device, tile).build(ids)
-        if part.record_counts:
-            part.last_counts = plan.counts.clone()
-        act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
-        if swap:
-            # few rows an expert: the gate/up product fetches each token row from where it lies
-            self.gemm(x, part.w_gate_up.view(E * I2, H), None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=True,
-                      bn=bn, n_out=inter, row_index=plan.sorted_pairs, row_div=k, rows=P)
-        else:
+            plan = part.plan_for(P, x.device, tile)
+            if fetch:
+                plan.build(ids)
+            else:
+                xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
+                if not plan.build(ids, x, xs).copied:      # the one-kernel plan of a small step copies the rows as well
+                    _check(lib().tl_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k, xs.data_ptr(),
+                                                P, H, ops.stream()), "gather_rows")
+        elif not fetch:
             xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
             _check(lib().tl_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k, xs.data_ptr(), P, H,
                                         ops.stream()), "gather_rows")
-            self.gemm(xs, part.w_gate_up.view(E * I2, H), None, act, rows_per_group=I2, plan=plan, swiglu=True,
-                      swap=False, bn=bn, n_out=inter)
+        if part.record_counts:
+            part.last_counts = plan.counts.clone()
+        act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
+        w_gate_up = part.w_gate_up.view(E * I2, H)
+        if fetch:
+            self.gemm(x, w_gate_up, None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=True, bn=bn, n_out=inter,
+                      row_index=plan.sorted_pairs, row_div=k, rows=P)
+        else:
+            self.gemm(xs, w_gate_up, None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=swap, bn=bn, n_out=inter)
         y = torch.empty(P, H, dtype=torch.float32, device=x.device)
         self.gemm(act, part.w_down.view(E * H, inter), None, y, rows_per_group=H, plan=plan, swap=swap, bn=bn, n_out=H)
         return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)
