@@ -277,7 +277,7 @@ def main() -> int:
         ms = max(e0.elapsed_time(e1), wall * 1e3)
         pages = max(len(engine.cache.table(0, r.request_id)) for r in reqs) if engine.cache.groups else 0
         h2d = 4 * (3 * batch + (batch + 1) + batch + batch + len(engine.cache.groups) * batch * max(pages, 1))
-        assert all(len(r.output) == warmup + steps for r in reqs)
+        assert all(sum(t >= 0 for t in r.output) == warmup + steps for r in reqs)      # a pending token may follow
         finish(reqs)
         return {"tok_s": batch * steps / (ms / 1e3), "h2d": h2d, "d2h": 4 * batch}
 

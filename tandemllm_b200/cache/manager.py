@@ -21,6 +21,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
 import torch
 
 from ..parts.base import PagedNeed, PagedSiteCache, SlotNeed, SlotSiteCache
@@ -81,6 +82,19 @@ class PageGroup:
     pool: PagePool
     page_size: int
     tables: dict = field(default_factory=dict)      # request id -> list of page ids by page index (-1: given back)
+    arrays: dict = field(default_factory=dict)      # request id -> the same table as an int32 array with room to grow
+                                                    # (what a step copies to the device without walking a list)
+
+    def extend(self, req, pages: list[int]) -> None:
+        table = self.tables[req]
+        arr = self.arrays[req]
+        n = len(table)
+        if n + len(pages) > arr.shape[0]:
+            grown = np.empty(max(2 * arr.shape[0], n + len(pages)), dtype=np.int32)
+            grown[:n] = arr[:n]
+            arr = self.arrays[req] = grown
+        arr[n:n + len(pages)] = pages
+        table.extend(pages)
 
     def pages_needed(self, req, new_len: int) -> int:
         table = self.tables.get(req, [])
@@ -138,6 +152,7 @@ class CacheManager:
         self._length[req] = 0
         for g in self.groups:
             g.tables[req] = []
+            g.arrays[req] = np.empty(64, dtype=np.int32)
         if self.device is not None:
             for i in self._slot_sites:
                 self.site_cache[i].state[slot].zero_()
@@ -171,7 +186,7 @@ class CacheManager:
         for g in self.groups:
             need = g.pages_needed(req, new_len)
             if need:
-                g.tables[req].extend(g.pool.take(need, req))
+                g.extend(req, g.pool.take(need, req))
 
     def advance(self, req, new_len: int) -> None:
         """The request now holds `new_len` tokens: windowed groups give back the pages no later row can read."""
@@ -188,6 +203,7 @@ class CacheManager:
                 g.pool.give_back(gone, req)
                 for j in range(min(first_needed, len(table))):
                     table[j] = -1
+                g.arrays[req][:min(first_needed, len(table))] = -1
 
     def free(self, req) -> None:
         """The request ends (or is preempted): every page and the slot go back."""
@@ -195,12 +211,18 @@ class CacheManager:
             raise RuntimeError(f"request {req!r} is not admitted (freed twice?)")
         for g in self.groups:
             g.pool.give_back([p for p in g.tables.pop(req) if p >= 0], req)
+            del g.arrays[req]
         self._free_slots.append(self._slot_of.pop(req))
         del self._length[req]
 
     # ---- what a step reads ----
     def table(self, group: int, req) -> list[int]:
         return self.groups[group].tables[req]
+
+    def table_array(self, group: int, req) -> "np.ndarray":
+        """The block table of `req` in `group` as an int32 array (a view: valid until the table next grows)."""
+        g = self.groups[group]
+        return g.arrays[req][:len(g.tables[req])]
 
     def max_table_len(self, reqs) -> int:
         return max((len(g.tables[r]) for g in self.groups for r in reqs), default=0)
@@ -221,6 +243,8 @@ class CacheManager:
             assert len(held) == len(set(held)), "a page is in two block tables"
             assert len(held) + g.pool.free == g.pool.num_pages, "a page was lost"
             assert len(set(g.pool._free)) == len(g.pool._free), "a page is on the free list twice"
+            for req, t in g.tables.items():
+                assert g.arrays[req][:len(t)].tolist() == t, f"the array of {req!r}'s table differs from the table"
             for req, t in g.tables.items():
                 for p in t:
                     assert p < 0 or g.pool.owner_of(p) == req, f"page {p} in the table of {req!r} is held by someone else"

@@ -66,6 +66,7 @@ struct NormParams {
 // With a router and many rows, a block norms this many rows before it multiplies them by the router's weights,
 // so that the weights are read once per block and not once per row.
 constexpr int MAX_ROWS_PER_BLOCK = 8;
+constexpr int PLAIN_ROWS_PER_BLOCK = 4;   // without a router
 
 // logits[rr, e] = rows[rr] . router_w[e] for the block's n_rows <= ROWS rows (in shared memory). Sixteen-byte loads,
 // eight of them in flight a lane, when the width allows.
@@ -110,7 +111,9 @@ __device__ __forceinline__ void router_logits(const NormParams& p, const float* 
   }
 }
 
-// One block per output row.
+// A block takes rows_per_block consecutive output rows at once, blockDim / rows_per_block threads (whole warps) a row:
+// one row for a decode step, several for a prompt, so that every thread has a few 16-byte loads of each input in
+// flight and the router's weights are read once a block.
 //   gather == nullptr: row r:  residual[r] += added[r];  normed[r] = w * residual[r] * rsqrt(mean + eps)
 //   gather != nullptr: output row i reads row gather[i] and leaves the residual as it is (the final norm of the
 //                      wanted rows only)
@@ -123,22 +126,23 @@ __global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 
   extern __shared__ __align__(16) float rows_buf[];
   float* scratch = rows_buf + (size_t)p.rows_per_block * p.hidden;
   float* logits = scratch + 33;
-  __shared__ int s_src[MAX_TOP_K];
-  __shared__ float s_w[MAX_TOP_K];
+  __shared__ int s_src[MAX_ROWS_PER_BLOCK][MAX_TOP_K];
+  __shared__ float s_w[MAX_ROWS_PER_BLOCK][MAX_TOP_K];
   chain_next();
   chain_wait();
   const int hidden = p.hidden;
   const int first_row = blockIdx.x * p.rows_per_block;
   const int n_rows = min(p.rows_per_block, p.out_rows - first_row);
-  for (int rr = 0; rr < n_rows; ++rr) {
-  const int out_r = first_row + rr;
+  const int G = blockDim.x / p.rows_per_block;           // threads a row
+  const int rr = threadIdx.x / G, t = threadIdx.x - rr * G;
+  const bool live = rr < n_rows;
+  const int out_r = first_row + (live ? rr : 0);
   float* row = rows_buf + (size_t)rr * hidden;
   const int r = p.gather ? p.gather[out_r] : out_r;
-  __syncthreads();            // the row before this one is done with the slot table and the reduction scratch
   if (p.expert_rows) {
-    if (threadIdx.x < 32) {
+    if (live && t < 32) {
       // the row's slots in ascending expert id (the slot index breaks ties): lane j ranks slot j among the others
-      const int k = p.top_k, j = threadIdx.x;
+      const int k = p.top_k, j = t;
       const bool mine = j < k;
       const int e = mine ? p.ids[(long long)r * k + j] : 0x7fffffff;
       const int src = mine ? p.pos_of_pair[(long long)r * k + j] : 0;
@@ -149,8 +153,8 @@ __global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 
         rank += (ei < e) || (ei == e && i < j);
       }
       if (mine) {
-        s_src[rank] = src;
-        s_w[rank] = w;
+        s_src[rr][rank] = src;
+        s_w[rr][rank] = w;
       }
     }
     __syncthreads();
@@ -159,82 +163,90 @@ __global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 
   const bool adds = p.delta || p.expert_rows;
   const bool vec = (hidden & 3) == 0;           // rows are then 16-byte aligned: four elements a step
   float ss = 0.f;
-  if (vec) {
-    const int h4 = hidden >> 2;
-    const float4* res4 = reinterpret_cast<const float4*>(res);
-    for (int c = threadIdx.x; c < h4; c += blockDim.x) {
-      float4 x = res4[c];
-      if (p.delta) {
-        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s = 0; s < p.parts; ++s) {
-          const float4 t = reinterpret_cast<const float4*>(p.delta + (long long)s * p.part_stride + (size_t)r * hidden)[c];
-          d.x += t.x; d.y += t.y; d.z += t.z; d.w += t.w;
+  if (live) {
+    if (vec) {
+      const int h4 = hidden >> 2;
+      const float4* res4 = reinterpret_cast<const float4*>(res);
+      for (int c = t; c < h4; c += G) {
+        float4 x = res4[c];
+        if (p.delta) {
+          float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s = 0; s < p.parts; ++s) {
+            const float4 v = reinterpret_cast<const float4*>(p.delta + (long long)s * p.part_stride + (size_t)r * hidden)[c];
+            d.x += v.x; d.y += v.y; d.z += v.z; d.w += v.w;
+          }
+          x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
         }
-        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
-      }
-      if (p.expert_rows) {
-        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int j = 0; j < p.top_k; ++j) {
-          const float4 t = reinterpret_cast<const float4*>(p.expert_rows + (long long)s_src[j] * hidden)[c];
-          const float w = s_w[j];
-          d.x = fmaf(w, t.x, d.x); d.y = fmaf(w, t.y, d.y); d.z = fmaf(w, t.z, d.z); d.w = fmaf(w, t.w, d.w);
+        if (p.expert_rows) {
+          float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int j = 0; j < p.top_k; ++j) {
+            const float4 v = reinterpret_cast<const float4*>(p.expert_rows + (long long)s_src[rr][j] * hidden)[c];
+            const float w = s_w[rr][j];
+            d.x = fmaf(w, v.x, d.x); d.y = fmaf(w, v.y, d.y); d.z = fmaf(w, v.z, d.z); d.w = fmaf(w, v.w, d.w);
+          }
+          x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
         }
-        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+        reinterpret_cast<float4*>(row)[c] = x;
+        ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
       }
-      reinterpret_cast<float4*>(row)[c] = x;
-      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
-    }
-  } else {
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-      float x = res[c];
-      if (p.delta) {
-        float d = 0.f;
-        for (int s = 0; s < p.parts; ++s) d += p.delta[(long long)s * p.part_stride + (size_t)r * hidden + c];
-        x += d;
+    } else {
+      for (int c = t; c < hidden; c += G) {
+        float x = res[c];
+        if (p.delta) {
+          float d = 0.f;
+          for (int s = 0; s < p.parts; ++s) d += p.delta[(long long)s * p.part_stride + (size_t)r * hidden + c];
+          x += d;
+        }
+        if (p.expert_rows) {
+          float d = 0.f;
+          for (int j = 0; j < p.top_k; ++j) d = fmaf(s_w[rr][j], p.expert_rows[(long long)s_src[rr][j] * hidden + c], d);
+          x += d;
+        }
+        row[c] = x;
+        ss += x * x;
       }
-      if (p.expert_rows) {
-        float d = 0.f;
-        for (int j = 0; j < p.top_k; ++j) d = fmaf(s_w[j], p.expert_rows[(long long)s_src[j] * hidden + c], d);
-        x += d;
-      }
-      row[c] = x;
-      ss += x * x;
     }
   }
-  ss = block_sum(ss, scratch);
+  // a row's sum of squares: its warps' sums, added in warp order
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  ss = 0.f;
+  for (int wi = rr * (G >> 5); wi < (rr + 1) * (G >> 5); ++wi) ss += scratch[wi];
   const float inv = rsqrtf(ss / (float)hidden + p.eps);
   T* out = (T*)p.normed + (size_t)out_r * hidden;
   float* out32 = p.normed32 ? p.normed32 + (size_t)out_r * hidden : nullptr;
-  if (vec) {
-    const int h4 = hidden >> 2;
-    for (int c = threadIdx.x; c < h4; c += blockDim.x) {
-      const float4 x = reinterpret_cast<const float4*>(row)[c];
-      if (!p.gather && adds) reinterpret_cast<float4*>(res)[c] = x;
-      const float4 w = reinterpret_cast<const float4*>(p.weight)[c];
-      const float4 y = make_float4(w.x * (x.x * inv), w.y * (x.y * inv), w.z * (x.z * inv), w.w * (x.w * inv));
-      if constexpr (sizeof(T) == 2) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
-        uint2 packed;
-        packed.x = *reinterpret_cast<uint32_t*>(&lo);
-        packed.y = *reinterpret_cast<uint32_t*>(&hi);
-        reinterpret_cast<uint2*>(out)[c] = packed;
-      } else {
-        reinterpret_cast<float4*>(out)[c] = y;
+  if (live) {
+    if (vec) {
+      const int h4 = hidden >> 2;
+      for (int c = t; c < h4; c += G) {
+        const float4 x = reinterpret_cast<const float4*>(row)[c];
+        if (!p.gather && adds) reinterpret_cast<float4*>(res)[c] = x;
+        const float4 w = reinterpret_cast<const float4*>(p.weight)[c];
+        const float4 y = make_float4(w.x * (x.x * inv), w.y * (x.y * inv), w.z * (x.z * inv), w.w * (x.w * inv));
+        if constexpr (sizeof(T) == 2) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+          uint2 packed;
+          packed.x = *reinterpret_cast<uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<uint32_t*>(&hi);
+          reinterpret_cast<uint2*>(out)[c] = packed;
+        } else {
+          reinterpret_cast<float4*>(out)[c] = y;
+        }
+        if (out32) reinterpret_cast<float4*>(out32)[c] = y;
+        reinterpret_cast<float4*>(row)[c] = y;
       }
-      if (out32) reinterpret_cast<float4*>(out32)[c] = y;
-      reinterpret_cast<float4*>(row)[c] = y;
-    }
-  } else {
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-      const float x = row[c];
-      if (!p.gather && adds) res[c] = x;
-      const float y = p.weight[c] * (x * inv);
-      out[c] = from_f32<T>(y);
-      if (out32) out32[c] = y;
-      row[c] = y;
+    } else {
+      for (int c = t; c < hidden; c += G) {
+        const float x = row[c];
+        if (!p.gather && adds) res[c] = x;
+        const float y = p.weight[c] * (x * inv);
+        out[c] = from_f32<T>(y);
+        if (out32) out32[c] = y;
+        row[c] = y;
+      }
     }
   }
-  }   // rows of this block
   if constexpr (ROUTE_PER > 0) {
     __syncthreads();
     // logits[row, e] = row . router_w[e]: each warp takes experts warp, warp + nwarps, ...; lanes stride over the
@@ -304,7 +316,8 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
     TL_REQUIRE(route_k > 0 && route_k <= E && route_k <= MAX_TOP_K && route_ids && route_wts,
                "router: top-%d of %d experts; up to top-%d is implemented", route_k, E, MAX_TOP_K);
   }
-  int rows_per_block = (router_w && out_rows > 64) ? MAX_ROWS_PER_BLOCK : 1;
+  // prompts: several rows a block (eight beside a router, whose weights are then read once for eight rows)
+  int rows_per_block = out_rows > 64 ? (router_w ? MAX_ROWS_PER_BLOCK : PLAIN_ROWS_PER_BLOCK) : 1;
   while (rows_per_block > 1 && (size_t)rows_per_block * (hidden + E) * sizeof(float) > 96 * 1024) rows_per_block /= 2;
   const size_t smem = ((size_t)rows_per_block * hidden + 33 + (router_w ? (size_t)rows_per_block * E : 0)) * sizeof(float);
   TL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory, the limit is 204800",
@@ -316,7 +329,8 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
   p.router_bias = router_bias; p.E = E; p.route_k = route_k; p.normalize = normalize; p.floor_ = floor_; p.scale = scale;
   p.route_ids = route_ids; p.route_wts = route_wts;
   p.rows_per_block = rows_per_block; p.out_rows = out_rows;
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (threads < 32 * rows_per_block) threads = 32 * rows_per_block;       // whole warps a row
   const dim3 grid(ceil_div(out_rows, rows_per_block));
   const int per = !router_w ? 0 : (E <= 32 ? 1 : (E <= 128 ? 4 : MAX_EXPERTS / 32));
 #define TL_NORM(T_, PER_)                                                                                         \

@@ -42,6 +42,18 @@ class EngineArgs:
     device: str = "cuda:0"
     graph: bool = True                  # capture decode-only steps in CUDA graphs (bfloat16)
     tensorcore: bool = True             # use the tcgen05 kernels in bfloat16
+    overlap: bool = True                # launch the next decode step before this one's tokens are read
+
+
+@dataclass
+class _Flight:
+    """A step that is launched and not yet accounted."""
+    batch: list                         # the scheduler's entries
+    host: torch.Tensor                  # pinned int32: the sampled tokens, then the kernels' status word
+    n: int                              # sampled tokens
+    event: torch.cuda.Event             # recorded behind the copies into `host`
+    tokens: torch.Tensor | None         # the sampled tokens on the device
+    index: dict                         # request id -> its place among them
 
 
 def require_cuda(device: str) -> torch.device:
@@ -61,6 +73,9 @@ class Engine:
             pages = args.parallel * (-(-args.max_len // args.block_size))
         self.cache = CacheManager(model.cache_needs(), num_pages=pages, max_requests=args.parallel,
                                   page_size=args.block_size, dtype=model.runtime.dtype, device=self.device)
+        self._results = [None, None]    # pinned host memory for a step's tokens and status, for two steps in the air
+        self._turn = 0
+        self._flight = None             # a step that is launched and not yet accounted
         self.step_function = StepFunction(model, self.cache, use_graphs=args.graph and model.graph_safe,
                                           max_graph_batch=args.parallel)
         self.sampler = Sampler(self.device)
@@ -148,17 +163,87 @@ class Engine:
         return req
 
     def run_step(self) -> list[Request]:
-        """One scheduler step: schedule, run, sample, account. Returns the requests that finished."""
-        batch = self.scheduler.schedule()
-        if not batch:
-            return []
+        """One scheduler step: schedule, run, sample, account. Returns the requests that finished.
+
+        With `overlap` (the default) and nothing but decoding to do, the step after this one is scheduled and launched
+        before this one's tokens are read: its token ids are the sampler's output, fed on the device, and its
+        integers are staged while the GPU works. A request that ends on a stop id has then run one row for nothing,
+        which is dropped; requests that end by their token limit are known beforehand and run no such row."""
+        sch = self.scheduler
+        while True:
+            if self._flight is None:
+                batch = sch.schedule()
+                if not batch:
+                    return []
+                self._flight = self._launch(batch, None)
+                sch.advance(batch)
+            cur, self._flight = self._flight, None
+            if self.args.overlap and self._runs_ahead(cur):
+                batch = sch.schedule()
+                if batch:
+                    self._flight = self._launch(batch, cur)
+                    sch.advance(batch)
+            # rows of requests that ended (or were aborted) after the step was launched count for nothing
+            live = any(s.request.last_slot is None or s.slot <= s.request.last_slot for s in cur.batch if s.samples) \
+                or not any(s.samples for s in cur.batch)
+            done = self._account(cur)
+            if self._flight is not None and not sch.has_unfinished():
+                # nothing is left to schedule: the step launched ahead holds the last tokens of requests that end by
+                # their token limit, or nothing but rows of requests that ended on a stop id
+                last, self._flight = self._flight, None
+                if any(s.finishes for s in last.batch):
+                    done += self._account(last)
+            if live or not sch.has_unfinished():
+                return done
+
+    def _account(self, flight: "_Flight") -> list[Request]:
+        """Wait for a launched step and hand its tokens to the scheduler; returns the requests that finished."""
+        flight.event.synchronize()
+        if self.step_function.check_status and int(flight.host[flight.n]):
+            self._flight = None
+            self.step_function.raise_on_fault()
+        return self.scheduler.resolve(flight.batch, flight.host[:flight.n].tolist())
+
+    def _runs_ahead(self, cur: "_Flight") -> bool:
+        """Whether the next step is known before this one's tokens are: every running request has just the token
+        pending that `cur` is computing, nobody waits to be admitted, and the rows and their pages fit."""
+        sch = self.scheduler
+        if sch.waiting or not sch.running or len(sch.running) > sch.budget:
+            return False
+        if any(r.pending != 1 or r.request_id not in cur.index for r in sch.running):
+            return False
+        return not sch._pages_short([(r, 1) for r in sch.running])
+
+    def _launch(self, batch, before: "_Flight | None") -> "_Flight":
+        """Run `batch` and its sampling without waiting for them. `before`: the step whose tokens this one's rows
+        take from the device."""
+        fn = self.step_function
         entries = [StepEntry(s.request.request_id, s.request.tokens[s.start:s.start + s.count],
                              [s.count - 1] if s.samples else []) for s in batch]
+        feedback = None
+        if before is not None:
+            feedback = (before.tokens, [before.index[e.request] for e in entries])
         with torch.cuda.device(self.device):
-            logits = self.step_function.run(entries)
+            # one wait a step: the chosen tokens and the kernels' status word come back together
+            checks, fn.check_status = fn.check_status, False
+            try:
+                logits = fn.run(entries, feedback)
+            finally:
+                fn.check_status = checks
             rows = [(s.request.params, len(s.request.prompt) + len(s.request.output)) for s in batch if s.samples]
-            tokens = self.sampler(logits, rows).tolist() if rows else []
-        return self.scheduler.update(batch, tokens)
+            n = len(rows)
+            self._turn ^= 1
+            host = self._results[self._turn]
+            if host is None or host.numel() < n + 1:
+                host = self._results[self._turn] = torch.empty(max(64, 2 * (n + 1)), dtype=torch.int32).pin_memory()
+            tokens = self.sampler(logits, rows) if n else None
+            if n:
+                host[:n].copy_(tokens, non_blocking=True)
+            host[n:n + 1].copy_(self.model.runtime.status, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+        index = {s.request.request_id: i for i, s in enumerate(x for x in batch if x.samples)}
+        return _Flight(batch, host, n, event, tokens, index)
 
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None
                  ) -> list[list[int]]:

@@ -32,6 +32,7 @@ from ..cache.manager import CacheManager
 from ..sampling.sampler import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PENDING = -1        # in a request's output: a token that a launched step is still computing
 
 
 @dataclass
@@ -45,6 +46,7 @@ class Request:
     finish_reason: str | None = None
     preemptions: int = 0
     order: int = 0
+    last_slot: int | None = None    # where in `output` the request's last token sits, once that is known
 
     @property
     def tokens(self) -> list[int]:
@@ -61,6 +63,8 @@ class Scheduled:
     start: int          # index of the first token fed this step
     count: int          # tokens fed this step
     samples: bool       # the portion ends at the request's last token: a new token is drawn from its last row
+    slot: int = -1      # where in the request's output that token goes (set when the step is accounted)
+    finishes: bool = False   # the request ends with this step
 
 
 @dataclass
@@ -175,33 +179,64 @@ class Scheduler:
         return out
 
     # ---- results in ----
-    def update(self, batch: list[Scheduled], new_tokens: list[int]) -> list[Request]:
-        """Account the step: `new_tokens` holds one token per entry with `samples`, in batch order.
-        Returns the requests that finished."""
-        done = []
-        it = iter(new_tokens)
+    def advance(self, batch: list[Scheduled]) -> None:
+        """Account what is known of a step as soon as it is launched: the rows are in the cache, every sampling
+        entry has a token coming (a PENDING place in its output until `resolve` fills it), and a request that
+        reaches its token limit or the window's end with that token leaves the running set now. The next step can
+        be scheduled, and launched with the pending tokens fed on the device, before this one's tokens are read."""
         for s in batch:
             r = s.request
             r.num_computed += s.count
             if not s.samples:
                 continue
-            tok = int(next(it))
-            r.output.append(tok)
-            stops = r.params.stop_token_ids if r.params.stop_token_ids is not None else self.stop_token_ids
-            if not r.params.ignore_eos and tok in stops:
-                r.finish_reason = "stop"
-            elif len(r.output) >= r.params.max_tokens:
+            r.output.append(PENDING)
+            s.slot = len(r.output) - 1
+            if len(r.output) >= r.params.max_tokens:
                 r.finish_reason = "length"
             elif len(r.prompt) + len(r.output) >= self.max_model_len:
                 r.finish_reason = "max_model_len"
             if r.finish_reason:
-                r.state = FINISHED
-                self.running.remove(r)
-                self.cache.free(r.request_id)
+                s.finishes = True
+                r.last_slot = s.slot
+                self._retire(r)
+
+    def _retire(self, r: Request) -> None:
+        r.state = FINISHED
+        self.running.remove(r)
+        self.cache.free(r.request_id)
+
+    def resolve(self, batch: list[Scheduled], new_tokens: list[int]) -> list[Request]:
+        """The step's tokens are here: `new_tokens` holds one per entry with `samples`, in batch order. Fills the
+        pending places, ends a request on a stop id (dropping what a step launched ahead of this one added for it)
+        and returns the requests that finished with this step."""
+        done = []
+        it = iter(new_tokens)
+        for s in batch:
+            if not s.samples:
+                continue
+            tok = int(next(it))
+            r = s.request
+            if (r.last_slot is not None and s.slot > r.last_slot) or s.slot >= len(r.output):
+                continue        # the request ended with an earlier token (or was aborted): this row ran for nothing
+            r.output[s.slot] = tok
+            stops = r.params.stop_token_ids if r.params.stop_token_ids is not None else self.stop_token_ids
+            if not r.params.ignore_eos and tok in stops:
+                r.finish_reason = "stop"
+                del r.output[s.slot + 1:]
+                r.last_slot = s.slot
+                if r.state != FINISHED:
+                    self._retire(r)
+                s.finishes = True
+            if s.finishes:
                 self.finished.append(r)
                 self.stats.finished += 1
                 done.append(r)
         return done
+
+    def update(self, batch: list[Scheduled], new_tokens: list[int]) -> list[Request]:
+        """Account a whole step at once: `advance`, then `resolve`. Returns the requests that finished."""
+        self.advance(batch)
+        return self.resolve(batch, new_tokens)
 
     def abort(self, request: Request) -> None:
         """Take a request out wherever it is; its pages and slot go back."""
@@ -210,4 +245,4 @@ class Scheduler:
             self.cache.free(request.request_id)
         elif request.state == WAITING:
             self.waiting.remove(request)
-        request.state, request.finish_reason = FINISHED, "aborted"
+        request.state, request.finish_reason, request.last_slot = FINISHED, "aborted", -1

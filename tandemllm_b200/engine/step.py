@@ -20,6 +20,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, OutOfPages
@@ -144,7 +145,7 @@ class StepFunction:
                 host[o["out"] + k] = r + w
                 k += 1
             for g in range(G):
-                t = cache.table(g, e.request)
+                t = cache.table_array(g, e.request)
                 base = o["tab"] + (g * B + b) * max_pages
                 host[base:base + len(t)] = t
                 host[base + len(t):base + max_pages] = -1
@@ -153,6 +154,25 @@ class StepFunction:
             max_ctx = max(max_ctx, start + n)
         host[o["start"] + B] = r
         return max_rows, max_ctx
+
+    def _fill_decode(self, host, o: dict, entries: list[StepEntry], max_pages: int) -> None:
+        """`_fill` for a step of one token a request whose logits are all wanted: whole columns at a time."""
+        cache = self.cache
+        B, G = len(entries), len(cache.groups)
+        reqs = [e.request for e in entries]
+        count = np.arange(B + 1, dtype=np.int32)
+        host[o["tok"]:o["tok"] + B] = [e.tokens[0] for e in entries]
+        host[o["pos"]:o["pos"] + B] = [cache.length_of(r) for r in reqs]
+        host[o["req"]:o["req"] + B] = count[:B]
+        host[o["start"]:o["start"] + B + 1] = count
+        host[o["slot"]:o["slot"] + B] = [cache.slot_of(r) for r in reqs]
+        host[o["out"]:o["out"] + B] = count[:B]
+        tables = host[o["tab"]:o["tab"] + G * B * max_pages].reshape(G, B, max_pages)
+        tables.fill(-1)
+        for g in range(G):
+            for b, r in enumerate(reqs):
+                t = cache.table_array(g, r)
+                tables[g, b, :t.shape[0]] = t
 
     def _context(self, dev: torch.Tensor, o: dict, B: int, R: int, n_out: int, max_pages: int, max_rows: int,
                  max_ctx: int, host_lists: dict) -> StepContext:
@@ -187,15 +207,20 @@ class StepFunction:
         return self._context(dev, o, B, R, n_out, max_pages, max_rows, max_ctx, lists)
 
     # ---- running ----
-    def run(self, entries: list[StepEntry]) -> torch.Tensor:
-        """Logits float32 [wanted, vocab] in the order of the entries and of their `want`."""
+    def run(self, entries: list[StepEntry], feedback: tuple[torch.Tensor, list[int]] | None = None) -> torch.Tensor:
+        """Logits float32 [wanted, vocab] in the order of the entries and of their `want`. `feedback` = (int32 token
+        ids on the device, an index into them for every entry): each entry brings one token, and it is taken from
+        there instead of from the entry (the step before this one may still be computing it)."""
         if not entries:
             return torch.empty(0, self.model.vocab_size, dtype=torch.float32, device=self.device)
+        if feedback is not None and (len(feedback[1]) != len(entries) or any(len(e.tokens) != 1 for e in entries)):
+            raise ValueError("tokens fed on the device: one token and one index for every entry")
         if (self.use_graphs and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and e.want == [0] for e in entries)):
-            logits = self._run_decode_graph(entries)
+            logits = self._run_decode_graph(entries, feedback)
         else:
             step = self.build(entries)
+            self._feed(step, feedback)
             logits = self.model.forward(step, self.cache.site_cache)
         for e in entries:
             self.cache.advance(e.request, self.cache.length_of(e.request) + len(e.tokens))
@@ -205,7 +230,16 @@ class StepFunction:
             self.raise_on_fault()
         return logits
 
-    def _run_decode_graph(self, entries: list[StepEntry]) -> torch.Tensor:
+    def _feed(self, step: StepContext, feedback) -> None:
+        if feedback is None:
+            return
+        source, index = feedback
+        if index == list(range(source.numel())):
+            step.token_ids.copy_(source)
+        else:
+            step.token_ids.copy_(source[torch.tensor(index, dtype=torch.int64).to(self.device, non_blocking=True)])
+
+    def _run_decode_graph(self, entries: list[StepEntry], feedback=None) -> torch.Tensor:
         """A decode-only step: eager the first time its shape is seen (and then captured), a graph replay after."""
         self._reserve(entries)
         cache = self.cache
@@ -225,9 +259,10 @@ class StepFunction:
             lists = {"row_start": list(range(B + 1)), "start_pos": None, "slots": None}
             slot = self._graphs[key] = _DecodeGraph(dev, self._context(dev, o, B, B, B, width, 1, ctx, lists))
         pinned = self._pinned(o["total"])
-        self._fill(pinned.numpy(), o, entries, width)
+        self._fill_decode(pinned.numpy(), o, entries, width)
         slot.dev.copy_(pinned[:o["total"]], non_blocking=True)
         self._staging.copied()
+        self._feed(slot.step, feedback)
         if slot.graph is not None:
             slot.graph.replay()
             self.graph_replays += 1

@@ -203,6 +203,36 @@ def test_finishing_on_stop_id_length_and_window():
     assert c.finish_reason == "length" and len(c.output) == 4
 
 
+def test_two_steps_in_the_air_drop_the_row_behind_a_stop_id():
+    """`advance` when a step is launched, `resolve` when its tokens are read, with the next step scheduled in
+    between: a request that ends on a stop id loses the row launched ahead of the news, one that ends by its token
+    limit never gets such a row, and the pages of both go back once."""
+    sched, fake = make()
+    a = Request("a", [1, 2], SamplingParams(max_tokens=50, stop_token_ids=(77,)))
+    b = Request("b", [5], SamplingParams(max_tokens=3, ignore_eos=True))
+    sched.add(a), sched.add(b)
+    first = sched.schedule()
+    fake.run(first)
+    sched.advance(first)
+    assert a.output == [-1] and b.output == [-1] and a.pending == 1
+    ahead = sched.schedule()                                   # scheduled before the first step's tokens are known
+    assert [(s.request.request_id, s.count) for s in ahead] == [("a", 1), ("b", 1)]
+    fake.run(ahead)
+    sched.advance(ahead)
+    assert sched.resolve(first, [40, 41]) == [] and a.output == [40, -1] and b.output == [41, -1]
+    third = sched.schedule()
+    fake.run(third)
+    sched.advance(third)                                       # b reaches its limit here: known without its token
+    assert b.state == "finished" and b not in sched.running and not sched.cache.has("b")
+    assert sched.resolve(ahead, [77, 42]) == [a]               # a's stop id: its row in `third` ran for nothing
+    assert a.output == [40, 77] and a.finish_reason == "stop" and not sched.cache.has("a")
+    assert sched.schedule() == []
+    assert sched.resolve(third, [99, 43]) == [b] and b.output == [41, 42, 43] and b.finish_reason == "length"
+    assert a.output == [40, 77] and sched.finished == [a, b] and not sched.has_unfinished()
+    sched.cache.check()
+    assert all(g.pool.free == g.pool.num_pages for g in sched.cache.groups)
+
+
 def test_refused_at_the_door():
     sched, _ = make(pages=4, max_len=100)
     with pytest.raises(ValueError, match="empty"):

@@ -249,6 +249,40 @@ def test_greedy_generation_through_the_entry_point(case):
         greedy_like_plain(case, prompt, out)
 
 
+def test_steps_launched_ahead_end_on_stop_ids_like_steps_taken_one_by_one(case):
+    """With `overlap` the step after a decode step is launched before its tokens are read. Requests that end on a
+    stop id (found one step late), by their token limit (known beforehand) and while others go on must give the
+    text, the reasons and the page accounts of an engine that takes one step at a time."""
+    from tandemllm_b200.sampling import SamplingParams
+    prompts = T.prompts(case.name)
+    free_run = case.engine(max_tokens=1024, overlap=False).generate(
+        prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+    # stop ids taken from the free-running text, so that requests end at different steps
+    # (every other request gets a stop id that never comes, and ends by its token limit)
+    absent = lambda out: next(t for t in range(case.cfg["vocab_size"]) if t not in out)
+    stops = [[out[5 + 3 * i]] if i % 2 == 0 else [absent(out)] for i, out in enumerate(free_run)]
+    params = [SamplingParams(temperature=0.0, max_tokens=12 + 4 * i, stop_token_ids=tuple(st))
+              for i, st in enumerate(stops)]
+    results = {}
+    for overlap in (False, True):
+        eng = case.engine(max_tokens=1024, overlap=overlap)
+        reqs = [eng.add_request(p, SamplingParams(**vars(sp))) for p, sp in zip(prompts, params)]
+        while eng.scheduler.has_unfinished():
+            eng.run_step()
+        results[overlap] = [(r.output, r.finish_reason) for r in reqs]
+        assert all(t >= 0 for r in reqs for t in r.output)
+        eng.cache.check()
+        assert all(g.pool.free == g.pool.num_pages for g in eng.cache.groups) and not eng.scheduler.running
+    if case.dtype == "float32":
+        assert results[True] == results[False]
+    for (out, reason), sp, free in zip(results[True], params, free_run):
+        assert reason in ("stop", "length") and len(out) <= sp.max_tokens
+        assert (out[-1] in sp.stop_token_ids) == (reason == "stop") and not set(out[:-1]) & set(sp.stop_token_ids)
+        if case.dtype == "float32":
+            assert out == free[:len(out)]
+    assert {reason for _, reason in results[True]} == {"stop", "length"} or len(prompts) < 2
+
+
 def test_sampled_generation_in_mixed_chunks_repeats_and_matches_the_plain_draws(case):
     """Temperature 0.7 with a fixed seed, prompts fed as chunks of 8 beside decode tokens: the same tokens whatever
     the batching, and each token is the plain implementation's keyed draw from the plain logits."""
