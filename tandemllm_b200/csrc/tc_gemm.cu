@@ -148,7 +148,9 @@ struct Smem {
   // stage, a little more for a third stage), so that two CTAs share an SM: one's epilogue runs under the other's main loop, and with chained launches the next product's CTA sits
   // beside the running one with its first weight tiles already on the way. Two CTAs an SM also put a decode step's
   // expert tiles (a few hundred CTAs) into one wave.
-  static constexpr int BUDGET = (SWAP && SWIGLU) ? 110 * 1024 : 100 * 1024;
+  // The swapped plain product keeps to a third: its CTAs stream little each (a decode step's down projections are a
+  // few hundred CTAs of half a MB), and three an SM put them into one wave.
+  static constexpr int BUDGET = SWAP ? (SWIGLU ? 110 * 1024 : 74 * 1024) : 100 * 1024;
   static constexpr int FIT = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = FIT > 8 ? 8 : (FIT < 2 ? 2 : FIT);
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
