@@ -164,7 +164,9 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    ap.add_argument("--layers", type=int, default=24, help="run only the first N layers (the line names both numbers)")
+    ap.add_argument("--sizes", default="8b", choices=("8b", "24b"),
+                    help="layer sizes: LFM2-8B-A1B (the default and the headline) or the 24B-A2B class (40 layers, 64 experts)")
+    ap.add_argument("--layers", type=int, default=0, help="run only the first N layers (the line names both numbers)")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
@@ -192,9 +194,16 @@ def main() -> int:
     from tandemllm_b200.sampling import SamplingParams
 
     raw = dict(CONFIG_8B)
-    if a.layers != 24:
+    model_name = "LFM2-8B-A1B layer sizes"
+    if a.sizes == "24b":
+        model_name = "LFM2.5-24B-A2B-class layer sizes"
+        raw.update(num_hidden_layers=40, intermediate_size=11776, moe_intermediate_size=1536, num_experts=64,
+                   layer_types=["full_attention" if i % 4 == 2 else "conv" for i in range(40)])
+    layers_of_model = raw["num_hidden_layers"]
+    a.layers = a.layers or layers_of_model
+    if a.layers != layers_of_model:
+        raw["layer_types"] = raw["layer_types"][:a.layers]
         raw["num_hidden_layers"] = a.layers
-        raw["layer_types"] = LAYER_TYPES_8B[:a.layers]
     cfg = Lfm2MoeConfig.from_dict(raw)
     pk = peaks()
     max_batch = 64 if not a.skip_points else a.batch
@@ -341,15 +350,17 @@ def main() -> int:
         points["decode_b64"] = round(device_decode(64, a.context, few, 3)["tok_s"], 1)
         pre = prefill(PREFILL_TOKENS)
     line = {
-        "metric": "decode tok/s at batch 8, context 8192 (LFM2-8B-A1B layer sizes, B200)",
+        "metric": f"decode tok/s at batch {a.batch}, context {a.context} ({model_name}, B200)",
         "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16" if a.dtype == "bfloat16" else "fp32",
         "data": "synthetic: random weights N(0, 0.02), uniform random token ids, random keys and values as context",
         "impl": "ours",
-        "config": {"model": "LFM2-8B-A1B layer sizes", "layers": a.layers, "layers_of_model": 24, "conv_layers": len(cfg.conv_layers),
-                   "attention_layers": len(cfg.attention_layers), "hidden": 2048, "heads": 32, "kv_heads": 8, "head_dim": 64,
-                   "dense_ffn": 7168, "experts": 32, "top_k": 4, "expert_ffn": 1792, "vocab": 65536,
+        "config": {"model": model_name, "layers": a.layers, "layers_of_model": layers_of_model,
+                   "conv_layers": len(cfg.conv_layers), "attention_layers": len(cfg.attention_layers),
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "dense_ffn": cfg.intermediate_size, "experts": cfg.num_experts,
+                   "top_k": cfg.num_experts_per_tok, "expert_ffn": cfg.moe_intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": a.batch, "seq_len": a.context, "parallelism": "none (1 GPU)", "page_tokens": 16,
                    "graph": a.graph, "l2": "inputs>L2 (a step reads GBs of weights)"},
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d"],
