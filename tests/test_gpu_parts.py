@@ -200,6 +200,64 @@ def register_toy():
     return ToyDecay
 
 
+def register_toy_switch_and_position():
+    """A feed-forward with routing of its own (the one expert with the largest router logit, unweighted) and another
+    position encoding (rotation of interleaved pairs, applied by the mixer between the norm and the cache write)."""
+    from tandemllm_b200.parts import Part, register_part
+    from tandemllm_b200.parts.linear import linear
+    from tandemllm_b200.weights.loader import TensorSpec
+
+    @register_part("feed_forward", "toy_switch")
+    class ToySwitch(Part):
+        def __init__(self, spec, prefix="", hidden_size=0, **_):
+            super().__init__(spec, prefix, hidden_size)
+            self.experts, self.inner = int(spec["experts"]), int(spec["inner"])
+
+        def weight_specs(self, present=None):
+            H, I = self.hidden_size, self.inner
+            out = [TensorSpec(self.prefix + "switch.weight", (self.experts, H))]
+            for e in range(self.experts):
+                out += [TensorSpec(f"{self.prefix}e{e}.up.weight", (I, H)), TensorSpec(f"{self.prefix}e{e}.down.weight", (H, I))]
+            return out
+
+        def bind(self, read, runtime):
+            self.runtime = runtime
+            self.w_switch = runtime.matrix(read(self.prefix + "switch.weight"))
+            self.w = [(runtime.matrix(read(f"{self.prefix}e{e}.up.weight")), runtime.matrix(read(f"{self.prefix}e{e}.down.weight")))
+                      for e in range(self.experts)]
+
+        def forward(self, x, step, x32=None, routing=None):
+            choice = linear(self.runtime, x, self.w_switch, out_dtype=torch.float32).argmax(-1)
+            out = torch.zeros(x.shape[0], self.hidden_size, dtype=torch.float32, device=x.device)
+            for e, (up, down) in enumerate(self.w):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    hidden = torch.relu(linear(self.runtime, x[rows].contiguous(), up))
+                    out[rows] = linear(self.runtime, hidden, down, out_dtype=torch.float32)
+            return out
+
+    @register_part("position_encoding", "toy_pairs")
+    class ToyPairs(Part):
+        def __init__(self, spec, head_dim=0, **_):
+            super().__init__(spec)
+            self.step_angle = float(spec["angle"])
+
+        def bind(self, read, runtime):
+            self.runtime = runtime
+
+        def fused_rotary(self):
+            return None                                             # not something the fused q/k kernel applies
+
+        def apply(self, q, k, positions):
+            ang = positions.float()[:, None, None] * self.step_angle
+            cos, sin = torch.cos(ang), torch.sin(ang)
+            for t in (q, k):                                        # in place: pair (2i, 2i+1) turns by position * angle
+                a, b = t[..., 0::2].float().clone(), t[..., 1::2].float().clone()
+                t[..., 0::2] = (a * cos - b * sin).to(t.dtype)
+                t[..., 1::2] = (a * sin + b * cos).to(t.dtype)
+    return ToySwitch, ToyPairs
+
+
 def toy_spec(raw):
     from tandemllm_b200.config import ModelSpec, PartSpec, Site
     from tandemllm_b200.config.spec import LayerSpec
@@ -213,11 +271,19 @@ def toy_spec(raw):
                                   "names": {"q": "q_proj", "k": "k_proj", "v": "v_proj", "out": "out_proj",
                                             "q_norm": "q_layernorm", "k_norm": "k_layernorm"}})
     toy = PartSpec("toy_decay", {"name": "decay"})
+    turned = PartSpec("attention", {"num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                                    "qk_norm": PartSpec("rmsnorm", {"eps": eps}),
+                                    "position": PartSpec("toy_pairs", {"angle": 0.37}), "window": None,
+                                    "names": {"q": "q_proj", "k": "k_proj", "v": "v_proj", "out": "out_proj",
+                                              "q_norm": "q_layernorm", "k_norm": "k_layernorm"}})
+    switch = PartSpec("toy_switch", {"experts": 3, "inner": 40})
     layers = (LayerSpec("blocks.0.", toy, ffn, norm("n1"), norm("n2")),
               LayerSpec("blocks.1.", attn, ffn, norm("n1"), norm("n2")),
-              LayerSpec("blocks.2.", attn, ffn, norm("n1"), norm("n2")))
-    # layer 0 runs twice (two states); layer 2 attends over the keys and values site 1 wrote
-    schedule = (Site(0), Site(1), Site(0), Site(2, cache_of=1))
+              LayerSpec("blocks.2.", attn, ffn, norm("n1"), norm("n2")),
+              LayerSpec("blocks.3.", turned, switch, norm("n1"), norm("n2")))
+    # layer 0 runs twice (two states); layer 2 attends over the keys and values site 1 wrote; layer 3 has the toy
+    # position encoding, the toy routed feed-forward and, with no window, pages of its own
+    schedule = (Site(0), Site(1), Site(0), Site(2, cache_of=1), Site(3))
     return ModelSpec("ToyForCausalLM", H, raw["vocab"], layers, schedule, PartSpec("rmsnorm", {"eps": eps}),
                      embedding_name="tok.weight", final_norm_prefix="out_norm.", head_name="head.weight",
                      name_prefixes=("",))
@@ -253,7 +319,36 @@ def toy_plain(raw, W, tokens):
     # keys and values come from site 1's input n1, queries from n3
     a = _cross_attention(n3, n1, mixed, cfg, raw["window"])
     h = ffn(h + a, "blocks.2.")
+    # site 4: attention with pairs turned by position * 0.37, no window; then the switch feed-forward
+    n4 = P.rms_norm(h, W["blocks.3.n1.weight"], eps)
+    h = h + _turned_attention(n4, {k.replace("blocks.3.", "x."): v for k, v in W.items() if k.startswith("blocks.3.")}, cfg)
+    n5 = P.rms_norm(h, W["blocks.3.n2.weight"], eps)
+    choice = (n5 @ W["blocks.3.switch.weight"].T).argmax(-1)
+    branch = torch.stack([torch.relu(n5[t] @ W[f"blocks.3.e{int(e)}.up.weight"].T) @ W[f"blocks.3.e{int(e)}.down.weight"].T
+                          for t, e in enumerate(choice)])
+    h = h + branch
     return P.rms_norm(h, W["out_norm.weight"], eps) @ W["head.weight"].T
+
+
+def _turned_attention(n, W, cfg):
+    T = n.shape[0]
+    Hq, Hk, D, eps = 4, 2, 16, cfg["norm_eps"]
+    q = P.rms_norm((n @ W["x.q_proj.weight"].T).view(T, Hq, D), W["x.q_layernorm.weight"], eps)
+    k = P.rms_norm((n @ W["x.k_proj.weight"].T).view(T, Hk, D), W["x.k_layernorm.weight"], eps)
+    v = (n @ W["x.v_proj.weight"].T).view(T, Hk, D)
+    ang = torch.arange(T).float()[:, None, None] * 0.37
+
+    def turn(t):
+        a, b = t[..., 0::2], t[..., 1::2]
+        out = torch.empty_like(t)
+        out[..., 0::2], out[..., 1::2] = a * torch.cos(ang) - b * torch.sin(ang), a * torch.sin(ang) + b * torch.cos(ang)
+        return out
+    q, k = turn(q), turn(k)
+    ks, vs = k.repeat_interleave(2, 1), v.repeat_interleave(2, 1)
+    s = torch.einsum("thd,shd->hts", q, ks) * D ** -0.5
+    i = torch.arange(T)
+    a = torch.softmax(s.masked_fill((i[None, :] > i[:, None])[None], float("-inf")), -1)
+    return torch.einsum("hts,shd->thd", a, vs).reshape(T, Hq * D) @ W["x.out_proj.weight"].T
 
 
 def _cross_attention(nq, nkv, W, cfg, window):
@@ -277,10 +372,11 @@ def _cross_attention(nq, nkv, W, cfg, window):
 def test_a_toy_architecture_registers_builds_and_steps(tmp_path):
     from tandemllm_b200.config import Architecture, register, unregister
     from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
-    from tandemllm_b200.parts import MIXERS, DecoderModel
+    from tandemllm_b200.parts import FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, DecoderModel
     from tandemllm_b200.weights.random_init import random_tensor
     from tandemllm_b200.weights.safetensors_io import write_file
     register_toy()
+    register_toy_switch_and_position()
     register(Architecture("toy", ("ToyForCausalLM",), ("toy",), lambda raw, folder, generation: toy_spec(raw)))
     try:
         raw = {"architectures": ["ToyForCausalLM"], "width": 48, "inner": 80, "vocab": 101, "eps": 1e-5, "window": 24}
@@ -289,10 +385,10 @@ def test_a_toy_architecture_registers_builds_and_steps(tmp_path):
         (tmp_path / "config.json").write_text(json.dumps(raw))
         write_file(str(tmp_path / "model.safetensors"), W)
         eng = Engine.from_folder(str(tmp_path), EngineArgs(dtype="float32", max_len=512, parallel=2, kv_blocks=6))
-        # two page groups would exist only with different needs; here site 1 owns the one windowed group and
-        # site 3 borrows it; the two toy sites have a state slot each
-        assert len(eng.cache.groups) == 1 and eng.cache.groups[0].need.window == 24
-        assert eng.cache.groups[0].sites == [1] and eng.cache._slot_sites == [0, 2]
+        # site 1 owns the windowed group and site 3 borrows it; site 4, with no window, has pages of its own; the two
+        # toy sites have a state slot each
+        assert len(eng.cache.groups) == 2 and [g.need.window for g in eng.cache.groups] == [24, None]
+        assert eng.cache.groups[0].sites == [1] and eng.cache.groups[1].sites == [4] and eng.cache._slot_sites == [0, 2]
         toks = torch.randint(0, 101, (90,), generator=torch.Generator().manual_seed(5)).tolist()
         want = toy_plain(raw, W, toks)
         eng.admit("t")
@@ -302,10 +398,12 @@ def test_a_toy_architecture_registers_builds_and_steps(tmp_path):
             at += n
         assert at == 90
         assert max_rel(torch.cat(outs), want) < 1e-4
-        # 90 tokens went through 6 pages of 16 because the window gives pages back
-        assert eng.cache.groups[0].pool.used <= 3
+        # 90 tokens went through 6 pages of 16 because the window gives pages back; the group without a window holds all
+        assert eng.cache.groups[0].pool.used <= 3 and eng.cache.groups[1].pool.used == 6
         eng.release("t")
-        assert eng.cache.groups[0].pool.free == 6
+        assert eng.cache.groups[0].pool.free == 6 and eng.cache.groups[1].pool.free == 6
     finally:
         unregister("toy")
         MIXERS.pop("toy_decay", None)
+        FEED_FORWARDS.pop("toy_switch", None)
+        POSITION_ENCODINGS.pop("toy_pairs", None)
