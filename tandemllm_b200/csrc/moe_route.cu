@@ -8,7 +8,7 @@
 //
 // The plan is a stable counting sort: pairs keep their row order inside an expert, so the order of every
 // sum is fixed by the inputs alone (the only atomics count integers). Two forms build the same plan: for any
-// number of pairs, a kernel that counts each chunk of 1024 pairs per expert and one that places them; and one
+// number of pairs, a kernel that counts each chunk of 256 pairs per expert and one that places them; and one
 // kernel for up to 4096 pairs (a decode step) that also copies the token rows into expert-sorted order for the
 // tensor-core kernels.
 #include "route.cuh"
@@ -26,7 +26,8 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
              wts + (long long)warp * k);
 }
 
-constexpr int PLAN_CHUNK = 1024;     // pairs a block of the two-kernel plan takes
+constexpr int PLAN_CHUNK = 256;      // pairs a block of the two-kernel plan takes
+constexpr int PLAN_WARPS = PLAN_CHUNK / 32;
 
 // grid ceil(P / PLAN_CHUNK): block b counts its chunk's pairs per expert into block_hist[b, :]
 __global__ void __launch_bounds__(PLAN_CHUNK) moe_hist_kernel(const int* __restrict__ ids, int P, int E,
@@ -46,20 +47,22 @@ __global__ void __launch_bounds__(PLAN_CHUNK) moe_hist_kernel(const int* __restr
 }
 
 // grid ceil(P / PLAN_CHUNK): block b places its chunk's pairs: a pair of expert e lands behind all pairs of lower
-// experts, behind the pairs of e in earlier chunks, and behind the earlier pairs of e in its own chunk, so the
-// sorted list keeps pair order within an expert. Block 0 also writes counts, offsets and the row tiles.
+// experts, behind the pairs of e in earlier chunks, behind those of e in earlier warps of its own chunk and behind the
+// earlier lanes of its own warp, so the sorted list keeps pair order within an expert. Block 0 also writes counts,
+// offsets and the row tiles.
 __global__ void __launch_bounds__(PLAN_CHUNK) moe_place_kernel(const int* __restrict__ ids, int P, int E, int tile_m,
                                                                const int* __restrict__ block_hist, int* __restrict__ counts,
                                                                int* __restrict__ offsets, int* __restrict__ sorted_pairs,
                                                                int* __restrict__ pos_of_pair, int* __restrict__ tile_group,
                                                                int* __restrict__ tile_row0, int* __restrict__ tile_rows,
                                                                int* __restrict__ n_tiles) {
-  __shared__ int total[MAX_EXPERTS];      // pairs of each expert in all chunks
-  __shared__ int base[MAX_EXPERTS];       // where this chunk's first pair of each expert lands
-  __shared__ int run[MAX_EXPERTS];        // pairs of each expert placed so far by this block's earlier warps
+  __shared__ int total[MAX_EXPERTS];                  // pairs of each expert in all chunks
+  __shared__ int base[MAX_EXPERTS];                   // where this chunk's first pair of each expert lands
+  __shared__ int in_warp[PLAN_WARPS][MAX_EXPERTS];    // pairs of each expert in each warp of this chunk, then the sums before each warp
   chain_next();
   chain_wait();
   const int b = blockIdx.x, nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < PLAN_WARPS * MAX_EXPERTS; i += PLAN_CHUNK) (&in_warp[0][0])[i] = 0;
   for (int e = tid; e < E; e += PLAN_CHUNK) {
     int all = 0, before = 0;
     for (int i = 0; i < nb; ++i) {
@@ -68,27 +71,48 @@ __global__ void __launch_bounds__(PLAN_CHUNK) moe_place_kernel(const int* __rest
       if (i < b) before += v;
     }
     total[e] = all;
-    run[e] = before;
+    base[e] = before;
   }
   __syncthreads();
-  for (int e = tid; e < E; e += PLAN_CHUNK) {
+  const int p = b * PLAN_CHUNK + tid;
+  int e = p < P ? ids[p] : -1;
+  if ((unsigned)e >= (unsigned)E) e = -1;
+  const bool hit = e >= 0;
+  const unsigned hits = __ballot_sync(0xffffffffu, hit);
+  unsigned same = 0;
+  if (hit) {
+    same = __match_any_sync(hits, e);
+    if (lane == __ffs(same) - 1) in_warp[warp][e] = __popc(same);
+  }
+  __syncthreads();
+  for (int x = tid; x < E; x += PLAN_CHUNK) {
     int lower = 0;
-    for (int i = 0; i < e; ++i) lower += total[i];
-    base[e] = lower + run[e];
+    for (int i = 0; i < x; ++i) lower += total[i];
+    base[x] += lower;
+    int run = 0;                                     // pairs of x in this chunk's earlier warps
+    for (int w = 0; w < PLAN_WARPS; ++w) {
+      const int c = in_warp[w][x];
+      in_warp[w][x] = run;
+      run += c;
+    }
     if (b == 0) {
-      counts[e] = total[e];
-      offsets[e] = lower;
-      if (e == E - 1) offsets[E] = lower + total[e];
+      counts[x] = total[x];
+      offsets[x] = lower;
+      if (x == E - 1) offsets[E] = lower + total[x];
     }
   }
   __syncthreads();
-  for (int e = tid; e < E; e += PLAN_CHUNK) run[e] = 0;
+  if (hit) {
+    const int at = base[e] + in_warp[warp][e] + __popc(same & ((1u << lane) - 1u));
+    sorted_pairs[at] = p;
+    pos_of_pair[p] = at;
+  }
   if (b == 0 && tid == 0) {
     int off = 0, tiles = 0;
-    for (int e = 0; e < E; ++e) {
-      const int cnt = total[e];
+    for (int x = 0; x < E; ++x) {
+      const int cnt = total[x];
       for (int t = 0; t * tile_m < cnt; ++t) {
-        tile_group[tiles] = e;
+        tile_group[tiles] = x;
         tile_row0[tiles] = off + t * tile_m;
         tile_rows[tiles] = min(tile_m, cnt - t * tile_m);
         ++tiles;
@@ -96,26 +120,6 @@ __global__ void __launch_bounds__(PLAN_CHUNK) moe_place_kernel(const int* __rest
       off += cnt;
     }
     *n_tiles = tiles;
-  }
-  __syncthreads();
-  const int p = b * PLAN_CHUNK + tid;
-  int e = p < P ? ids[p] : -1;
-  if ((unsigned)e >= (unsigned)E) e = -1;
-  const bool hit = e >= 0;
-  for (int w = 0; w < PLAN_CHUNK / 32; ++w) {     // warp after warp, so that earlier pairs land first
-    if (warp == w) {
-      const unsigned hits = __ballot_sync(0xffffffffu, hit);
-      if (hit) {
-        const unsigned same = __match_any_sync(hits, e);
-        const int placed = run[e];
-        __syncwarp(hits);
-        const int at = base[e] + placed + __popc(same & ((1u << lane) - 1u));
-        sorted_pairs[at] = p;
-        pos_of_pair[p] = at;
-        if (lane == __ffs(same) - 1) run[e] = placed + __popc(same);
-      }
-    }
-    __syncthreads();
   }
 }
 

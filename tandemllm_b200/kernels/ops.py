@@ -365,7 +365,7 @@ class MoePlan:
         self.tile_row0 = torch.zeros(self.max_tiles_cap, **i32)
         self.tile_rows = torch.zeros(self.max_tiles_cap, **i32)
         self.n_tiles = torch.zeros(1, **i32)
-        self.block_hist = torch.zeros(-(-max(max_pairs, 1) // 1024) * num_experts, **i32)   # per-chunk counts
+        self.block_hist = torch.zeros(-(-max(max_pairs, 1) // 256) * num_experts, **i32)    # per-chunk counts
         self.pairs = 0
         self.max_tiles = 1
 
