@@ -43,6 +43,8 @@ struct NormParams {
   int parts;
   long long part_stride;
   const float* expert_rows;
+  int expert_parts;          // the expert rows come as this many partial sums (1: whole), expert_part_stride floats apart
+  long long expert_part_stride;
   const int* pos_of_pair;
   const int* ids;
   const float* wts;
@@ -180,7 +182,12 @@ __global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 
         if (p.expert_rows) {
           float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
           for (int j = 0; j < p.top_k; ++j) {
-            const float4 v = reinterpret_cast<const float4*>(p.expert_rows + (long long)s_src[rr][j] * hidden)[c];
+            float4 v = reinterpret_cast<const float4*>(p.expert_rows + (long long)s_src[rr][j] * hidden)[c];
+            for (int s = 1; s < p.expert_parts; ++s) {       // a down projection split along k: its partial sums, in order
+              const float4 more = reinterpret_cast<const float4*>(p.expert_rows + (long long)s * p.expert_part_stride +
+                                                                  (long long)s_src[rr][j] * hidden)[c];
+              v.x += more.x; v.y += more.y; v.z += more.z; v.w += more.w;
+            }
             const float w = s_w[rr][j];
             d.x = fmaf(w, v.x, d.x); d.y = fmaf(w, v.y, d.y); d.z = fmaf(w, v.z, d.z); d.w = fmaf(w, v.w, d.w);
           }
@@ -199,7 +206,12 @@ __global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 
         }
         if (p.expert_rows) {
           float d = 0.f;
-          for (int j = 0; j < p.top_k; ++j) d = fmaf(s_w[rr][j], p.expert_rows[(long long)s_src[rr][j] * hidden + c], d);
+          for (int j = 0; j < p.top_k; ++j) {
+            float v = p.expert_rows[(long long)s_src[rr][j] * hidden + c];
+            for (int s = 1; s < p.expert_parts; ++s)
+              v += p.expert_rows[(long long)s * p.expert_part_stride + (long long)s_src[rr][j] * hidden + c];
+            d = fmaf(s_w[rr][j], v, d);
+          }
           x += d;
         }
         row[c] = x;
@@ -301,7 +313,8 @@ extern "C" void tl_set_chained_launches(int enabled) { chained_launches() = enab
 
 // See NormParams for the forms of what is added. Null pointers switch a form or the router off.
 extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, long long part_stride,
-                              const float* expert_rows, const int* pos_of_pair, const int* ids, const float* wts, int top_k,
+                              const float* expert_rows, int expert_parts, long long expert_part_stride,
+                              const int* pos_of_pair, const int* ids, const float* wts, int top_k,
                               const float* weight, void* normed, float* normed32, const int* gather, int out_rows,
                               int hidden, float eps, int dtype, const float* router_w, const float* router_bias, int E,
                               int route_k, int normalize, float floor_, float scale, int* route_ids, float* route_wts,
@@ -324,6 +337,7 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
              hidden, smem);
   NormParams p = {};
   p.residual = residual; p.delta = delta; p.parts = parts; p.part_stride = part_stride; p.expert_rows = expert_rows;
+p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = expert_part_stride;
   p.pos_of_pair = pos_of_pair; p.ids = ids; p.wts = wts; p.top_k = top_k; p.weight = weight; p.eps = eps;
   p.normed = normed; p.normed32 = normed32; p.gather = gather; p.hidden = hidden; p.router_w = router_w;
   p.router_bias = router_bias; p.E = E; p.route_k = route_k; p.normalize = normalize; p.floor_ = floor_; p.scale = scale;

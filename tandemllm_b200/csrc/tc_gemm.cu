@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     const int quad = warp & 3;
     const int m_row = quad * 32 + lane;                  // row of the M side this thread owns
     bool ok = num_kb > 0 ? mbar_wait(acc_ready, 0) : true;
-    if (num_kb == 0) chain_wait();      // an empty k range writes zeros, and nothing else has ordered them behind the kernels in front
+    if (num_kb <= 0) chain_wait();      // an empty k range writes zeros, and nothing else has ordered them behind the kernels in front
     if (!ok) {
       *aborted = 1;
       atomicExch(p.status, 11);
@@ -741,7 +741,7 @@ extern "C" int tl_tc_token_tile(int swap, int bn) { return swap ? bn : TILE_M; }
 
 // X [M, K] (row stride ldx), W [groups * rows_per_group, K] (row stride ldw). Plain: groups = 1, tile_group = nullptr.
 // swiglu: W holds 2 N rows per group (gate then up) and C = silu(gate) * up. out_dtype: TL_BF16 or TL_FP32.
-// splits > 1 (swap, not swiglu, not grouped): `partial` must hold splits * M * N floats.
+// splits > 1 (swap, not swiglu): `partial` must hold splits * M * N floats; a grouped product leaves the sums to the caller.
 // row_index (swap, grouped; or null): the tile map's rows are positions of this list, and position i stands for row
 // row_index[i] / row_div of X; without it X itself is in the tile map's order.
 extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
@@ -756,8 +756,8 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
              ldx, ldw);
   TL_REQUIRE(((uintptr_t)X & 15) == 0 && ((uintptr_t)W & 15) == 0, "tensor-core gemm: operands must be 16-byte aligned");
   TL_REQUIRE(out_dtype == TL_BF16 || out_dtype == TL_FP32, "tensor-core gemm: output dtype %d", out_dtype);
-  TL_REQUIRE(splits >= 1 && (splits == 1 || (swap && !swiglu && !tile_group && partial)),
-             "tensor-core gemm: split-K needs the swapped plain kernel and a workspace");
+  TL_REQUIRE(splits >= 1 && (splits == 1 || (swap && !swiglu && partial && (!tile_group || !reduce))),
+             "tensor-core gemm: split-K needs the swapped plain kernel and a workspace (grouped: the caller adds the sums)");
   TL_REQUIRE(!bias || !swiglu, "tensor-core gemm: a bias with the SwiGLU epilogue is not implemented");
   TL_REQUIRE(!row_index || (swap && tile_group && row_div >= 1),
              "tensor-core gemm: a row index needs the swapped grouped kernel (divisor %d)", row_div);
@@ -774,7 +774,8 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles; p.status = status;
   p.row_index = row_index; p.row_div = row_index ? row_div : 1;
   const int tok_tile = swap ? bn : TILE_M, n_tile = swap ? TILE_M : bn;
-  dim3 grid(ceil_div(N, n_tile), tile_group ? max_tiles : ceil_div(M, tok_tile), ceil_div(total_kb, p.k_blocks_per_split));
+  // one CTA layer a split, also where rounding leaves the last splits without k-blocks: they write zeros
+  dim3 grid(ceil_div(N, n_tile), tile_group ? max_tiles : ceil_div(M, tok_tile), splits);
   TL_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "tensor-core gemm: grid %u x %u x %u exceeds the limits", grid.x, grid.y, grid.z);
   int e;
   if (persistent) {

@@ -32,7 +32,8 @@ def dtype_code(dtype: torch.dtype) -> int:
 
 _SIGNATURES = {
     "tl_embed_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "tl_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+    "tl_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                       c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                        c_float, c_float, c_void_p, c_void_p, c_void_p],
     "tl_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -146,12 +147,18 @@ class ExpertRows:
     """A routed expert layer's output still as one row per (row, slot) pair in expert-sorted order [pairs, hidden]
     (32-bit), with what is needed to weigh and add them per row."""
 
-    def __init__(self, rows: torch.Tensor, pos_of_pair: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor):
-        self.rows, self.pos_of_pair, self.ids, self.wts = rows, pos_of_pair, ids, wts
+    def __init__(self, rows: torch.Tensor, pos_of_pair: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, parts: int = 1):
+        """`parts` > 1: `rows` is [parts, pairs, hidden], partial sums of a down projection split along k."""
+        self.rows, self.pos_of_pair, self.ids, self.wts, self.parts = rows, pos_of_pair, ids, wts, parts
 
     def materialize(self) -> torch.Tensor:
-        out = torch.empty(self.ids.shape[0], self.rows.shape[1], dtype=torch.float32, device=self.rows.device)
-        check(core().tl_moe_combine(ptr(self.rows), ptr(self.pos_of_pair), ptr(self.ids), ptr(self.wts), ptr(out),
+        rows = self.rows
+        if self.parts > 1:
+            rows = rows[0].clone()
+            for part in self.rows[1:]:
+                rows += part
+        out = torch.empty(self.ids.shape[0], rows.shape[-1], dtype=torch.float32, device=rows.device)
+        check(core().tl_moe_combine(ptr(rows), ptr(self.pos_of_pair), ptr(self.ids), ptr(self.wts), ptr(out),
                                     out.shape[0], out.shape[1], self.ids.shape[1], stream()), "moe_combine")
         return out
 
@@ -174,11 +181,13 @@ def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
         _need(out32, torch.float32, "normed32")
     dense = parts = stride = 0
     rows_ptr = pos = ids = wts = None
-    top_k = 0
+    top_k, eparts, estride = 0, 1, 0
     if isinstance(delta, PartialSums):
         dense, parts, stride = delta.data.data_ptr(), delta.parts, delta.rows * delta.hidden
     elif isinstance(delta, ExpertRows):
         rows_ptr, pos, ids, wts, top_k = delta.rows, delta.pos_of_pair, delta.ids, delta.wts, delta.ids.shape[1]
+        if delta.parts > 1:
+            eparts, estride = delta.parts, delta.rows.shape[1] * delta.rows.shape[2]
     elif delta is not None:
         _need(delta, torch.float32, "delta")
         dense, parts = delta.data_ptr(), 1
@@ -188,7 +197,8 @@ def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
     if route:
         _need(r["weight"], torch.float32, "router weight"); _need(r["ids"], torch.int32, "ids"); _need(r["wts"], torch.float32, "wts")
     check(core().tl_add_rmsnorm(
-        ptr(residual), dense or None, parts, stride, ptr(rows_ptr), ptr(pos), ptr(ids), ptr(wts), top_k, ptr(weight),
+        ptr(residual), dense or None, parts, stride, ptr(rows_ptr), eparts, estride, ptr(pos), ptr(ids), ptr(wts), top_k,
+        ptr(weight),
         ptr(out), ptr(out32), ptr(gather), n_out, hidden, float(eps), dtype_code(out.dtype), ptr(r.get("weight")),
         ptr(r.get("bias")), r["weight"].shape[0] if route else 0, int(r.get("k", 0)), int(r.get("normalize", 0)),
         float(r.get("floor", 0.0)), float(r.get("scale", 1.0)), ptr(r.get("ids")), ptr(r.get("wts")), stream()),

@@ -103,7 +103,7 @@ class TensorCore:
 
     # ---- x @ w^T (+ bias) ----
     def gemm(self, x, w2d, bias, out, *, rows_per_group=0, plan=None, swiglu=False, swap=None, bn=None, n_out=None,
-             defer: bool = False, row_index=None, row_div: int = 1, rows: int | None = None):
+             defer: bool = False, row_index=None, row_div: int = 1, rows: int | None = None, splits: int = 1):
         """Runs the product into `out`. With `defer`, a product that was split along k is left as partial sums and
         returned as `ops.PartialSums` (nothing is written to `out`); otherwise returns None. With `row_index` (grouped,
         swapped) the plan's position i stands for row row_index[i] // row_div of x, and `rows` is the number of
@@ -114,8 +114,10 @@ class TensorCore:
             swap = M <= 128
         if bn is None:
             bn = _pow2_at_least(M) if swap else 256        # 256 without swap: the persistent kernel
-        splits, partial = 1, None
-        if swap and plan is None and not swiglu:
+        forced, partial = splits > 1, None
+        if forced:
+            partial = out           # the caller's [splits, M, N] partial sums begin at `out`; the caller adds them
+        elif swap and plan is None and not swiglu:
             ctas = -(-N // 128) * -(-M // bn)
             kb = -(-K // 64)
             if ctas < SM_COUNT and kb >= 8:
@@ -124,7 +126,7 @@ class TensorCore:
                     partial = self.workspace(splits * M * N)
         # `defer` True: a 32-bit result may stay in partial sums; "rounded": so may one of any precision, and its
         # consumer rounds the sum to the output's precision
-        deferred = bool(defer) and splits > 1 and (out.dtype == torch.float32 or defer == "rounded")
+        deferred = forced or (bool(defer) and splits > 1 and (out.dtype == torch.float32 or defer == "rounded"))
         tg = tr0 = trs = nt = None
         max_tiles = 0
         if plan is not None:
@@ -136,7 +138,7 @@ class TensorCore:
             ops.ptr(partial), int(not deferred),
             self.status.data_ptr(), ops.stream())
         _check(code, "gemm_tc", kernels=2 if splits > 1 and not deferred else 1)
-        if not deferred:
+        if not deferred or forced:
             return None
         return ops.PartialSums(partial, splits, M, N, None if out.dtype == torch.float32 else out.dtype)
 
@@ -197,8 +199,16 @@ class TensorCore:
                       row_index=plan.sorted_pairs, row_div=k, rows=P)
         else:
             self.gemm(xs, w_gate_up, None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=swap, bn=bn, n_out=inter)
+        w_down = part.w_down.view(E * H, inter)
+        ctas = min(P, E) * -(-H // 128)
+        if fetch and ctas < SM_COUNT and inter >= 512:
+            # as few pairs: the down product is split along k as well, and the norm kernel adds its partial sums
+            splits = max(2, min(-(-inter // 64) // 4, -(-SM_COUNT // ctas), 16))
+            y = self.workspace(splits * P * H)[:splits * P * H].view(splits, P, H)
+            self.gemm(act, w_down, None, y[0], rows_per_group=H, plan=plan, swap=True, bn=bn, n_out=H, splits=splits)
+            return ops.ExpertRows(y, plan.pos_of_pair, ids, wts, parts=splits)
         y = torch.empty(P, H, dtype=torch.float32, device=x.device)
-        self.gemm(act, part.w_down.view(E * H, inter), None, y, rows_per_group=H, plan=plan, swap=swap, bn=bn, n_out=H)
+        self.gemm(act, w_down, None, y, rows_per_group=H, plan=plan, swap=swap, bn=bn, n_out=H)
         return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)
 
 

@@ -99,6 +99,7 @@ def test_split_k_is_used_and_repeatable():
 
 
 @pytest.mark.parametrize("R,E,k,H,I", [(4, 8, 2, 128, 64), (8, 32, 4, 256, 192), (64, 8, 3, 136, 72), (700, 6, 2, 128, 96),
+                                       (1, 32, 4, 256, 1024), (2, 16, 3, 200, 520), (5, 6, 2, 136, 72),
                                        (2048, 4, 2, 64, 128)])
 def test_grouped_experts_with_swiglu(R, E, k, H, I):
     from tandemllm_b200.config import PartSpec
@@ -118,11 +119,16 @@ def test_grouped_experts_with_swiglu(R, E, k, H, I):
     part.bind(lambda n: W[n], rt)
     x = rnd(R, H, seed=12)
     ids, wts = part.route(x.float().to(DEV))
-    rows = impl.experts(part, x.to(DEV), ids, wts)
-    assert rows is not None
-    out = rows.materialize()
+    from tandemllm_b200.kernels import ops
+    result = impl.experts(part, x.to(DEV), ids, wts)
+    assert result is not None
+    out = result.materialize()
+    # the same rows as the norm kernel adds them (partial sums of a split down product included)
+    residual = torch.zeros(R, H, dtype=torch.float32, device=DEV)
+    ops.add_rmsnorm(residual, result, torch.ones(H, device=DEV), 1e-5, torch.empty(R, H, dtype=torch.bfloat16, device=DEV))
     torch.cuda.synchronize()
     assert int(rt.status) == 0
+    assert (residual - out).abs().max() <= 1e-5 * out.abs().max()
     want = torch.zeros(R, H)
     xf, idc, wc = x.float(), ids.cpu(), wts.cpu()
     for e in range(E):
