@@ -58,7 +58,8 @@ template <int D> __device__ __forceinline__ int swz(int row, int chunk) { return
 template <int D, bool KEYSPLIT, int STAGES>
 __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-    const int* __restrict__ block_table, int max_pages, int page_size, int page_shift, const int* __restrict__ tiles,
+    const int* __restrict__ block_table, int max_pages, int page_size, int page_shift, int num_pages,
+    const int* __restrict__ tiles,
     const int* __restrict__ positions, float scale, int window, bf16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, int n_spans, int split, int Hq, int Hk, int* __restrict__ status) {
   constexpr int CH = D / 8;                 // 16-byte chunks per row
@@ -110,7 +111,7 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
     long long off = 0;
     if (valid) {
       const int pg = page_shift >= 0 ? kp >> page_shift : kp / page_size;
-      const int page = table[pg];
+      const int page = table_page(table, pg, max_pages, num_pages);
       if (page < 0) {
         atomicExch(status, 3);
         valid = false;
@@ -326,7 +327,7 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
 
 template <int D, bool KEYSPLIT, int STAGES>
 static int launch_mma(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int max_pages,
-                      int page_size, const int* tiles, int n_tiles, const int* positions, float scale, int window,
+                      int page_size, int num_pages, const int* tiles, int n_tiles, const int* positions, float scale, int window,
                       void* out, float* part_o, float* part_ml, int n_spans, int split, int Hq, int Hk, int* status,
                       cudaStream_t stream) {
   constexpr int SMEM = ((KEYSPLIT ? 16 : 64) + 2 * STAGES * 64) * D * 2;
@@ -344,7 +345,7 @@ static int launch_mma(const void* q, const void* k_cache, const void* v_cache, c
   dim3 grid(n_tiles, Hk, split ? n_spans : 1);
   return (int)launch_chained(attention_mma_kernel<D, KEYSPLIT, STAGES>, grid, dim3(128), SMEM, stream, (const bf16*)q,
                              (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size, page_shift,
-                             tiles, positions, scale, window, (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status);
+                             num_pages, tiles, positions, scale, window, (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status);
 }
 
 }  // namespace tl
@@ -366,7 +367,7 @@ extern "C" int tl_attention_mma_supported(int Hq, int Hk, int D) {
 // form that splits the keys among the warps runs. With split, scratch holds rows * Hq * n_spans * (D + 2) floats and
 // the caller runs the join afterwards (tl_attention_join) when n_spans > 1.
 extern "C" int tl_paged_attention_mma(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                      int max_pages, int page_size, const int* tiles, int n_tiles, int max_tile_rows,
+                                      int max_pages, int page_size, int num_pages, const int* tiles, int n_tiles, int max_tile_rows,
                                       const int* positions, float scale, int window, void* out, float* scratch, int rows,
                                       int Hq, int Hk, int D, int n_spans, int split, int* status, cudaStream_t stream) {
   if (rows == 0 || n_tiles == 0) return 0;
@@ -382,7 +383,7 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_cache, const 
   float* part_ml = scratch ? scratch + (long long)rows * Hq * n_spans * D : nullptr;
   const bool keysplit = max_tile_rows * (Hq / Hk) <= 16;
 #define TL_MMA(D_, KS_, ST_)                                                                                               \
-  launch_mma<D_, KS_, ST_>(q, k_cache, v_cache, block_table, max_pages, page_size, tiles, n_tiles, positions, scale, window, \
+  launch_mma<D_, KS_, ST_>(q, k_cache, v_cache, block_table, max_pages, page_size, num_pages, tiles, n_tiles, positions, scale, window, \
                            out, part_o, part_ml, n_spans, split, Hq, Hk, status, stream)
   if (D == 64) return keysplit ? TL_MMA(64, true, 4) : TL_MMA(64, false, 2);
   return keysplit ? TL_MMA(128, true, 3) : TL_MMA(128, false, 2);

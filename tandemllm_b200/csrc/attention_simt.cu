@@ -25,7 +25,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) qk_prepare_kernel(
     const T* __restrict__ qkv, long long ld_qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
     float eps, const float* __restrict__ inv_freq, int rotary_dim, const int* __restrict__ positions,
-    const int* __restrict__ req_of_row, const int* __restrict__ block_table, int max_pages, int page_size,
+    const int* __restrict__ req_of_row, const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, T* __restrict__ k_out,
     T* __restrict__ v_out, int Hq, int Hk, int D, int* __restrict__ status) {
   __shared__ float vec[4][MAX_HEAD_DIM];
@@ -54,8 +54,8 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(
     dst = q_out + ((long long)r * Hq + head) * D;
   } else if (k_cache) {
     const int b = req_of_row[r];
-    const int page = block_table[(long long)b * max_pages + pos / page_size];
-    if (page < 0) {   // no page behind this position: record it and drop the write
+    const int page = table_page(block_table + (long long)b * max_pages, pos / page_size, max_pages, num_pages);
+    if (page < 0) {   // no page behind this position (or an entry outside the pool): record it and drop the write
       if (lane == 0) atomicExch(status, 2);
       return;
     }
@@ -90,11 +90,11 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(
 template <typename T>
 __global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v, const int* __restrict__ positions,
                                 const int* __restrict__ req_of_row, const int* __restrict__ block_table, int max_pages,
-                                int page_size, T* __restrict__ k_cache, T* __restrict__ v_cache, int Hk, int D,
+                                int page_size, int num_pages, T* __restrict__ k_cache, T* __restrict__ v_cache, int Hk, int D,
                                 int* __restrict__ status) {
   const int r = blockIdx.x, kvh = blockIdx.y;
   const int pos = positions[r], b = req_of_row[r];
-  const int page = block_table[(long long)b * max_pages + pos / page_size];
+  const int page = table_page(block_table + (long long)b * max_pages, pos / page_size, max_pages, num_pages);
   if (page < 0) {
     if (threadIdx.x == 0) atomicExch(status, 2);
     return;
@@ -111,7 +111,7 @@ __global__ void kv_store_kernel(const T* __restrict__ k, const T* __restrict__ v
 template <typename T>
 __global__ void __launch_bounds__(128) paged_attention_simt_kernel(
     const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
-    const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ req_of_row,
+    const int* __restrict__ block_table, int max_pages, int page_size, int num_pages, const int* __restrict__ req_of_row,
     const int* __restrict__ positions, float scale, int window, T* __restrict__ out, int Hq, int Hk, int D,
     int* __restrict__ status) {
   __shared__ float qs[4][MAX_HEAD_DIM];
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(128) paged_attention_simt_kernel(
     long long off = -1;
     float s = -INFINITY;
     if (valid) {
-      const int page = table[kp / page_size];
+      const int page = table_page(table, kp / page_size, max_pages, num_pages);
       if (page < 0) {
         atomicExch(status, 3);      // a visible key without a page: recorded, the key is skipped
       } else {
@@ -193,7 +193,7 @@ static int check_heads(const char* what, int Hq, int Hk, int D) {
 
 extern "C" int tl_qk_prepare(const void* qkv, long long ld_qkv, const float* q_weight, const float* k_weight, float eps,
                              const float* inv_freq, int rotary_dim, const int* positions, const int* req_of_row,
-                             const int* block_table, int max_pages, int page_size, void* q_out, void* k_cache,
+                             const int* block_table, int max_pages, int page_size, int num_pages, void* q_out, void* k_cache,
                              void* v_cache, void* k_out, void* v_out, int rows, int Hq, int Hk, int D, int dtype,
                              int* status, cudaStream_t stream) {
   if (rows == 0) return 0;
@@ -207,36 +207,38 @@ extern "C" int tl_qk_prepare(const void* qkv, long long ld_qkv, const float* q_w
   cudaError_t e;
   if (dtype == TL_FP32)
     e = launch_chained(qk_prepare_kernel<float>, grid, dim3(128), 0, stream, (const float*)qkv, ld_qkv, q_weight, k_weight, eps,
-                       inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, (float*)q_out,
+                       inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, num_pages, (float*)q_out,
                        (float*)k_cache, (float*)v_cache, (float*)k_out, (float*)v_out, Hq, Hk, D, status);
   else
     e = launch_chained(qk_prepare_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)qkv, ld_qkv, q_weight, k_weight, eps,
-                       inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, (bf16*)q_out,
+                       inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, num_pages, (bf16*)q_out,
                        (bf16*)k_cache, (bf16*)v_cache, (bf16*)k_out, (bf16*)v_out, Hq, Hk, D, status);
   return (int)e;
 }
 
 extern "C" int tl_kv_store(const void* k, const void* v, const int* positions, const int* req_of_row,
-                           const int* block_table, int max_pages, int page_size, void* k_cache, void* v_cache, int rows,
-                           int Hk, int D, int dtype, int* status, cudaStream_t stream) {
+                           const int* block_table, int max_pages, int page_size, int num_pages, void* k_cache, void* v_cache,
+                           int rows, int Hk, int D, int dtype, int* status, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (int e = check_heads("kv_store", Hk, Hk, D)) return e;
   dim3 grid(rows, Hk);
   TL_REQUIRE(Hk <= 65535, "kv_store: %d KV heads exceed the grid limit", Hk);
   if (dtype == TL_FP32)
     kv_store_kernel<float><<<grid, 64, 0, stream>>>((const float*)k, (const float*)v, positions, req_of_row, block_table,
-                                                    max_pages, page_size, (float*)k_cache, (float*)v_cache, Hk, D, status);
+                                                    max_pages, page_size, num_pages, (float*)k_cache, (float*)v_cache, Hk, D,
+                                                    status);
   else
     kv_store_kernel<bf16><<<grid, 64, 0, stream>>>((const bf16*)k, (const bf16*)v, positions, req_of_row, block_table,
-                                                   max_pages, page_size, (bf16*)k_cache, (bf16*)v_cache, Hk, D, status);
+                                                   max_pages, page_size, num_pages, (bf16*)k_cache, (bf16*)v_cache, Hk, D,
+                                                   status);
   TL_LAUNCH_CHECK();
   return 0;
 }
 
 extern "C" int tl_paged_attention_simt(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                       int max_pages, int page_size, const int* req_of_row, const int* positions,
-                                       float scale, int window, void* out, int rows, int Hq, int Hk, int D, int dtype,
-                                       int* status, cudaStream_t stream) {
+                                       int max_pages, int page_size, int num_pages, const int* req_of_row,
+                                       const int* positions, float scale, int window, void* out, int rows, int Hq, int Hk,
+                                       int D, int dtype, int* status, cudaStream_t stream) {
   if (rows == 0) return 0;
   if (int e = check_heads("paged_attention", Hq, Hk, D)) return e;
   TL_REQUIRE(page_size > 0 && max_pages > 0 && window >= 0, "paged_attention: page size %d, table width %d, window %d",
@@ -244,12 +246,12 @@ extern "C" int tl_paged_attention_simt(const void* q, const void* k_cache, const
   dim3 grid(rows, ceil_div(Hq, 4));
   if (dtype == TL_FP32)
     paged_attention_simt_kernel<float><<<grid, 128, 0, stream>>>(
-        (const float*)q, (const float*)k_cache, (const float*)v_cache, block_table, max_pages, page_size, req_of_row,
-        positions, scale, window, (float*)out, Hq, Hk, D, status);
+        (const float*)q, (const float*)k_cache, (const float*)v_cache, block_table, max_pages, page_size, num_pages,
+        req_of_row, positions, scale, window, (float*)out, Hq, Hk, D, status);
   else
     paged_attention_simt_kernel<bf16><<<grid, 128, 0, stream>>>(
-        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size, req_of_row,
-        positions, scale, window, (bf16*)out, Hq, Hk, D, status);
+        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size, num_pages,
+        req_of_row, positions, scale, window, (bf16*)out, Hq, Hk, D, status);
   TL_LAUNCH_CHECK();
   return 0;
 }

@@ -43,7 +43,7 @@ template <> struct Vec<bf16> {
 template <typename T, int GM>
 __global__ void __launch_bounds__(128) attention_span_kernel(
     const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
-    const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ req_of_row,
+    const int* __restrict__ block_table, int max_pages, int page_size, int num_pages, const int* __restrict__ req_of_row,
     const int* __restrict__ positions, float scale, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
     T* __restrict__ out, int Hq, int Hk, int D, int n_spans, int* __restrict__ status) {
   constexpr int VEC = Vec<T>::N;
@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
 
   for (int i = tid; i < n_keys; i += 128) {
     const int kp = k_begin + i;
-    const int page = table[kp / page_size];
+    const int page = table_page(table, kp / page_size, max_pages, num_pages);
     if (page < 0) {
       atomicExch(status, 3);
       offs[i] = -1;
@@ -301,7 +301,7 @@ static size_t span_smem(int D) {
 
 template <typename T, int GM>
 static int launch_spans(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int max_pages,
-                        int page_size, const int* req_of_row, const int* positions, float scale, int window, void* out,
+                        int page_size, int num_pages, const int* req_of_row, const int* positions, float scale, int window, void* out,
                         float* part_o, float* part_ml, int rows, int Hq, int Hk, int D, int n_spans, int* status,
                         cudaStream_t stream) {
   static bool set = false;
@@ -313,8 +313,8 @@ static int launch_spans(const void* q, const void* k_cache, const void* v_cache,
   }
   dim3 grid(rows, Hk, n_spans);
   attention_span_kernel<T, GM><<<grid, 128, span_smem<T, GM>(D), stream>>>(
-      (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, max_pages, page_size, req_of_row, positions, scale,
-      window, part_o, part_ml, (T*)out, Hq, Hk, D, n_spans, status);
+      (const T*)q, (const T*)k_cache, (const T*)v_cache, block_table, max_pages, page_size, num_pages, req_of_row, positions,
+      scale, window, part_o, part_ml, (T*)out, Hq, Hk, D, n_spans, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (n_spans > 1) {
@@ -338,7 +338,7 @@ extern "C" long long tl_attention_scratch_floats(int rows, int Hq, int D, int n_
 }
 
 extern "C" int tl_paged_attention_split(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                        int max_pages, int page_size, const int* req_of_row, const int* positions,
+                                        int max_pages, int page_size, int num_pages, const int* req_of_row, const int* positions,
                                         float scale, int window, void* out, float* scratch, int rows, int Hq, int Hk, int D,
                                         int n_spans, int dtype, int* status, cudaStream_t stream) {
   if (rows == 0) return 0;
@@ -352,8 +352,8 @@ extern "C" int tl_paged_attention_split(const void* q, const void* k_cache, cons
   float* part_o = scratch;
   float* part_ml = scratch + (long long)rows * Hq * n_spans * D;
   const bool small = Hq / Hk <= 4;
-#define TL_SPANS(T, GM) launch_spans<T, GM>(q, k_cache, v_cache, block_table, max_pages, page_size, req_of_row, positions, \
-                                            scale, window, out, part_o, part_ml, rows, Hq, Hk, D, n_spans, status, stream)
+#define TL_SPANS(T, GM) launch_spans<T, GM>(q, k_cache, v_cache, block_table, max_pages, page_size, num_pages, req_of_row, \
+                                            positions, scale, window, out, part_o, part_ml, rows, Hq, Hk, D, n_spans, status, stream)
   if (dtype == TL_FP32) return small ? TL_SPANS(float, 4) : TL_SPANS(float, 8);
   return small ? TL_SPANS(bf16, 4) : TL_SPANS(bf16, 8);
 #undef TL_SPANS
@@ -424,6 +424,7 @@ extern "C" int tl_paged_attention_split_static(const void* q, const void* k_cach
     scratch = tl_static_scratch_address[device];
   }
   // from here on it is the ordinary entry point, which launches the two kernels and allocates nothing
-  return tl_paged_attention_split(q, k_cache, v_cache, block_table, max_pages, page_size, req_of_row, positions, scale,
+  // (the pool's size is not among this entry point's arguments: 0, only the sign of a table entry is checked)
+  return tl_paged_attention_split(q, k_cache, v_cache, block_table, max_pages, page_size, 0, req_of_row, positions, scale,
                                   window, out, scratch, rows, Hq, Hk, D, n_spans, dtype, status, stream);
 }

@@ -55,6 +55,15 @@ typedef __nv_bfloat16 bf16;
 __device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void chain_next() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Entry `index` of a request's block table, or -1 when there is none: the index lies past the table, the entry is
+// negative (a page given back or never taken) or it names no page of the pool (`num_pages`; 0: the pool's size is
+// not known and only the sign is checked). Kernels record what they skip in the status word instead of faulting.
+__device__ __forceinline__ int table_page(const int* __restrict__ table, int index, int max_pages, int num_pages) {
+  if (index < 0 || index >= max_pages) return -1;
+  const int page = table[index];
+  return (page < 0 || (num_pages > 0 && page >= num_pages)) ? -1 : page;
+}
+
 // Off unless switched on (tl_set_chained_launches): measured on a B200, decode steps replayed from CUDA graphs gained
 // nothing from chaining (3.50 ms against 3.51 ms a step at batch 8, and batch 1 lost 7 %), because a graph replay
 // already hides launch latency; the kernels' own run times are what a step consists of.

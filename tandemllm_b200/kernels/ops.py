@@ -49,14 +49,14 @@ _SIGNATURES = {
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tl_short_conv_state": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "tl_qk_prepare": [c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                      c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                       c_void_p, c_void_p],
-    "tl_kv_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+    "tl_kv_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_void_p, c_void_p],
-    "tl_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+    "tl_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "tl_attention_spans": [c_int],
-    "tl_paged_attention_split": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+    "tl_paged_attention_split": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "tl_attention_join": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "tl_router_topk": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p,
@@ -288,7 +288,8 @@ def qk_prepare(qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions, re
     max_pages = block_table.shape[1] if block_table is not None else 0
     check(core().tl_qk_prepare(ptr(qkv), qkv.stride(0), ptr(q_weight), ptr(k_weight), float(eps), ptr(inv_freq),
                                int(rotary_dim), ptr(positions), ptr(req_of_row), ptr(block_table), max_pages,
-                               int(page_size), ptr(q_out), ptr(k_cache), ptr(v_cache), ptr(k_out), ptr(v_out), rows,
+                               int(page_size), k_cache.shape[0] if k_cache is not None else 0, ptr(q_out), ptr(k_cache),
+                               ptr(v_cache), ptr(k_out), ptr(v_out), rows,
                                num_heads, num_kv_heads, head_dim, dtype_code(qkv.dtype), ptr(status), stream()),
           "qk_prepare")
 
@@ -297,8 +298,8 @@ def kv_store(k, v, positions, req_of_row, block_table, page_size, k_cache, v_cac
     _need(k, k_cache.dtype, "k"); _need(v, v_cache.dtype, "v")
     rows, Hk, D = k.shape
     check(core().tl_kv_store(ptr(k), ptr(v), ptr(positions), ptr(req_of_row), ptr(block_table), block_table.shape[1],
-                             int(page_size), ptr(k_cache), ptr(v_cache), rows, Hk, D, dtype_code(k.dtype), ptr(status),
-                             stream()), "kv_store")
+                             int(page_size), k_cache.shape[0], ptr(k_cache), ptr(v_cache), rows, Hk, D, dtype_code(k.dtype),
+                             ptr(status), stream()), "kv_store")
 
 
 def paged_attention_simt(q, k_cache, v_cache, block_table, page_size, req_of_row, positions, scale, window, out,
@@ -307,7 +308,7 @@ def paged_attention_simt(q, k_cache, v_cache, block_table, page_size, req_of_row
     rows, Hq, D = q.shape
     Hk = k_cache.shape[1]
     check(core().tl_paged_attention_simt(ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.shape[1],
-                                         int(page_size), ptr(req_of_row), ptr(positions), float(scale),
+                                         int(page_size), k_cache.shape[0], ptr(req_of_row), ptr(positions), float(scale),
                                          int(window or 0), ptr(out), rows, Hq, Hk, D, dtype_code(q.dtype), ptr(status),
                                          stream()), "paged_attention")
     return out
@@ -333,7 +334,7 @@ def paged_attention_split(q, k_cache, v_cache, block_table, page_size, req_of_ro
         raise KernelError(f"attention scratch of {scratch.numel()} floats, "
                           f"{attention_scratch_floats(rows, Hq, D, n_spans)} needed")
     check(core().tl_paged_attention_split(ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.shape[1],
-                                          int(page_size), ptr(req_of_row), ptr(positions), float(scale),
+                                          int(page_size), k_cache.shape[0], ptr(req_of_row), ptr(positions), float(scale),
                                           int(window or 0), ptr(out), ptr(scratch), rows, Hq, Hk, D, int(n_spans),
                                           dtype_code(q.dtype), ptr(status), stream()), "paged_attention_split",
           kernels=2 if n_spans > 1 else 1)

@@ -51,7 +51,7 @@ def lib():
         l.tl_tc_token_tile.argtypes = [c_int, c_int]
         l.tl_tc_token_tile.restype = c_int
         l.tl_tc_last_error.restype = ctypes.c_char_p
-        l.tl_paged_attention_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+        l.tl_paged_attention_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                              c_void_p, ctypes.c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                              c_int, c_void_p, c_void_p]
         l.tl_paged_attention_mma.restype = c_int
@@ -95,9 +95,12 @@ class TensorCore:
     def __init__(self, device, status: torch.Tensor):
         self.device, self.status = device, status
         self._workspace = None
+        self._outgrown = []
 
     def workspace(self, floats: int) -> torch.Tensor:
         if self._workspace is None or self._workspace.numel() < floats:
+            if self._workspace is not None:
+                self._outgrown.append(self._workspace)      # a captured decode graph may still write to the smaller one
             self._workspace = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=self.device)
         return self._workspace
 
@@ -253,7 +256,7 @@ class TensorCore:
         scratch = runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans)) if span_keys else None
         code = lib().tl_paged_attention_mma(
             q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
-            tiles.data_ptr(), n_tiles, min(tile_rows, step.max_rows_per_request), step.positions.data_ptr(),
+            cache.k.shape[0], tiles.data_ptr(), n_tiles, min(tile_rows, step.max_rows_per_request), step.positions.data_ptr(),
             float(scale), int(window or 0), out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, span_keys, self.status.data_ptr(), ops.stream())
         _check(code, "attention_mma")
         if span_keys:

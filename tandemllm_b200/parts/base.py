@@ -89,6 +89,9 @@ class Runtime:
         pool = self.__dict__.setdefault("_scratch", {})
         buf = pool.get((name, dtype))
         if buf is None or buf.numel() < numel:
+            if buf is not None:
+                # a captured decode graph may still write to the smaller buffer: it is kept, not freed
+                self.__dict__.setdefault("_outgrown", []).append(buf)
             buf = pool[(name, dtype)] = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
         return buf
 

@@ -70,6 +70,7 @@ class SigmoidTopKExperts(Part):
         self.n = dict(spec["names"])
         self.base = prefix + self.n["experts"]
         self._plans: dict[int, ops.MoePlan] = {}
+        self._outgrown: list[ops.MoePlan] = []
         self.stacked = False
         self.record_counts = False  # when set, `last_counts` keeps the pairs routed to each expert in the last pass
         self.last_counts = None
@@ -134,6 +135,8 @@ class SigmoidTopKExperts(Part):
         plan = self._plans.get(tile_rows)
         if plan is None or plan.max_pairs < pairs:
             cap = max(pairs, 64) if plan is None else max(pairs, 2 * plan.max_pairs)
+            if plan is not None:
+                self._outgrown.append(plan)         # a captured decode graph may still use the smaller plan's buffers
             plan = self._plans[tile_rows] = ops.MoePlan(cap, self.num_experts, tile_rows, device)
         return plan
 

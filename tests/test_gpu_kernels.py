@@ -539,6 +539,25 @@ def test_qk_prepare_norm_rotary_and_page_write(dtype, Hq, Hk, D, rot):
     # a write to a position without a page is recorded, not performed
     o.kv_store(k_out[:1], v_out[:1], i32([50]), i32([1]), table.to(DEV), page, kc2, vc2, status)
     assert int(status) == 2
+    # so are a table entry that names no page of the pool and a position past the table's width (a corrupted table
+    # or position must end as a status word, never as a wild address)
+    before = (kc2.clone(), vc2.clone())
+    wild = table.clone()
+    wild[1, positions[r] // page] = kc2.shape[0] + 1000
+    for tab, pos in ((wild, positions[r]), (table, table.shape[1] * page + 5)):
+        status.zero_()
+        o.kv_store(k_out[:1], v_out[:1], i32([pos]), i32([1]), tab.to(DEV), page, kc2, vc2, status)
+        assert int(status) == 2
+        status.zero_()
+        o.qk_prepare(qkv[:1].to(DEV), qw.to(DEV), kw.to(DEV), eps, inv_freq.to(DEV), rot, i32([pos]), i32([1]), tab.to(DEV),
+                     page, q_out[:1], kc2, vc2, None, None, Hq, Hk, D, status)
+        assert int(status) == 2
+        out1 = torch.zeros(1, Hq, D, dtype=dtype, device=DEV)
+        for kind in KERNELS:
+            status.zero_()
+            attend(o, kind, q_out[:1], kc2, vc2, tab.to(DEV), page, i32([1]), i32([pos]), 1.0, None, out1, status)
+            assert int(status) == 3, kind
+    assert torch.equal(kc2, before[0]) and torch.equal(vc2, before[1])
 
 
 def test_refused_sizes_are_clear_errors():

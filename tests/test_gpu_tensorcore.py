@@ -188,7 +188,7 @@ def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window):
     scale = 0.9 / D ** 0.5
     qd, kd, vd, td = q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV)      # kept alive until the kernel has run
     code = lib.tl_paged_attention_mma(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(),
-                                      table.shape[1], page, tiles.data_ptr(), tiles.shape[0], int(tiles[:, 2].max()),
+                                      table.shape[1], page, kd.shape[0], tiles.data_ptr(), tiles.shape[0], int(tiles[:, 2].max()),
                                       pos_dev.data_ptr(), scale,
                                       window or 0, out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, int(split),
                                       rt.status.data_ptr(), ops.stream())
