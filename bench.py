@@ -158,6 +158,54 @@ def prefill_flops(cfg, tokens: int) -> float:
     return float(per_token) * T + attention + 2.0 * H * cfg.vocab_size
 
 
+def mixed_serving(cfg, model_name: str, a) -> int:
+    """Long-context mixed serving through the scheduler: what the line says. Not the headline; no roofline."""
+    import math
+
+    import torch
+
+    from tandemllm_b200.engine import Engine, EngineArgs
+    from tandemllm_b200.sampling import SamplingParams
+    requests, longest, new_tokens, budget_tokens = 64, 32768, 64, 262144
+    engine = Engine.from_config(cfg, seed=0, args=EngineArgs(
+        dtype=a.dtype, max_len=longest + new_tokens + 16, parallel=requests, block_size=16, kv_blocks=budget_tokens // 16,
+        max_batched_tokens=2048, chunk_size=512, graph=a.graph == "on"))
+    moe = [layer.feed_forward for layer in engine.model.layers if hasattr(layer.feed_forward, "num_experts")]
+    for part in moe:
+        part.load = torch.zeros(part.num_experts, dtype=torch.int64, device=engine.device)
+    g = torch.Generator().manual_seed(5)
+    lengths = [int(math.exp(math.log(128) + float(torch.rand(1, generator=g)) * math.log(longest / 128))) for _ in range(requests)]
+    reqs = []
+    for i, n in enumerate(lengths):
+        sp = SamplingParams(temperature=0.0, max_tokens=new_tokens, ignore_eos=True) if i % 2 == 0 else \
+            SamplingParams(temperature=0.8, top_k=50, top_p=0.95, seed=100 + i, max_tokens=new_tokens, ignore_eos=True)
+        reqs.append(engine.add_request(torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(), sp))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    steps = 0
+    while engine.scheduler.has_unfinished():
+        engine.run_step()
+        steps += 1
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    st = engine.scheduler.stats
+    assert all(len(r.output) == new_tokens and min(r.output) >= 0 for r in reqs)
+    engine.cache.check()
+    load = torch.stack([part.load for part in moe]).double()               # [layers, experts] pairs routed
+    share = load / load.sum(1, keepdim=True)
+    print(json.dumps({
+        "scenario": "mixed serving", "model": model_name, "layers": cfg.num_hidden_layers, "requests": requests,
+        "prompt_tokens": sum(lengths), "longest_prompt": max(lengths), "new_tokens_each": new_tokens,
+        "cache_budget_tokens": budget_tokens, "page_tokens": 16, "portion": 512, "sampling": "greedy and temperature 0.8, alternating",
+        "seconds": round(seconds, 2), "steps": steps, "tokens_per_s": round(st.rows / seconds, 1),
+        "prompt_rows": st.prompt_rows, "decode_rows": st.decode_rows, "preemptions": st.preemptions,
+        "pages_reused": engine.cache.groups[0].pool.reused, "graph_replays": engine.step_function.graph_replays,
+        "expert_load": {"pairs_routed": int(load.sum()), "largest_share_of_a_layer": round(float(share.max()), 4),
+                        "smallest_share_of_a_layer": round(float(share.min()), 4), "even_share": round(1.0 / load.shape[1], 4)},
+        "dtype": "bf16" if a.dtype == "bfloat16" else "fp32", "data": "synthetic: random weights, uniform random token ids"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -173,6 +221,10 @@ def main() -> int:
     ap.add_argument("--graph", default="on", choices=("on", "off"))
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--only", choices=("prefill",), help="measure only this part and print it (a profiling aid)")
+    ap.add_argument("--scenario", choices=("mixed",),
+                    help="mixed: 64 requests with prompts of 128 to 32768 tokens (log-uniform) under a cache budget that makes "
+                         "them queue, portions of 512 beside decode tokens, greedy and temperature 0.8 mixed, expert load "
+                         "recorded; prints its own line (not the headline)")
     ap.add_argument("--chain", default="off", choices=("on", "off"),
                     help="programmatic dependent launch between the kernels (for comparison; ordinary launches by default)")
     ap.add_argument("--profile", action="store_true",
@@ -205,6 +257,8 @@ def main() -> int:
         raw["layer_types"] = raw["layer_types"][:a.layers]
         raw["num_hidden_layers"] = a.layers
     cfg = Lfm2MoeConfig.from_dict(raw)
+    if a.scenario == "mixed":
+        return mixed_serving(cfg, model_name, a)
     pk = peaks()
     max_batch = 64 if not a.skip_points else a.batch
     room = a.context + a.steps + a.warmup + 80

@@ -9,8 +9,9 @@ Every step:
      its pages and slot go back, it returns to the FRONT of the waiting line with everything it has
      (prompt and generated tokens) still to feed, and is recomputed when it is admitted again; the step
      function gives the same logits for recomputed text as for the original, so its output is unchanged;
-  4. waiting requests are admitted, oldest first, while a slot is free, budget is left and the pages of
-     their first portion are free; admission never preempts.
+  4. waiting requests are admitted, oldest first, while a slot is free, budget is left, the pages of their
+     first portion are free and, beside running requests, all the text they bring fits next to all the text
+     those still have to feed; admission never preempts.
 A request whose prompt plus `max_tokens` can never fit in the whole pool, or exceeds `max_model_len`, is
 refused when it is added.
 
@@ -122,6 +123,25 @@ class Scheduler:
         wants = [(r.request_id, r.num_computed + n) for r, n in chosen]
         return not self.cache.can_reserve(wants)
 
+    def _whole_text_fits(self, newcomer: Request, chosen: list[tuple[Request, int]]) -> bool:
+        """Whether the free pages cover what the running requests and `newcomer` need to feed all the text they have
+        (a group with a window never holds more than its window, a portion and a page of one request)."""
+        ps = self.cache.page_size
+        totals = {id(q): (q, len(q.prompt) + len(q.output)) for q in self.running}
+        totals[id(newcomer)] = (newcomer, len(newcomer.prompt) + len(newcomer.output))
+        for g in self.cache.groups:
+            need = 0
+            for q, total in totals.values():
+                table = g.tables.get(q.request_id, [])
+                more = -(-total // ps) - len(table)
+                if g.need.window is not None:
+                    span = -(-(g.need.window + self.chunk_size + ps) // ps)
+                    more = min(more, span - sum(1 for p in table if p >= 0))
+                need += max(0, more)
+            if need > g.pool.free:
+                return False
+        return True
+
     def _preempt(self, victim: Request) -> None:
         self.cache.free(victim.request_id)
         self.running.remove(victim)
@@ -158,6 +178,11 @@ class Scheduler:
         while not short and self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
             r = self.waiting[0]
             n = min(r.pending, self.chunk_size, budget)
+            # Beside running requests a newcomer is let in only if all the text it has to feed fits next to all the
+            # text they still have to feed: letting it in on the strength of its first portion alone would have them
+            # fight for pages and recompute each other's prompts over and over.
+            if self.running and not self._whole_text_fits(r, chosen):
+                break
             self.cache.admit(r.request_id)
             if self._pages_short(chosen + [(r, n)]):
                 self.cache.free(r.request_id)

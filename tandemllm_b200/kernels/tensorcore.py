@@ -195,6 +195,8 @@ class TensorCore:
                                         ops.stream()), "gather_rows")
         if part.record_counts:
             part.last_counts = plan.counts.clone()
+        if part.load is not None:
+            part.load.add_(plan.counts)
         act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
         w_gate_up = part.w_gate_up.view(E * I2, H)
         if fetch:

@@ -74,6 +74,8 @@ class SigmoidTopKExperts(Part):
         self.stacked = False
         self.record_counts = False  # when set, `last_counts` keeps the pairs routed to each expert in the last pass
         self.last_counts = None
+        self.load = None            # when set to an integer tensor [experts] on the device: the pairs routed to each
+                                    # expert are added to it in every pass (set it before decode graphs are captured)
 
     def _stacked(self, present) -> bool:
         return present is not None and (self.base + ".gate_up_proj") in present
@@ -154,6 +156,8 @@ class SigmoidTopKExperts(Part):
         plan = self.plan_for(R * self.top_k, x.device).build(ids)
         if self.record_counts:
             self.last_counts = plan.counts.clone()
+        if self.load is not None:
+            self.load.add_(plan.counts)
         act = torch.empty(R * self.top_k, self.inter, dtype=x.dtype, device=x.device)
         ops.gemm_simt_grouped(x, plan.sorted_pairs, self.top_k, self.w_gate_up, act, plan, swiglu=True)
         y = torch.empty(R * self.top_k, H, dtype=torch.float32, device=x.device)

@@ -270,6 +270,26 @@ def test_out_of_pages_preempts_the_newest_and_recomputes_the_same_text():
     assert len(starts) > 3
 
 
+def test_a_newcomer_waits_until_its_whole_text_fits_beside_the_running():
+    """12 pages; two prompts of 150 tokens (10 pages each), portions of 16. Let in on the strength of its first portion,
+    the second would fight the first for pages and both would be recomputed again and again; instead it waits until
+    the first is done: no preemption, and every prompt token is fed once."""
+    sched, fake = make(pages=12, reqs=4, budget=32, chunk=16, max_len=400)
+    a, b, c = req("a", 150, max_tokens=4), req("b", 150, max_tokens=4), req("c", 20, max_tokens=4)
+    for r in (a, b, c):
+        sched.add(r)
+    drive(sched, fake)
+    assert sched.stats.preemptions == 0 and sched.stats.prompt_rows == 150 + 150 + 20
+    first_b = next(i for i, batch in enumerate(fake.batches) if any(rid == "b" for rid, *_ in batch))
+    last_a = max(i for i, batch in enumerate(fake.batches) if any(rid == "a" for rid, *_ in batch))
+    assert first_b > last_a, "b (10 pages) cannot sit beside a (10 pages) in 12"
+    # c's two pages do fit beside b's ten: it is let in while b still feeds its prompt
+    first_c = next(i for i, batch in enumerate(fake.batches) if any(rid == "c" for rid, *_ in batch))
+    last_b = max(i for i, batch in enumerate(fake.batches) if any(rid == "b" for rid, *_ in batch))
+    assert first_c < last_b
+    assert all(len(r.output) == 4 for r in (a, b, c))
+
+
 def test_random_load_finishes_everything_with_few_pages():
     rng = random.Random(1)
     sched, fake = make(pages=10, reqs=4, budget=24, chunk=7, max_len=120)
