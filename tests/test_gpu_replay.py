@@ -222,6 +222,35 @@ def test_a_captured_graph_survives_the_growth_of_kept_buffers(case):
         assert torch.equal(a[key], b[key]), key
 
 
+def test_contexts_longer_than_a_span_of_keys(case):
+    """700 tokens: portions whose keys lie in several spans (the CUDA-core kernels cut keys into spans of 256, the
+    tensor-core kernel splits contexts above 512 over its grid), then 60 tokens decoded one by one across span and
+    page edges, eagerly and from graphs."""
+    rid = "long"
+    if rid not in case.ref:
+        toks = T.long_tokens(case.name, 700, seed=77)
+        margins = []
+        case.requests[rid] = toks
+        case.ref[rid] = P.forward(case.cfg, case.W, toks, margins=margins)
+        case.margin[rid] = torch.stack(margins).min(0).values
+    toks = case.requests[rid]
+    trace, at = [], 0
+    for n in (300, 250, 90):
+        trace.append({"step": len(trace), "entries": [{"id": rid, "tokens": toks[at:at + n], "want": list(range(n))}], "end": []})
+        at += n
+    while at < len(toks):
+        trace.append({"step": len(trace), "entries": [{"id": rid, "tokens": [toks[at]], "want": [0]}], "end": []})
+        at += 1
+    try:
+        for graph in (False, True):
+            got = case.replay(case.engine(max_tokens=768, graph=graph), trace)
+            assert len(got) == len(toks)
+            case.compare(got, f"a context of 700 tokens (graphs {graph})")
+    finally:
+        for d in (case.requests, case.ref, case.margin):
+            d.pop(rid, None)
+
+
 def test_first_tokens_of_a_sequence(case):
     """A sequence shorter than the conv taps and than a page; and a first portion of one token."""
     eng = case.engine(max_tokens=128)
