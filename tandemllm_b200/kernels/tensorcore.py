@@ -145,6 +145,15 @@ class TensorCore:
             return None
         return ops.PartialSums(partial, splits, M, N, None if out.dtype == torch.float32 else out.dtype)
 
+    def gated(self, x, w_gate_up, out) -> bool:
+        """out = silu(x gate^T) * (x up^T) for w_gate_up = [gate rows; up rows], in the persistent kernel with the SwiGLU
+        epilogue; False (nothing done) for a decode step's few rows or operands the kernels do not take."""
+        inter = w_gate_up.shape[0] // 2
+        if x.shape[0] <= 128 or not usable(x, w_gate_up) or inter % 8 or out.stride(-1) != 1 or out.dtype != torch.bfloat16:
+            return False
+        self.gemm(x, w_gate_up, None, out, swiglu=True, swap=False, n_out=inter)
+        return True
+
     def linear(self, x, w, bias, out, defer: bool = False):
         """False when the kernels do not take these operands; else True, or the deferred partial sums."""
         if not usable(x, w) or out.stride(-1) != 1:

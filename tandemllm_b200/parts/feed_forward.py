@@ -44,9 +44,11 @@ class SwiGLU(Part):
         self.w_down = runtime.matrix(read(self.n["down"] + ".weight"))
 
     def forward(self, x, step, x32=None, routing=None):
-        gu = linear(self.runtime, x, self.w_gate_up)
         act = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
-        ops.silu_mul(gu, act)
+        tc = self.runtime.tensorcore
+        if tc is None or not tc.gated(x, self.w_gate_up, act):      # prompts: gate, up and silu(gate) * up in one kernel
+            gu = linear(self.runtime, x, self.w_gate_up)
+            ops.silu_mul(gu, act)
         return linear(self.runtime, act, self.w_down, out_dtype=torch.float32, defer=True)
 
 

@@ -83,6 +83,21 @@ def test_every_tile_shape_in_both_orientations(swap, bn):
     assert rel(out, x.float() @ w.float().T) < 1e-3
 
 
+@pytest.mark.parametrize("M,H,I", [(300, 136, 200), (129, 64, 72), (2048, 256, 640)])
+def test_dense_gate_up_with_the_swiglu_epilogue(M, H, I):
+    """A prompt's dense feed-forward: gate, up and silu(gate) * up in the persistent kernel (gate and up rows of the
+    same outputs stacked into one operand), tails in every dimension; a decode step's few rows are left to the caller."""
+    impl, rt = tc()
+    x, w = rnd(M, H, seed=30), rnd(2 * I, H, seed=31, scale=0.2)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert impl.gated(x.to(DEV), w.to(DEV), out)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    g, u = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
+    assert rel(out, torch.nn.functional.silu(g) * u) < 1e-2
+    assert not impl.gated(x[:8].to(DEV), w.to(DEV), out[:8])
+
+
 def test_split_k_is_used_and_repeatable():
     impl, rt = tc()
     M, N, K = 8, 256, 4096                      # 2 CTAs without a split: the k range is cut
