@@ -145,6 +145,11 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
   const float scale2 = scale * 1.4426950408889634f;   // scores are kept in units of log 2: exponentials are exp2
 
   const bool active = wrow < nq * G;
+  // the warp's 16 M rows: whether all of them are query rows, the earliest position among them and the latest start
+  // of a window (what decides, for the whole warp, whether a key tile needs masking)
+  const bool rows_all_valid = (wrow + 15) / G < nq;
+  const int first_pos = pos0 + wrow / G;
+  const int last_w_lo = window > 0 ? max(0, pos0 + (wrow + 15) / G - window + 1) : 0;
   float o[D / 8][4];
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -186,16 +191,28 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
     // ---- mask, running maximum ----
     const int key0 = kt * KT + n_base * 8 + (lane & 3) * 2;
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
+    // Most key tiles of a prompt lie wholly before every row of the warp and inside every row's window: nothing to mask.
+    const bool open = !KEYSPLIT && rows_all_valid && kt * KT >= k_lo && kt * KT + KT - 1 <= min(k_hi, first_pos) && kt * KT >= last_w_lo;
+    if (open) {
 #pragma unroll
-    for (int n = 0; n < NS; ++n) {
+      for (int n = 0; n < NS; ++n) {
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int kp = key0 + n * 8 + e;
-        const bool in = kp >= k_lo && kp <= k_hi;
-        s[n][e] = (in && v_lo && kp <= p_lo && kp >= w_lo) ? s[n][e] * scale2 : -INFINITY;
-        s[n][2 + e] = (in && v_hi && kp <= p_hi && kp >= w_hi) ? s[n][2 + e] * scale2 : -INFINITY;
-        mx_lo = fmaxf(mx_lo, s[n][e]);
-        mx_hi = fmaxf(mx_hi, s[n][2 + e]);
+        for (int e = 0; e < 4; ++e) s[n][e] *= scale2;
+        mx_lo = fmaxf(mx_lo, fmaxf(s[n][0], s[n][1]));
+        mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NS; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kp = key0 + n * 8 + e;
+          const bool in = kp >= k_lo && kp <= k_hi;
+          s[n][e] = (in && v_lo && kp <= p_lo && kp >= w_lo) ? s[n][e] * scale2 : -INFINITY;
+          s[n][2 + e] = (in && v_hi && kp <= p_hi && kp >= w_hi) ? s[n][2 + e] * scale2 : -INFINITY;
+          mx_lo = fmaxf(mx_lo, s[n][e]);
+          mx_hi = fmaxf(mx_hi, s[n][2 + e]);
+        }
       }
     }
     mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
