@@ -257,9 +257,13 @@ class TensorCore:
         # Few tiles and long contexts (decoding): split the keys over CTAs as well, in spans long enough that a CTA's
         # start-up is a small part of its work and short enough that the grid still has a few CTAs per SM.
         span_keys = 0
-        if step.max_context > 512 and n_tiles * Hk < 8 * SM_COUNT:
+        ctas, slots = n_tiles * Hk, 3 * SM_COUNT         # about three CTAs of the decode form run on an SM at once
+        if step.max_context > 512 and 2 * ctas <= slots:
+            # a handful of requests: as many spans as fill the GPU once, so that nobody runs in a second, thin wave
+            span_keys = max(256, -(-(-(-step.max_context // (slots // ctas))) // 64) * 64)
+        elif step.max_context > 512 and ctas < 8 * SM_COUNT:
             span_keys = 256
-            while span_keys < 2048 and n_tiles * Hk * -(-step.max_context // (2 * span_keys)) >= 4 * SM_COUNT:
+            while span_keys < 2048 and ctas * -(-step.max_context // (2 * span_keys)) >= 4 * SM_COUNT:
                 span_keys *= 2
         spans = -(-step.max_context // span_keys) if span_keys else 1
         if spans <= 1:
