@@ -25,8 +25,18 @@ __device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, ui
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// 16 bytes through the read-only path, zeros when not valid. Volatile, so that the compiler keeps a round's loads in
+// front of its MMAs, all in flight together, instead of moving each load next to its use to save registers.
 __device__ __forceinline__ uint4 load16(const bf16* p, bool valid) {
-  return valid ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0u, 0u, 0u, 0u);
+  uint4 v;
+  asm volatile(
+      "{\n\t.reg .pred ok;\n\t"
+      "setp.ne.b32 ok, %5, 0;\n\t"
+      "mov.b32 %0, 0;\n\tmov.b32 %1, 0;\n\tmov.b32 %2, 0;\n\tmov.b32 %3, 0;\n\t"
+      "@ok ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(p), "r"((int)valid));
+  return v;
 }
 
 // NT: token tiles of 8 (M <= 8 NT). UNROLL chunks of 32 k-elements are in flight a warp: with eight, a k of 2048
@@ -34,7 +44,7 @@ __device__ __forceinline__ uint4 load16(const bf16* p, bool valid) {
 template <int NT, typename TOut>
 __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_mma_kernel(
     const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ w, long long ldw, const float* __restrict__ bias,
-    TOut* __restrict__ out, long long ldc, int M, int N, int K) {
+    TOut* __restrict__ out, long long ldc, int M, int N, int K, uint32_t zero) {
   constexpr int UNROLL = NT == 1 ? 8 : (NT == 2 ? 4 : 2);
   __shared__ float part[SKINNY_WARPS][NT][16][8 + 1];
   chain_next();
@@ -72,6 +82,10 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_mma_kernel(
 #pragma unroll
       for (int j = 0; j < NT; ++j) b[u][j] = load16(x_row[j] + c * 32, in && x_ok[j]);
     }
+    // The round's first MMA is made to wait for the round's last loads: otherwise the compiler moves every MMA up
+    // to just behind its own loads, and the warp, which issues in order, stalls there with most loads not yet sent.
+    // (`zero` is 0, which only the host knows: the compiler can neither drop the term nor the dependence it carries)
+    a_lo[0].x ^= (a_lo[UNROLL - 1].w ^ a_hi[UNROLL - 1].w ^ b[UNROLL - 1][NT - 1].w) & zero;
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
@@ -125,9 +139,9 @@ extern "C" int tl_gemm_skinny_mma(const void* x, long long ldx, const void* w, l
   do {                                                                                                                  \
     if (out_dtype == TL_FP32)                                                                                           \
       return (int)launch_chained(gemm_skinny_mma_kernel<NT_, float>, grid, block, 0, stream, (const bf16*)x, ldx,       \
-                                 (const bf16*)w, ldw, bias, (float*)out, ldc, M, N, K);                                 \
+                                 (const bf16*)w, ldw, bias, (float*)out, ldc, M, N, K, 0u);                                 \
     return (int)launch_chained(gemm_skinny_mma_kernel<NT_, bf16>, grid, block, 0, stream, (const bf16*)x, ldx,          \
-                               (const bf16*)w, ldw, bias, (bf16*)out, ldc, M, N, K);                                    \
+                               (const bf16*)w, ldw, bias, (bf16*)out, ldc, M, N, K, 0u);                                    \
   } while (0)
   if (nt == 1) TL_SKINNY(1);
   if (nt == 2) TL_SKINNY(2);
