@@ -63,6 +63,7 @@ struct NormParams {
   int* route_ids;            // [rows, route_k]
   float* route_wts;
   int rows_per_block, out_rows;
+  unsigned zero;             // 0 (see router_logits_one_row)
 };
 
 // With a router and many rows, a block norms this many rows before it multiplies them by the router's weights,
@@ -113,6 +114,43 @@ __device__ __forceinline__ void router_logits(const NormParams& p, const float* 
   }
 }
 
+// The same for a block's single row (a decode step), written so that a lane's sixteen 16-byte loads of an expert's
+// weights are all on their way before the first product needs one: the first product is made to depend on every
+// load (`zero` is 0, which only the host knows), or the compiler would set each product right behind its own load and
+// the warp, which issues in order, would wait there with the other loads unsent. The sum is built in the same order
+// as above.
+__device__ __forceinline__ void router_logits_one_row(const NormParams& p, const float* row, float* logits, int lane,
+                                                      int warp, int nwarps) {
+  constexpr int CH = 16;
+  const int hidden = p.hidden, h4 = hidden >> 2;
+  const float4* row4 = reinterpret_cast<const float4*>(row);
+  for (int e = warp; e < p.E; e += nwarps) {
+    const float4* w4 = reinterpret_cast<const float4*>(p.router_w + (size_t)e * hidden);
+    float acc = 0.f;
+    for (int c0 = lane; c0 < h4; c0 += 32 * CH) {
+      float4 wv[CH];
+      unsigned all = 0u;
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int c = c0 + 32 * i;
+        wv[i] = c < h4 ? __ldg(w4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        all ^= __float_as_uint(wv[i].w);
+      }
+      wv[0].x = __uint_as_float(__float_as_uint(wv[0].x) ^ (all & p.zero));
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int c = c0 + 32 * i;
+        if (c < h4) {
+          const float4 x = row4[c];
+          acc = fmaf(x.w, wv[i].w, fmaf(x.z, wv[i].z, fmaf(x.y, wv[i].y, fmaf(x.x, wv[i].x, acc))));
+        }
+      }
+    }
+    const float v = warp_sum(acc);
+    if (lane == 0) logits[e] = v;
+  }
+}
+
 // A block takes rows_per_block consecutive output rows at once, blockDim / rows_per_block threads (whole warps) a row:
 // one row for a decode step, several for a prompt, so that every thread has a few 16-byte loads of each input in
 // flight and the router's weights are read once a block.
@@ -122,8 +160,9 @@ __device__ __forceinline__ void router_logits(const NormParams& p, const float* 
 // normed32 (optional) receives the normalised row unrounded. With a router, the row's logits are computed from
 // the unrounded row in 32-bit, and the choice and weights are written as well.
 // ROUTE_PER: 0 without a router (a small kernel, three blocks an SM), else the experts a lane of the choosing warp holds.
-template <typename T, int ROUTE_PER>
-__global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 : 1)) add_rmsnorm_kernel(NormParams p) {
+// ONE_ROW: the launch gives every block one row (a decode step: few blocks, which may take all the registers they like).
+template <typename T, int ROUTE_PER, bool ONE_ROW>
+__global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) add_rmsnorm_kernel(NormParams p) {
   // rows_per_block rows of `hidden` floats, 33 for the reduction, then rows_per_block x E logits
   extern __shared__ __align__(16) float rows_buf[];
   float* scratch = rows_buf + (size_t)p.rows_per_block * p.hidden;
@@ -180,16 +219,35 @@ __global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 
           x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
         }
         if (p.expert_rows) {
+          // four expert rows at a time, all loaded (with the further parts of a split down product) before the first
+          // is used; added in ascending expert id as ever
           float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int j = 0; j < p.top_k; ++j) {
-            float4 v = reinterpret_cast<const float4*>(p.expert_rows + (long long)s_src[rr][j] * hidden)[c];
+          constexpr int STEP = ONE_ROW ? 4 : 1;        // (a prompt's blocks keep to few registers and to one row at a time)
+          for (int j0 = 0; j0 < p.top_k; j0 += STEP) {
+            float4 v[STEP];
+#pragma unroll
+            for (int i = 0; i < STEP; ++i)
+              v[i] = j0 + i < p.top_k ? reinterpret_cast<const float4*>(p.expert_rows + (long long)s_src[rr][j0 + i] * hidden)[c]
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
             for (int s = 1; s < p.expert_parts; ++s) {       // a down projection split along k: its partial sums, in order
-              const float4 more = reinterpret_cast<const float4*>(p.expert_rows + (long long)s * p.expert_part_stride +
-                                                                  (long long)s_src[rr][j] * hidden)[c];
-              v.x += more.x; v.y += more.y; v.z += more.z; v.w += more.w;
+              float4 more[STEP];
+#pragma unroll
+              for (int i = 0; i < STEP; ++i)
+                more[i] = j0 + i < p.top_k
+                              ? reinterpret_cast<const float4*>(p.expert_rows + (long long)s * p.expert_part_stride +
+                                                                (long long)s_src[rr][j0 + i] * hidden)[c]
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+              for (int i = 0; i < STEP; ++i) {
+                v[i].x += more[i].x; v[i].y += more[i].y; v[i].z += more[i].z; v[i].w += more[i].w;
+              }
             }
-            const float w = s_w[rr][j];
-            d.x = fmaf(w, v.x, d.x); d.y = fmaf(w, v.y, d.y); d.z = fmaf(w, v.z, d.z); d.w = fmaf(w, v.w, d.w);
+#pragma unroll
+            for (int i = 0; i < STEP; ++i)
+              if (j0 + i < p.top_k) {
+                const float w = s_w[rr][j0 + i];
+                d.x = fmaf(w, v[i].x, d.x); d.y = fmaf(w, v[i].y, d.y); d.z = fmaf(w, v[i].z, d.z); d.w = fmaf(w, v[i].w, d.w);
+              }
           }
           x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
         }
@@ -265,7 +323,8 @@ __global__ void __launch_bounds__(512, ROUTE_PER == 0 ? 3 : (ROUTE_PER <= 4 ? 2 
     // columns; an expert's weights are read once for all rows of the block. A row's sum is built in the same order
     // whether the block holds one row or several.
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    if (n_rows == 1) router_logits<1>(p, rows_buf, logits, 1, lane, warp, nwarps);
+    if (ONE_ROW && (p.hidden & 3) == 0) router_logits_one_row(p, rows_buf, logits, lane, warp, nwarps);
+    else if (n_rows == 1) router_logits<1>(p, rows_buf, logits, 1, lane, warp, nwarps);
     else router_logits<MAX_ROWS_PER_BLOCK>(p, rows_buf, logits, n_rows, lane, warp, nwarps);
     __syncthreads();
     for (int rr = warp; rr < n_rows; rr += nwarps)
@@ -342,16 +401,21 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
   p.normed = normed; p.normed32 = normed32; p.gather = gather; p.hidden = hidden; p.router_w = router_w;
   p.router_bias = router_bias; p.E = E; p.route_k = route_k; p.normalize = normalize; p.floor_ = floor_; p.scale = scale;
   p.route_ids = route_ids; p.route_wts = route_wts;
-  p.rows_per_block = rows_per_block; p.out_rows = out_rows;
+  p.rows_per_block = rows_per_block; p.out_rows = out_rows; p.zero = 0u;
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (threads < 32 * rows_per_block) threads = 32 * rows_per_block;       // whole warps a row
   const dim3 grid(ceil_div(out_rows, rows_per_block));
   const int per = !router_w ? 0 : (E <= 32 ? 1 : (E <= 128 ? 4 : MAX_EXPERTS / 32));
-#define TL_NORM(T_, PER_)                                                                                         \
-  do {                                                                                                            \
-    if (smem > 48 * 1024)                                                                                         \
-      cudaFuncSetAttribute(add_rmsnorm_kernel<T_, PER_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    return (int)launch_chained(add_rmsnorm_kernel<T_, PER_>, grid, dim3(threads), smem, stream, p);               \
+#define TL_NORM1(T_, PER_, ONE_)                                                                                          \
+  do {                                                                                                                    \
+    if (smem > 48 * 1024)                                                                                                 \
+      cudaFuncSetAttribute(add_rmsnorm_kernel<T_, PER_, ONE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+    return (int)launch_chained(add_rmsnorm_kernel<T_, PER_, ONE_>, grid, dim3(threads), smem, stream, p);                 \
+  } while (0)
+#define TL_NORM(T_, PER_)                          \
+  do {                                             \
+    if (rows_per_block == 1) TL_NORM1(T_, PER_, true); \
+    TL_NORM1(T_, PER_, false);                     \
   } while (0)
   if (dtype == TL_FP32) {
     if (per == 0) TL_NORM(float, 0);
@@ -364,6 +428,7 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
   if (per == 4) TL_NORM(bf16, 4);
   TL_NORM(bf16, MAX_EXPERTS / 32);
 #undef TL_NORM
+#undef TL_NORM1
 }
 
 extern "C" int tl_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
