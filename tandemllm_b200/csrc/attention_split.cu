@@ -281,15 +281,39 @@ __global__ void attention_join_kernel(const float* __restrict__ part_o, const fl
   const int s0 = lo / span_keys, s1 = pos / span_keys;
   if (s0 == s1) return;                                 // written directly by the span kernel
   const long long base = ((long long)r * Hq + h) * n_spans;
+  // Spans are taken eight at a time, with all of a group's loads issued before the first is used: taken one by one,
+  // every span would cost a trip to memory of its own.
+  constexpr int GROUP = 8;
+  const float2* ml2 = reinterpret_cast<const float2*>(part_ml);      // (max, sum) pairs
   float m = -INFINITY;
-  for (int s = s0; s <= s1; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+  for (int g0 = s0; g0 <= s1; g0 += GROUP) {
+    float v[GROUP];
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) v[i] = g0 + i <= s1 ? ml2[base + g0 + i].x : -INFINITY;
+#pragma unroll
+    for (int i = 0; i < GROUP; ++i) m = fmaxf(m, v[i]);
+  }
   float denom = 0.f;
-  for (int s = s0; s <= s1; ++s) denom += expf(part_ml[(base + s) * 2] - m) * part_ml[(base + s) * 2 + 1];
-  const float inv = denom > 0.f ? 1.f / denom : 0.f;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float o = 0.f;
-    for (int s = s0; s <= s1; ++s) o += expf(part_ml[(base + s) * 2] - m) * part_o[(base + s) * D + d];
-    out[((long long)r * Hq + h) * D + d] = from_f32<T>(o * inv);
+    float o = 0.f, sum = 0.f;
+    for (int g0 = s0; g0 <= s1; g0 += GROUP) {
+      float2 w[GROUP];
+      float x[GROUP];
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) {
+        const bool in = g0 + i <= s1;
+        w[i] = in ? ml2[base + g0 + i] : make_float2(-INFINITY, 0.f);
+        x[i] = in ? part_o[(base + g0 + i) * D + d] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < GROUP; ++i) {
+        const float f = w[i].x == -INFINITY ? 0.f : expf(w[i].x - m);       // spans in ascending order
+        sum += f * w[i].y;
+        o += f * x[i];
+      }
+    }
+    denom = sum;
+    out[((long long)r * Hq + h) * D + d] = from_f32<T>(denom > 0.f ? o / denom : 0.f);
   }
 }
 

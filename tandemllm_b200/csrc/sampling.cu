@@ -79,16 +79,26 @@ __device__ __forceinline__ Best row_best(const float* __restrict__ row, int V) {
   b.i = 0x7fffffff;
   if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
     const float4* row4 = reinterpret_cast<const float4*>(row);
-#pragma unroll 8
-    for (int i = threadIdx.x; i < (V >> 2); i += blockDim.x) {
-      const float4 x = row4[i];
-      const float v[4] = {x.x, x.y, x.z, x.w};
+    const int n4 = V >> 2, stride = blockDim.x;
+    constexpr int GROUP = 8;                     // loads issued together, then compared in index order
+    for (int i0 = threadIdx.x; i0 < n4; i0 += GROUP * stride) {
+      float4 x[GROUP];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        Best c;
-        c.v = v[j];
-        c.i = 4 * i + j;
-        if (c.v == c.v) b = better(b, c);
+      for (int g = 0; g < GROUP; ++g) {
+        const int i = i0 + g * stride;
+        x[g] = i < n4 ? row4[i] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int g = 0; g < GROUP; ++g) {
+        const int i = i0 + g * stride;
+        const float v[4] = {x[g].x, x[g].y, x[g].z, x[g].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          Best c;
+          c.v = v[j];
+          c.i = 4 * i + j;
+          if (i < n4 && c.v == c.v) b = better(b, c);
+        }
       }
     }
   } else {
