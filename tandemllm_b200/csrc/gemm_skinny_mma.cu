@@ -117,6 +117,102 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_mma_kernel(
   }
 }
 
+
+// The same for the routed experts of a very small step (up to eight rows): grid (ceil(N / 16), plan tiles), a CTA takes
+// 16 outputs of one tile's expert for the tile's token rows (at most 8: the plan is built with tiles of 8). With SWIGLU
+// it multiplies by the expert's gate rows and up rows of those outputs and stores silu(gate) * up. Token rows are
+// fetched through `row_index` (position i of the plan stands for row row_index[i] / row_div of x) or, without it, lie
+// in the plan's order. Tiles past *n_tiles exit at once. A few experts' weights are all such a step reads: many small
+// CTAs that start at once stream them faster than the few 128-row CTAs of the tcgen05 product.
+template <bool SWIGLU, typename TOut>
+__global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
+    const bf16* __restrict__ x, long long ldx, const int* __restrict__ row_index, int row_div, const bf16* __restrict__ w,
+    long long ldw, long long rows_per_group, TOut* __restrict__ out, long long ldc, int N, int K,
+    const int* __restrict__ tile_group, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
+    const int* __restrict__ n_tiles, int* __restrict__ status, uint32_t zero) {
+  constexpr int W_TILES = SWIGLU ? 2 : 1;
+  constexpr int UNROLL = SWIGLU ? 4 : 8;
+  __shared__ float part[SKINNY_WARPS][W_TILES][16][8 + 1];
+  chain_next();
+  chain_wait();
+  const int tile = blockIdx.y;
+  if (tile >= *n_tiles) return;
+  const int tok0 = tile_row0[tile];
+  int rows = tile_rows[tile];
+  if (rows > 8) {                                      // the plan was built with taller tiles than this kernel takes
+    if (threadIdx.x == 0) atomicExch(status, 5);
+    rows = 8;
+  }
+  const long long w_base = (long long)tile_group[tile] * rows_per_group;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const bool v_lo = n0 + g < N, v_hi = n0 + g + 8 < N;
+  const bf16* w_lo[W_TILES];
+  const bf16* w_hi[W_TILES];
+#pragma unroll
+  for (int j = 0; j < W_TILES; ++j) {
+    const long long first = w_base + (long long)j * N + n0;               // gate rows, then (SWIGLU) the up rows
+    w_lo[j] = w + (first + (v_lo ? g : 0)) * ldw + t * 8;
+    w_hi[j] = w + (first + (v_hi ? g + 8 : 0)) * ldw + t * 8;
+  }
+  const bool x_ok = g < rows;
+  const int pos = tok0 + (x_ok ? g : 0);
+  const bf16* x_row = x + (long long)(row_index ? row_index[pos] / row_div : pos) * ldx + t * 8;
+  float acc[W_TILES][4];
+#pragma unroll
+  for (int j = 0; j < W_TILES; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+  const int chunks = (K + 31) / 32;
+  for (int c0 = warp; c0 < chunks; c0 += SKINNY_WARPS * UNROLL) {
+    uint4 a_lo[UNROLL][W_TILES], a_hi[UNROLL][W_TILES], b[UNROLL];
+    uint32_t all = 0u;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = c0 + u * SKINNY_WARPS;
+      const bool in = c < chunks && c * 32 + t * 8 < K;
+#pragma unroll
+      for (int j = 0; j < W_TILES; ++j) {
+        a_lo[u][j] = load16(w_lo[j] + c * 32, in && v_lo);
+        a_hi[u][j] = load16(w_hi[j] + c * 32, in && v_hi);
+        all ^= a_lo[u][j].w ^ a_hi[u][j].w;
+      }
+      b[u] = load16(x_row + c * 32, in && x_ok);
+      all ^= b[u].w;
+    }
+    a_lo[0][0].x ^= all & zero;                 // the round's first MMA waits for all of the round's loads (zero is 0)
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+      for (int j = 0; j < W_TILES; ++j) {
+        mma_16816(acc[j], a_lo[u][j].x, a_hi[u][j].x, a_lo[u][j].y, a_hi[u][j].y, b[u].x, b[u].y);
+        mma_16816(acc[j], a_lo[u][j].z, a_hi[u][j].z, a_lo[u][j].w, a_hi[u][j].w, b[u].z, b[u].w);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < W_TILES; ++j) {
+    part[warp][j][g][2 * t] = acc[j][0];
+    part[warp][j][g][2 * t + 1] = acc[j][1];
+    part[warp][j][g + 8][2 * t] = acc[j][2];
+    part[warp][j][g + 8][2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 16 * 8; i += SKINNY_WARPS * 32) {
+    const int row = i & 15, m = i >> 4;
+    if (m >= rows || n0 + row >= N) continue;
+    float v[W_TILES];
+#pragma unroll
+    for (int j = 0; j < W_TILES; ++j) {
+      v[j] = 0.f;
+#pragma unroll
+      for (int s = 0; s < SKINNY_WARPS; ++s) v[j] += part[s][j][row][m];
+    }
+    const float r = SWIGLU ? v[0] / (1.f + expf(-v[0])) * v[W_TILES - 1] : v[0];
+    out[(long long)(tok0 + m) * ldc + n0 + row] = from_f32<TOut>(r);
+  }
+}
+
 }  // namespace tl
 
 using namespace tl;
@@ -148,4 +244,31 @@ extern "C" int tl_gemm_skinny_mma(const void* x, long long ldx, const void* w, l
   if (nt == 3) TL_SKINNY(3);
   TL_SKINNY(4);
 #undef TL_SKINNY
+}
+
+// The routed experts of a very small step. x [*, K] bfloat16; w [groups * rows_per_group, K] bfloat16 with, per group, N
+// rows (or, with swiglu, N gate rows then N up rows); the plan's tiles hold at most 8 rows; out [pairs, N] in the plan's
+// order, bfloat16 or 32-bit. row_index (or null) and row_div as in the kernel's comment.
+extern "C" int tl_gemm_skinny_grouped(const void* x, long long ldx, const int* row_index, int row_div, const void* w,
+                                      long long ldw, long long rows_per_group, void* out, long long ldc, int N, int K,
+                                      int swiglu, int out_dtype, const int* tile_group, const int* tile_row0,
+                                      const int* tile_rows, const int* n_tiles, int max_tiles, int* status,
+                                      cudaStream_t stream) {
+  if (max_tiles == 0 || N == 0) return 0;
+  TL_REQUIRE(N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && row_div >= 1 && max_tiles <= 65535,
+             "skinny grouped product: %d outputs, k %d, strides %lld and %lld", N, K, ldx, ldw);
+  TL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && tile_group && tile_row0 && tile_rows && n_tiles,
+             "skinny grouped product: operands must be 16-byte aligned and the plan complete (%d)", 0);
+  const dim3 grid(ceil_div(N, 16), max_tiles), block(SKINNY_WARPS * 32);
+#define TL_GROUPED(SW_, T_)                                                                                              \
+  return (int)launch_chained(gemm_skinny_grouped_kernel<SW_, T_>, grid, block, 0, stream, (const bf16*)x, ldx, row_index,  \
+                             row_div, (const bf16*)w, ldw, rows_per_group, (T_*)out, ldc, N, K, tile_group, tile_row0,    \
+                             tile_rows, n_tiles, status, 0u)
+  if (swiglu) {
+    if (out_dtype == TL_FP32) TL_GROUPED(true, float);
+    TL_GROUPED(true, bf16);
+  }
+  if (out_dtype == TL_FP32) TL_GROUPED(false, float);
+  TL_GROUPED(false, bf16);
+#undef TL_GROUPED
 }

@@ -42,7 +42,8 @@ class KernelFault(RuntimeError):
 
 
 _STATUS = {1: "a token id outside the vocabulary", 2: "a key/value write to a position without a page",
-           3: "a visible key without a page", 4: "an attention tile with more rows than its kernel takes", 11: "a pipeline wait that ran out in a tensor-core kernel"}
+           3: "a visible key without a page", 4: "an attention tile with more rows than its kernel takes",
+           5: "a plan tile with more rows than its kernel takes", 11: "a pipeline wait that ran out in a tensor-core kernel"}
 
 CONTEXT_BUCKET = 1024       # a decode graph serves contexts up to the next multiple of this
 

@@ -35,6 +35,8 @@ SM_COUNT = 148
 SKINNY_TOKENS = 32              # up to this many token rows ...
 SKINNY_K = 2048                 # ... of at most this many elements (one round of loads a warp) ...
 SKINNY_BYTES = 64 << 20         # ... against at most this many bytes of weights go to the register-only kernel
+SKINNY_ROWS = 8                 # rows of a step up to which the experts go to its grouped form (an expert then has at
+                                # most 8 pairs: one plan tile of 8)
 _lib = None
 
 
@@ -64,6 +66,10 @@ def lib():
         l.tl_gemm_skinny_mma.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int,
                                          c_int, c_int, c_int, c_void_p]
         l.tl_gemm_skinny_mma.restype = c_int
+        l.tl_gemm_skinny_grouped.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
+                                             c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_int, c_void_p, c_void_p]
+        l.tl_gemm_skinny_grouped.restype = c_int
         _lib = l
     return _lib
 
@@ -177,6 +183,31 @@ class TensorCore:
         bn = 16 if avg <= 12 else 32 if avg <= 24 else 64 if swap else 256
         return swap, bn, lib().tl_tc_token_tile(int(swap), bn)
 
+    def _experts_of_a_tiny_step(self, part, x, ids, wts, plan):
+        """Up to eight rows: a few experts' weights and nothing else to read, so the product whose CTAs are many and
+        start at once (16 outputs each, operands straight into registers, all loads in flight) beats the tcgen05
+        one, whose CTAs of 128 outputs are few and each wait for a TMA ring to fill. An expert has at most as many
+        pairs as the step has rows, so a plan in tiles of 8 has one tile an expert."""
+        E, I2, H = part.w_gate_up.shape
+        inter, (R, k) = I2 // 2, ids.shape
+        P = R * k
+        if plan is None or plan.tile_m != 8:
+            plan = part.plan_for(P, x.device, 8).build(ids)
+        if part.load is not None:
+            part.load.add_(plan.counts)
+        tiles = (plan.tile_group.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr(), plan.n_tiles.data_ptr(),
+                 plan.max_tiles)
+        act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
+        _check(lib().tl_gemm_skinny_grouped(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k,
+                                            part.w_gate_up.data_ptr(), H, I2, act.data_ptr(), inter, inter, H, 1,
+                                            ops.dtype_code(act.dtype), *tiles, self.status.data_ptr(), ops.stream()),
+               "gemm_skinny_grouped")
+        y = torch.empty(P, H, dtype=torch.float32, device=x.device)
+        _check(lib().tl_gemm_skinny_grouped(act.data_ptr(), inter, None, 1, part.w_down.data_ptr(), inter, H, y.data_ptr(), H,
+                                            H, inter, 0, ops.dtype_code(y.dtype), *tiles, self.status.data_ptr(),
+                                            ops.stream()), "gemm_skinny_grouped")
+        return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)
+
     def experts(self, part, x, ids, wts, plan=None):
         """The routed experts of `part` on rows x: an `ops.ExpertRows` (to be weighed and added per row), or None
         when the kernels do not take the shapes. `plan`: the routing plan when something built it already."""
@@ -186,6 +217,8 @@ class TensorCore:
             return None
         R, k = ids.shape
         P = R * k
+        if R <= SKINNY_ROWS and H % 8 == 0 and not part.record_counts:
+            return self._experts_of_a_tiny_step(part, x, ids, wts, plan)
         swap, bn, tile = self.expert_tile(P, E)
         fetch = swap and P <= 2 * E           # a row or two a tile: the gate/up product fetches each token row by its index
         xs = None
