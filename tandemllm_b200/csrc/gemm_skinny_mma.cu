@@ -122,30 +122,63 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_mma_kernel(
 // 16 outputs of one tile's expert for the tile's token rows (at most 8: the plan is built with tiles of 8). With SWIGLU
 // it multiplies by the expert's gate rows and up rows of those outputs and stores silu(gate) * up. Token rows are
 // fetched through `row_index` (position i of the plan stands for row row_index[i] / row_div of x) or, without it, lie
-// in the plan's order. Tiles past *n_tiles exit at once. A few experts' weights are all such a step reads: many small
+// in the plan's order. Tiles past *n_tiles exit at once. Without a plan (`pair_group`: the group of each of n_pairs <= 256
+// pairs, tile_* null) tile p is pair p, out row p, x row p / row_div: the CTAs find each group's pairs themselves. A few experts' weights are all such a step reads: many small
 // CTAs that start at once stream them faster than the few 128-row CTAs of the tcgen05 product.
 template <bool SWIGLU, typename TOut>
 __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
     const bf16* __restrict__ x, long long ldx, const int* __restrict__ row_index, int row_div, const bf16* __restrict__ w,
     long long ldw, long long rows_per_group, TOut* __restrict__ out, long long ldc, int N, int K,
     const int* __restrict__ tile_group, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
-    const int* __restrict__ n_tiles, int* __restrict__ status, uint32_t zero) {
+    const int* __restrict__ n_tiles, const int* __restrict__ pair_group, int n_pairs, int n_groups,
+    int* __restrict__ status, uint32_t zero) {
   constexpr int W_TILES = SWIGLU ? 2 : 1;
   constexpr int UNROLL = SWIGLU ? 4 : 8;
   __shared__ float part[SKINNY_WARPS][W_TILES][16][8 + 1];
+  __shared__ uint32_t s_match[SKINNY_WARPS];
+  __shared__ int s_pair[8];
   chain_next();
   chain_wait();
   const int tile = blockIdx.y;
-  if (tile >= *n_tiles) return;
-  const int tok0 = tile_row0[tile];
-  int rows = tile_rows[tile];
-  if (rows > 8) {                                      // the plan was built with taller tiles than this kernel takes
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  int rows, group;
+  if (pair_group) {
+    // No plan: tile p stands for pair p. The CTA of the first pair of a group takes all of the group's pairs (they are
+    // at most as many as the step has rows), the CTAs of the group's later pairs have nothing to do.
+    group = pair_group[tile];
+    const int mine = (int)threadIdx.x < n_pairs ? pair_group[threadIdx.x] : -1;
+    const uint32_t match = __ballot_sync(0xffffffffu, mine == group);
+    if (lane == 0) s_match[warp] = match;
+    __syncthreads();
+    if (group < 0 || group >= n_groups) return;
+    int before = 0, total = 0;                         // matching pairs before this thread's, and in all
+    bool earlier = false;                              // a matching pair before pair `tile`
+#pragma unroll
+    for (int w2 = 0; w2 < SKINNY_WARPS; ++w2) {
+      const uint32_t m = s_match[w2];
+      total += __popc(m);
+      if (w2 < warp) before += __popc(m);
+      const int first = w2 * 32;
+      if (first < tile) earlier |= (m & (tile - first >= 32 ? 0xffffffffu : (1u << (tile - first)) - 1u)) != 0u;
+    }
+    if (earlier) return;
+    before += __popc(match & ((1u << lane) - 1u));
+    if (mine == group && before < 8) s_pair[before] = threadIdx.x;
+    rows = total;
+    __syncthreads();
+  } else {
+    if (tile >= *n_tiles) return;
+    rows = tile_rows[tile];
+    group = tile_group[tile];
+    if (threadIdx.x < 8) s_pair[threadIdx.x] = tile_row0[tile] + threadIdx.x;
+    __syncthreads();
+  }
+  if (rows > 8) {                                      // taller tiles than this kernel takes
     if (threadIdx.x == 0) atomicExch(status, 5);
     rows = 8;
   }
-  const long long w_base = (long long)tile_group[tile] * rows_per_group;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
+  const long long w_base = (long long)group * rows_per_group;
   const int n0 = blockIdx.x * 16;
   const bool v_lo = n0 + g < N, v_hi = n0 + g + 8 < N;
   const bf16* w_lo[W_TILES];
@@ -157,8 +190,8 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
     w_hi[j] = w + (first + (v_hi ? g + 8 : 0)) * ldw + t * 8;
   }
   const bool x_ok = g < rows;
-  const int pos = tok0 + (x_ok ? g : 0);
-  const bf16* x_row = x + (long long)(row_index ? row_index[pos] / row_div : pos) * ldx + t * 8;
+  const int pos = s_pair[x_ok ? g : 0];
+  const bf16* x_row = x + (long long)(row_index ? row_index[pos] / row_div : pos / row_div) * ldx + t * 8;
   float acc[W_TILES][4];
 #pragma unroll
   for (int j = 0; j < W_TILES; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
@@ -209,7 +242,7 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
       for (int s = 0; s < SKINNY_WARPS; ++s) v[j] += part[s][j][row][m];
     }
     const float r = SWIGLU ? v[0] / (1.f + expf(-v[0])) * v[W_TILES - 1] : v[0];
-    out[(long long)(tok0 + m) * ldc + n0 + row] = from_f32<TOut>(r);
+    out[(long long)s_pair[m] * ldc + n0 + row] = from_f32<TOut>(r);
   }
 }
 
@@ -252,18 +285,22 @@ extern "C" int tl_gemm_skinny_mma(const void* x, long long ldx, const void* w, l
 extern "C" int tl_gemm_skinny_grouped(const void* x, long long ldx, const int* row_index, int row_div, const void* w,
                                       long long ldw, long long rows_per_group, void* out, long long ldc, int N, int K,
                                       int swiglu, int out_dtype, const int* tile_group, const int* tile_row0,
-                                      const int* tile_rows, const int* n_tiles, int max_tiles, int* status,
-                                      cudaStream_t stream) {
+                                      const int* tile_rows, const int* n_tiles, int max_tiles, const int* pair_group,
+                                      int n_pairs, int n_groups, int* status, cudaStream_t stream) {
+  if (pair_group) max_tiles = n_pairs;
   if (max_tiles == 0 || N == 0) return 0;
   TL_REQUIRE(N >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && row_div >= 1 && max_tiles <= 65535,
              "skinny grouped product: %d outputs, k %d, strides %lld and %lld", N, K, ldx, ldw);
-  TL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && tile_group && tile_row0 && tile_rows && n_tiles,
-             "skinny grouped product: operands must be 16-byte aligned and the plan complete (%d)", 0);
+  TL_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
+                 (pair_group ? (n_pairs <= SKINNY_WARPS * 32 && n_groups >= 1 && !row_index)
+                             : (tile_group && tile_row0 && tile_rows && n_tiles)),
+             "skinny grouped product: operands must be 16-byte aligned and the plan complete, or at most %d pairs given",
+             SKINNY_WARPS * 32);
   const dim3 grid(ceil_div(N, 16), max_tiles), block(SKINNY_WARPS * 32);
 #define TL_GROUPED(SW_, T_)                                                                                              \
   return (int)launch_chained(gemm_skinny_grouped_kernel<SW_, T_>, grid, block, 0, stream, (const bf16*)x, ldx, row_index,  \
                              row_div, (const bf16*)w, ldw, rows_per_group, (T_*)out, ldc, N, K, tile_group, tile_row0,    \
-                             tile_rows, n_tiles, status, 0u)
+                             tile_rows, n_tiles, pair_group, n_pairs, n_groups, status, 0u)
   if (swiglu) {
     if (out_dtype == TL_FP32) TL_GROUPED(true, float);
     TL_GROUPED(true, bf16);

@@ -115,7 +115,7 @@ def test_split_k_is_used_and_repeatable():
 
 @pytest.mark.parametrize("R,E,k,H,I", [(4, 8, 2, 128, 64), (8, 32, 4, 256, 192), (64, 8, 3, 136, 72), (700, 6, 2, 128, 96),
                                        (1, 32, 4, 256, 1024), (2, 16, 3, 200, 520), (5, 6, 2, 136, 72),
-                                       (8, 4, 4, 72, 40), (7, 3, 3, 88, 24),        # every expert holds every row
+                                       (8, 4, 4, 72, 40), (7, 3, 3, 88, 24), (8, 2, 2, 72, 40),     # every expert holds every row
                                        (2048, 4, 2, 64, 128)])
 def test_grouped_experts_with_swiglu(R, E, k, H, I):
     from tandemllm_b200.config import PartSpec
@@ -139,6 +139,12 @@ def test_grouped_experts_with_swiglu(R, E, k, H, I):
     result = impl.experts(part, x.to(DEV), ids, wts)
     assert result is not None
     out = result.materialize()
+    # with the experts' load counted a small step builds a routing plan, without it needs none: the same bits
+    part.load = torch.zeros(E, dtype=torch.int64, device=DEV)
+    counted = impl.experts(part, x.to(DEV), ids, wts).materialize()
+    assert torch.equal(part.load.cpu(), torch.bincount(ids.cpu().flatten().long(), minlength=E))
+    assert torch.equal(counted, out)
+    part.load = None
     # the same rows as the norm kernel adds them (partial sums of a split down product included)
     residual = torch.zeros(R, H, dtype=torch.float32, device=DEV)
     ops.add_rmsnorm(residual, result, torch.ones(H, device=DEV), 1e-5, torch.empty(R, H, dtype=torch.bfloat16, device=DEV))
@@ -153,6 +159,48 @@ def test_grouped_experts_with_swiglu(R, E, k, H, I):
             h = torch.nn.functional.silu(xf[rows] @ w13[e, :I].float().T) * (xf[rows] @ w13[e, I:].float().T)
             want.index_add_(0, rows, (h.to(torch.bfloat16).float() @ w2[e].float().T) * wc[rows, slot, None])
     assert rel(out, want) < 2e-2
+
+
+@pytest.mark.parametrize("R,E,k", [(8, 40, 6), (8, 9, 6), (7, 300, 32), (3, 33, 32)])
+def test_experts_of_a_small_step_without_a_plan_at_every_count_of_pairs(R, E, k, monkeypatch):
+    """The form in which the products' CTAs find each expert's pairs in the ids themselves is used for a few pairs only;
+    it takes up to 256 (pairs in several warps of the CTA that looks for them): the same bits as with a plan."""
+    from tandemllm_b200.config import PartSpec
+    from tandemllm_b200.kernels import tensorcore
+    from tandemllm_b200.parts import make_part
+    H, I = 72, 40
+    outs = []
+    for cap in (256, 0):
+        monkeypatch.setattr(tensorcore, "SKINNY_PAIRS", cap)
+        impl, rt = tc()
+        spec = PartSpec("sigmoid_topk_experts", {"num_experts": E, "top_k": k, "intermediate_size": I, "expert_bias": False,
+                                                 "normalize": True, "scale": 1.0,
+                                                 "names": {"router": "gate", "bias": "expert_bias", "experts": "experts",
+                                                           "gate": "w1", "up": "w3", "down": "w2"}})
+        part = make_part("feed_forward", spec, prefix="m.", hidden_size=H)
+        W = {"m.gate.weight": rnd(E, H, seed=9, scale=0.5).float()}
+        w13, w2 = rnd(E, 2 * I, H, seed=10, scale=0.2), rnd(E, H, I, seed=11, scale=0.2)
+        for e in range(E):
+            W[f"m.experts.{e}.w1.weight"], W[f"m.experts.{e}.w3.weight"] = w13[e, :I], w13[e, I:]
+            W[f"m.experts.{e}.w2.weight"] = w2[e]
+        part.weight_specs(set(W))
+        part.bind(lambda n: W[n], rt)
+        x = rnd(R, H, seed=12).to(DEV)
+        ids, wts = part.route(x.float())
+        result = impl.experts(part, x, ids, wts)
+        assert (result.pos_of_pair is impl._pair_order) == (cap > 0)
+        outs.append(result.materialize())
+        torch.cuda.synchronize()
+        assert int(rt.status) == 0
+    assert torch.equal(outs[0], outs[1])
+    want = torch.zeros(R, H)
+    xf, idc, wc = x.float().cpu(), ids.cpu(), wts.cpu()
+    for e in range(E):
+        rows, slot = torch.where(idc == e)
+        if rows.numel():
+            h = torch.nn.functional.silu(xf[rows] @ w13[e, :I].float().T) * (xf[rows] @ w13[e, I:].float().T)
+            want.index_add_(0, rows, (h.to(torch.bfloat16).float() @ w2[e].float().T) * wc[rows, slot, None])
+    assert rel(outs[0], want) < 2e-2
 
 
 @pytest.mark.parametrize("split", [0, 256, 512])
