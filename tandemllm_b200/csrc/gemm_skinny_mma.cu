@@ -246,6 +246,103 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
   }
 }
 
+// The in-projection of a short-convolution mixer and the convolution behind it, for a decode step of at most 8 rows
+// (one row a request): w [3 hidden, K] holds the B, C and x rows of every channel. A CTA owns 8 channels: their B and C
+// rows are the two halves of one MMA tile, their x rows the lower half of a second. Its epilogue rounds the three sums
+// to bfloat16 as the projection alone would, convolves bx = B x with the request's state, writes y = C conv and shifts
+// the state: the same bits as the projection kernel above followed by short_conv_decode_kernel (conv.cu), one launch
+// less a layer.
+constexpr int CONV_MAX_TAPS = 16;
+__global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_conv_kernel(
+    const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ w, long long ldw, const float* __restrict__ proj_bias,
+    const float* __restrict__ taps, const float* __restrict__ conv_bias, float* __restrict__ state,
+    const int* __restrict__ state_slot, const int* __restrict__ req_of_row, const int* __restrict__ positions,
+    bf16* __restrict__ y, int M, int hidden, int K, int n_taps, int write_state, uint32_t zero) {
+  constexpr int UNROLL = 4;
+  __shared__ float part[SKINNY_WARPS][2][16][8 + 1];
+  chain_next();
+  chain_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int c0 = blockIdx.x * 8;
+  const bool ch_ok = c0 + g < hidden;
+  const long long ch = ch_ok ? c0 + g : 0;
+  const bf16* w_b = w + ch * ldw + t * 8;
+  const bf16* w_c = w + (hidden + ch) * ldw + t * 8;
+  const bf16* w_x = w + (2LL * hidden + ch) * ldw + t * 8;
+  const bool x_ok = g < M;
+  const bf16* x_row = x + (long long)(x_ok ? g : 0) * ldx + t * 8;
+  float acc[2][4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  const int chunks = (K + 31) / 32;
+  for (int k0 = warp; k0 < chunks; k0 += SKINNY_WARPS * UNROLL) {
+    uint4 a_b[UNROLL], a_c[UNROLL], a_x[UNROLL], b[UNROLL];
+    uint32_t all = 0u;
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = k0 + u * SKINNY_WARPS;
+      const bool in = c < chunks && c * 32 + t * 8 < K;
+      a_b[u] = load16(w_b + c * 32, in && ch_ok);
+      a_c[u] = load16(w_c + c * 32, in && ch_ok);
+      a_x[u] = load16(w_x + c * 32, in && ch_ok);
+      b[u] = load16(x_row + c * 32, in && x_ok);
+      all ^= a_b[u].w ^ a_c[u].w ^ a_x[u].w ^ b[u].w;
+    }
+    a_b[0].x ^= all & zero;                     // the round's first MMA waits for all of the round's loads (zero is 0)
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      mma_16816(acc[0], a_b[u].x, a_c[u].x, a_b[u].y, a_c[u].y, b[u].x, b[u].y);
+      mma_16816(acc[0], a_b[u].z, a_c[u].z, a_b[u].w, a_c[u].w, b[u].z, b[u].w);
+      mma_16816(acc[1], a_x[u].x, 0u, a_x[u].y, 0u, b[u].x, b[u].y);
+      mma_16816(acc[1], a_x[u].z, 0u, a_x[u].w, 0u, b[u].z, b[u].w);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    part[warp][j][g][2 * t] = acc[j][0];
+    part[warp][j][g][2 * t + 1] = acc[j][1];
+    part[warp][j][g + 8][2 * t] = acc[j][2];
+    part[warp][j][g + 8][2 * t + 1] = acc[j][3];
+  }
+  __syncthreads();
+  if (threadIdx.x >= 64) return;
+  const int e = threadIdx.x & 7, m = threadIdx.x >> 3;        // channel c0 + e of row m
+  const int c = c0 + e;
+  if (m >= M || c >= hidden) return;
+  float in[3];                                                 // B, C, x as the projection alone would have stored them
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    float v = 0.f;
+#pragma unroll
+    for (int s = 0; s < SKINNY_WARPS; ++s) v += part[s][j >> 1][e + (j & 1) * 8][m];
+    if (proj_bias) v += proj_bias[(long long)j * hidden + c];
+    in[j] = to_f32(from_f32<bf16>(v));
+  }
+  // from here on: short_conv_decode_kernel, line by line
+  const int pos = positions[m];
+  const float bx = in[0] * in[2];
+  const int S = n_taps - 1;
+  float* st = state + ((long long)state_slot[req_of_row[m]] * S) * hidden;
+  float old[CONV_MAX_TAPS];
+#pragma unroll 1
+  for (int s = 0; s < S; ++s) old[s] = st[(long long)s * hidden + c];
+  float sum = conv_bias ? conv_bias[c] : 0.f;
+#pragma unroll 1
+  for (int j = 0; j < n_taps; ++j) {
+    const int back = n_taps - 1 - j;
+    if (pos - back < 0) continue;                // before the sequence's first token: zero
+    const float v = back == 0 ? bx : old[S - back];
+    sum = fmaf(taps[(long long)c * n_taps + j], v, sum);
+  }
+  y[(long long)m * hidden + c] = from_f32<bf16>(in[1] * sum);
+  if (write_state) {
+#pragma unroll 1
+    for (int s = 0; s + 1 < S; ++s) st[(long long)s * hidden + c] = (pos - (S - (s + 1)) >= 0) ? old[s + 1] : 0.f;
+    st[(long long)(S - 1) * hidden + c] = bx;
+  }
+}
+
 }  // namespace tl
 
 using namespace tl;
@@ -308,4 +405,22 @@ extern "C" int tl_gemm_skinny_grouped(const void* x, long long ldx, const int* r
   if (out_dtype == TL_FP32) TL_GROUPED(false, float);
   TL_GROUPED(false, bf16);
 #undef TL_GROUPED
+}
+
+// in-projection + short convolution of a decode step of at most 8 rows (one row a request): x [M, K] bfloat16,
+// w [3 hidden, K] bfloat16 (B rows, C rows, x rows), proj_bias [3 hidden] or null, taps [hidden, n_taps] 32-bit,
+// conv_bias [hidden] or null, state [slots, n_taps - 1, hidden] 32-bit, y [M, hidden] bfloat16.
+extern "C" int tl_gemm_skinny_conv(const void* x, long long ldx, const void* w, long long ldw, const float* proj_bias,
+                                   const float* taps, const float* conv_bias, float* state, const int* state_slot,
+                                   const int* req_of_row, const int* positions, void* y, int M, int hidden, int K,
+                                   int n_taps, int write_state, cudaStream_t stream) {
+  if (M == 0) return 0;
+  TL_REQUIRE(M >= 1 && M <= 8 && hidden >= 1 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
+             "skinny in-projection + conv: %d rows, %d channels, k %d, strides %lld and %lld", M, hidden, K, ldx, ldw);
+  TL_REQUIRE(n_taps >= 2 && n_taps <= CONV_MAX_TAPS && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0,
+             "skinny in-projection + conv: %d taps (2..%d), operands 16-byte aligned", n_taps, CONV_MAX_TAPS);
+  const dim3 grid(ceil_div(hidden, 8)), block(SKINNY_WARPS * 32);
+  return (int)launch_chained(gemm_skinny_conv_kernel, grid, block, 0, stream, (const bf16*)x, ldx, (const bf16*)w, ldw,
+                             proj_bias, taps, conv_bias, state, state_slot, req_of_row, positions, (bf16*)y, M, hidden, K,
+                             n_taps, write_state, 0u);
 }

@@ -71,6 +71,9 @@ def lib():
                                              c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
         l.tl_gemm_skinny_grouped.restype = c_int
+        l.tl_gemm_skinny_conv.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        l.tl_gemm_skinny_conv.restype = c_int
         _lib = l
     return _lib
 
@@ -176,6 +179,24 @@ class TensorCore:
                                             ops.stream()), "gemm_skinny_mma")
             return True
         return self.gemm(x, w, bias, out, defer=defer) or True
+
+    def in_proj_conv(self, x, w_in, b_in, taps, b_taps, state, state_slot, req_of_row, positions, y,
+                     write_state: bool = True) -> bool:
+        """A short-convolution mixer's in-projection and convolution of a decode step of at most 8 rows (one row a
+        request) in one kernel: the same bits as `linear` into bfloat16 followed by `ops.short_conv_decode`. False
+        when the shapes are not those of the register-only product."""
+        M, K = x.shape
+        H = y.shape[1]
+        if (M > 8 or not usable(x, w_in) or K > SKINNY_K or 3 * H * K * 2 > SKINNY_BYTES or w_in.shape[0] != 3 * H
+                or y.dtype != torch.bfloat16 or not y.is_contiguous() or taps.dtype != torch.float32
+                or not taps.is_contiguous() or state.dtype != torch.float32 or not state.is_contiguous()
+                or not lib().tl_gemm_skinny_supported(M, 3 * H, K, x.stride(0), w_in.stride(0))):
+            return False
+        _check(lib().tl_gemm_skinny_conv(x.data_ptr(), x.stride(0), w_in.data_ptr(), w_in.stride(0), ops.ptr(b_in),
+                                         taps.data_ptr(), ops.ptr(b_taps), state.data_ptr(), state_slot.data_ptr(),
+                                         req_of_row.data_ptr(), positions.data_ptr(), y.data_ptr(), M, H, K, taps.shape[1],
+                                         int(write_state), ops.stream()), "gemm_skinny_conv")
+        return True
 
     # ---- routed experts ----
     def expert_tile(self, pairs: int, experts: int) -> tuple[bool, int, int]:

@@ -61,10 +61,14 @@ class ShortConvMixer(Part):
         H = self.hidden_size
         y = torch.empty(x.shape[0], H, dtype=x.dtype, device=x.device)
         if step.max_rows_per_request == 1:
-            # decoding: one kernel convolves and shifts the state, and adds the projection's partial sums itself
-            bcx = linear(self.runtime, x, self.w_in, self.b_in, defer="rounded")
-            ops.short_conv_decode(bcx, self.w_taps, self.b_taps, cache.state, step.state_slot, step.req_of_row,
-                                  step.positions, y, write_state=writes_cache)
+            # decoding. A handful of rows: the in-projection's kernel convolves and shifts the state in its epilogue.
+            # More: one kernel convolves and shifts the state, and adds the projection's partial sums itself.
+            tc = self.runtime.tensorcore
+            if tc is None or not tc.in_proj_conv(x, self.w_in, self.b_in, self.w_taps, self.b_taps, cache.state,
+                                                 step.state_slot, step.req_of_row, step.positions, y, writes_cache):
+                bcx = linear(self.runtime, x, self.w_in, self.b_in, defer="rounded")
+                ops.short_conv_decode(bcx, self.w_taps, self.b_taps, cache.state, step.state_slot, step.req_of_row,
+                                      step.positions, y, write_state=writes_cache)
             return linear(self.runtime, y, self.w_out, self.b_out, out_dtype=torch.float32, defer=True)
         bcx = linear(self.runtime, x, self.w_in, self.b_in)
         ops.short_conv(bcx, self.w_taps, self.b_taps, cache.state, step.state_slot, step.req_of_row, step.row_start,

@@ -70,6 +70,55 @@ def test_few_tokens_through_registers_alone(M, N, K):
     assert not lib.tl_gemm_skinny_supported(33, N, K, K, K) and not lib.tl_gemm_skinny_supported(M, N, K + 4, K + 4, K + 4)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("H,K,taps,use_bias", [(200, 136, 3, False), (96, 64, 4, True), (64, 2048, 2, False),
+                                               (300, 520, 7, True), (2048, 2048, 3, False)])
+def test_in_projection_and_short_conv_in_one_kernel(M, H, K, taps, use_bias):
+    """A decode step's in-projection with the convolution and the state's shift in its epilogue: the same bits as the
+    projection into bfloat16 followed by the convolution's own decode kernel; channel counts with a tail in the CTA's
+    eight, k with a short last chunk, sequences at their first positions beside later ones, a state left alone."""
+    from tandemllm_b200.kernels import ops
+    impl, rt = tc()
+    dev = lambda t: None if t is None else t.to(DEV)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    x, w = dev(rnd(M, K, seed=40)), dev(rnd(3 * H, K, seed=41, scale=0.1))
+    b_in = dev(torch.randn(3 * H, generator=torch.Generator().manual_seed(42))) if use_bias else None
+    b_taps = dev(torch.randn(H, generator=torch.Generator().manual_seed(43))) if use_bias else None
+    tw = dev(torch.randn(H, taps, generator=torch.Generator().manual_seed(44)))
+    state = torch.randn(9, taps - 1, H, generator=torch.Generator().manual_seed(45))
+    starts, slots = [0, 1, 2, 5, 40, 3, 0, 9][:M], [2, 0, 3, 4, 6, 8, 1, 5][:M]
+    rows = i32(list(range(M)))
+    # the two kernels
+    bcx = torch.empty(M, 3 * H, dtype=torch.bfloat16, device=DEV)
+    assert impl.linear(x, w, b_in, bcx) is True
+    st_two, y_two = dev(state.clone()), torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+    ops.short_conv_decode(bcx, tw, b_taps, st_two, i32(slots), rows, i32(starts), y_two)
+    # the one
+    st, y = dev(state.clone()), torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert impl.in_proj_conv(x, w, b_in, tw, b_taps, st, i32(slots), rows, i32(starts), y)
+    kept, y_kept = dev(state.clone()), torch.empty_like(y)
+    assert impl.in_proj_conv(x, w, b_in, tw, b_taps, kept, i32(slots), rows, i32(starts), y_kept, write_state=False)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    assert torch.equal(y, y_two) and torch.equal(st, st_two)
+    assert torch.equal(y_kept, y_two) and torch.equal(kept.cpu(), state)
+    # and the plain formula: bx = B x, y = C (bias + sum_j taps[j] bx[pos - (taps - 1) + j]), inputs before position 0 zero
+    z = x.float().cpu() @ w.float().cpu().T + (0 if b_in is None else b_in.cpu())
+    assert rel(bcx, z) < 1e-2
+    z = bcx.float().cpu()                       # (the projection as it was rounded, so that the state compares exactly)
+    B, C, X = z[:, :H], z[:, H:2 * H], z[:, 2 * H:]
+    for m in range(M):
+        hist = torch.cat([state[slots[m]], (B[m] * X[m])[None]])            # the last `taps` inputs, oldest first
+        for j in range(taps):
+            if starts[m] - (taps - 1 - j) < 0:
+                hist[j] = 0
+        conv = (tw.cpu().T * hist).sum(0) + (0 if b_taps is None else b_taps.cpu())
+        assert rel(y[m], C[m] * conv) < 1e-2, m
+        assert torch.allclose(st[slots[m]].cpu(), hist[1:], atol=1e-6), m
+    assert not impl.in_proj_conv(dev(rnd(9, K, seed=46)), w, b_in, tw, b_taps, st, i32(list(range(9))), i32(list(range(9))),
+                                 i32([1] * 9), torch.empty(9, H, dtype=torch.bfloat16, device=DEV))
+
+
 @pytest.mark.parametrize("swap,bn", [(True, 16), (True, 32), (True, 64), (True, 128), (True, 256), (False, 16),
                                      (False, 64), (False, 128), (False, 256)])
 def test_every_tile_shape_in_both_orientations(swap, bn):
