@@ -77,6 +77,41 @@ template <int ROWS>
 __device__ __forceinline__ void router_logits(const NormParams& p, const float* rows, float* logits, int n_rows, int lane,
                                               int warp, int nwarps) {
   const int hidden = p.hidden;
+  if (ROWS > 1 && (hidden & 3) == 0) {
+    // two experts a pass: a piece of a row read from shared memory serves both (these reads are what the loop waits for)
+    const int h4 = hidden >> 2;
+    for (int e = warp; e < p.E; e += 2 * nwarps) {
+      const int e2 = e + nwarps;
+      const bool two = e2 < p.E;
+      const float4* wa = reinterpret_cast<const float4*>(p.router_w + (size_t)e * hidden);
+      const float4* wb = reinterpret_cast<const float4*>(p.router_w + (size_t)(two ? e2 : e) * hidden);
+      float acc_a[ROWS], acc_b[ROWS];
+#pragma unroll
+      for (int rr = 0; rr < ROWS; ++rr) acc_a[rr] = acc_b[rr] = 0.f;
+#pragma unroll 2
+      for (int c = lane; c < h4; c += 32) {
+        const float4 va = __ldg(wa + c), vb = __ldg(wb + c);
+#pragma unroll
+        for (int rr = 0; rr < ROWS; ++rr)
+          if (rr < n_rows) {
+            const float4 x = reinterpret_cast<const float4*>(rows + (size_t)rr * hidden)[c];
+            acc_a[rr] = fmaf(x.w, va.w, fmaf(x.z, va.z, fmaf(x.y, va.y, fmaf(x.x, va.x, acc_a[rr]))));
+            acc_b[rr] = fmaf(x.w, vb.w, fmaf(x.z, vb.z, fmaf(x.y, vb.y, fmaf(x.x, vb.x, acc_b[rr]))));
+          }
+      }
+#pragma unroll
+      for (int rr = 0; rr < ROWS; ++rr) {
+        if (rr < n_rows) {
+          const float a = warp_sum(acc_a[rr]), b = warp_sum(acc_b[rr]);
+          if (lane == 0) {
+            logits[rr * p.E + e] = a;
+            if (two) logits[rr * p.E + e2] = b;
+          }
+        }
+      }
+    }
+    return;
+  }
   for (int e = warp; e < p.E; e += nwarps) {
     const float* w = p.router_w + (size_t)e * hidden;
     float acc[ROWS];
@@ -204,7 +239,29 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
   const bool adds = p.delta || p.expert_rows;
   const bool vec = (hidden & 3) == 0;           // rows are then 16-byte aligned: four elements a step
   float ss = 0.f;
-  if (live) {
+  // A row that gets a plain tensor added (or nothing) and whose thread holds at most IN_REGS 16-byte pieces of it: all
+  // of the thread's loads are sent before the first is used, and the pieces stay in registers until they are normed.
+  constexpr int IN_REGS = 4;
+  const bool in_regs = vec && !p.expert_rows && p.parts <= 1 && (hidden >> 2) <= G * IN_REGS;
+  float4 xr[IN_REGS];
+  if (in_regs) {
+    const int h4 = hidden >> 2;
+    const float4* res4 = reinterpret_cast<const float4*>(res);
+    const float4* d4 = p.delta ? reinterpret_cast<const float4*>(p.delta + (size_t)r * hidden) : nullptr;
+    float4 dr[IN_REGS];
+#pragma unroll
+    for (int i = 0; i < IN_REGS; ++i) {
+      const int c = t + i * G;
+      const bool ok = live && c < h4;
+      xr[i] = ok ? res4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      dr[i] = ok && d4 ? d4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < IN_REGS; ++i) {
+      xr[i].x += dr[i].x; xr[i].y += dr[i].y; xr[i].z += dr[i].z; xr[i].w += dr[i].w;
+      ss += xr[i].x * xr[i].x + xr[i].y * xr[i].y + xr[i].z * xr[i].z + xr[i].w * xr[i].w;
+    }
+  } else if (live) {
     if (vec) {
       const int h4 = hidden >> 2;
       const float4* res4 = reinterpret_cast<const float4*>(res);
@@ -222,7 +279,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
           // four expert rows at a time, all loaded (with the further parts of a split down product) before the first
           // is used; added in ascending expert id as ever
           float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-          constexpr int STEP = ONE_ROW ? 4 : 1;        // (a prompt's blocks keep to few registers and to one row at a time)
+          constexpr int STEP = 4;
           for (int j0 = 0; j0 < p.top_k; j0 += STEP) {
             float4 v[STEP];
 #pragma unroll
@@ -289,8 +346,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
   if (live) {
     if (vec) {
       const int h4 = hidden >> 2;
-      for (int c = t; c < h4; c += G) {
-        const float4 x = reinterpret_cast<const float4*>(row)[c];
+      auto finish = [&](int c, const float4 x) {
         if (!p.gather && adds) reinterpret_cast<float4*>(res)[c] = x;
         const float4 w = reinterpret_cast<const float4*>(p.weight)[c];
         const float4 y = make_float4(w.x * (x.x * inv), w.y * (x.y * inv), w.z * (x.z * inv), w.w * (x.w * inv));
@@ -304,7 +360,14 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
           reinterpret_cast<float4*>(out)[c] = y;
         }
         if (out32) reinterpret_cast<float4*>(out32)[c] = y;
-        reinterpret_cast<float4*>(row)[c] = y;
+        if (ROUTE_PER > 0) reinterpret_cast<float4*>(row)[c] = y;      // the router reads the normed rows from here
+      };
+      if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < IN_REGS; ++i)
+          if (t + i * G < h4) finish(t + i * G, xr[i]);
+      } else {
+        for (int c = t; c < h4; c += G) finish(c, reinterpret_cast<const float4*>(row)[c]);
       }
     } else {
       for (int c = t; c < hidden; c += G) {
