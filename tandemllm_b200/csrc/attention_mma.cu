@@ -15,7 +15,13 @@
 //               the join kernel of attention_split.cu adds the spans in order (decoding at long contexts). The
 //               caller picks S so that the grid fills the GPU: short spans for one request, long ones for many.
 // The tile table (request, first row, rows) comes from the host with the step's other integers.
-#include "common.cuh"
+//
+// TMA (decoding, page sizes that divide 64 or are multiples of it): a fifth warp is the producer. For every key tile
+// its lanes look the tile's pages up and each sends one bulk tensor copy (a page's rows of one KV head, 64 columns, with
+// the 128-byte swizzle the ldmatrix reads expect) onto the stage's `full` mbarrier; the four consumer warps wait on
+// it, compute, and arrive on the stage's `empty` mbarrier. No thread of a consumer warp computes an address or issues
+// a copy, and the CTA never stops at a block-wide barrier inside the loop. Every mbarrier wait is bounded (status 11).
+#include "tma.cuh"
 
 namespace tl {
 
@@ -51,25 +57,42 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // row so that the eight rows an ldmatrix reads fall into different banks.
 template <int D> __device__ __forceinline__ int swz(int row, int chunk) { return row * (D * 2) + ((chunk ^ (row & 7)) << 4); }
 
+// The same for a key or value tile. Tiles that TMA wrote consist of D / 64 halves of 64 columns, each [64 keys][128
+// bytes] with the 128-byte swizzle (for a head size of 64 that is the layout above).
+template <int D, bool TMA> __device__ __forceinline__ int kv_off(int row, int chunk) {
+  if constexpr (TMA) return (chunk >> 3) * (KT * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+  return swz<D>(row, chunk);
+}
+
 // KEYSPLIT: every tile of the launch has at most 16 M rows in use (decoding: one query row of up to 16 heads). The
 // four warps then share those rows and split each 64-key tile among themselves, 16 keys a warp, each with its own
 // running (max, sum, output); they are merged in warp order through shared memory at the end. Otherwise each warp
 // owns 16 of the tile's 64 M rows and walks all keys. STAGES is the depth of the cp.async ring of key/value tiles.
-template <int D, bool KEYSPLIT, int STAGES>
-__global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
+struct KvMaps {
+  CUtensorMap k, v;       // the key and value caches as [pages * KV heads * page size, D], boxes of box_rows x 64 columns
+};
+
+template <int D, bool KEYSPLIT, int STAGES, bool TMA>
+__global__ void __launch_bounds__(TMA ? 160 : 128, D == 64 ? (TMA ? 3 : 4) : 2) attention_mma_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     const int* __restrict__ block_table, int max_pages, int page_size, int page_shift, int num_pages,
     const int* __restrict__ tiles,
     const int* __restrict__ positions, float scale, int window, bf16* __restrict__ out, float* __restrict__ part_o,
-    float* __restrict__ part_ml, int n_spans, int split, int Hq, int Hk, int* __restrict__ status) {
+    float* __restrict__ part_ml, int n_spans, int split, int Hq, int Hk, int* __restrict__ status,
+    const __grid_constant__ KvMaps maps, int box_rows) {
+  static_assert(!TMA || KEYSPLIT, "the producer warp exists in the decoding form only");
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int TILE_BYTES = 64 * D * 2;
   constexpr int QROWS = KEYSPLIT ? 16 : 64;
   constexpr int NS = KEYSPLIT ? 2 : 8;      // 8-key score tiles a warp computes per key tile
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  // TMA's swizzle is a function of the shared-memory address: its tiles start on 1024-byte boundaries
+  uint8_t* smem = TMA ? (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023) : smem_raw;
   uint8_t* sq = smem;                            // [QROWS][D]
   uint8_t* sk = sq + QROWS * D * 2;              // [STAGES][64][D]
   uint8_t* sv = sk + STAGES * TILE_BYTES;        // [STAGES][64][D]
+  uint64_t* full = reinterpret_cast<uint64_t*>(sv + STAGES * TILE_BYTES);      // TMA: [STAGES], then empty [STAGES]
+  uint64_t* empty = full + STAGES;
 
   chain_next();
   chain_wait();
@@ -94,8 +117,18 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
   if (k_lo > k_hi) return;
   const int kt_first = k_lo / KT, kt_last = k_hi / KT;
 
+  if constexpr (TMA) {
+    if (tid == 0) {
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(&full[s], 1);           // the producer's arrival, with the bytes of the stage's copies
+        mbar_init(&empty[s], 4);          // one arrival a consumer warp
+      }
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+  }
   // ---- Q tile: M row m = (query row m / G, head m % G); rows past the tile's queries are zero ----
-  for (int i = tid; i < QROWS * CH; i += 128) {
+  for (int i = tid; i < QROWS * CH && tid < 128; i += 128) {
     const int m = i / CH, c = i % CH;
     const int qi = m / G, hj = m % G;
     const bool valid = qi < nq;
@@ -128,11 +161,65 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
       cp_async16(dv + swz<D>(my_key, c), v_cache + off + c * 8, valid);
     }
   };
+  if constexpr (!TMA) {
 #pragma unroll
-  for (int s0 = 0; s0 < STAGES - 1; ++s0) {
-    if (kt_first + s0 <= kt_last) load_kv(kt_first + s0, s0);
+    for (int s0 = 0; s0 < STAGES - 1; ++s0) {
+      if (kt_first + s0 <= kt_last) load_kv(kt_first + s0, s0);
+      cp_async_commit();
+    }
+  } else {
     cp_async_commit();
+    if (warp == 4) {
+      // ---- the producer warp: lane i sends box i of every tile (a page's rows, 64 columns, of the keys or the values) ----
+      constexpr int HALVES = D / 64;
+      const int n_boxes = (KT / box_rows) * HALVES * 2;
+      const uint32_t box_bytes = (uint32_t)box_rows * 128u;
+      const int which = lane & 1, half = (lane >> 1) % HALVES, pi = lane / (2 * HALVES);
+      bool ok = true;
+      int issued = 0;
+      for (int kt = kt_first; kt <= kt_last; ++kt) {
+        const int it = kt - kt_first, stage = it % STAGES;
+        if (it >= STAGES && !mbar_wait(&empty[stage], ((it / STAGES) - 1) & 1)) {
+          ok = false;
+          break;
+        }
+        bool need = false;
+        int y = 0;
+        uint8_t* dst = (which ? sv : sk) + stage * TILE_BYTES + half * (KT * 128) + pi * box_rows * 128;
+        if (lane < n_boxes) {
+          const int key0 = kt * KT + pi * box_rows;                    // the box's first key position
+          need = key0 + box_rows - 1 >= k_lo && key0 <= k_hi;         // (a page no row of the tile sees may be gone)
+          if (need) {
+            const int pg = page_shift >= 0 ? key0 >> page_shift : key0 / page_size;
+            const int page = table_page(table, pg, max_pages, num_pages);
+            if (page < 0) {
+              atomicExch(status, 3);
+              need = false;
+            } else {
+              y = (page * Hk + g) * page_size + (key0 - pg * page_size);
+            }
+          }
+          // values that are not fetched are multiplied by weights of zero: they must be numbers
+          if (!need && which)
+            for (uint32_t j = 0; j < box_bytes; j += 16) *reinterpret_cast<uint4*>(dst + j) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        const uint32_t n_need = __popc(__ballot_sync(0xffffffffu, need));
+        if (lane == 0) mbar_expect_tx(&full[stage], n_need * box_bytes);
+        __syncwarp();
+        if (need) tma_load_2d(dst, which ? &maps.v : &maps.k, &full[stage], half * 64, y);
+        issued = it + 1;
+      }
+      if (!ok) {
+        // a consumer gave up: what was sent must still land before the CTA's shared memory is given back
+        if (lane == 0) atomicExch(status, 11);
+        for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
+      }
+    } else {
+      cp_async_wait<0>();
+      asm volatile("bar.sync 1, 128;" ::: "memory");       // the four consumer warps: the Q tile is complete
+    }
   }
+  const bool consumer = !TMA || warp < 4;
 
   // this thread's two M rows and their query positions
   const int wrow = KEYSPLIT ? 0 : warp * 16;
@@ -156,14 +243,21 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
   uint32_t qf[D / 16][4];
 
-  for (int kt = kt_first; kt <= kt_last; ++kt) {
+  for (int kt = kt_first; consumer && kt <= kt_last; ++kt) {
     const int it = kt - kt_first;
     const int stage = it % STAGES;
-    cp_async_wait<STAGES - 2>();      // this thread's copies of tile kt have landed
-    __syncthreads();                  // everybody's have, and everybody is done with the tile before
-    if (kt + STAGES - 1 <= kt_last) load_kv(kt + STAGES - 1, (it + STAGES - 1) % STAGES);
-    cp_async_commit();
-    if (!active) continue;            // a warp whose 16 M rows lie past the tile's queries only helps with the loads
+    if constexpr (TMA) {
+      if (!mbar_wait(&full[stage], (it / STAGES) & 1)) {      // the tile's copies have landed
+        if (lane == 0) atomicExch(status, 11);
+        break;
+      }
+    } else {
+      cp_async_wait<STAGES - 2>();      // this thread's copies of tile kt have landed
+      __syncthreads();                  // everybody's have, and everybody is done with the tile before
+      if (kt + STAGES - 1 <= kt_last) load_kv(kt + STAGES - 1, (it + STAGES - 1) % STAGES);
+      cp_async_commit();
+    }
+    if (!TMA && !active) continue;    // a warp whose 16 M rows lie past the tile's queries only helps with the loads
     if (kt == kt_first) {
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
@@ -183,7 +277,7 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
       for (int n = 0; n < NS; n += 2) {
         uint32_t b0, b1, b2, b3;
         const int row = (n_base + n + (lane >> 4)) * 8 + (lane & 7), c = kk * 2 + ((lane >> 3) & 1);
-        ldmatrix_x4(smem_addr(ks + swz<D>(row, c)), b0, b1, b2, b3);
+        ldmatrix_x4(smem_addr(ks + kv_off<D, TMA>(row, c)), b0, b1, b2, b3);
         mma_bf16(s[n], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b0, b1);
         mma_bf16(s[n + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], b2, b3);
       }
@@ -254,10 +348,14 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
       for (int n = 0; n < D / 8; n += 2) {
         uint32_t b0, b1, b2, b3;
         const int row = (n_base / 2 + j) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = n + (lane >> 4);
-        ldmatrix_x4_trans(smem_addr(vs + swz<D>(row, c)), b0, b1, b2, b3);
+        ldmatrix_x4_trans(smem_addr(vs + kv_off<D, TMA>(row, c)), b0, b1, b2, b3);
         mma_bf16(o[n], pf[j][0], pf[j][1], pf[j][2], pf[j][3], b0, b1);
         mma_bf16(o[n + 1], pf[j][0], pf[j][1], pf[j][2], pf[j][3], b2, b3);
       }
+    }
+    if constexpr (TMA) {
+      __syncwarp();                                  // every lane has read the stage
+      if (lane == 0) mbar_arrive(&empty[stage]);
     }
   }
   cp_async_wait<0>();
@@ -308,7 +406,7 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
     float* mml = mo + 4 * 16 * D;                          // [4][16][2]
     __syncthreads();                                       // every warp is done with the key/value stages
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < 2 && consumer; ++half) {
       const int r = (lane >> 2) + half * 8;
       float* dst = mo + (warp * 16 + r) * D + (lane & 3) * 2;
 #pragma unroll
@@ -322,7 +420,7 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
       }
     }
     __syncthreads();
-    for (int i = tid; i < 16 * (D / 2); i += 128) {
+    for (int i = tid; i < 16 * (D / 2) && consumer; i += 128) {
       const int r = i / (D / 2), col = (i % (D / 2)) * 2;
       if (r >= nq * G) continue;
       float mrow = -INFINITY;
@@ -342,16 +440,17 @@ __global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_mma_kernel(
   }
 }
 
-template <int D, bool KEYSPLIT, int STAGES>
+template <int D, bool KEYSPLIT, int STAGES, bool TMA>
 static int launch_mma(const void* q, const void* k_cache, const void* v_cache, const int* block_table, int max_pages,
                       int page_size, int num_pages, const int* tiles, int n_tiles, const int* positions, float scale, int window,
                       void* out, float* part_o, float* part_ml, int n_spans, int split, int Hq, int Hk, int* status,
                       cudaStream_t stream) {
-  constexpr int SMEM = ((KEYSPLIT ? 16 : 64) + 2 * STAGES * 64) * D * 2;
+  // with TMA: room to start the tiles on a 1024-byte boundary, and the stages' mbarriers behind them
+  constexpr int SMEM = ((KEYSPLIT ? 16 : 64) + 2 * STAGES * 64) * D * 2 + (TMA ? 1024 + 2 * STAGES * 8 : 0);
   static_assert(!KEYSPLIT || 4 * 16 * (D + 2) * 4 <= 2 * STAGES * 64 * D * 2, "the merge buffer reuses the stages");
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D, KEYSPLIT, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<D, KEYSPLIT, STAGES, TMA>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return (int)e;
     set = true;
@@ -359,10 +458,25 @@ static int launch_mma(const void* q, const void* k_cache, const void* v_cache, c
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size;) ++page_shift;
+  KvMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  const int box_rows = page_size < KT ? page_size : KT;
+  if (TMA) {
+    const long long cache_rows = (long long)num_pages * Hk * page_size;
+    int e = tensor_map(k_cache, cache_rows, D, D, box_rows, &maps.k);
+    if (e == 0) e = tensor_map(v_cache, cache_rows, D, D, box_rows, &maps.v);
+    if (e != 0) return e;
+  }
   dim3 grid(n_tiles, Hk, split ? n_spans : 1);
-  return (int)launch_chained(attention_mma_kernel<D, KEYSPLIT, STAGES>, grid, dim3(128), SMEM, stream, (const bf16*)q,
-                             (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size, page_shift,
-                             num_pages, tiles, positions, scale, window, (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status);
+  return (int)launch_chained(attention_mma_kernel<D, KEYSPLIT, STAGES, TMA>, grid, dim3(TMA ? 160 : 128), SMEM, stream,
+                             (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, page_size,
+                             page_shift, num_pages, tiles, positions, scale, window, (bf16*)out, part_o, part_ml, n_spans, split,
+                             Hq, Hk, status, maps, box_rows);
+}
+
+static int& decode_with_tma() {
+  static int on = 1;
+  return on;
 }
 
 }  // namespace tl
@@ -399,10 +513,18 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_cache, const 
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (long long)rows * Hq * n_spans * D : nullptr;
   const bool keysplit = max_tile_rows * (Hq / Hk) <= 16;
-#define TL_MMA(D_, KS_, ST_)                                                                                               \
-  launch_mma<D_, KS_, ST_>(q, k_cache, v_cache, block_table, max_pages, page_size, num_pages, tiles, n_tiles, positions, scale, window, \
-                           out, part_o, part_ml, n_spans, split, Hq, Hk, status, stream)
-  if (D == 64) return keysplit ? TL_MMA(64, true, 4) : TL_MMA(64, false, 2);
-  return keysplit ? TL_MMA(128, true, 3) : TL_MMA(128, false, 2);
+  // the producer warp's copies are whole pages (or 64-row pieces of one) that tile the 64 keys of a stage, every box on
+  // a 1024-byte boundary of shared memory; the caches start on 16-byte boundaries and hold at most 2^31 rows
+  const bool tma = keysplit && decode_with_tma() && ((page_size % 8 == 0 && KT % page_size == 0) || page_size % KT == 0) &&
+                   ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 &&
+                   (long long)num_pages * Hk * page_size < (1LL << 31);
+#define TL_MMA(D_, KS_, ST_, TMA_)                                                                                          \
+  launch_mma<D_, KS_, ST_, TMA_>(q, k_cache, v_cache, block_table, max_pages, page_size, num_pages, tiles, n_tiles, positions, \
+                                 scale, window, out, part_o, part_ml, n_spans, split, Hq, Hk, status, stream)
+  if (D == 64) return keysplit ? (tma ? TL_MMA(64, true, 4, true) : TL_MMA(64, true, 4, false)) : TL_MMA(64, false, 2, false);
+  return keysplit ? (tma ? TL_MMA(128, true, 3, true) : TL_MMA(128, true, 3, false)) : TL_MMA(128, false, 2, false);
 #undef TL_MMA
 }
+
+// 0: the decoding form fetches keys and values with cp.async from every thread instead of a producer warp's TMA copies
+extern "C" void tl_attention_mma_use_tma(int on) { decode_with_tma() = on; }

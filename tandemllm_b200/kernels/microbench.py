@@ -110,6 +110,8 @@ def attention(a) -> dict:
     cache = types.SimpleNamespace(k=kc, v=vc, page_size=page)
     out = torch.empty(R, Hq, D, dtype=torch.bfloat16, device=DEV)
     if a.kernel == "mma":
+        from . import tensorcore
+        tensorcore.lib().tl_attention_mma_use_tma(int(a.copies == "tma"))
         fn = lambda: rt.tensorcore.attention(q, cache, table, step, D ** -0.5, None, out, rt)
     else:
         spans = ops.attention_spans(L)
@@ -158,6 +160,8 @@ def main(argv=None) -> int:
     t.add_argument("--kv-heads", type=int, default=8)
     t.add_argument("--head-dim", type=int, default=64)
     t.add_argument("--kernel", default="mma", choices=("mma", "split"))
+    t.add_argument("--copies", default="tma", choices=("tma", "cp.async"),
+                   help="decoding with the mma kernel: a producer warp's TMA copies, or cp.async from every thread")
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)
     n.add_argument("--hidden", type=int, default=2048)

@@ -58,6 +58,8 @@ def lib():
                                              c_void_p, ctypes.c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                              c_int, c_void_p, c_void_p]
         l.tl_paged_attention_mma.restype = c_int
+        l.tl_attention_mma_use_tma.argtypes = [c_int]
+        l.tl_attention_mma_use_tma.restype = None
         l.tl_attention_mma_tile_rows.argtypes = [c_int, c_int]
         l.tl_attention_mma_tile_rows.restype = c_int
         l.tl_attention_mma_supported.argtypes = [c_int, c_int, c_int]
