@@ -20,69 +20,151 @@ namespace tl {
 
 constexpr int MAX_HEAD_DIM = 256;
 
-// grid (rows, ceil((Hq + 2 Hk) / 4)), 128 threads: one warp per (row, head of the fused qkv row).
-template <typename T>
+// grid (rows, groups of heads), 128 threads: a block takes `heads_per_block` consecutive heads of one fused qkv row (all of
+// them when they fit QK_GROUP_FLOATS), brings them into shared memory with 16-byte loads that are all in flight at once,
+// and its warps then take a head each in turn. The row's rotation angles are computed once a block.
+constexpr int QK_GROUP_FLOATS = 8192;
+
+// DS: the head size when it is 64 or 128 and the whole head is rotated (a lane then owns DS / 64 pairs (f, f + DS / 2), its
+// weights and its angles for all heads, and the loops unroll), else 0 (any size, any rotary part).
+template <typename T, int DS>
 __global__ void __launch_bounds__(128) qk_prepare_kernel(
     const T* __restrict__ qkv, long long ld_qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
     float eps, const float* __restrict__ inv_freq, int rotary_dim, const int* __restrict__ positions,
     const int* __restrict__ req_of_row, const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, T* __restrict__ k_out,
-    T* __restrict__ v_out, int Hq, int Hk, int D, int* __restrict__ status) {
-  __shared__ float vec[4][MAX_HEAD_DIM];
+    T* __restrict__ v_out, int Hq, int Hk, int D, int heads_per_block, int* __restrict__ status) {
+  __shared__ __align__(16) float vec[QK_GROUP_FLOATS];
+  __shared__ float s_sin[MAX_HEAD_DIM / 2], s_cos[MAX_HEAD_DIM / 2];
   chain_next();
   chain_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x;
-  const int head = blockIdx.y * 4 + warp;
-  if (head >= Hq + 2 * Hk) return;
-  const T* src = qkv + (long long)r * ld_qkv + (long long)head * D;
-  float* x = vec[warp];
-  float ss = 0.f;
-  for (int i = lane; i < D; i += 32) {
-    const float v = to_f32(src[i]);
-    x[i] = v;
-    ss += v * v;
-  }
-  ss = warp_sum(ss);
-  __syncwarp();
-  const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hk;
-  const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hk);
+  const int head0 = blockIdx.y * heads_per_block;
+  const int n_heads = min(heads_per_block, Hq + 2 * Hk - head0);
   const int pos = positions[r];
-
-  T* dst;
-  if (is_q) {
-    dst = q_out + ((long long)r * Hq + head) * D;
-  } else if (k_cache) {
+  // sincosf of a large argument is a hundred instructions, and the angles are the same for all heads of the row
+  if (inv_freq && (int)threadIdx.x < rotary_dim / 2)
+    sincosf((float)pos * inv_freq[threadIdx.x], &s_sin[threadIdx.x], &s_cos[threadIdx.x]);
+  const T* src = qkv + (long long)r * ld_qkv + (long long)head0 * D;
+  const int n = n_heads * D;
+  constexpr int V = 16 / (int)sizeof(T);
+  if (((uintptr_t)src % 16) == 0 && n % V == 0) {
+    for (int i = threadIdx.x; i < n / V; i += 128) {
+      const uint4 raw = reinterpret_cast<const uint4*>(src)[i];
+      const T* e = reinterpret_cast<const T*>(&raw);
+      float f[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) f[j] = to_f32(e[j]);
+#pragma unroll
+      for (int j = 0; j < V; j += 4)
+        *reinterpret_cast<float4*>(vec + i * V + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += 128) vec[i] = to_f32(src[i]);
+  }
+  __syncthreads();
+  // where this row's key and value go
+  long long kv_at = -1;
+  if (k_cache) {
     const int b = req_of_row[r];
     const int page = table_page(block_table + (long long)b * max_pages, pos / page_size, max_pages, num_pages);
-    if (page < 0) {   // no page behind this position (or an entry outside the pool): record it and drop the write
-      if (lane == 0) atomicExch(status, 2);
-      return;
-    }
-    T* base = is_k ? k_cache : v_cache;
-    dst = base + (((long long)page * Hk + kvh) * page_size + pos % page_size) * D;
-  } else {
-    dst = (is_k ? k_out : v_out) + ((long long)r * Hk + kvh) * D;
+    if (page >= 0) kv_at = ((long long)page * Hk) * page_size + pos % page_size;
   }
-
-  if (is_q || is_k) {
-    const float* w = is_q ? q_weight : k_weight;
-    const float inv = w ? rsqrtf(ss / (float)D + eps) : 1.f;
-    const int half = rotary_dim / 2;
-    for (int i = lane; i < D; i += 32) {
-      float v = x[i] * inv * (w ? w[i] : 1.f);
-      if (inv_freq && i < rotary_dim) {
-        const int f = i < half ? i : i - half;
-        const int j = i < half ? i + half : i - half;
-        const float other = x[j] * inv * (w ? w[j] : 1.f);
-        float s, c;
-        sincosf((float)pos * inv_freq[f], &s, &c);
-        v = i < half ? v * c - other * s : v * c + other * s;
-      }
-      dst[i] = from_f32<T>(v);
+  if constexpr (DS > 0) {
+    constexpr int PAIRS = DS / 64, HALF = DS / 2;
+    float wq[2 * PAIRS], wk[2 * PAIRS], sn[PAIRS], cs[PAIRS];
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) {
+      const int f = lane + 32 * p;
+      wq[2 * p] = q_weight ? q_weight[f] : 1.f;
+      wq[2 * p + 1] = q_weight ? q_weight[f + HALF] : 1.f;
+      wk[2 * p] = k_weight ? k_weight[f] : 1.f;
+      wk[2 * p + 1] = k_weight ? k_weight[f + HALF] : 1.f;
+      sn[p] = inv_freq ? s_sin[f] : 0.f;
+      cs[p] = inv_freq ? s_cos[f] : 1.f;
     }
-  } else {
-    for (int i = lane; i < D; i += 32) dst[i] = from_f32<T>(x[i]);
+    for (int h = warp; h < n_heads; h += 4) {
+      const int head = head0 + h;
+      const float* x = vec + h * DS;
+      float a[PAIRS], b2[PAIRS], ss = 0.f;
+      // (the sum of squares in the order of the general form: elements lane, lane + 32, ...)
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p) a[p] = x[lane + 32 * p];
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p) b2[p] = x[lane + 32 * p + HALF];
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p) ss += a[p] * a[p];
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p) ss += b2[p] * b2[p];
+      ss = warp_sum(ss);
+      const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hk;
+      const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hk);
+      T* dst;
+      if (is_q) {
+        dst = q_out + ((long long)r * Hq + head) * DS;
+      } else if (k_cache) {
+        if (kv_at < 0) {
+          if (lane == 0) atomicExch(status, 2);
+          continue;
+        }
+        dst = (is_k ? k_cache : v_cache) + (kv_at + (long long)kvh * page_size) * DS;
+      } else {
+        dst = (is_k ? k_out : v_out) + ((long long)r * Hk + kvh) * DS;
+      }
+      if (is_q || is_k) {
+        const float inv = (is_q ? q_weight : k_weight) ? rsqrtf(ss / (float)DS + eps) : 1.f;
+#pragma unroll
+        for (int p = 0; p < PAIRS; ++p) {
+          const int f = lane + 32 * p;
+          const float u = a[p] * inv * (is_q ? wq[2 * p] : wk[2 * p]), v = b2[p] * inv * (is_q ? wq[2 * p + 1] : wk[2 * p + 1]);
+          dst[f] = from_f32<T>(u * cs[p] - v * sn[p]);
+          dst[f + HALF] = from_f32<T>(v * cs[p] + u * sn[p]);
+        }
+      } else {
+#pragma unroll
+        for (int p = 0; p < PAIRS; ++p) {
+          dst[lane + 32 * p] = from_f32<T>(a[p]);
+          dst[lane + 32 * p + HALF] = from_f32<T>(b2[p]);
+        }
+      }
+    }
+    return;
+  }
+  for (int h = warp; h < n_heads; h += 4) {
+    const int head = head0 + h;
+    const float* x = vec + h * D;
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) ss += x[i] * x[i];
+    ss = warp_sum(ss);
+    const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hk;
+    const int kvh = is_q ? 0 : (is_k ? head - Hq : head - Hq - Hk);
+    T* dst;
+    if (is_q) {
+      dst = q_out + ((long long)r * Hq + head) * D;
+    } else if (k_cache) {
+      if (kv_at < 0) {   // no page behind this position (or an entry outside the pool): record it and drop the write
+        if (lane == 0) atomicExch(status, 2);
+        continue;
+      }
+      dst = (is_k ? k_cache : v_cache) + (kv_at + (long long)kvh * page_size) * D;
+    } else {
+      dst = (is_k ? k_out : v_out) + ((long long)r * Hk + kvh) * D;
+    }
+    if (is_q || is_k) {
+      const float* w = is_q ? q_weight : k_weight;
+      const float inv = w ? rsqrtf(ss / (float)D + eps) : 1.f;
+      const int half = inv_freq ? rotary_dim / 2 : 0;
+      for (int f = lane; f < half; f += 32) {          // a lane rotates the pair (f, f + half)
+        const float a = x[f] * inv * (w ? w[f] : 1.f), b2 = x[f + half] * inv * (w ? w[f + half] : 1.f);
+        const float sn = s_sin[f], c = s_cos[f];
+        dst[f] = from_f32<T>(a * c - b2 * sn);
+        dst[f + half] = from_f32<T>(b2 * c + a * sn);
+      }
+      for (int i = 2 * half + lane; i < D; i += 32) dst[i] = from_f32<T>(x[i] * inv * (w ? w[i] : 1.f));
+    } else {
+      for (int i = lane; i < D; i += 32) dst[i] = from_f32<T>(x[i]);
+    }
   }
 }
 
@@ -202,17 +284,26 @@ extern "C" int tl_qk_prepare(const void* qkv, long long ld_qkv, const float* q_w
              "qk_prepare: rotary size %d for head size %d", rotary_dim, D);
   TL_REQUIRE((k_cache && v_cache && page_size > 0 && max_pages > 0) || (k_out && v_out),
              "qk_prepare: neither cache pages nor plain outputs for k and v");
-  dim3 grid(rows, ceil_div(Hq + 2 * Hk, 4));
+  const int heads_per_block = max(1, min(Hq + 2 * Hk, QK_GROUP_FLOATS / D));
+  dim3 grid(rows, ceil_div(Hq + 2 * Hk, heads_per_block));
   TL_REQUIRE(grid.y <= 65535, "qk_prepare: %d heads exceed the grid limit", Hq + 2 * Hk);
+  // the unrolled form: the whole head is rotated (or nothing is) and a lane's pairs are (f, f + D / 2)
+  const int ds = (!inv_freq || rotary_dim == D) && (D == 64 || D == 128) ? D : 0;
   cudaError_t e;
-  if (dtype == TL_FP32)
-    e = launch_chained(qk_prepare_kernel<float>, grid, dim3(128), 0, stream, (const float*)qkv, ld_qkv, q_weight, k_weight, eps,
-                       inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, num_pages, (float*)q_out,
-                       (float*)k_cache, (float*)v_cache, (float*)k_out, (float*)v_out, Hq, Hk, D, status);
-  else
-    e = launch_chained(qk_prepare_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)qkv, ld_qkv, q_weight, k_weight, eps,
-                       inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, num_pages, (bf16*)q_out,
-                       (bf16*)k_cache, (bf16*)v_cache, (bf16*)k_out, (bf16*)v_out, Hq, Hk, D, status);
+#define TL_QK(T_, DS_)                                                                                                     \
+  e = launch_chained(qk_prepare_kernel<T_, DS_>, grid, dim3(128), 0, stream, (const T_*)qkv, ld_qkv, q_weight, k_weight, eps, \
+                     inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, num_pages, (T_*)q_out,  \
+                     (T_*)k_cache, (T_*)v_cache, (T_*)k_out, (T_*)v_out, Hq, Hk, D, heads_per_block, status)
+  if (dtype == TL_FP32) {
+    if (ds == 64) TL_QK(float, 64);
+    else if (ds == 128) TL_QK(float, 128);
+    else TL_QK(float, 0);
+  } else {
+    if (ds == 64) TL_QK(bf16, 64);
+    else if (ds == 128) TL_QK(bf16, 128);
+    else TL_QK(bf16, 0);
+  }
+#undef TL_QK
   return (int)e;
 }
 
