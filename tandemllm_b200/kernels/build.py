@@ -37,7 +37,7 @@ LIBRARIES: dict[str, list[str]] = {
     # the tcgen05 / TMA kernels of the bfloat16 path; a 32-bit run never builds or loads them
     "tensorcore": ["tc_gemm.cu", "attention_mma.cu", "gemm_skinny_mma.cu"],
 }
-HEADERS = ["common.cuh", "route.cuh", "attention_noalloc.h"]
+HEADERS = ["common.cuh", "route.cuh", "attention_noalloc.h", "tma.cuh"]
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
