@@ -28,6 +28,7 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
 
 constexpr int PLAN_CHUNK = 256;      // pairs a block of the two-kernel plan takes
 constexpr int PLAN_WARPS = PLAN_CHUNK / 32;
+constexpr int SELF_COUNT_PAIRS = 16384;   // up to here the placing kernel needs no histogram kernel in front
 
 // grid ceil(P / PLAN_CHUNK): block b counts its chunk's pairs per expert into block_hist[b, :]
 __global__ void __launch_bounds__(PLAN_CHUNK) moe_hist_kernel(const int* __restrict__ ids, int P, int E,
@@ -62,16 +63,39 @@ __global__ void __launch_bounds__(PLAN_CHUNK) moe_place_kernel(const int* __rest
   chain_next();
   chain_wait();
   const int b = blockIdx.x, nb = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int i = tid; i < PLAN_WARPS * MAX_EXPERTS; i += PLAN_CHUNK) (&in_warp[0][0])[i] = 0;
-  for (int e = tid; e < E; e += PLAN_CHUNK) {
-    int all = 0, before = 0;
-    for (int i = 0; i < nb; ++i) {
-      const int v = block_hist[(long long)i * E + e];
-      all += v;
-      if (i < b) before += v;
+  for (int w = 0; w < PLAN_WARPS; ++w)
+    for (int e = tid; e < E; e += PLAN_CHUNK) in_warp[w][e] = 0;
+  if (block_hist) {
+    for (int e = tid; e < E; e += PLAN_CHUNK) {
+      int all = 0, before = 0;
+      for (int i = 0; i < nb; ++i) {
+        const int v = block_hist[(long long)i * E + e];
+        all += v;
+        if (i < b) before += v;
+      }
+      total[e] = all;
+      base[e] = before;
     }
-    total[e] = all;
-    base[e] = before;
+  } else {
+    // No histograms from a kernel in front (a moderate number of pairs): the block counts all pairs itself, those of the
+    // chunks before its own into base, the others into total.
+    for (int e = tid; e < E; e += PLAN_CHUNK) total[e] = base[e] = 0;
+    __syncthreads();
+    const int mine = b * PLAN_CHUNK;
+    constexpr int BATCH = 16;                       // loads of a thread that are sent before the first is counted
+    for (int i0 = 0; i0 < P; i0 += BATCH * PLAN_CHUNK) {
+      int v[BATCH];
+#pragma unroll
+      for (int j = 0; j < BATCH; ++j) {
+        const int i = i0 + j * PLAN_CHUNK + tid;
+        v[j] = i < P ? ids[i] : -1;
+      }
+#pragma unroll
+      for (int j = 0; j < BATCH; ++j)
+        if ((unsigned)v[j] < (unsigned)E) atomicAdd(i0 + j * PLAN_CHUNK < mine ? &base[v[j]] : &total[v[j]], 1);
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += PLAN_CHUNK) total[e] += base[e];
   }
   __syncthreads();
   const int p = b * PLAN_CHUNK + tid;
@@ -99,6 +123,16 @@ __global__ void __launch_bounds__(PLAN_CHUNK) moe_place_kernel(const int* __rest
       counts[x] = total[x];
       offsets[x] = lower;
       if (x == E - 1) offsets[E] = lower + total[x];
+      // the expert's row tiles come behind those of the experts before it
+      int tiles = 0;
+      for (int i = 0; i < x; ++i) tiles += (total[i] + tile_m - 1) / tile_m;
+      const int cnt = total[x];
+      for (int t = 0; t * tile_m < cnt; ++t, ++tiles) {
+        tile_group[tiles] = x;
+        tile_row0[tiles] = lower + t * tile_m;
+        tile_rows[tiles] = min(tile_m, cnt - t * tile_m);
+      }
+      if (x == E - 1) *n_tiles = tiles;
     }
   }
   __syncthreads();
@@ -106,20 +140,6 @@ __global__ void __launch_bounds__(PLAN_CHUNK) moe_place_kernel(const int* __rest
     const int at = base[e] + in_warp[warp][e] + __popc(same & ((1u << lane) - 1u));
     sorted_pairs[at] = p;
     pos_of_pair[p] = at;
-  }
-  if (b == 0 && tid == 0) {
-    int off = 0, tiles = 0;
-    for (int x = 0; x < E; ++x) {
-      const int cnt = total[x];
-      for (int t = 0; t * tile_m < cnt; ++t) {
-        tile_group[tiles] = x;
-        tile_row0[tiles] = off + t * tile_m;
-        tile_rows[tiles] = min(tile_m, cnt - t * tile_m);
-        ++tiles;
-      }
-      off += cnt;
-    }
-    *n_tiles = tiles;
   }
 }
 
@@ -238,6 +258,9 @@ extern "C" int tl_moe_max_tiles(int pairs, int E, int tile_m) {
 
 // Builds the plan of `pairs` (row, slot) pairs. With `x` (bfloat16 rows [pairs / top_k, width], stride ldx) it also
 // writes x_sorted[i] = x[sorted_pairs[i] / top_k]. Returns the number of kernels it launched through *launched.
+// 1 when tl_moe_plan runs its one-kernel form for these sizes, the form that also copies the token rows it is given
+extern "C" int tl_moe_plan_copies_rows(int pairs, int E) { return pairs > 0 && pairs <= SMALL_PLAN_PAIRS && E <= MAX_EXPERTS; }
+
 extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int top_k, int* counts, int* offsets,
                            int* sorted_pairs, int* pos_of_pair, int* tile_group, int* tile_row0, int* tile_rows,
                            int* n_tiles, int* block_hist, const void* x, long long ldx, void* x_sorted, int width,
@@ -257,13 +280,17 @@ extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int top
   }
   TL_REQUIRE(E <= MAX_EXPERTS && block_hist, "moe plan: %d experts; up to %d are implemented", E, MAX_EXPERTS);
   const int chunks = ceil_div(pairs, PLAN_CHUNK);
-  cudaError_t e = launch_chained(moe_hist_kernel, dim3(chunks), dim3(PLAN_CHUNK), 0, stream, ids, pairs, E, block_hist);
+  // up to SELF_COUNT_PAIRS every placing block counts all pairs itself (64 passes of its 256 threads at most): one kernel
+  const bool self_count = pairs <= SELF_COUNT_PAIRS;
+  cudaError_t e = cudaSuccess;
+  if (!self_count)
+    e = launch_chained(moe_hist_kernel, dim3(chunks), dim3(PLAN_CHUNK), 0, stream, ids, pairs, E, block_hist);
   if (e != cudaSuccess) return (int)e;
   e = launch_chained(moe_place_kernel, dim3(chunks), dim3(PLAN_CHUNK), 0, stream, ids, pairs, E, tile_m,
-                     (const int*)block_hist, counts, offsets, sorted_pairs, pos_of_pair, tile_group, tile_row0, tile_rows,
-                     n_tiles);
+                     self_count ? (const int*)nullptr : (const int*)block_hist, counts, offsets, sorted_pairs, pos_of_pair,
+                     tile_group, tile_row0, tile_rows, n_tiles);
   if (e != cudaSuccess) return (int)e;
-  if (launched) *launched = 2;
+  if (launched) *launched = self_count ? 1 : 2;
   return 0;
 }
 

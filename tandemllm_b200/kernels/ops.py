@@ -62,6 +62,7 @@ _SIGNATURES = {
     "tl_router_topk": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p,
                        c_void_p],
     "tl_moe_max_tiles": [c_int, c_int, c_int],
+    "tl_moe_plan_copies_rows": [c_int, c_int],
     "tl_moe_plan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                     c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -397,7 +398,7 @@ class MoePlan:
                                  ctypes.addressof(launched), stream()), "moe_plan", kernels=0)
         global launches
         launches += launched.value
-        self.copied = x is not None and launched.value == 1
+        self.copied = x is not None and bool(core().tl_moe_plan_copies_rows(pairs, self.num_experts))
         return self
 
 

@@ -115,11 +115,12 @@ def test_add_rmsnorm_adds_deferred_branch_outputs_and_routes(dtype, R):
     close(out, n32, dtype, "normed rows beside the router")
 
 
-@pytest.mark.parametrize("P_rows,E,k", [(8, 32, 4), (64, 6, 3), (1500, 8, 4), (3000, 200, 3), (1025, 1000, 5)])
+@pytest.mark.parametrize("P_rows,E,k", [(8, 32, 4), (64, 6, 3), (1500, 8, 4), (3000, 200, 3), (1025, 1000, 5), (4096, 32, 4),
+                                        (6000, 8, 3), (4500, 64, 4)])
 def test_plan_forms_agree_and_copy_rows(P_rows, E, k):
-    """The one-kernel plan (a decode step) and the chunked plan (many pairs: pairs of one expert spread over
-    several chunks and warps) are the same stable sort; the one-kernel form also copies the token rows into
-    expert-sorted order."""
+    """The one-kernel plan (a decode step), the chunked plan whose blocks count all pairs themselves (up to 16384 pairs)
+    and the chunked plan behind a histogram kernel (more; pairs of one expert spread over many chunks and warps) are
+    the same stable sort; the one-kernel form also copies the token rows into expert-sorted order."""
     o = ops()
     g = torch.Generator().manual_seed(9)
     ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(P_rows)]).int().to(DEV)
@@ -135,6 +136,10 @@ def test_plan_forms_agree_and_copy_rows(P_rows, E, k):
     nt = int(plan.n_tiles)
     assert nt == sum(-(-int(c) // 16) for c in plan.counts.cpu())
     assert sum(int(r) for r in plan.tile_rows[:nt].cpu()) == P_rows * k
+    want_tiles = [(e, int(plan.offsets[e]) + t, min(16, int(c) - t)) for e, c in enumerate(plan.counts.cpu().tolist())
+                  for t in range(0, int(c), 16)]
+    assert list(zip(plan.tile_group[:nt].cpu().tolist(), plan.tile_row0[:nt].cpu().tolist(),
+                    plan.tile_rows[:nt].cpu().tolist())) == want_tiles
     groups, row0 = plan.tile_group[:nt].cpu().tolist(), plan.tile_row0[:nt].cpu().tolist()
     assert groups == sorted(groups) and all(int(plan.offsets[g]) <= r < int(plan.offsets[g + 1]) for g, r in zip(groups, row0))
     assert plan.copied == (P_rows * k <= 4096)
