@@ -100,6 +100,131 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __rest
   store_run<T, V>(y + (long long)r * hidden + c, cv);
 }
 
+// The same for a prompt's many rows: a thread walks CONV_RUN consecutive rows for its 8 channels with the last KT - 1
+// inputs bx in registers, so every B, C and x is read once, and the loads of four rows are sent before the first is
+// used. Rows of a run that belong to several requests (a run across a request's edge) go the way of the kernel above,
+// row by row. Same results: a tap whose input lies before the sequence's first token multiplies a zero here and is
+// left out there.
+constexpr int CONV_RUN = 8;
+template <typename T, int KT>
+__global__ void __launch_bounds__(128) short_conv_run_kernel(const T* __restrict__ bcx, const float* __restrict__ taps,
+                                                             const float* __restrict__ bias, const float* __restrict__ state,
+                                                             const int* __restrict__ state_slot,
+                                                             const int* __restrict__ req_of_row,
+                                                             const int* __restrict__ row_start,
+                                                             const int* __restrict__ positions, T* __restrict__ y, int rows,
+                                                             int hidden) {
+  constexpr int V = 8, S = KT - 1;
+  chain_next();
+  chain_wait();
+  const int r0 = blockIdx.x * CONV_RUN;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  if (c >= hidden) return;
+  const int n = min(CONV_RUN, rows - r0);
+  const long long ld = 3LL * hidden;
+  float tp[KT][V], bs[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    bs[i] = bias ? bias[c + i] : 0.f;
+#pragma unroll
+    for (int j = 0; j < KT; ++j) tp[j][i] = taps[(long long)(c + i) * KT + j];
+  }
+  const int b = req_of_row[r0];
+  if (req_of_row[r0 + n - 1] != b) {
+    // several requests in the run: every row looks its inputs up by itself
+    for (int r = r0; r < r0 + n; ++r) {
+      const int rb = req_of_row[r], first = row_start[rb], pos = positions[r];
+      const float* st = state + ((long long)state_slot[rb] * S) * hidden;
+      float acc[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = bs[i];
+#pragma unroll
+      for (int j = 0; j < KT; ++j) {
+        const int back = KT - 1 - j;
+        if (pos - back < 0) continue;
+        const int rr = r - back;
+        float v[V];
+        if (rr >= first) {
+          float bv[V], xv[V];
+          load_run<T, V>(bcx + (long long)rr * ld + c, bv);
+          load_run<T, V>(bcx + (long long)rr * ld + 2 * hidden + c, xv);
+#pragma unroll
+          for (int i = 0; i < V; ++i) v[i] = bv[i] * xv[i];
+        } else {
+          load_run<float, V>(st + (long long)(KT - 1 - (first - rr)) * hidden + c, v);
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(tp[j][i], v[i], acc[i]);
+      }
+      float cv[V];
+      load_run<T, V>(bcx + (long long)r * ld + hidden + c, cv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) cv[i] *= acc[i];
+      store_run<T, V>(y + (long long)r * hidden + c, cv);
+    }
+    return;
+  }
+  // one request: the window starts with the S inputs before row r0 (earlier rows of the step, the state, or zeros)
+  const int first = row_start[b], pos0 = positions[r0];
+  const float* st = state + ((long long)state_slot[b] * S) * hidden;
+  float win[S][V];                                  // win[s]: the input S - s rows back
+#pragma unroll
+  for (int s2 = 0; s2 < S; ++s2) {
+    const int back = S - s2, rr = r0 - back;
+#pragma unroll
+    for (int i = 0; i < V; ++i) win[s2][i] = 0.f;
+    if (pos0 - back >= 0) {
+      if (rr >= first) {
+        float bv[V], xv[V];
+        load_run<T, V>(bcx + (long long)rr * ld + c, bv);
+        load_run<T, V>(bcx + (long long)rr * ld + 2 * hidden + c, xv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) win[s2][i] = bv[i] * xv[i];
+      } else {
+        load_run<float, V>(st + (long long)(KT - 1 - (first - rr)) * hidden + c, win[s2]);
+      }
+    }
+  }
+  constexpr int AHEAD = 4;
+  for (int q0 = 0; q0 < n; q0 += AHEAD) {
+    float bv[AHEAD][V], cv[AHEAD][V], xv[AHEAD][V];
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+      const int r = min(r0 + q0 + a, r0 + n - 1);     // (past the run's end: the last row again, not stored)
+      const T* row = bcx + (long long)r * ld + c;
+      load_run<T, V>(row, bv[a]);
+      load_run<T, V>(row + hidden, cv[a]);
+      load_run<T, V>(row + 2 * hidden, xv[a]);
+    }
+#pragma unroll
+    for (int a = 0; a < AHEAD; ++a) {
+      if (q0 + a >= n) break;
+      float bx[V], acc[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        bx[i] = bv[a][i] * xv[a][i];
+        acc[i] = bs[i];
+      }
+#pragma unroll
+      for (int j = 0; j < S; ++j)
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fmaf(tp[j][i], win[j][i], acc[i]);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        acc[i] = fmaf(tp[S][i], bx[i], acc[i]);
+        cv[a][i] *= acc[i];
+      }
+      store_run<T, V>(y + (long long)(r0 + q0 + a) * hidden + c, cv[a]);
+#pragma unroll
+      for (int j = 0; j + 1 < S; ++j)
+#pragma unroll
+        for (int i = 0; i < V; ++i) win[j][i] = win[j + 1][i];
+#pragma unroll
+      for (int i = 0; i < V; ++i) win[S - 1][i] = bx[i];
+    }
+  }
+}
+
 // new state = last K-1 of [old state ; this step's bx rows], per request and channel; one thread does both
 // the reads and the writes of its channel, so no other thread's input is overwritten early.
 template <typename T>
@@ -204,6 +329,22 @@ extern "C" int tl_short_conv(const void* bcx, const float* taps, const float* bi
   const bool wide = hidden % 8 == 0 && ((uintptr_t)bcx % 16) == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)state % 16) == 0;
   dim3 grid(rows, ceil_div(hidden, 128 * (wide ? 8 : 1)));
   TL_REQUIRE(grid.y <= 65535, "short_conv: hidden size %d exceeds the grid limit", hidden);
+  // many rows, 16-byte accesses, 2 to 4 taps: the form that walks runs of rows
+  if (wide && rows >= 4 * CONV_RUN && K <= 4) {
+    dim3 run_grid(ceil_div(rows, CONV_RUN), grid.y);
+#define TL_RUN(T_, K_)                                                                                                     \
+  return (int)launch_chained(short_conv_run_kernel<T_, K_>, run_grid, dim3(128), 0, stream, (const T_*)bcx, taps, bias,   \
+                             state, state_slot, req_of_row, row_start, positions, (T_*)y, rows, hidden)
+    if (dtype == TL_FP32) {
+      if (K == 2) TL_RUN(float, 2);
+      if (K == 3) TL_RUN(float, 3);
+      TL_RUN(float, 4);
+    }
+    if (K == 2) TL_RUN(bf16, 2);
+    if (K == 3) TL_RUN(bf16, 3);
+    TL_RUN(bf16, 4);
+#undef TL_RUN
+  }
 #define TL_CONV(T_, V_)                                                                                                   \
   return (int)launch_chained(short_conv_kernel<T_, V_>, grid, dim3(128), 0, stream, (const T_*)bcx, taps, bias, state,    \
                              state_slot, req_of_row, row_start, positions, (T_*)y, hidden, K)

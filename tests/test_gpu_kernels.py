@@ -299,6 +299,44 @@ def test_short_conv_mixed_batch_and_state(dtype, K, H, use_bias):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("K,H,use_bias", [(3, 200, False), (4, 96, True), (2, 64, False), (7, 304, True), (3, 2048, False)])
+def test_short_conv_of_long_portions_walks_runs_of_rows(dtype, K, H, use_bias):
+    """Portions of many rows (the kernel form in which a thread walks eight consecutive rows with the last inputs in
+    registers): requests whose edges fall inside a run, a new sequence shorter than the taps, one that starts at
+    position 1, a single row between long portions, a last run that is not full; against the plain formula and, bit
+    for bit, against the row-by-row kernel (the same rows given in two calls too short for the run form)."""
+    o = ops()
+    lens, starts, slots = [37, 2, 64, 1, 30, 11], [0, 0, 5, 9, 1, 3], [2, 0, 3, 5, 1, 6]
+    R = sum(lens)
+    bcx = rnd(R, 3 * H, seed=20).to(dtype)
+    taps_w, bias = rnd(H, K, seed=21), (rnd(H, seed=22) if use_bias else None)
+    state = rnd(7, K - 1, H, seed=23)
+    row_start = [0]
+    for n in lens:
+        row_start.append(row_start[-1] + n)
+    req_of_row = sum(([b] * n for b, n in enumerate(lens)), [])
+    positions = sum((list(range(s0, s0 + n)) for s0, n in zip(starts, lens)), [])
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    dev = lambda t: None if t is None else t.to(DEV)
+    y = torch.full((R, H), float("nan"), dtype=dtype, device=DEV)
+    o.short_conv(dev(bcx), dev(taps_w), dev(bias), dev(state), i32(slots), i32(req_of_row), i32(row_start), i32(positions), y)
+    for b in range(len(lens)):
+        old = state[slots[b]].clone()
+        if starts[b] < K - 1:
+            old[:K - 1 - starts[b]] = 0
+        rows = slice(row_start[b], row_start[b + 1])
+        want_y, _ = plain_conv_with_state(bcx[rows].float(), taps_w, bias, old, K)
+        close(y[rows], want_y, dtype, f"request {b}")
+    # the same numbers as the row-by-row kernel: every request alone in a call of few rows, its state advanced by hand
+    for b in (1, 3, 5):
+        rows = slice(row_start[b], row_start[b + 1])
+        alone = torch.empty(lens[b], H, dtype=dtype, device=DEV)
+        o.short_conv(dev(bcx[rows]), dev(taps_w), dev(bias), dev(state), i32([slots[b]]), i32([0] * lens[b]), i32([0, lens[b]]),
+                     i32(positions[rows]), alone)
+        assert torch.equal(alone, y[rows]), b
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("K,H,use_bias", [(3, 200, False), (4, 96, True), (2, 64, False), (7, 300, True)])
 def test_short_conv_of_single_rows_in_one_kernel(dtype, K, H, use_bias):
     """A step of one row a request (decoding) runs one kernel for the convolution and the state's shift: the same
