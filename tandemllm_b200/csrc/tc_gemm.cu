@@ -576,12 +576,24 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TOut* __
 }
 
 // rows[i, :] = x[index[i] / div, :]   (the expert-sorted copy of the token rows)
-__global__ void gather_rows_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ index, int div,
-                                   bf16* __restrict__ out, int width) {
-  const int i = blockIdx.x;
+// A warp a row, eight rows a block; a lane's (up to eight) 16-byte pieces of a pass are all loaded before the first is stored.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const bf16* __restrict__ x, long long ldx,
+                                                          const int* __restrict__ index, int div, bf16* __restrict__ out,
+                                                          int width, int rows) {
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (i >= rows) return;
   const uint4* src = (const uint4*)(x + (long long)(index[i] / div) * ldx);
   uint4* dst = (uint4*)(out + (long long)i * width);
-  for (int c = threadIdx.x; c < width / 8; c += blockDim.x) dst[c] = src[c];
+  const int n = width / 8;
+  for (int c0 = lane; c0 < n; c0 += 8 * 32) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + 32 * j < n) v[j] = src[c0 + 32 * j];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (c0 + 32 * j < n) dst[c0 + 32 * j] = v[j];
+  }
 }
 
 // ------------------------------------------------------------------------------------------ host side
@@ -717,7 +729,7 @@ extern "C" int tl_gather_rows(const void* x, long long ldx, const int* index, in
                               cudaStream_t stream) {
   if (rows == 0) return 0;
   TL_REQUIRE(width % 8 == 0 && ldx % 8 == 0 && div >= 1, "gather_rows: width %d, stride %lld, div %d", width, ldx, div);
-  gather_rows_kernel<<<rows, 128, 0, stream>>>((const bf16*)x, ldx, index, div, (bf16*)out, width);
+  gather_rows_kernel<<<ceil_div(rows, 8), 256, 0, stream>>>((const bf16*)x, ldx, index, div, (bf16*)out, width, rows);
   TL_LAUNCH_CHECK();
   return 0;
 }
