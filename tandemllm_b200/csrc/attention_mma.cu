@@ -80,7 +80,6 @@ __global__ void __launch_bounds__(TMA ? 160 : 128, D == 64 ? (TMA ? 3 : 4) : 2) 
     const int* __restrict__ positions, float scale, int window, bf16* __restrict__ out, float* __restrict__ part_o,
     float* __restrict__ part_ml, int n_spans, int split, int Hq, int Hk, int* __restrict__ status,
     const __grid_constant__ KvMaps maps, int box_rows) {
-  static_assert(!TMA || KEYSPLIT, "the producer warp exists in the decoding form only");
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int TILE_BYTES = 64 * D * 2;
   constexpr int QROWS = KEYSPLIT ? 16 : 64;
@@ -257,7 +256,12 @@ __global__ void __launch_bounds__(TMA ? 160 : 128, D == 64 ? (TMA ? 3 : 4) : 2) 
       if (kt + STAGES - 1 <= kt_last) load_kv(kt + STAGES - 1, (it + STAGES - 1) % STAGES);
       cp_async_commit();
     }
-    if (!TMA && !active) continue;    // a warp whose 16 M rows lie past the tile's queries only helps with the loads
+    if (!active) {                    // a warp whose 16 M rows lie past the tile's queries only helps with the loads
+      if constexpr (TMA) {
+        if (lane == 0) mbar_arrive(&empty[stage]);
+      }
+      continue;
+    }
     if (kt == kt_first) {
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
@@ -393,7 +397,7 @@ __global__ void __launch_bounds__(TMA ? 160 : 128, D == 64 ? (TMA ? 3 : 4) : 2) 
   if constexpr (!KEYSPLIT) {
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      if (!(half ? v_hi : v_lo)) continue;
+      if (!consumer || !(half ? v_hi : v_lo)) continue;
       const int r = half ? r_hi : r_lo;
       const float l = half ? l_hi : l_lo, mrow = half ? m_hi : m_lo;
 #pragma unroll
@@ -515,14 +519,17 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_cache, const 
   const bool keysplit = max_tile_rows * (Hq / Hk) <= 16;
   // the producer warp's copies are whole pages (or 64-row pieces of one) that tile the 64 keys of a stage, every box on
   // a 1024-byte boundary of shared memory; the caches start on 16-byte boundaries and hold at most 2^31 rows
-  const bool tma = keysplit && decode_with_tma() && ((page_size % 8 == 0 && KT % page_size == 0) || page_size % KT == 0) &&
+  const bool tma = decode_with_tma() && ((page_size % 8 == 0 && KT % page_size == 0) || page_size % KT == 0) &&
                    ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 &&
                    (long long)num_pages * Hk * page_size < (1LL << 31);
 #define TL_MMA(D_, KS_, ST_, TMA_)                                                                                          \
   launch_mma<D_, KS_, ST_, TMA_>(q, k_cache, v_cache, block_table, max_pages, page_size, num_pages, tiles, n_tiles, positions, \
                                  scale, window, out, part_o, part_ml, n_spans, split, Hq, Hk, status, stream)
-  if (D == 64) return keysplit ? (tma ? TL_MMA(64, true, 4, true) : TL_MMA(64, true, 4, false)) : TL_MMA(64, false, 2, false);
-  return keysplit ? (tma ? TL_MMA(128, true, 3, true) : TL_MMA(128, true, 3, false)) : TL_MMA(128, false, 2, false);
+  if (D == 64)
+    return keysplit ? (tma ? TL_MMA(64, true, 4, true) : TL_MMA(64, true, 4, false))
+                    : (tma ? TL_MMA(64, false, 3, true) : TL_MMA(64, false, 2, false));
+  return keysplit ? (tma ? TL_MMA(128, true, 3, true) : TL_MMA(128, true, 3, false))
+                  : (tma ? TL_MMA(128, false, 2, true) : TL_MMA(128, false, 2, false));
 #undef TL_MMA
 }
 
