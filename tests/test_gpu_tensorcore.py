@@ -255,7 +255,8 @@ def test_experts_of_a_small_step_without_a_plan_at_every_count_of_pairs(R, E, k,
 @pytest.mark.parametrize("split", [0, 256, 512])
 @pytest.mark.parametrize("Hq,Hk,D,page,window", [(8, 2, 64, 16, None), (4, 4, 64, 16, None), (6, 2, 128, 32, None),
                                                  (8, 1, 64, 16, 100), (32, 8, 64, 16, None), (3, 1, 64, 64, None),
-                                                 (5, 1, 128, 16, 300)])
+                                                 (5, 1, 128, 16, 300), (8, 2, 64, 128, None), (4, 1, 128, 128, 200),
+                                                 (4, 2, 64, 48, None)])
 def test_attention_on_tensor_cores(split, Hq, Hk, D, page, window):
     """Prompt portions of several lengths, a sequence's first rows and decode rows at short and long contexts in
     one call, unsplit and split over key spans, against whole-sequence attention."""
@@ -267,7 +268,8 @@ def test_attention_on_tensor_cores(split, Hq, Hk, D, page, window):
     (8, 2, 64, 16, None, [1, 1, 1, 1, 1, 1, 1]), (32, 8, 64, 16, None, [1, 1, 1, 1, 1, 1, 1]),
     (16, 1, 64, 16, 100, [1, 1, 1, 1, 1, 1, 1]), (6, 2, 128, 32, None, [1, 1, 1, 1, 1, 1, 1]),
     (8, 2, 64, 24, 70, [4, 2, 3, 1, 4, 1, 2]), (3, 3, 128, 16, None, [16, 5, 7, 1, 9, 2, 16]),
-    (5, 1, 64, 64, 300, [3, 1, 2, 3, 1, 1, 3])])
+    (5, 1, 64, 64, 300, [3, 1, 2, 3, 1, 1, 3]), (8, 2, 64, 128, None, [1, 1, 1, 1, 1, 1, 1]),
+    (4, 1, 128, 256, 150, [1, 2, 1, 3, 1, 1, 4]), (16, 4, 64, 32, 500, [1, 1, 1, 1, 1, 1, 1])])
 def test_attention_of_small_tiles_splits_the_keys_among_warps(split, Hq, Hk, D, page, window, news):
     """Tiles whose rows and heads fit 16 M rows (decoding, and portions of a few rows) run the kernel form in which
     each warp takes a quarter of every key tile: contexts that end inside a warp's quarter, at a tile's edge, a
