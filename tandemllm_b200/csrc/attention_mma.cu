@@ -16,7 +16,7 @@
 //               caller picks S so that the grid fills the GPU: short spans for one request, long ones for many.
 // The tile table (request, first row, rows) comes from the host with the step's other integers.
 //
-// TMA (decoding, page sizes that divide 64 or are multiples of it): a fifth warp is the producer. For every key tile
+// TMA (page sizes that divide 64 or are multiples of it; both forms of the kernel): a fifth warp is the producer. For every key tile
 // its lanes look the tile's pages up and each sends one bulk tensor copy (a page's rows of one KV head, 64 columns, with
 // the 128-byte swizzle the ldmatrix reads expect) onto the stage's `full` mbarrier; the four consumer warps wait on
 // it, compute, and arrive on the stage's `empty` mbarrier. No thread of a consumer warp computes an address or issues
@@ -533,5 +533,5 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_cache, const 
 #undef TL_MMA
 }
 
-// 0: the decoding form fetches keys and values with cp.async from every thread instead of a producer warp's TMA copies
+// 0: keys and values are fetched with cp.async from every thread instead of a producer warp's TMA copies
 extern "C" void tl_attention_mma_use_tma(int on) { decode_with_tma() = on; }
