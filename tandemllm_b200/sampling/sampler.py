@@ -63,12 +63,19 @@ class Sampler:
         self._cap = 0
 
     def _staging(self, n: int):
+        """A pinned block and its device copy for n rows. Three pairs take turns, each waiting only for the copy that last
+        read it, so that a step can be launched while the one before it still runs."""
         if n > self._cap:
             self._cap = max(64, 2 * n)
             # one pinned block: temperature, top_p, min_p (float32) | top_k, position (int32) | seed (int64)
-            self._host = torch.empty(7 * self._cap, dtype=torch.int32, pin_memory=True)
-            self._dev = torch.empty(7 * self._cap, dtype=torch.int32, device=self.device)
-        return self._host, self._dev
+            self._hosts = [torch.empty(7 * self._cap, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+            self._devs = [torch.empty(7 * self._cap, dtype=torch.int32, device=self.device) for _ in range(3)]
+            self._events = [None, None, None]
+            self._turn = 0
+        self._turn = (self._turn + 1) % 3
+        if self._events[self._turn] is not None:
+            self._events[self._turn].synchronize()
+        return self._hosts[self._turn], self._devs[self._turn]
 
     def __call__(self, logits: torch.Tensor, rows: list[tuple[SamplingParams, int]]) -> torch.Tensor:
         """int32 [n] token ids for float32 logits [n, V]."""
@@ -82,7 +89,6 @@ class Sampler:
             return ops.argmax(logits, out)
         host, dev = self._staging(n)
         c = self._cap
-        torch.cuda.current_stream().synchronize()       # the previous copy out of `host` has finished
         f = host.view(torch.float32)
         seeds = host[5 * c:7 * c].view(torch.int64)
         for i, (p, pos) in enumerate(rows):
@@ -93,6 +99,9 @@ class Sampler:
             host[4 * c + i] = pos
             seeds[i] = p.resolved_seed() if not p.greedy else 0
         dev.copy_(host, non_blocking=True)
+        event = self._events[self._turn] or torch.cuda.Event()
+        event.record()
+        self._events[self._turn] = event
         df = dev.view(torch.float32)
         return ops.sample(logits, df[0:n], dev[3 * c:3 * c + n], df[c:c + n], df[2 * c:2 * c + n],
                           dev[5 * c:7 * c].view(torch.int64)[:n], dev[4 * c:4 * c + n], out)
