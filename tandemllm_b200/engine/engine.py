@@ -218,7 +218,7 @@ class Engine:
         """Run `batch` and its sampling without waiting for them. `before`: the step whose tokens this one's rows
         take from the device."""
         fn = self.step_function
-        entries = [StepEntry(s.request.request_id, s.request.tokens[s.start:s.start + s.count],
+        entries = [StepEntry(s.request.request_id, s.request.span(s.start, s.count),
                              [s.count - 1] if s.samples else []) for s in batch]
         feedback = None
         if before is not None:

@@ -53,6 +53,15 @@ class Request:
     def tokens(self) -> list[int]:
         return self.prompt + self.output
 
+    def span(self, start: int, count: int) -> list[int]:
+        """tokens[start:start + count] without putting the whole text together (a step of a long request asks for one)."""
+        n, end = len(self.prompt), start + count
+        if end <= n:
+            return self.prompt[start:end]
+        if start >= n:
+            return self.output[start - n:end - n]
+        return self.prompt[start:] + self.output[:end - n]
+
     @property
     def pending(self) -> int:
         return len(self.prompt) + len(self.output) - self.num_computed
