@@ -399,9 +399,9 @@ def main() -> int:
     points = {}
     pre = None
     if not a.skip_points:
-        few = max(8, a.steps // 4)
-        points["decode_b1"] = round(device_decode(1, a.context, few, 3)["tok_s"], 1)
-        points["decode_b64"] = round(device_decode(64, a.context, few, 3)["tok_s"], 1)
+        few = max(16, a.steps // 2)
+        points["decode_b1"] = round(device_decode(1, a.context, few, a.warmup)["tok_s"], 1)
+        points["decode_b64"] = round(device_decode(64, a.context, few, a.warmup)["tok_s"], 1)
         pre = prefill(PREFILL_TOKENS)
     line = {
         "metric": f"decode tok/s at batch {a.batch}, context {a.context} ({model_name}, B200)",
