@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_mma_kernel(
 }
 
 
-// The same for the routed experts of a very small step (up to eight rows): grid (ceil(N / 16), plan tiles), a CTA takes
+// The same for the routed experts of a small step (a dozen rows): grid (ceil(N / 16), plan tiles), a CTA takes
 // 16 outputs of one tile's expert for the tile's token rows (at most 8: the plan is built with tiles of 8). With SWIGLU
 // it multiplies by the expert's gate rows and up rows of those outputs and stores silu(gate) * up. Token rows are
 // fetched through `row_index` (position i of the plan stands for row row_index[i] / row_div of x) or, without it, lie

@@ -190,14 +190,14 @@ def test_decode_graph_equals_eager_bit_for_bit(case):
 
 
 def test_a_captured_graph_survives_the_growth_of_kept_buffers(case):
-    """Nine requests decode from a captured graph; then thirty decode together, which outgrows the routing plan (and
-    whatever else is kept between steps) that the graph of nine was captured with; then the nine decode on from the old
-    graph. A buffer freed on growth would be written by that replay while it belongs to somebody else. Every step's
+    """Seventeen requests decode from a captured graph; then thirty decode together, which outgrows the routing plan (and
+    whatever else is kept between steps) that the graph of seventeen was captured with; then the seventeen decode on from
+    the old graph. A buffer freed on growth would be written by that replay while it belongs to somebody else. Every step's
     logits equal the eager engine's bit for bit."""
     n_many = 30
     toks = {f"m{i}": T.long_tokens(case.name, 24, seed=300 + i) for i in range(n_many)}
     first = [{"step": 0, "entries": [{"id": r, "tokens": t[:8], "want": []} for r, t in toks.items()], "end": []}]
-    pair = [f"m{i}" for i in range(9)]      # (nine: past the experts' form for up to eight rows, which has a plan of its own)
+    pair = [f"m{i}" for i in range(17)]     # (seventeen: past the experts' form for a dozen rows, which has a plan of its own)
     trace, at = list(first), {r: 8 for r in toks}
 
     def decode(who):
@@ -216,7 +216,7 @@ def test_a_captured_graph_survives_the_growth_of_kept_buffers(case):
     assert engines[0].step_function.graph_replays >= 6
     if case.dtype == "bfloat16" and case.name == "b":       # 8 experts, top-3: 90 pairs in tiles of 16 outgrow the plan for 64
         moe = [l.feed_forward for l in engines[0].model.layers if hasattr(l.feed_forward, "num_experts")]
-        assert any(p._outgrown for p in moe), "the plan of the graph of nine was outgrown by the step of thirty"
+        assert any(p._outgrown for p in moe), "the plan of the graph of seventeen was outgrown by the step of thirty"
     assert a.keys() == b.keys()
     for key in a:
         assert torch.equal(a[key], b[key]), key
