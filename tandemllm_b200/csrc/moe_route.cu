@@ -184,21 +184,24 @@ __global__ void __launch_bounds__(128) moe_plan_small_kernel(const int* __restri
     counts[ex] = cnt;
   }
   __syncthreads();
-  if (tid == 0) {
+  // a thread an expert: its pairs and row tiles come behind those of the experts before it
+  for (int ex = tid; ex < E; ex += 128) {
     int off = 0, tiles = 0;
-    for (int ex = 0; ex < E; ++ex) {
-      offsets[ex] = off;
-      const int cnt = s_counts[ex];
-      for (int t = 0; t * tile_m < cnt; ++t) {
-        tile_group[tiles] = ex;
-        tile_row0[tiles] = off + t * tile_m;
-        tile_rows[tiles] = min(tile_m, cnt - t * tile_m);
-        ++tiles;
-      }
-      off += cnt;
+    for (int i = 0; i < ex; ++i) {
+      off += s_counts[i];
+      tiles += (s_counts[i] + tile_m - 1) / tile_m;
     }
-    offsets[E] = off;
-    *n_tiles = tiles;
+    offsets[ex] = off;
+    const int cnt = s_counts[ex];
+    for (int t = 0; t * tile_m < cnt; ++t, ++tiles) {
+      tile_group[tiles] = ex;
+      tile_row0[tiles] = off + t * tile_m;
+      tile_rows[tiles] = min(tile_m, cnt - t * tile_m);
+    }
+    if (ex == E - 1) {
+      offsets[E] = off + cnt;
+      *n_tiles = tiles;
+    }
   }
 }
 
