@@ -14,9 +14,13 @@ Choice of kernel by shape:
   more rows              the persistent kernel: one CTA an SM walks over tiles of 128 token rows by 256 weight rows,
                          its loads, its MMAs and its epilogue running side by side on two accumulators.
 Experts: the plan's tiles carry the expert, gate/up and SwiGLU run in one kernel, the down projection writes 32-bit
-rows that the next norm kernel weighs and adds (`ops.ExpertRows`). With a row or two an expert the gate/up product
-fetches each token row by its index; with more, the rows are copied into expert-sorted order first (by the plan
-kernel itself for a small step).
+rows that the next norm kernel weighs and adds (`ops.ExpertRows`). A step of up to 16 rows runs both products in the
+grouped form of the register-only kernel (plan tiles of 8 rows; with at most 16 pairs no plan at all: the CTAs find each
+expert's pairs in the ids). Above that the tcgen05 kernels: with a row or two an expert the gate/up product fetches each
+token row by its index; with more, the rows are copied into expert-sorted order first (by the plan kernel itself for
+a small step).
+A short-convolution mixer's in-projection of up to 8 decode rows runs with the convolution and the state's shift in its
+epilogue (`in_proj_conv`). Attention (`csrc/attention_mma.cu`) is dispatched from here as well.
 Anything the kernels do not take (k or a row stride not a multiple of 8 elements, as TMA needs 16-byte strides)
 goes back to the CUDA-core kernels by returning None.
 """
