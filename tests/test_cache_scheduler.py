@@ -313,3 +313,16 @@ def test_abort_gives_everything_back():
     drive(sched, fake)
     assert a.finish_reason == "aborted" and b.finish_reason == "length"
     assert sched.cache.groups[0].pool.free == 64
+
+
+def test_a_span_of_a_request_is_a_slice_of_its_whole_text():
+    """`Request.span` (what a step takes, without joining prompt and output) against slicing the joined text: spans
+    inside the prompt, inside the output, across the seam, empty and past the end."""
+    rng = random.Random(5)
+    for _ in range(50):
+        r = Request("r", [rng.randrange(100) for _ in range(rng.randrange(0, 9))], SamplingParams())
+        r.output = [rng.randrange(100) for _ in range(rng.randrange(0, 9))]
+        whole = r.tokens
+        for start in range(len(whole) + 2):
+            for count in range(0, len(whole) + 2 - start):
+                assert r.span(start, count) == whole[start:start + count], (r.prompt, r.output, start, count)
