@@ -1,11 +1,11 @@
 """Single kernels on small cases, timed with CUDA events: the commands behind the summaries under `profiles/`.
 
-    python -m tandemllm_b200.kernels.microbench expert_gemm --tokens 8
-    python -m tandemllm_b200.kernels.microbench dense_gemm --rows 8 --n 6144 --k 2048
-    python -m tandemllm_b200.kernels.microbench dense_gemm --rows 2048 --n 6144 --k 2048
-    python -m tandemllm_b200.kernels.microbench attention --batch 8 --context 8192
-    python -m tandemllm_b200.kernels.microbench attention --batch 1 --rows 2048 --context 2048
-    python -m tandemllm_b200.kernels.microbench norm --rows 8
+    python microbench.py expert_gemm --tokens 8
+    python microbench.py dense_gemm --rows 8 --n 6144 --k 2048
+    python microbench.py dense_gemm --rows 2048 --n 6144 --k 2048
+    python microbench.py attention --batch 8 --context 8192
+    python microbench.py attention --batch 1 --rows 2048 --context 2048
+    python microbench.py norm --rows 8
 
 Sizes default to the LFM2-8B-A1B layer (hidden 2048, 32 experts of width 1792 top-4, 32/8 heads of 64). Inputs are
 larger than the 126 MB L2 or a 256 MB buffer is written between timed launches, so DRAM figures mean something; a
@@ -17,9 +17,14 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
 import sys
 import types
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
 import torch
 
@@ -45,8 +50,8 @@ def timed(fn, iters: int, flush: bool = True) -> float:
 
 
 def runtime():
-    from ..parts import Runtime
-    from . import tensorcore
+    from tandemllm_b200.parts import Runtime
+    from tandemllm_b200.kernels import tensorcore
     rt = Runtime(torch.device(DEV), torch.bfloat16)
     tensorcore.enable(rt)
     return rt
@@ -54,8 +59,8 @@ def runtime():
 
 def expert_gemm(a) -> dict:
     """The routed experts of one layer: plan + gate/up with SwiGLU + down, for `tokens` rows."""
-    from ..config import PartSpec
-    from ..parts import make_part
+    from tandemllm_b200.config import PartSpec
+    from tandemllm_b200.parts import make_part
     rt = runtime()
     E, H, I, k, R = a.experts, a.hidden, a.inter, a.top_k, a.tokens
     spec = PartSpec("sigmoid_topk_experts", {"num_experts": E, "top_k": k, "intermediate_size": I, "expert_bias": False,
@@ -92,7 +97,7 @@ def dense_gemm(a) -> dict:
 
 def attention(a) -> dict:
     """`rows` query rows per request at the end of a context of `context` positions, `batch` requests."""
-    from . import ops
+    from tandemllm_b200.kernels import ops
     rt = runtime()
     Hq, Hk, D, page = a.heads, a.kv_heads, a.head_dim, 16
     B, n, L = a.batch, a.rows, a.context
@@ -110,7 +115,7 @@ def attention(a) -> dict:
     cache = types.SimpleNamespace(k=kc, v=vc, page_size=page)
     out = torch.empty(R, Hq, D, dtype=torch.bfloat16, device=DEV)
     if a.kernel == "mma":
-        from . import tensorcore
+        from tandemllm_b200.kernels import tensorcore
         tensorcore.lib().tl_attention_mma_use_tma(int(a.copies == "tma"))
         fn = lambda: rt.tensorcore.attention(q, cache, table, step, D ** -0.5, None, out, rt)
     else:
@@ -126,7 +131,7 @@ def attention(a) -> dict:
 
 
 def norm(a) -> dict:
-    from . import ops
+    from tandemllm_b200.kernels import ops
     ops.core()
     R, H = a.rows, a.hidden
     res = torch.randn(R, H, device=DEV)

@@ -3,6 +3,7 @@
   generate        token ids in, token ids out, through the scheduler and the step function
   random-weights  write a model folder (config.json, model.safetensors) from a config.json and a seed
   replay          the trace replay program (the same as bin/trace_run)
+  bench           the measurement program (the same as bench.py at the repository's root)
 
 Option names follow the reference's command lines where it has them: `--model`, `--max-len`, `--tokens`,
 `--graph on|off`, `--json` (tools/lfm_check.py:374-418), `--temperature`, `--top-p`, `--top-k`, `--parallel`
@@ -31,6 +32,9 @@ def _engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--chunk-size", type=int, default=512, help="longest prompt portion in one step")
     p.add_argument("--graph", default="on", choices=("on", "off"), help="CUDA graphs for decode-only steps")
     p.add_argument("--device", default="cuda:0")
+    p.add_argument("--log", help="append one JSON line a scheduler step here (rows, pages, milliseconds)")
+    p.add_argument("--log-routing", action="store_true",
+                   help="count the experts every step touches in every routed layer (into the step records and --log)")
 
 
 def _build_engine(a):
@@ -38,7 +42,7 @@ def _build_engine(a):
     from .engine import Engine, EngineArgs
     args = EngineArgs(dtype=a.dtype, max_len=a.max_len, parallel=a.parallel, block_size=a.block_size,
                       kv_blocks=a.kv_blocks, max_batched_tokens=a.max_batched_tokens, chunk_size=a.chunk_size,
-                      device=a.device, graph=a.graph == "on")
+                      device=a.device, graph=a.graph == "on", log=a.log, record_routing=a.log_routing)
     if a.random_weights is not None:
         if not a.config:
             raise SystemExit("--random-weights needs --config FILE (a config.json)")
@@ -102,6 +106,17 @@ def cmd_replay(a) -> int:
     return 0
 
 
+def cmd_bench(a) -> int:
+    import os
+    import runpy
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+    if not os.path.isfile(path):
+        raise SystemExit(f"bench.py is not beside the package ({path})")
+    sys.argv = [path] + a.rest
+    runpy.run_path(path, run_name="__main__")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m tandemllm_b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -133,6 +148,9 @@ def main(argv=None) -> int:
     p = sub.add_parser("replay", help="the trace replay program; options as for bin/trace_run")
     p.add_argument("rest", nargs=argparse.REMAINDER)
     p.set_defaults(fn=cmd_replay)
+    b = sub.add_parser("bench", help="the measurement program; options as for bench.py")
+    b.add_argument("rest", nargs=argparse.REMAINDER)
+    b.set_defaults(fn=cmd_bench)
     a = ap.parse_args(argv)
     return a.fn(a)
 

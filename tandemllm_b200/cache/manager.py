@@ -130,6 +130,7 @@ class CacheManager:
         self._slot_of: dict = {}
         self._length: dict = {}
         self.preemptions = 0
+        self._slot_init: dict[int, object] = {}       # site -> what a slot is set to when a request takes it
         if device is not None:
             for gi, g in enumerate(self.groups):
                 shape = (num_pages, g.need.kv_heads, page_size, g.need.head_dim)
@@ -139,10 +140,15 @@ class CacheManager:
             for i in self._slot_sites:
                 need = needs[i]
                 self.site_cache[i] = SlotSiteCache(torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device))
+                init = need.init
+                if isinstance(init, torch.Tensor):
+                    init = init.to(device=device, dtype=need.dtype)
+                self._slot_init[i] = init
 
     # ---- requests ----
     def admit(self, req) -> int:
-        """Give `req` a state slot (zeroed) and empty block tables; returns the slot."""
+        """Give `req` a state slot (set to its site's initial value: zeros unless the need says otherwise) and empty
+        block tables; returns the slot."""
         if req in self._slot_of:
             raise RuntimeError(f"request {req!r} is already admitted")
         if not self._free_slots:
@@ -155,7 +161,13 @@ class CacheManager:
             g.arrays[req] = np.empty(64, dtype=np.int32)
         if self.device is not None:
             for i in self._slot_sites:
-                self.site_cache[i].state[slot].zero_()
+                init = self._slot_init.get(i)
+                if init is None:
+                    self.site_cache[i].state[slot].zero_()
+                elif isinstance(init, torch.Tensor):
+                    self.site_cache[i].state[slot].copy_(init.expand_as(self.site_cache[i].state[slot]))
+                else:
+                    self.site_cache[i].state[slot].fill_(init)
         return slot
 
     def has(self, req) -> bool:

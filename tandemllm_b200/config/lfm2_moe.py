@@ -242,6 +242,9 @@ class Lfm2MoeConfig:
             layers=layers, schedule=plain_schedule(c.num_hidden_layers), final_norm=norm,
             embedding_name="embed_tokens.weight", final_norm_prefix="embedding_norm.",
             head_name=None if c.tie_word_embeddings else "lm_head.weight",
+            # a tied checkpoint may still store a copy of the head (the reference reads it when given,
+            # engine/models/lfm2_moe/ref.py:96-97; here the tied model ignores it)
+            ignored_names=("lm_head.weight",) if c.tie_word_embeddings else (),
             max_positions=c.max_position_embeddings, stop_token_ids=tuple(c.eos_token_ids),
         )
 

@@ -63,9 +63,11 @@ class ModelSpec:
     layers: tuple[LayerSpec, ...]
     schedule: tuple[Site, ...]
     final_norm: PartSpec
-    embedding_name: str = "embed_tokens.weight"
-    final_norm_prefix: str = "embedding_norm."
+    embedding_name: str = field(kw_only=True)       # the embedding table's tensor name; an architecture says its own
+    final_norm_prefix: str = field(kw_only=True)    # the last norm's part of its tensors' names
     head_name: str | None = None           # None: the head is the embedding (tied)
+    ignored_names: tuple[str, ...] = ()    # stored tensors that are neither read nor an error (a tied model's copy
+                                           # of its head, for one)
     max_positions: int = 1 << 17
     stop_token_ids: tuple[int, ...] = ()
     name_prefixes: tuple[str, ...] = ("model.",)   # stored names may carry one of these in front

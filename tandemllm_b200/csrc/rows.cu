@@ -498,7 +498,8 @@ extern "C" int tl_silu_mul(const void* gate_up, void* out, int rows, int inter, 
   if (rows == 0) return 0;
   TL_REQUIRE(rows > 0 && inter > 0, "silu_mul: rows %d width %d", rows, inter);
   const long long n = (long long)rows * inter;
-  const int blocks = (int)(ceil_div64(n, 256) < 148 * 16 ? ceil_div64(n, 256) : 148 * 16);
+  const long long most = (long long)sm_count() * 16;
+  const int blocks = (int)(ceil_div64(n, 256) < most ? ceil_div64(n, 256) : most);
   cudaError_t e;
   if (dtype == TL_FP32)
     e = launch_chained(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out,

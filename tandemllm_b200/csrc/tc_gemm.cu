@@ -689,7 +689,8 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   if (persistent) {
     const int out_n = swiglu ? 128 : 256;
     const long long work = (long long)ceil_div(N, out_n) * (tile_group ? max_tiles : ceil_div(M, TILE_M));
-    const dim3 pgrid((unsigned)(work < 148 ? work : 148));
+    const int sms = sm_count();
+    const dim3 pgrid((unsigned)(work < sms ? work : sms));
     if (swiglu) e = out_dtype == TL_BF16 ? launch_persistent<true, bf16>(tmW, tmX, p, pgrid, stream)
                                          : launch_persistent<true, float>(tmW, tmX, p, pgrid, stream);
     else e = out_dtype == TL_BF16 ? launch_persistent<false, bf16>(tmW, tmX, p, pgrid, stream)

@@ -13,8 +13,12 @@ temperature / top_p / top_k / min_p / seed on the request.
 
 from __future__ import annotations
 
+import json
+import time
+from collections import deque
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
@@ -22,6 +26,7 @@ from ..config.registry import read_model_config, resolve_model_folder, spec_of
 from ..parts.base import Runtime
 from ..parts.model import DecoderModel
 from ..sampling.sampler import Sampler, SamplingParams
+from ..settings import SETTINGS
 from ..weights.loader import DictWeights, FolderWeights
 from ..weights.random_init import random_weights
 from .scheduler import Request, Scheduler
@@ -43,6 +48,8 @@ class EngineArgs:
     graph: bool = True                  # capture decode-only steps in CUDA graphs (bfloat16)
     tensorcore: bool = True             # use the tcgen05 kernels in bfloat16
     overlap: bool = True                # launch the next decode step before this one's tokens are read
+    log: str | None = None              # a file that gets one JSON line a scheduler step (default: $TANDEMLLM_STEP_LOG)
+    record_routing: bool = False        # count, step by step, the pairs routed to every expert of every routed layer
 
 
 @dataclass
@@ -54,6 +61,9 @@ class _Flight:
     event: torch.cuda.Event             # recorded behind the copies into `host`
     tokens: torch.Tensor | None         # the sampled tokens on the device
     index: dict                         # request id -> its place among them
+    record: dict                        # the step's record, completed when the step is accounted
+    started: float                      # host clock at launch
+    routed: torch.Tensor | None = None  # pinned: the routing counters as they stood after this step
 
 
 def require_cuda(device: str) -> torch.device:
@@ -83,6 +93,16 @@ class Engine:
                                    chunk_size=args.chunk_size, max_model_len=args.max_len,
                                    stop_token_ids=model.spec.stop_token_ids)
         self._next_id = 0
+        # ---- records: one dict a scheduler step (the reference keeps `route_trace` and `host_ms` per step,
+        # engine/models/lfm2_moe/engine.py:125, :236-240, :457) ----
+        self.records: deque[dict] = deque(maxlen=4096)
+        self._log_path = args.log or SETTINGS.get("STEP_LOG")
+        self._log_file = None
+        self._routed_parts: list = []
+        self._routing = self._routing_seen = None
+        self._routed_host = [None, None]
+        if args.record_routing:
+            self.set_routing_record(True)
 
     # ---- construction ----
     @classmethod
@@ -147,20 +167,55 @@ class Engine:
         self.scheduler.add(req)
         return req
 
-    def add_request_with_context(self, prompt: list[int], params: SamplingParams | None = None, request_id=None) -> Request:
-        """For measurement: a running request whose prompt, except its last token, counts as already computed. Its
-        pages are reserved and hold whatever they held (fill the cache tensors first for realistic values), so a
-        decode step at a long context can be timed without running the prompt. The text it generates is not meaningful."""
-        req = self.add_request(prompt, params, request_id)
-        self.scheduler.waiting.remove(req)
-        self.cache.admit(req.request_id)
-        n = len(req.prompt) - 1
-        self.cache.reserve(req.request_id, n)
-        self.cache.advance(req.request_id, n)
-        req.num_computed = n
-        req.state = "running"
-        self.scheduler.running.append(req)
-        return req
+    # ---- records ----
+    def set_routing_record(self, on: bool) -> None:
+        """Count (or stop counting) the pairs every step routes to each expert of each routed feed-forward; a step's
+        record then holds `experts_touched` (per routed layer, in run order) and `pairs_routed`. The counting is a
+        kernel of the pass, so it works in steps replayed from graphs; graphs captured before the switch are dropped."""
+        parts = []
+        for layer in self.model.layers:
+            ff = layer.feed_forward
+            if hasattr(ff, "count_into") and hasattr(ff, "num_experts"):
+                parts.append(ff)
+        self.step_function.drop_graphs()
+        self._routed_parts = parts if on else []
+        self._routing = self._routing_seen = None
+        if on and parts:
+            sizes = [p.num_experts for p in parts]
+            self._routing = torch.zeros(sum(sizes), dtype=torch.int64, device=self.device)
+            self._routing_seen = np.zeros(sum(sizes), dtype=np.int64)
+            at = 0
+            for p, n in zip(parts, sizes):
+                p.count_into(self._routing[at:at + n])
+                at += n
+        else:
+            for p in parts:
+                p.count_into(None)
+
+    def _finish_record(self, flight: "_Flight", finished: int) -> None:
+        rec = flight.record
+        rec["ms"] = round((time.perf_counter() - flight.started) * 1e3, 3)
+        rec["finished"] = finished
+        if flight.routed is not None:
+            now = flight.routed.numpy().copy()
+            delta, at, touched = now - self._routing_seen, 0, []
+            self._routing_seen = now
+            for p in self._routed_parts:
+                touched.append(int((delta[at:at + p.num_experts] > 0).sum()))
+                at += p.num_experts
+            rec["experts_touched"] = touched
+            rec["pairs_routed"] = int(delta.sum())
+            rec["routed"] = delta          # numpy int64, per routed layer its experts in a row (not written to the log)
+        self.records.append(rec)
+        if self._log_path:
+            if self._log_file is None:
+                self._log_file = open(self._log_path, "a")
+            self._log_file.write(json.dumps({k: v for k, v in rec.items() if k != "routed"}) + "\n")
+            self._log_file.flush()
+
+    @property
+    def last_record(self) -> dict | None:
+        return self.records[-1] if self.records else None
 
     def run_step(self) -> list[Request]:
         """One scheduler step: schedule, run, sample, account. Returns the requests that finished.
@@ -202,7 +257,9 @@ class Engine:
         if self.step_function.check_status and int(flight.host[flight.n]):
             self._flight = None
             self.step_function.raise_on_fault()
-        return self.scheduler.resolve(flight.batch, flight.host[:flight.n].tolist())
+        done = self.scheduler.resolve(flight.batch, flight.host[:flight.n].tolist())
+        self._finish_record(flight, len(done))
+        return done
 
     def _runs_ahead(self, cur: "_Flight") -> bool:
         """Whether the next step is known before this one's tokens are: every running request has just the token
@@ -218,6 +275,7 @@ class Engine:
         """Run `batch` and its sampling without waiting for them. `before`: the step whose tokens this one's rows
         take from the device."""
         fn = self.step_function
+        started = time.perf_counter()
         entries = [StepEntry(s.request.request_id, s.request.span(s.start, s.count),
                              [s.count - 1] if s.samples else []) for s in batch]
         feedback = None
@@ -240,10 +298,23 @@ class Engine:
             if n:
                 host[:n].copy_(tokens, non_blocking=True)
             host[n:n + 1].copy_(self.model.runtime.status, non_blocking=True)
+            routed = None
+            if self._routing is not None:
+                routed = self._routed_host[self._turn]
+                if routed is None or routed.numel() != self._routing.numel():
+                    routed = self._routed_host[self._turn] = torch.empty(self._routing.numel(), dtype=torch.int64).pin_memory()
+                routed.copy_(self._routing, non_blocking=True)
             event = torch.cuda.Event()
             event.record()
         index = {s.request.request_id: i for i, s in enumerate(x for x in batch if x.samples)}
-        return _Flight(batch, host, n, event, tokens, index)
+        sch, rows = self.scheduler, sum(s.count for s in batch)
+        decode_rows = sum(1 for s in batch if s.count == 1 and s.samples and s.request.output)
+        record = {"step": fn.steps, "requests": len(batch), "rows": rows, "prompt_rows": rows - decode_rows,
+                  "decode_rows": decode_rows, "sampled": n, "from_graph": fn.last_from_graph,
+                  "pages_used": [g.pool.used for g in self.cache.groups],
+                  "pages_free": [g.pool.free for g in self.cache.groups],
+                  "running": len(sch.running), "waiting": len(sch.waiting), "preemptions": sch.stats.preemptions}
+        return _Flight(batch, host, n, event, tokens, index, record, started, routed)
 
     def generate(self, prompts: list[list[int]], params: SamplingParams | list[SamplingParams] | None = None
                  ) -> list[list[int]]:
@@ -261,5 +332,20 @@ class Engine:
         return [r.output for r in reqs]
 
     def stats(self) -> dict:
+        fn = self.step_function
         return {"scheduler": vars(self.scheduler.stats), "cache": self.cache.stats(),
-                "steps": self.step_function.steps, "rows": self.step_function.rows_run}
+                "steps": fn.steps, "rows": fn.rows_run, "graph_replays": fn.graph_replays, "graphs_kept": len(fn._graphs),
+                "graphs_dropped": fn.graphs_dropped}
+
+    def decode_bytes(self, batch: int, context: int, experts_read: list[int] | None = None) -> dict:
+        """Bytes one decode step of `batch` requests at `context` tokens has to read: see `DecoderModel.decode_bytes`,
+        plus the keys and values of the live requests in every page group (a windowed group holds its window)."""
+        out = self.model.decode_bytes(batch, experts_read)
+        elem = self.cache.site_cache[self.cache.groups[0].sites[0]].k.element_size() if self.cache.groups else 0
+        kv = 0
+        for g in self.cache.groups:
+            span = context if g.need.window is None else min(context, g.need.window)
+            kv += len(g.sites) * 2 * g.need.kv_heads * g.need.head_dim * elem * span * batch
+        out["kv"] = kv
+        out["total"] += kv
+        return out

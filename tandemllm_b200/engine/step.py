@@ -13,11 +13,16 @@ are the same case, because every kernel takes rows with explicit request, positi
 Decode-only steps (every request brings one token and wants its logits) can run from CUDA graphs, as the
 reference replays one graph per decode token (engine.py:745-794): a graph is captured per batch size,
 block-table width and context bucket the first time that shape has run eagerly, and replayed afterwards
-from the same staged integers. The kernels and their order are the eager step's own.
+from the same staged integers. The kernels and their order are the eager step's own. Context buckets grow
+with the context (an eighth of the context's power of two, at least 1024 tokens), so a request that decodes
+from 1 to 128k tokens passes through a few dozen of them, and at most `max_graphs` graphs are kept: beyond
+that the least recently replayed one is dropped (at a moment when the stream is idle anyway, just before a
+new one is captured).
 """
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 
 import numpy as np
@@ -26,6 +31,7 @@ import torch
 from ..cache.manager import CacheManager, OutOfPages
 from ..kernels import ops
 from ..parts.base import StepContext
+from ..settings import SETTINGS
 
 
 @dataclass
@@ -45,7 +51,18 @@ _STATUS = {1: "a token id outside the vocabulary", 2: "a key/value write to a po
            3: "a visible key without a page", 4: "an attention tile with more rows than its kernel takes",
            5: "a plan tile with more rows than its kernel takes", 11: "a pipeline wait that ran out in a tensor-core kernel"}
 
-CONTEXT_BUCKET = 1024       # a decode graph serves contexts up to the next multiple of this
+CONTEXT_BUCKET = 1024       # the smallest context bucket of a decode graph
+
+
+def context_bucket(longest: int) -> int:
+    """The context a decode graph is captured for when its longest request holds `longest` tokens: the next
+    multiple of g, g being an eighth of the power of two at or below `longest` and at least CONTEXT_BUCKET. A graph
+    then serves contexts at most an eighth shorter than the one its kernels' grids were sized for, and contexts up to
+    2^n fall into 8 buckets an octave."""
+    g = CONTEXT_BUCKET
+    while g * 16 <= longest:
+        g *= 2
+    return -(-longest // g) * g
 
 
 class _Staging:
@@ -81,7 +98,7 @@ class _DecodeGraph:
 
 class StepFunction:
     def __init__(self, model, cache: CacheManager, check_status: bool = True, use_graphs: bool = False,
-                 max_graph_batch: int = 64):
+                 max_graph_batch: int = 64, max_graphs: int | None = None):
         self.model, self.cache = model, cache
         self.device = model.runtime.device
         self.check_status = check_status
@@ -89,11 +106,15 @@ class StepFunction:
         self.max_graph_batch = max_graph_batch
         self._staging: _Staging | None = None
         self._device_ints = None
-        self._graphs: dict[tuple, _DecodeGraph] = {}
+        self._graphs: OrderedDict[tuple, _DecodeGraph] = OrderedDict()      # least recently used first
         self._graph_pool = None
+        self.max_graphs = max(1, max_graphs if max_graphs is not None else SETTINGS.get_int("GRAPHS"))
+        self.graphs_dropped = 0
+        self.trace: dict | None = None      # when a dict: every step runs eagerly and its parts may record into it
         self.steps = 0
         self.rows_run = 0
         self.graph_replays = 0
+        self.last_from_graph = False        # whether the last step was a graph replay
 
     # ---- laying a batch out ----
     def _pinned(self, n: int) -> torch.Tensor:
@@ -177,13 +198,15 @@ class StepFunction:
 
     def _context(self, dev: torch.Tensor, o: dict, B: int, R: int, n_out: int, max_pages: int, max_rows: int,
                  max_ctx: int, host_lists: dict) -> StepContext:
+        if self.trace is not None:
+            self.trace.clear()
         G = len(self.cache.groups)
         tables = [dev[o["tab"] + g * B * max_pages:o["tab"] + (g + 1) * B * max_pages].view(B, max_pages) for g in range(G)]
         return StepContext(
             n_rows=R, n_requests=B, token_ids=dev[o["tok"]:o["tok"] + R], positions=dev[o["pos"]:o["pos"] + R],
             req_of_row=dev[o["req"]:o["req"] + R], row_start=dev[o["start"]:o["start"] + B + 1],
             state_slot=dev[o["slot"]:o["slot"] + B], block_tables=tables, out_rows=dev[o["out"]:o["out"] + n_out],
-            n_out=n_out, max_rows_per_request=max_rows, max_context=max_ctx, host=host_lists)
+            n_out=n_out, max_rows_per_request=max_rows, max_context=max_ctx, host=host_lists, trace=self.trace)
 
     def build(self, entries: list[StepEntry]) -> StepContext:
         """Reserve pages for the batch and stage its integers on the device (one host-to-device copy)."""
@@ -216,7 +239,8 @@ class StepFunction:
             return torch.empty(0, self.model.vocab_size, dtype=torch.float32, device=self.device)
         if feedback is not None and (len(feedback[1]) != len(entries) or any(len(e.tokens) != 1 for e in entries)):
             raise ValueError("tokens fed on the device: one token and one index for every entry")
-        if (self.use_graphs and len(entries) <= self.max_graph_batch
+        self.last_from_graph = False
+        if (self.use_graphs and self.trace is None and len(entries) <= self.max_graph_batch
                 and all(len(e.tokens) == 1 and e.want == [0] for e in entries)):
             logits = self._run_decode_graph(entries, feedback)
         else:
@@ -250,12 +274,13 @@ class StepFunction:
         while width < pages:
             width *= 2
         longest = max(cache.length_of(e.request) for e in entries) + 1
-        ctx = -(-longest // CONTEXT_BUCKET) * CONTEXT_BUCKET
+        ctx = context_bucket(longest)
         key = (B, width, ctx)
         o = self._layout(B, B, B, len(cache.groups), width)
         slot = self._graphs.get(key)
-        fresh = slot is None
-        if fresh:
+        if slot is not None:
+            self._graphs.move_to_end(key)
+        else:
             dev = torch.empty(o["total"], dtype=torch.int32, device=self.device)
             lists = {"row_start": list(range(B + 1)), "start_pos": None, "slots": None}
             slot = self._graphs[key] = _DecodeGraph(dev, self._context(dev, o, B, B, B, width, 1, ctx, lists))
@@ -267,12 +292,18 @@ class StepFunction:
         if slot.graph is not None:
             slot.graph.replay()
             self.graph_replays += 1
+            self.last_from_graph = True
             ops.launches += slot.kernels
             return slot.logits
         # the first step of this shape runs eagerly (it also sizes every kept buffer); then the same calls are
         # captured for the steps that follow. Capturing launches nothing.
         logits = self.model.forward(slot.step, cache.site_cache)
         torch.cuda.current_stream().synchronize()
+        while len(self._graphs) > self.max_graphs:
+            # The stream is idle, so no replay of the dropped graph is running. Its logits go back to the graphs' shared
+            # pool with it; a caller that still holds them from an earlier step has had them read (the stream is idle).
+            self._graphs.popitem(last=False)
+            self.graphs_dropped += 1
         if self._graph_pool is None:
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
@@ -283,6 +314,12 @@ class StepFunction:
         ops.launches = before
         slot.graph = graph
         return logits
+
+    def drop_graphs(self) -> None:
+        """Forget every captured graph (what a step runs has changed: the next decode steps run eagerly and are
+        captured again)."""
+        torch.cuda.current_stream().synchronize()
+        self._graphs.clear()
 
     def raise_on_fault(self) -> None:
         code = int(self.model.runtime.status.item())

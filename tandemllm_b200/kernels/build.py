@@ -26,6 +26,8 @@ import threading
 import time
 from concurrent.futures import ThreadPoolExecutor
 
+from ..settings import SETTINGS
+
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
@@ -52,7 +54,7 @@ def say(text: str) -> None:
 
 
 def find_nvcc() -> str | None:
-    for cand in (os.environ.get("TANDEMLLM_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+    for cand in (SETTINGS.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
             return cand
     return None
@@ -60,7 +62,7 @@ def find_nvcc() -> str | None:
 
 def build_dir() -> str:
     """`csrc/_build` in the tree; where the tree cannot be written, a per-user folder under the temp dir."""
-    want = os.environ.get("TANDEMLLM_BUILD_DIR") or os.path.join(CSRC, "_build")
+    want = SETTINGS.get("BUILD_DIR") or os.path.join(CSRC, "_build")
     try:
         os.makedirs(want, exist_ok=True)
         probe = os.path.join(want, f".w{os.getpid()}")

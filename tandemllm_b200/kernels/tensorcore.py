@@ -35,7 +35,6 @@ import torch
 from . import ops
 from .build import load
 
-SM_COUNT = 148
 SKINNY_TOKENS = 32              # up to this many token rows ...
 SKINNY_K = 2048                 # ... of at most this many elements (one round of loads a warp) ...
 SKINNY_BYTES = 64 << 20         # ... against at most this many bytes of weights go to the register-only kernel
@@ -111,6 +110,7 @@ def usable(x: torch.Tensor, w: torch.Tensor) -> bool:
 class TensorCore:
     def __init__(self, device, status: torch.Tensor):
         self.device, self.status = device, status
+        self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self._workspace = None
         self._pair_order = None
         self._outgrown = []
@@ -141,8 +141,8 @@ class TensorCore:
         elif swap and plan is None and not swiglu:
             ctas = -(-N // 128) * -(-M // bn)
             kb = -(-K // 64)
-            if ctas < SM_COUNT and kb >= 8:
-                splits = max(1, min(kb // 4, -(-SM_COUNT // ctas), 16))
+            if ctas < self.sm_count and kb >= 8:
+                splits = max(1, min(kb // 4, -(-self.sm_count // ctas), 16))
                 if splits > 1:
                     partial = self.workspace(splits * M * N)
         # `defer` True: a 32-bit result may stay in partial sums; "rounded": so may one of any precision, and its
@@ -262,7 +262,7 @@ class TensorCore:
             return None
         R, k = ids.shape
         P = R * k
-        if R <= SKINNY_ROWS and H % 8 == 0 and not part.record_counts:
+        if R <= SKINNY_ROWS and H % 8 == 0:
             return self._experts_of_a_tiny_step(part, x, ids, wts, plan)
         swap, bn, tile = self.expert_tile(P, E)
         fetch = swap and P <= 2 * E           # a row or two a tile: the gate/up product fetches each token row by its index
@@ -280,8 +280,6 @@ class TensorCore:
             xs = torch.empty(P, H, dtype=x.dtype, device=x.device)
             _check(lib().tl_gather_rows(x.data_ptr(), x.stride(0), plan.sorted_pairs.data_ptr(), k, xs.data_ptr(), P, H,
                                         ops.stream()), "gather_rows")
-        if part.record_counts:
-            part.last_counts = plan.counts.clone()
         if part.load is not None:
             part.load.add_(plan.counts)
         act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
@@ -293,9 +291,9 @@ class TensorCore:
             self.gemm(xs, w_gate_up, None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=swap, bn=bn, n_out=inter)
         w_down = part.w_down.view(E * H, inter)
         ctas = min(P, E) * -(-H // 128)
-        if fetch and ctas < SM_COUNT and inter >= 512:
+        if fetch and ctas < self.sm_count and inter >= 512:
             # as few pairs: the down product is split along k as well, and the norm kernel adds its partial sums
-            splits = max(2, min(-(-inter // 64) // 4, -(-SM_COUNT // ctas), 16))
+            splits = max(2, min(-(-inter // 64) // 4, -(-self.sm_count // ctas), 16))
             y = self.workspace(splits * P * H)[:splits * P * H].view(splits, P, H)
             self.gemm(act, w_down, None, y[0], rows_per_group=H, plan=plan, swap=True, bn=bn, n_out=H, splits=splits)
             return ops.ExpertRows(y, plan.pos_of_pair, ids, wts, parts=splits)
@@ -335,13 +333,13 @@ class TensorCore:
         # Few tiles and long contexts (decoding): split the keys over CTAs as well, in spans long enough that a CTA's
         # start-up is a small part of its work and short enough that the grid still has a few CTAs per SM.
         span_keys = 0
-        ctas, slots = n_tiles * Hk, 3 * SM_COUNT         # about three CTAs of the decode form run on an SM at once
+        ctas, slots = n_tiles * Hk, 3 * self.sm_count         # about three CTAs of the decode form run on an SM at once
         if step.max_context > 512 and 2 * ctas <= slots:
             # a handful of requests: as many spans as fill the GPU once, so that nobody runs in a second, thin wave
             span_keys = max(256, -(-(-(-step.max_context // (slots // ctas))) // 64) * 64)
-        elif step.max_context > 512 and ctas < 8 * SM_COUNT:
+        elif step.max_context > 512 and ctas < 8 * self.sm_count:
             span_keys = 256
-            while span_keys < 2048 and ctas * -(-step.max_context // (2 * span_keys)) >= 4 * SM_COUNT:
+            while span_keys < 2048 and ctas * -(-step.max_context // (2 * span_keys)) >= 4 * self.sm_count:
                 span_keys *= 2
         spans = -(-step.max_context // span_keys) if span_keys else 1
         if spans <= 1:

@@ -16,8 +16,11 @@ Interfaces (duck-typed; the base classes below document them and hold the shared
                   cache_need() -> PagedNeed | SlotNeed | None
                   forward(x, step, cache, writes_cache=True) -> branch output
   FeedForward     weight_specs(present);  bind(read, runtime);
-                  forward(x, step, x32=None, routing=None) -> branch output
-                  optional: wants_x32 (also gets the normed rows unrounded), router_args(rows, device)
+                  forward(x, step) -> branch output
+                  optional: forward_from(norm, residual, delta, step) -> branch output: the feed-forward runs the norm
+                  in front of it itself (residual += delta, x = norm(residual)), so that what it wants from that norm
+                  beyond the rounded rows (the unrounded rows, a router run inside the norm kernel) stays between the
+                  two of them; `Part.forward_from` is the plain form, which an arrangement may rely on
   Arrangement     run(layer, residual, pending, step, cache, writes_cache) -> pending  (the not-yet-added branch output)
 
 A branch output is what a mixer or feed-forward adds to the residual stream: a float32 tensor [R, hidden], or one of
@@ -27,6 +30,14 @@ the deferred forms of `kernels.ops` (`PartialSums`, `ExpertRows`) that the next 
 `step` is the `StepContext` of the running batch: rows of several requests flattened, with each row's
 request, position and the request's tables and slots. `cache` is what the cache manager made for the
 site from the mixer's `cache_need()`.
+
+What a part written in torch may read of a step. The device tensors of `StepContext` are always there. `step.host`
+holds host copies for launch shapes and for parts that loop in Python: `row_start` (list, B + 1) always; `start_pos`
+and `slots` (lists, B) in an eager step, and None in a decode step that runs from a CUDA graph, because a replayed
+graph sees new positions and slots only through the device tensors. A part that needs those host lists must leave
+`graph_safe` False (the default); the step function then never captures a step that runs it.
+`step.trace` is None, or a dict into which a part may put what it decided for this step (the routed feed-forward
+appends (its prefix, the chosen expert ids) under "routes"); a traced step always runs eagerly.
 """
 
 from __future__ import annotations
@@ -113,9 +124,11 @@ class PagedNeed:
 
 @dataclass(frozen=True)
 class SlotNeed:
-    """Per-request state of fixed size, zeroed when a request takes the slot."""
+    """Per-request state of fixed size. When a request takes the slot it is set to `init`: None for zeros, a
+    number to fill it with, or a tensor of `shape` (or broadcastable to it) that is copied in."""
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+    init: Any = field(default=None, compare=False)
 
 
 @dataclass
@@ -147,6 +160,7 @@ class StepContext:
     max_rows_per_request: int = 0   # host copies, for launch shapes
     max_context: int = 0
     host: dict = field(default_factory=dict)   # host-side copies of the lists above (for parts written in torch)
+    trace: dict | None = None       # when a dict: parts may record what they decided in this step (eager steps only)
 
 
 class Part:
@@ -171,3 +185,19 @@ class Part:
 
     def cache_need(self):
         return None
+
+    def step_bytes(self, elem: int, **_) -> int:
+        """Bytes of this part's weights that a step reads when it uses each of them once: matrices in the compute
+        dtype (`elem` bytes an element), vectors in 32-bit. Parts that read only some of their weights in a step
+        (routed experts) answer for themselves; nested parts (a mixer's norms) are counted by their owner."""
+        total = 0
+        for spec in self.weight_specs(None):
+            n = 1
+            for d in spec.shape:
+                n *= d
+            total += n * (elem if spec.role == "matrix" else 4)
+        return total
+
+    def forward_from(self, norm, residual: torch.Tensor, delta, step: "StepContext"):
+        """A feed-forward behind its norm: residual += delta, x = norm(residual), the branch output of x."""
+        return self.forward(norm.add_norm(residual, delta), step)

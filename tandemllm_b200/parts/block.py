@@ -20,16 +20,9 @@ class PreNormResidual:
         n = layer.mixer_norm.add_norm(residual, pending)
         d = layer.mixer.forward(n, step, cache, writes_cache=writes_cache)
         ff = layer.feed_forward
-        route = ff.router_args(residual.shape[0], residual.device) if hasattr(ff, "router_args") else None
-        if route is not None:
-            # few rows: the norm kernel runs the layer's router on its unrounded output as it goes
-            n = layer.feed_forward_norm.add_norm(residual, d, route=route)
-            return ff.forward(n, step, routing=(route["ids"], route["wts"]))
-        if getattr(ff, "wants_x32", False):
-            n, n32 = layer.feed_forward_norm.add_norm(residual, d, want32=True)
-            return ff.forward(n, step, x32=n32)
-        n = layer.feed_forward_norm.add_norm(residual, d)
-        return ff.forward(n, step)
+        if hasattr(ff, "forward_from"):
+            return ff.forward_from(layer.feed_forward_norm, residual, d, step)
+        return ff.forward(layer.feed_forward_norm.add_norm(residual, d), step)
 
 
 class Layer:

@@ -43,7 +43,7 @@ class SwiGLU(Part):
                                     runtime.matrix(read(self.n["up"] + ".weight"))]).contiguous()
         self.w_down = runtime.matrix(read(self.n["down"] + ".weight"))
 
-    def forward(self, x, step, x32=None, routing=None):
+    def forward(self, x, step):
         act = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
         tc = self.runtime.tensorcore
         if tc is None or not tc.gated(x, self.w_gate_up, act):      # prompts: gate, up and silu(gate) * up in one kernel
@@ -74,10 +74,7 @@ class SigmoidTopKExperts(Part):
         self._plans: dict[int, ops.MoePlan] = {}
         self._outgrown: list[ops.MoePlan] = []
         self.stacked = False
-        self.record_counts = False  # when set, `last_counts` keeps the pairs routed to each expert in the last pass
-        self.last_counts = None
-        self.load = None            # when set to an integer tensor [experts] on the device: the pairs routed to each
-                                    # expert are added to it in every pass (set it before decode graphs are captured)
+        self.load = None            # see `count_into`
 
     def _stacked(self, present) -> bool:
         return present is not None and (self.base + ".gate_up_proj") in present
@@ -114,7 +111,34 @@ class SigmoidTopKExperts(Part):
                 self.w_gate_up[e, I:].copy_(read(f"{self.base}.{e}.{self.n['up']}.weight"))
                 self.w_down[e].copy_(read(f"{self.base}.{e}.{self.n['down']}.weight"))
 
-    wants_x32 = True        # the block hands the normed rows unrounded as well: router logits are 32-bit end to end
+    def expected_experts_read(self, rows: int) -> float:
+        """Distinct experts that `rows` rows choose when every expert is as likely as any other."""
+        E, k = self.num_experts, self.top_k
+        return E * (1.0 - (1.0 - k / E) ** rows)
+
+    def step_bytes(self, elem: int, experts_read: float | None = None, rows: int = 1, **_) -> int:
+        """The router (32-bit) and the expert bias, and `experts_read` experts' matrices (default: the expected number
+        of distinct experts `rows` rows choose)."""
+        H, I, E = self.hidden_size, self.inter, self.num_experts
+        n = self.expected_experts_read(rows) if experts_read is None else experts_read
+        return int(E * H * 4 + (E * 4 if self.use_bias else 0) + n * 3 * H * I * elem)
+
+    def count_into(self, counts: torch.Tensor | None) -> None:
+        """From now on every pass adds the pairs it routed to each expert to `counts` (an integer tensor [experts] on
+        the device; None stops it). The adding is a kernel of the pass, so it also happens in steps replayed from CUDA
+        graphs that were captured while it was on; the engine drops its graphs when it switches this."""
+        self.load = counts
+
+    def forward_from(self, norm, residual, delta, step):
+        """The norm in front and this layer in one go. The router's logits are 32-bit end to end: for few rows the norm
+        kernel runs the router itself on its unrounded output as it goes; for many, it also hands the unrounded rows."""
+        route = self.router_args(residual.shape[0], residual.device)
+        if route is not None:
+            x = norm.add_norm(residual, delta, route=route)
+            return self.forward(x, step, routing=(route["ids"], route["wts"]))
+        x, x32 = norm.add_norm(residual, delta, want32=True)
+        return self.forward(x, step, x32=x32)
+
     def router_args(self, rows: int, device):
         """What the norm kernel in front of the layer needs to run this layer's router on its `rows` output rows
         (for many rows the kernel norms several rows per block, so the router's weights are read once per block)."""
@@ -150,14 +174,14 @@ class SigmoidTopKExperts(Part):
         the router; else it runs here, on `x32` (the unrounded normed rows) where given."""
         R, H = x.shape[0], self.hidden_size
         ids, wts = routing if routing is not None else self.route(x32 if x32 is not None else x.float())
+        if step is not None and step.trace is not None:
+            step.trace.setdefault("routes", []).append((self.prefix, ids))
         tc = self.runtime.tensorcore
         if tc is not None and x.dtype == torch.bfloat16:
             rows = tc.experts(self, x, ids, wts)
             if rows is not None:
                 return rows
         plan = self.plan_for(R * self.top_k, x.device).build(ids)
-        if self.record_counts:
-            self.last_counts = plan.counts.clone()
         if self.load is not None:
             self.load.add_(plan.counts)
         act = torch.empty(R * self.top_k, self.inter, dtype=x.dtype, device=x.device)

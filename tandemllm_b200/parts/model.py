@@ -44,8 +44,8 @@ class DecoderModel:
         s = self.spec
         present = weights.present()
         specs = self.weight_specs(present)
-        # a tied model may still store a copy of the head: it is not read, and not an error
-        weights.check(specs, ignore=(lambda n: n == "lm_head.weight") if s.head_name is None else None)
+        ignored = set(s.ignored_names)
+        weights.check(specs, ignore=(lambda n: n in ignored) if ignored else None)
         self.runtime = runtime
         self.embedding = runtime.matrix(weights.read(s.embedding_name))
         self.head = runtime.matrix(weights.read(s.head_name)) if s.head_name else self.embedding
@@ -67,6 +67,32 @@ class DecoderModel:
                     elif hasattr(v, "weight_specs") and v is not o:
                         stack.append(v)
         return total
+
+    def decode_bytes(self, batch: int, experts_read: list[float] | None = None) -> dict:
+        """Bytes of weights one decode step of `batch` rows reads, every weight it uses once (the reference accounts a
+        token the same way, engine/models/lfm2_moe/pack.py:292-315): per site of the run order its norms', mixer's and
+        feed-forward's weights as the parts themselves count them (`Part.step_bytes`), the last norm, the head, and
+        `batch` rows of the embedding. `experts_read[i]`: the experts the i-th routed site of the run order really
+        read (default: what uniform routing of `batch` rows would). The cache's bytes are the engine's to add."""
+        elem = torch.empty(0, dtype=self.runtime.dtype).element_size() if self.runtime else 2
+        it = iter(experts_read) if experts_read is not None else None
+        dense = experts = 0
+        for site in self.spec.schedule:
+            layer = self.layers[site.layer]
+            for part in layer.parts:
+                if hasattr(part, "expected_experts_read"):
+                    n = next(it) if it is not None else None
+                    whole = part.step_bytes(elem, experts_read=n, rows=batch)
+                    fixed = part.step_bytes(elem, experts_read=0)
+                    dense += fixed
+                    experts += whole - fixed
+                else:
+                    dense += part.step_bytes(elem)
+        dense += self.final_norm.step_bytes(elem)
+        head = self.vocab_size * self.hidden_size * elem
+        embed = batch * self.hidden_size * elem
+        return {"dense": dense, "experts": experts, "head": head, "embedding_rows": embed,
+                "total": dense + experts + head + embed}
 
     @property
     def graph_safe(self) -> bool:

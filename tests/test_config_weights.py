@@ -86,25 +86,28 @@ def test_registering_another_architecture(tmp_path):
         layer = LayerSpec("blocks.0.", PartSpec("short_conv", {"taps": 2, "names": {"in": "a", "taps": "b", "out": "c"}}),
                           PartSpec("swiglu", {"intermediate_size": 32, "names": {"gate": "g", "up": "u", "down": "d"}}),
                           PartSpec("rmsnorm", {"eps": raw["eps"], "name": "n1"}), PartSpec("rmsnorm", {"eps": raw["eps"], "name": "n2"}))
-        return ModelSpec("ToyForCausalLM", 16, 40, (layer,), (Site(0), Site(0)), norm)
+        return ModelSpec("ToyForCausalLM", 16, 40, (layer,), (Site(0), Site(0)), norm, embedding_name="tok.weight",
+                         final_norm_prefix="last_norm.")
     register(Architecture("toy", ("ToyForCausalLM",), ("toy",), read))
     try:
         (tmp_path / "config.json").write_text(json.dumps({"architectures": ["ToyForCausalLM"], "eps": 1e-5}))
         arch, spec = read_model_config(str(tmp_path))
         assert arch.name == "toy" and len(spec.schedule) == 2
         names = [s.name for s in DecoderModel(spec).weight_specs()]
-        assert "blocks.0.a.weight" in names and "blocks.0.n1.weight" in names and "embedding_norm.weight" in names
+        assert "blocks.0.a.weight" in names and "blocks.0.n1.weight" in names and "last_norm.weight" in names and "tok.weight" in names
     finally:
         unregister("toy")
 
 
 def test_schedule_is_checked():
     norm = PartSpec("rmsnorm", {"eps": 1e-5})
+    names = dict(embedding_name="e.weight", final_norm_prefix="n.")
     with pytest.raises(ValueError, match="not before"):
-        ModelSpec("X", 8, 8, (), (Site(0, cache_of=0),), norm) if False else ModelSpec(
-            "X", 8, 8, (None,), (Site(0), Site(0, cache_of=1)), norm)
+        ModelSpec("X", 8, 8, (None,), (Site(0), Site(0, cache_of=1)), norm, **names)
     with pytest.raises(ValueError, match="names layer"):
-        ModelSpec("X", 8, 8, (None,), (Site(1),), norm)
+        ModelSpec("X", 8, 8, (None,), (Site(1),), norm, **names)
+    with pytest.raises(TypeError, match="embedding_name"):      # an architecture names its own tensors: no default
+        ModelSpec("X", 8, 8, (None,), (Site(0),), norm)
 
 
 # ------------------------------------------------------------------------------------------ weights

@@ -1,0 +1,139 @@
+"""The knob table, the command line's help and argument errors, the decode-graph context buckets, a slot's initial
+value, and the model's byte account: everything here runs without a GPU."""
+
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tests import tiny_configs as T
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PACKAGE = os.path.join(ROOT, "tandemllm_b200")
+
+
+def test_every_knob_is_read_through_the_table():
+    """No module of the package looks at the environment except `settings.py` (the reference holds its engine to the
+    same rule, tests/test_settings.py there)."""
+    offenders = []
+    for folder, _, files in os.walk(PACKAGE):
+        for name in files:
+            if not name.endswith(".py") or os.path.join(folder, name) == os.path.join(PACKAGE, "settings.py"):
+                continue
+            text = open(os.path.join(folder, name)).read()
+            for m in re.finditer(r"os\.environ|os\.getenv|getenv\(|environ\[", text):
+                offenders.append(f"{os.path.relpath(os.path.join(folder, name), ROOT)}:{text[:m.start()].count(chr(10)) + 1}")
+    assert not offenders, offenders
+    for script in ("bin/trace_run", "bench.py", "microbench.py", "__graft_entry__.py"):
+        assert "os.environ" not in open(os.path.join(ROOT, script)).read(), script
+
+
+def test_knobs_have_defaults_readers_and_live_values():
+    from tandemllm_b200.settings import KNOBS, Settings
+    for name, (default, meaning, reader) in KNOBS.items():
+        assert meaning and os.path.isfile(os.path.join(PACKAGE, reader)), name
+        text = open(os.path.join(PACKAGE, reader)).read()
+        assert f'"{name}"' in text, f"{reader} does not read {name}"
+    s = Settings(env={"TANDEMLLM_GRAPHS": "5", "TANDEMLLM_NVCC": ""})
+    assert s.get_int("GRAPHS") == 5 and s.is_set("GRAPHS") and s.get("NVCC") is None and not s.is_set("NVCC")
+    assert Settings(env={}).get_int("GRAPHS") == int(KNOBS["GRAPHS"][0])
+    with pytest.raises(KeyError, match="not a registered knob"):
+        s.get("NO_SUCH_KNOB")
+    with pytest.raises(ValueError, match="integer"):
+        Settings(env={"TANDEMLLM_GRAPHS": "many"}).get_int("GRAPHS")
+    d = s.describe()
+    assert d["GRAPHS"]["value"] == "5" and d["GRAPHS"]["set"] and d["BUILD_DIR"]["read_in"] == "kernels/build.py"
+
+
+def test_build_reads_its_knobs_from_the_live_environment(monkeypatch, tmp_path):
+    from tandemllm_b200.kernels import build
+    monkeypatch.setenv("TANDEMLLM_BUILD_DIR", str(tmp_path / "b"))
+    assert build.build_dir() == str(tmp_path / "b")
+    fake = tmp_path / "nvcc"
+    fake.write_text("#!/bin/sh\n")
+    fake.chmod(0o755)
+    monkeypatch.setenv("TANDEMLLM_NVCC", str(fake))
+    assert build.find_nvcc() == str(fake)
+
+
+def run_cli(*args):
+    return subprocess.run([sys.executable, "-m", "tandemllm_b200", *args], cwd=ROOT, capture_output=True, text=True, timeout=120)
+
+
+def test_command_line_help_and_argument_errors(tmp_path):
+    r = run_cli("--help")
+    assert r.returncode == 0 and "generate" in r.stdout and "random-weights" in r.stdout and "replay" in r.stdout
+    r = run_cli("generate", "--help")
+    for option in ("--model", "--max-len", "--temperature", "--top-p", "--top-k", "--parallel", "--tokens", "--graph", "--json", "--log"):
+        assert option in r.stdout, option
+    assert run_cli().returncode == 2
+    assert run_cli("generate", "--dtype", "float16").returncode == 2
+    r = run_cli("generate")
+    assert r.returncode != 0 and "--model" in r.stderr
+    r = run_cli("generate", "--random-weights", "3")
+    assert r.returncode != 0 and "--config" in r.stderr
+    r = run_cli("random-weights", "--out", str(tmp_path / "m"))
+    assert r.returncode == 2 and "--config" in r.stderr
+
+
+def test_random_weights_command_writes_a_folder_the_loader_takes(tmp_path):
+    import json
+
+    from tandemllm_b200.config import read_model_config, spec_of
+    from tandemllm_b200.parts.model import DecoderModel
+    from tandemllm_b200.weights.loader import FolderWeights
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(T.TINY_A))
+    r = run_cli("random-weights", "--config", str(cfg), "--out", str(tmp_path / "m"), "--seed", "4", "--dtype", "float32")
+    assert r.returncode == 0, r.stderr
+    arch, config = read_model_config(str(tmp_path / "m"))
+    spec = spec_of(config)
+    weights = FolderWeights(str(tmp_path / "m"), spec.name_prefixes)
+    weights.check(DecoderModel(spec).weight_specs(weights.present()))
+
+
+def test_context_buckets_of_decode_graphs_are_few_and_close():
+    from tandemllm_b200.engine.step import context_bucket
+    seen = set()
+    for n in list(range(1, 20000)) + list(range(20000, 131073, 7)):
+        b = context_bucket(n)
+        assert n <= b and (b <= 1024 or b - n < max(1024, n // 7)), (n, b)
+        seen.add(b)
+    assert len(seen) <= 48
+
+
+def test_a_slot_starts_from_what_its_need_says():
+    from tandemllm_b200.cache.manager import CacheManager
+    from tandemllm_b200.parts.base import SlotNeed
+    needs = [SlotNeed((2, 3)), SlotNeed((3,), torch.float32, init=1.5), SlotNeed((2, 3), torch.float32, init=torch.arange(3.0))]
+    cache = CacheManager(needs, num_pages=4, max_requests=2, device="cpu")
+    for sc in cache.site_cache:
+        sc.state.fill_(7.0)
+    slot = cache.admit("r")
+    assert torch.equal(cache.site_cache[0].state[slot], torch.zeros(2, 3))
+    assert torch.equal(cache.site_cache[1].state[slot], torch.full((3,), 1.5))
+    assert torch.equal(cache.site_cache[2].state[slot], torch.arange(3.0).expand(2, 3))
+    assert float(cache.site_cache[0].state[1 - slot].min()) == 7.0           # the other slot is left alone
+
+
+def test_the_model_accounts_the_bytes_of_a_decode_step_from_its_parts():
+    from tandemllm_b200.config import Lfm2MoeConfig
+    from tandemllm_b200.parts.model import DecoderModel
+    c = Lfm2MoeConfig.from_dict(T.TINY_A)
+    model = DecoderModel(c.to_spec())
+    H, V, I, Im, E, k = 64, 256, 128, 32, 4, 2
+    got = model.decode_bytes(batch=3, experts_read=[2, 3, 4])
+    conv = (3 * H * H + H * H) * 2 + H * 3 * 4 + 2 * H * 4               # in/out matrices (bf16), taps and two norms (32-bit)
+    attn = (4 * 16 + 2 * 2 * 16) * H * 2 + H * 4 * 16 * 2 + 2 * 16 * 4 + 2 * H * 4
+    router = E * H * 4 + E * 4
+    want_dense = 2 * conv + 2 * attn + 3 * H * I * 2 + 3 * router + H * 4
+    assert got["dense"] == want_dense
+    assert got["experts"] == (2 + 3 + 4) * 3 * H * Im * 2
+    assert got["head"] == V * H * 2 and got["embedding_rows"] == 3 * H * 2
+    assert got["total"] == got["dense"] + got["experts"] + got["head"] + got["embedding_rows"]
+    # without a count: what uniform routing would read
+    uniform = model.decode_bytes(batch=3)["experts"]
+    assert uniform == 3 * int(E * (1 - (1 - k / E) ** 3) * 3 * H * Im * 2)
