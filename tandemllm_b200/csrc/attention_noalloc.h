@@ -23,6 +23,11 @@
 //    streams, two host threads) race on it and give wrong results; run them one after another on one stream.
 //  * Nothing in the array has to start at zero and nothing is cleared: the join kernel reads exactly the elements that
 //    the span kernel of the same call wrote. What an earlier call left behind is never read.
+//  * `n_spans` must cover the longest row: n_spans >= max(positions) / 256 + 1 (what tl_attention_spans returns for the
+//    longest context). A row that lies past it is not read out of bounds: its keys beyond the last span are left out, the
+//    status word gets 3, and the result of that row is wrong. `num_pages` is the number of pages in k_cache and v_cache;
+//    a block-table entry at or beyond it is treated as a missing page (status 3), as everywhere in this library
+//    (0: the pool's size is unknown and only an entry's sign is checked).
 //  * It calls no cudaMalloc, no cudaFree and no library routine that allocates. Inputs, outputs, the block table and
 //    the status word are the caller's, exactly as for tl_paged_attention_split.
 #pragma once
@@ -38,7 +43,7 @@ extern "C" {
 // Same arguments and result as tl_paged_attention_split without its `scratch` argument. Returns 0, a cudaError_t, or
 // TL_BAD_ARGUMENT (100001) after storing a message that tl_last_error() returns.
 int tl_paged_attention_split_static(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                    int max_pages, int page_size, const int* req_of_row, const int* positions,
+                                    int max_pages, int page_size, int num_pages, const int* req_of_row, const int* positions,
                                     float scale, int window, void* out, int rows, int Hq, int Hk, int D, int n_spans,
                                     int dtype, int* status, cudaStream_t stream);
 

@@ -52,6 +52,9 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
   const int tid = threadIdx.x;
   const int pos = positions[r];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  // A row whose position lies past the spans the caller sized its scratch for: its far keys have no CTA and no place in
+  // the scratch. Recorded like a visible key without a page (the join stops at the last span there is).
+  if (span == n_spans - 1 && tid == 0 && pos / SPAN >= n_spans && status != nullptr) atomicExch(status, 3);
   const int k_begin = max(lo, span * SPAN), k_end = min(pos + 1, (span + 1) * SPAN);
   if (k_begin >= k_end) return;
   const int n_keys = k_end - k_begin;
@@ -278,8 +281,8 @@ __global__ void attention_join_kernel(const float* __restrict__ part_o, const fl
   const int r = blockIdx.x, h = blockIdx.y;
   const int pos = positions[r];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-  const int s0 = lo / span_keys, s1 = pos / span_keys;
-  if (s0 == s1) return;                                 // written directly by the span kernel
+  const int s0 = lo / span_keys, s1 = min(pos / span_keys, n_spans - 1);      // never past the scratch's last span
+  if (s0 >= s1) return;                                 // one span: written directly by the span kernel
   const long long base = ((long long)r * Hq + h) * n_spans;
   // Spans are taken eight at a time, with all of a group's loads issued before the first is used: taken one by one,
   // every span would cost a trip to memory of its own.
@@ -419,7 +422,7 @@ static float* tl_static_scratch_address[TL_MAX_DEVICES];     // per device, look
 static std::mutex tl_static_scratch_mutex;
 
 extern "C" int tl_paged_attention_split_static(const void* q, const void* k_cache, const void* v_cache,
-                                               const int* block_table, int max_pages, int page_size,
+                                               const int* block_table, int max_pages, int page_size, int num_pages,
                                                const int* req_of_row, const int* positions, float scale, int window,
                                                void* out, int rows, int Hq, int Hk, int D, int n_spans, int dtype,
                                                int* status, cudaStream_t stream) {
@@ -448,7 +451,6 @@ extern "C" int tl_paged_attention_split_static(const void* q, const void* k_cach
     scratch = tl_static_scratch_address[device];
   }
   // from here on it is the ordinary entry point, which launches the two kernels and allocates nothing
-  // (the pool's size is not among this entry point's arguments: 0, only the sign of a table entry is checked)
-  return tl_paged_attention_split(q, k_cache, v_cache, block_table, max_pages, page_size, 0, req_of_row, positions, scale,
+  return tl_paged_attention_split(q, k_cache, v_cache, block_table, max_pages, page_size, num_pages, req_of_row, positions, scale,
                                   window, out, scratch, rows, Hq, Hk, D, n_spans, dtype, status, stream);
 }

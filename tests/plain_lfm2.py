@@ -5,10 +5,13 @@ Every function is written from the reference's formulas and cites where (paths a
 project's own). The reference's model code imports on the CPU here, and this file was compared with it
 once on a tiny random model: `tests/golden/make_golden.py` ran `Lfm2MoeRef` (engine/models/lfm2_moe/ref.py)
 and stored its logits in `tests/golden/tiny_a_reference.npz`; `tests/test_plain.py` holds this file to
-those numbers. Three options the reference refuses (engine/models/lfm2_moe/config.py:47-48: conv bias,
-un-normalised top-k weights, an untied head) rest on the formulas alone: the bias vectors are added where
-a bias of that projection or convolution belongs, the renormalisation step is skipped, and the head
-reads `lm_head.weight`.
+those numbers. Three options the reference refuses for this family (engine/models/lfm2_moe/config.py:47-48:
+conv bias, un-normalised top-k weights, an untied head) cannot be run through that class; they rest on the
+formulas, read where the reference's sibling families implement the same options: a causal depthwise
+convolution's bias is added to the tap sum before what follows it (engine/models/nemotron_h/ref.py:195-201),
+projection biases are those of a linear layer, un-normalised top-k weights skip the division and nothing else
+(engine/models/flashnext/ref.py:484-485; the scaling is a line of its own, engine/models/lfm2_moe/ref.py:197),
+and the head reads `lm_head.weight` when there is one (engine/models/lfm2_moe/ref.py:96-97).
 
 Weights are a dict of canonical names (the checkpoint's without `model.`), as in ref.py:21-29.
 The configuration is a plain dict with config.json's keys.
@@ -121,17 +124,21 @@ def dense_mlp(n: torch.Tensor, W: dict, p: str) -> torch.Tensor:
     return (torch.nn.functional.silu(n @ W[p + "w1.weight"].T) * (n @ W[p + "w3.weight"].T)) @ W[p + "w2.weight"].T
 
 
-def route(n: torch.Tensor, W: dict, p: str, cfg: dict) -> tuple[torch.Tensor, torch.Tensor]:
+def route(n: torch.Tensor, W: dict, p: str, cfg: dict, forced: torch.Tensor | None = None
+          ) -> tuple[torch.Tensor, torch.Tensor]:
     """(ids [T, k], weights [T, k]) (engine/models/lfm2_moe/ref.py:185-197): sigmoid scores; with an expert bias the
     choice is the top-k of score + bias and the weights are the chosen scores; weights / (sum + 1e-6) when
     normalised (always, in the reference); times routed_scaling_factor. Ties go to the lower expert id
-    (engine/models/lfm2_moe/kernels.py:277)."""
+    (engine/models/lfm2_moe/kernels.py:277). `forced` [T, k] replaces the choice (the weights are still this
+    function's own): what another implementation chose at a near tie."""
     k = cfg_get(cfg, "num_experts_per_tok", 4)
     logits = n @ W[p + "gate.weight"].T
     s = logits.sigmoid()
     choice = s + W[p + "expert_bias"] if cfg_get(cfg, "use_expert_bias", True) else s
     # stable descending sort: the lower id first among equals
     ids = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :k]
+    if forced is not None:
+        ids = forced.long()
     w = torch.gather(s, 1, ids)
     if cfg_get(cfg, "norm_topk_prob", True):
         w = w / (w.sum(dim=-1, keepdim=True) + 1e-6)
@@ -156,12 +163,13 @@ def routing_margin(n: torch.Tensor, W: dict, p: str, cfg: dict) -> torch.Tensor:
     return top[:, k - 1] - top[:, k]
 
 
-def moe(n: torch.Tensor, W: dict, p: str, cfg: dict, margins: list | None = None) -> torch.Tensor:
+def moe(n: torch.Tensor, W: dict, p: str, cfg: dict, margins: list | None = None,
+        forced: torch.Tensor | None = None) -> torch.Tensor:
     """engine/models/lfm2_moe/ref.py:207-214: each chosen expert's output times its weight, added in ascending
     expert id. `margins`, when given, collects each layer's routing margins."""
     if margins is not None:
         margins.append(routing_margin(n, W, p, cfg))
-    ids, w = route(n, W, p, cfg)
+    ids, w = route(n, W, p, cfg, forced)
     out = torch.zeros_like(n)
     for e in sorted(set(ids.reshape(-1).tolist())):
         rows, slot = torch.where(ids == e)
@@ -170,11 +178,12 @@ def moe(n: torch.Tensor, W: dict, p: str, cfg: dict, margins: list | None = None
 
 
 def forward(cfg: dict, W: dict, tokens: list[int] | torch.Tensor, dtype=torch.float32,
-            margins: list | None = None) -> torch.Tensor:
+            margins: list | None = None, forced_routes: dict | None = None, rows: list[int] | None = None) -> torch.Tensor:
     """Logits [T, vocab] (32-bit) of a whole sequence (engine/models/lfm2_moe/ref.py:218-241): embed; per layer
     n = norm(h), h += mixer(n), n = norm(h), h += ffn(n); final norm `embedding_norm`; head = lm_head.weight
     if the model has an untied head, else the embedding. `margins` collects the routing margins [T] of every
-    MoE layer."""
+    MoE layer. `forced_routes` {layer index: ids [T, k]} replaces those layers' choice of experts. `rows`: the
+    logits of these positions only (the head of a large vocabulary over thousands of rows is most of the work)."""
     W = {k: (v.to(dtype) if v.is_floating_point() and not k.endswith("expert_bias") else v) for k, v in W.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     eps = cfg_get(cfg, "norm_eps", 1e-5)
@@ -190,7 +199,10 @@ def forward(cfg: dict, W: dict, tokens: list[int] | torch.Tensor, dtype=torch.fl
             h = h + short_conv(n, W, p + "conv.", cfg_get(cfg, "conv_L_cache", 3), bool(cfg.get("conv_bias", False)))
         n = rms_norm(h, W[p + "ffn_norm.weight"], eps)
         f = p + "feed_forward."
-        h = h + (moe(n, W, f, cfg, margins) if li >= dense_layers else dense_mlp(n, W, f))
+        forced = forced_routes.get(li) if forced_routes else None
+        h = h + (moe(n, W, f, cfg, margins, forced) if li >= dense_layers else dense_mlp(n, W, f))
+    if rows is not None:
+        h = h[torch.as_tensor(rows, dtype=torch.long)]
     h = rms_norm(h, W["embedding_norm.weight"], eps)
     tied = cfg.get("tie_word_embeddings", cfg.get("tie_embedding", True))
     head = W["embed_tokens.weight"] if tied else W["lm_head.weight"]

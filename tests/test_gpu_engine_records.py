@@ -1,0 +1,145 @@
+"""The engine's per-step records and routing counts, the bound on captured decode graphs, and the command line run as a
+user runs it (random-weights, then generate), on the GPU."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tests import plain_lfm2 as P
+from tests import tiny_configs as T
+from tests.helpers import random_model_weights, write_folder
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def folder_of(name, tmp_path, dtype=torch.float32):
+    cfg = T.CONFIGS[name]
+    W = random_model_weights(cfg, T.SEEDS[name], T.STD[name], bf16_exact=True)
+    return write_folder(str(tmp_path / name), cfg, W, dtype), cfg, W
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_every_step_leaves_a_record_and_a_log_line(tmp_path, dtype):
+    from tandemllm_b200.engine import Engine, EngineArgs
+    from tandemllm_b200.sampling import SamplingParams
+    folder, cfg, W = folder_of("c", tmp_path, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    log = tmp_path / "steps.jsonl"
+    eng = Engine.from_folder(folder, EngineArgs(dtype=dtype, max_len=256, parallel=3, chunk_size=16, max_batched_tokens=24,
+                                                log=str(log), record_routing=True))
+    prompts = [T.long_tokens("c", n, seed=3 + n) for n in (40, 9, 21)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    records = list(eng.records)
+    lines = [json.loads(ln) for ln in log.read_text().splitlines()]
+    assert len(lines) == len(records) and len(records) >= 12
+    assert [r["step"] for r in records] == sorted(r["step"] for r in records)
+    # rows: every prompt token and every generated token but each request's last went through a step exactly once
+    assert sum(r["rows"] for r in records) == sum(len(p) for p in prompts) + sum(len(o) - 1 for o in outs)
+    assert sum(r["sampled"] for r in records) == sum(len(o) for o in outs)
+    assert sum(r["finished"] for r in records) == 3
+    moe_layers = sum(1 for i in range(cfg["num_hidden_layers"]) if i >= cfg["num_dense_layers"])
+    k, E = cfg["num_experts_per_tok"], cfg["num_experts"]
+    for r, line in zip(records, lines):
+        assert r["rows"] == r["prompt_rows"] + r["decode_rows"] and r["rows"] <= 24 and r["ms"] > 0
+        assert len(r["experts_touched"]) == moe_layers and r["pairs_routed"] == r["rows"] * k * moe_layers
+        assert all(1 <= n <= min(E, r["rows"] * k) for n in r["experts_touched"])
+        assert r["routed"].shape == (moe_layers * E,) and "routed" not in line
+        assert line["experts_touched"] == r["experts_touched"] and line["pages_used"] == r["pages_used"]
+        assert r["pages_used"][0] + r["pages_free"][0] == eng.cache.groups[0].pool.num_pages
+    assert any(r["from_graph"] for r in records) and not records[0]["from_graph"]
+    # one step's count against the plain implementation's routing of the same rows: the first step is the first portion
+    # (16 tokens) of the first prompt alone
+    first = records[0]
+    assert first["rows"] == 16 and first["requests"] == 1
+    if dtype == "float32":
+        routes = {}
+        orig = P.route
+
+        def spy(n, Wd, p, c, forced=None):
+            ids, w = orig(n, Wd, p, c, forced)
+            routes[p] = ids
+            return ids, w
+        P.route = spy
+        try:
+            P.forward(cfg, W, prompts[0][:16])
+        finally:
+            P.route = orig
+        want = [int(torch.unique(ids).numel()) for _, ids in sorted(routes.items())]
+        assert first["experts_touched"] == want
+    # switching the record off stops the counting and drops nothing else
+    eng.set_routing_record(False)
+    eng.generate([prompts[1]], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    assert "experts_touched" not in eng.last_record
+
+
+def test_captured_decode_graphs_stay_bounded_while_batch_and_context_grow(tmp_path):
+    """Batches of 1 to 6 requests decode, one of them from the third round on at a context in another bucket, with room
+    for 4 graphs only: the step function never keeps more, drops the least recently used, keeps giving the eager
+    engine's logits bit for bit, and the device memory it holds stops growing."""
+    from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
+    folder, cfg, W = folder_of("c", tmp_path, torch.bfloat16)
+    engines = [Engine.from_folder(folder, EngineArgs(dtype="bfloat16", max_len=8192, parallel=6, graph=g)) for g in (True, False)]
+    engines[0].step_function.max_graphs = 4
+    toks = {i: T.long_tokens("c", 40, seed=50 + i) for i in range(6)}
+    reserved = []
+    for eng in engines:
+        for i in toks:
+            eng.admit(i)
+    out = [[], []]
+    for j, eng in enumerate(engines):
+        fn = eng.step_function
+        for i, t in toks.items():
+            # contexts that differ by whole buckets without running thousands of tokens: the cache counts positions only
+            eng.step([StepEntry(i, t[:8], [])])
+        for round_ in range(6):
+            if round_ == 2:
+                eng.step([StepEntry(0, T.long_tokens("c", 1100, seed=99), [])])
+            for B in (1, 2, 3, 6, 4, 5):
+                for _ in range(3):
+                    entries = [StepEntry(i, [toks[i][8 + len(out[j]) % 30]], [0]) for i in range(B)]
+                    out[j].append(eng.step(entries).clone())
+                if j == 0:
+                    assert len(fn._graphs) <= 4
+            if j == 0:
+                torch.cuda.synchronize()
+                reserved.append(torch.cuda.memory_reserved())
+    fn = engines[0].step_function
+    assert fn.graphs_dropped >= 6 and fn.graph_replays > 20 and len(fn._graphs) == 4
+    assert len({k[2] for k in fn._graphs}) == 1 and fn._graphs and next(iter(fn._graphs))[2] == 2048
+    assert reserved[5] <= reserved[3] + (8 << 20), reserved        # no growth once every shape has been seen once
+    assert len(out[0]) == len(out[1])
+    for a, b in zip(*out):
+        assert torch.equal(a, b)
+
+
+def test_random_weights_then_generate_as_subprocesses(tmp_path):
+    """`python -m tandemllm_b200 random-weights` writes a folder, `generate --model` reads it: the printed tokens are
+    the plain implementation's greedy text from the same stored weights."""
+    from tandemllm_b200.weights.safetensors_io import index_folder, read_tensor
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(T.TINY_A))
+    model = tmp_path / "model"
+    run = lambda *args: subprocess.run([sys.executable, "-m", "tandemllm_b200", *args], cwd=ROOT, capture_output=True,
+                                       text=True, timeout=600)
+    r = run("random-weights", "--config", str(cfg), "--out", str(model), "--seed", "9", "--dtype", "float32", "--norm-std", "0.1")
+    assert r.returncode == 0, r.stderr[-2000:]
+    prompts = ["5 17 3 200 41 8", "9,9,250"]
+    log = tmp_path / "log.jsonl"
+    r = run("generate", "--model", str(model), "--dtype", "float32", "--tokens", "8", "--ignore-eos", "--max-len", "128",
+            "--parallel", "2", "--prompt-ids", prompts[0], "--prompt-ids", prompts[1], "--json", str(tmp_path / "out.json"),
+            "--log", str(log), "--log-routing")
+    assert r.returncode == 0, r.stderr[-2000:]
+    printed = [[int(t) for t in ln.split("] ")[1].split()] for ln in r.stdout.splitlines() if ln.startswith("[")]
+    stored = index_folder(str(model))
+    W = {name[len("model."):] if name.startswith("model.") else name: read_tensor(st).float() for name, st in stored.items()}
+    for text, got in zip(prompts, printed):
+        prompt = [int(t) for t in text.replace(",", " ").split()]
+        assert got == P.greedy(T.TINY_A, W, prompt, 8)
+    saved = json.loads((tmp_path / "out.json").read_text())
+    assert saved["outputs"] == printed and saved["generated"] == 16
+    lines = [json.loads(ln) for ln in log.read_text().splitlines()]
+    assert lines and all("experts_touched" in ln and "ms" in ln for ln in lines)

@@ -320,6 +320,75 @@ def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window):
         at += n
 
 
+@pytest.mark.parametrize("use_tma", [1, 0])
+@pytest.mark.parametrize("split", [0, 256])
+@pytest.mark.parametrize("D,page", [(64, 16), (64, 48), (64, 128), (128, 16), (128, 48), (128, 128)])
+def test_window_edge_on_tensor_cores(D, page, split, use_tma):
+    """The tensor-core kernel's window: with a window of w the key w positions behind a row is out and the one w - 1
+    behind it is in. One key is made to match the queries so strongly that the output is its value when it is visible:
+    at the first position inside the window of the checked row (in), and one before it (out). A decode row, and a prompt
+    portion whose rows straddle that key (visible to its first rows, hidden from its last). Pages wholly behind every
+    row's window are gone (-1 in the table), which must not be recorded as a missing page. With and without a split over
+    key spans, with the producer warp's TMA copies and with cp.async from every thread."""
+    import types
+
+    from tandemllm_b200.kernels import ops, tensorcore
+    from tests.test_gpu_kernels import paged_setup, plain_attention
+    impl, rt = tc()
+    lib = tensorcore.lib()
+    Hq, Hk, w = 4, 1, 150
+    seqs, news = [700, 420], [1, 40]                     # a decode row at 699; a portion at positions 380..419
+    lib.tl_attention_mma_use_tma(use_tma)
+    try:
+        for which, hot in (("decode, in", 699 - w + 1), ("decode, out", 699 - w), ("portion, straddled", 419 - w + 1 - 20)):
+            kc, vc, table, ks, vs = paged_setup(seqs, Hk, D, page, torch.bfloat16, seed=70)
+            # every query of a request is one direction plus a little noise, so that one key can match them all
+            g = torch.Generator().manual_seed(71)
+            base = torch.randn(2, D, generator=g)
+            q = torch.cat([(base[bb] + 0.25 * torch.randn(n, Hq, D, generator=g)) for bb, n in enumerate(news)]).to(torch.bfloat16)
+            b = 0 if which.startswith("decode") else 1
+            key = (6 * base[b] / base[b].norm()).to(torch.bfloat16)
+            ks[b][hot] = key.float()
+            kc[int(table[b, hot // page]), :, hot % page] = key
+            for bb, (L, n) in enumerate(zip(seqs, news)):      # pages that even the portion's first row no longer sees
+                table[bb, :max(0, (L - n) - w + 1) // page] = -1
+            positions = sum((list(range(L - n, L)) for L, n in zip(seqs, news)), [])
+            pos_dev = torch.tensor(positions, dtype=torch.int32, device=DEV)
+            step = types.SimpleNamespace(n_requests=2, max_rows_per_request=max(news), max_context=max(seqs),
+                                         positions=pos_dev, host={"row_start": [0, 1, 41]})
+            tiles = impl.query_tiles(step, lib.tl_attention_mma_tile_rows(Hq, Hk))
+            spans = -(-max(seqs) // split) if split else 1
+            R = sum(news)
+            scratch = torch.full((ops.attention_scratch_floats(R, Hq, D, spans),), float("nan"), device=DEV) if split else None
+            out = torch.full((R, Hq, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+            qd, kd, vd, td = q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV)
+            code = lib.tl_paged_attention_mma(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(), table.shape[1], page,
+                                              kd.shape[0], tiles.data_ptr(), tiles.shape[0], int(tiles[:, 2].max()),
+                                              pos_dev.data_ptr(), 1.0, w, out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans,
+                                              int(split), rt.status.data_ptr(), ops.stream())
+            assert code == 0
+            if split:
+                ops.attention_join(scratch, pos_dev, w, out, spans, split)
+            torch.cuda.synchronize()
+            assert int(rt.status) == 0, f"{which}: a page behind the window was asked for"
+            at = 0
+            for bb, (L, n) in enumerate(zip(seqs, news)):
+                want = plain_attention(q[at:at + n].float(), ks[bb], vs[bb], 1.0, w)
+                assert rel(out[at:at + n], want) < 2e-2, f"{which}: sequence {bb}"
+                at += n
+            # the planted key does decide: the rows that see it put most of their weight on it, the others none
+            if b == 0:
+                sees = which == "decode, in"
+                moved = rel(out[:1], vs[0][hot][None].expand(1, Hq, D))
+                assert (moved < 0.2) == sees, (which, moved)
+            else:
+                first, last = out[1], out[40]                  # positions 380 (sees the key) and 419 (does not)
+                assert rel(first[None], vs[1][hot][None].expand(1, Hq, D)) < 0.2
+                assert rel(last[None], vs[1][hot][None].expand(1, Hq, D)) > 0.5
+    finally:
+        lib.tl_attention_mma_use_tma(1)
+
+
 def test_decode_tiles_are_built_on_the_device():
     import types
     impl, rt = tc()
