@@ -215,7 +215,7 @@ def reference_arm(a) -> int:
     def decode(batch: int, context: int, steps: int, warmup: int) -> dict:
         states = []
         for _ in range(batch):
-            st = ref.new_state(context + steps + warmup + 8)
+            st = ref.new_state(context + REPEATS * steps + warmup + 8)
             for li in st.k:                                   # a synthetic context, as in the other arm
                 st.k[li][:, :context - 1].normal_(0, 0.5)
                 st.v[li][:, :context - 1].normal_(0, 0.5)
@@ -349,7 +349,7 @@ class LaunchTimer:
                 "tl_moe_plan": "routing plan", "tl_gather_rows": "rows into expert order", "tl_short_conv": "short conv",
                 "tl_short_conv_decode": "short conv", "tl_short_conv_state": "short conv", "tl_embed_rows": "embedding",
                 "tl_gemm_simt": "32-bit products", "tl_gemm_simt_grouped": "32-bit expert products",
-                "tl_silu_mul": "SwiGLU gate", "tl_argmax": "argmax", "tl_sample": "sampling",
+                "tl_gated_mul": "gate activation", "tl_argmax": "argmax", "tl_sample": "sampling",
                 "tl_router_topk": "router top-k", "tl_moe_combine": "expert combine", "tl_kv_store": "cache write"}.get(name, name)
 
     def __enter__(self):

@@ -199,10 +199,14 @@ __global__ void __launch_bounds__(TMA ? 160 : 128, D == 64 ? (TMA ? 3 : 4) : 2) 
             }
           }
           // values that are not fetched are multiplied by weights of zero: they must be numbers
-          if (!need && which)
+          if (!need && which) {
             for (uint32_t j = 0; j < box_bytes; j += 16) *reinterpret_cast<uint4*>(dst + j) = make_uint4(0u, 0u, 0u, 0u);
+            // these bytes are written by TMA (the async proxy) when the stage comes round again
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          }
         }
         const uint32_t n_need = __popc(__ballot_sync(0xffffffffu, need));
+        __syncwarp();       // every lane's zeros are written before lane 0's arrival, which may complete the phase by itself
         if (lane == 0) mbar_expect_tx(&full[stage], n_need * box_bytes);
         __syncwarp();
         if (need) tma_load_2d(dst, which ? &maps.v : &maps.k, &full[stage], half * 64, y);

@@ -141,6 +141,25 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[32];
 }
 
+// Gated feed-forwards: out = act(gate) * up. The activation travels as an integer (the launchers' `act` / `swiglu`
+// argument: 0 means a plain product without gating, 1 the SiLU of the LFM2 experts). All in 32-bit.
+#define TL_ACT_NONE 0
+#define TL_ACT_SILU 1
+#define TL_ACT_GELU 2        // the exact form: x * 0.5 * (1 + erf(x / sqrt(2)))
+#define TL_ACT_RELU2 3       // max(x, 0)^2
+#define TL_ACT_IDENTITY 4    // gate * up
+#define TL_ACT_LAST 4
+
+__device__ __forceinline__ float gate_activation(float g, int act) {
+  switch (act) {
+    case TL_ACT_GELU: return 0.5f * g * (1.f + erff(g * 0.70710678118654752f));
+    case TL_ACT_RELU2: { const float r = fmaxf(g, 0.f); return r * r; }
+    case TL_ACT_IDENTITY: return g;
+    default: return g / (1.f + expf(-g));
+  }
+}
+__device__ __forceinline__ float gated(float g, float u, int act) { return gate_activation(g, act) * u; }
+
 // The current device's number of SMs (asked once a device; 148 on a B200), for grids sized to the GPU.
 inline int sm_count() {
   static int counts[64] = {0};

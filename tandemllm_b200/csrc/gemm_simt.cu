@@ -29,7 +29,7 @@ struct GemmParams {
   const int* n_tiles;      // [1]
   const int* a_gather;     // [M] or nullptr: A row of sorted row i is a_gather[i] / a_div
   int a_div;
-  int swiglu;              // 1: W holds 2 N rows per group; C = silu(A W[0:N]^T) * (A W[N:2N]^T)
+  int swiglu;              // a gate activation TL_ACT_* (1: SiLU): W holds 2 N rows per group; C = act(A W[0:N]^T) * (A W[N:2N]^T)
 };
 
 template <typename TIn, typename TOut, bool SWIGLU>
@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(256) gemm_tiled_kernel(GemmParams p) {
       if (n >= p.N) continue;
       float v = acc[i][j];
       if constexpr (SWIGLU) {
-        v = v / (1.f + expf(-v)) * acc2[i][j];
+        v = gated(v, acc2[i][j], p.swiglu);
       } else {
         if (p.bias) v += p.bias[n];
       }

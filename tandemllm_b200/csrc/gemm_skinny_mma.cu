@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
     long long ldw, long long rows_per_group, TOut* __restrict__ out, long long ldc, int N, int K,
     const int* __restrict__ tile_group, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
     const int* __restrict__ n_tiles, const int* __restrict__ pair_group, int n_pairs, int n_groups,
-    int* __restrict__ status, uint32_t zero) {
+    int* __restrict__ status, int act, uint32_t zero) {
   constexpr int W_TILES = SWIGLU ? 2 : 1;
   constexpr int UNROLL = SWIGLU ? 4 : 8;
   __shared__ float part[SKINNY_WARPS][W_TILES][16][8 + 1];
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
 #pragma unroll
       for (int s = 0; s < SKINNY_WARPS; ++s) v[j] += part[s][j][row][m];
     }
-    const float r = SWIGLU ? v[0] / (1.f + expf(-v[0])) * v[W_TILES - 1] : v[0];
+    const float r = SWIGLU ? gated(v[0], v[W_TILES - 1], act) : v[0];
     out[(long long)s_pair[m] * ldc + n0 + row] = from_f32<TOut>(r);
   }
 }
@@ -377,7 +377,7 @@ extern "C" int tl_gemm_skinny_mma(const void* x, long long ldx, const void* w, l
 }
 
 // The routed experts of a very small step. x [*, K] bfloat16; w [groups * rows_per_group, K] bfloat16 with, per group, N
-// rows (or, with swiglu, N gate rows then N up rows); the plan's tiles hold at most 8 rows; out [pairs, N] in the plan's
+// rows (or, with swiglu, which is then the gate's activation TL_ACT_*, N gate rows then N up rows); the plan's tiles hold at most 8 rows; out [pairs, N] in the plan's
 // order, bfloat16 or 32-bit. row_index (or null) and row_div as in the kernel's comment.
 extern "C" int tl_gemm_skinny_grouped(const void* x, long long ldx, const int* row_index, int row_div, const void* w,
                                       long long ldw, long long rows_per_group, void* out, long long ldc, int N, int K,
@@ -393,11 +393,13 @@ extern "C" int tl_gemm_skinny_grouped(const void* x, long long ldx, const int* r
                              : (tile_group && tile_row0 && tile_rows && n_tiles)),
              "skinny grouped product: operands must be 16-byte aligned and the plan complete, or at most %d pairs given",
              SKINNY_WARPS * 32);
+  TL_REQUIRE(swiglu >= 0 && swiglu <= TL_ACT_LAST, "skinny grouped product: gate activation %d is not one of 0..%d", swiglu,
+             TL_ACT_LAST);
   const dim3 grid(ceil_div(N, 16), max_tiles), block(SKINNY_WARPS * 32);
 #define TL_GROUPED(SW_, T_)                                                                                              \
   return (int)launch_chained(gemm_skinny_grouped_kernel<SW_, T_>, grid, block, 0, stream, (const bf16*)x, ldx, row_index,  \
                              row_div, (const bf16*)w, ldw, rows_per_group, (T_*)out, ldc, N, K, tile_group, tile_row0,    \
-                             tile_rows, n_tiles, pair_group, n_pairs, n_groups, status, 0u)
+                             tile_rows, n_tiles, pair_group, n_pairs, n_groups, status, swiglu, 0u)
   if (swiglu) {
     if (out_dtype == TL_FP32) TL_GROUPED(true, float);
     TL_GROUPED(true, bf16);

@@ -247,6 +247,8 @@ extern "C" int tl_router_topk(const float* logits, long long ld, const float* bi
   TL_REQUIRE(k > 0 && k <= E && k <= MAX_TOP_K, "router: top-%d of %d experts; up to top-%d is implemented", k, E,
              MAX_TOP_K);
   TL_REQUIRE(ld >= E, "router: row stride %lld for %d experts", ld, E);
+  TL_REQUIRE(normalize >= 0 && (normalize >> 1) <= TL_SCORE_LAST, "router: scoring function %d is not one of 0..%d",
+             normalize >> 1, TL_SCORE_LAST);
   router_topk_kernel<<<ceil_div(rows, 4), 128, 0, stream>>>(logits, ld, bias, rows, E, k, normalize, floor_, scale, ids,
                                                             wts);
   TL_LAUNCH_CHECK();

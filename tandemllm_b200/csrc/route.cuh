@@ -1,12 +1,21 @@
-// The router's choice for one row, run by one full warp: sigmoid scores, the top-k of score + bias (the bias for
-// the choice only), weights = chosen scores, divided by (their sum + floor) when normalised, times scale.
+// The router's choice for one row, run by one full warp: scores (the sigmoid of each logit, or the softmax over all
+// experts' logits), the top-k of score + bias (the bias for the choice only), weights = chosen scores, divided by
+// (their sum + floor) when normalised, times scale.
 // Ties go to the lower expert id; a NaN score is chosen only when nothing else is left.
-// (engine/models/lfm2_moe/ref.py:185-197, engine/models/lfm2_moe/kernels.py:265-287 of the reference)
+// (engine/models/lfm2_moe/ref.py:185-197, engine/models/lfm2_moe/kernels.py:265-287 of the reference; the softmax
+// scoring is what its other routed families use, engine/models/flashnext/ref.py:479-487)
+//
+// The launchers' `normalize` argument carries both choices: bit 0 = divide the chosen weights by their sum,
+// bits 1.. = the scoring function (TL_SCORE_SIGMOID 0, TL_SCORE_SOFTMAX 1).
 #pragma once
 
 #include "common.cuh"
 
 namespace tl {
+
+#define TL_SCORE_SIGMOID 0
+#define TL_SCORE_SOFTMAX 1
+#define TL_SCORE_LAST 1
 
 constexpr int MAX_EXPERTS = 1024;
 constexpr int MAX_TOP_K = 32;
@@ -17,12 +26,26 @@ template <int PER>
 __device__ __forceinline__ void warp_route_sized(const float* lg, const float* __restrict__ bias, int E, int k,
                                                  int normalize, float floor_, float scale, int* ids, float* wts) {
   const int lane = threadIdx.x & 31;
+  const int scoring = normalize >> 1;
+  normalize &= 1;
   float score[PER], choice[PER];
+  float top = -INFINITY, denom = 1.f;
+  if (scoring == TL_SCORE_SOFTMAX) {        // the row's largest logit and the sum of exponentials, over the whole warp
+#pragma unroll
+    for (int t = 0; t < PER; ++t)
+      if (lane + 32 * t < E) top = fmaxf(top, lg[lane + 32 * t]);
+    top = warp_max(top);
+    float part = 0.f;
+#pragma unroll
+    for (int t = 0; t < PER; ++t)
+      if (lane + 32 * t < E) part += expf(lg[lane + 32 * t] - top);
+    denom = warp_sum(part);
+  }
 #pragma unroll
   for (int t = 0; t < PER; ++t) {
     const int e = lane + 32 * t;
     if (e < E) {
-      const float s = 1.f / (1.f + expf(-lg[e]));
+      const float s = scoring == TL_SCORE_SOFTMAX ? expf(lg[e] - top) / denom : 1.f / (1.f + expf(-lg[e]));
       score[t] = s;
       choice[t] = bias ? s + bias[e] : s;
       if (!(choice[t] == choice[t])) choice[t] = -INFINITY;

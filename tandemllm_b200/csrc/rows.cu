@@ -397,9 +397,9 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
   }
 }
 
-// out[r, i] = silu(gate_up[r, i]) * gate_up[r, inter + i]
+// out[r, i] = act(gate_up[r, i]) * gate_up[r, inter + i]
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows, int inter, int act) {
   chain_next();
   chain_wait();
   const long long n = rows * inter;
@@ -408,7 +408,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     const int c = (int)(i - r * inter);
     const float g = to_f32(gate_up[r * 2 * inter + c]);
     const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
-    out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
+    out[i] = from_f32<T>(gated(g, u, act));
   }
 }
 
@@ -450,6 +450,8 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
     TL_REQUIRE(E > 0 && E <= MAX_EXPERTS, "router: %d experts; up to %d are implemented", E, MAX_EXPERTS);
     TL_REQUIRE(route_k > 0 && route_k <= E && route_k <= MAX_TOP_K && route_ids && route_wts,
                "router: top-%d of %d experts; up to top-%d is implemented", route_k, E, MAX_TOP_K);
+    TL_REQUIRE(normalize >= 0 && (normalize >> 1) <= TL_SCORE_LAST, "router: scoring function %d is not one of 0..%d",
+               normalize >> 1, TL_SCORE_LAST);
   }
   // prompts: several rows a block (eight beside a router, whose weights are then read once for eight rows)
   int rows_per_block = out_rows > 64 ? (router_w ? MAX_ROWS_PER_BLOCK : PLAIN_ROWS_PER_BLOCK) : 1;
@@ -494,18 +496,20 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
 #undef TL_NORM1
 }
 
-extern "C" int tl_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, cudaStream_t stream) {
+// out [rows, inter] = act(gate_up[:, :inter]) * gate_up[:, inter:], act one of TL_ACT_SILU .. TL_ACT_IDENTITY
+extern "C" int tl_gated_mul(const void* gate_up, void* out, int rows, int inter, int act, int dtype, cudaStream_t stream) {
   if (rows == 0) return 0;
-  TL_REQUIRE(rows > 0 && inter > 0, "silu_mul: rows %d width %d", rows, inter);
+  TL_REQUIRE(rows > 0 && inter > 0, "gated_mul: rows %d width %d", rows, inter);
+  TL_REQUIRE(act >= TL_ACT_SILU && act <= TL_ACT_LAST, "gated_mul: gate activation %d is not one of 1..%d", act, TL_ACT_LAST);
   const long long n = (long long)rows * inter;
   const long long most = (long long)sm_count() * 16;
   const int blocks = (int)(ceil_div64(n, 256) < most ? ceil_div64(n, 256) : most);
   cudaError_t e;
   if (dtype == TL_FP32)
     e = launch_chained(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out,
-                       (long long)rows, inter);
+                       (long long)rows, inter, act);
   else
     e = launch_chained(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out,
-                       (long long)rows, inter);
+                       (long long)rows, inter, act);
   return (int)e;
 }

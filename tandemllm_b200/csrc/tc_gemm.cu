@@ -46,8 +46,15 @@ struct TcParams {
   const int* n_tiles;
   const int* row_index;       // grouped, swapped: token row of sorted position i is row_index[i] / row_div of X (or nullptr:
   int row_div;                // X is already in sorted order)
+  int act;                    // the gate's activation of a gated product (TL_ACT_*), 0 for a plain one
+  int skip_kb;                // -1; a test sets the k-block whose copies the producer leaves out, so that a wait runs out
   int* status;
 };
+
+inline int& skip_kb_for_test() {
+  static int kb = -1;
+  return kb;
+}
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle: 8-row groups are
 // 1024 bytes apart (stride byte offset), version 1 (sm_100), layout type 2 (SWIZZLE_128B).
@@ -94,8 +101,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 template <typename TOut> __device__ __forceinline__ void store_out(TOut* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
 
 template <int BN, bool SWAP, bool SWIGLU>
 struct Smem {
@@ -218,9 +223,11 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
       }
     };
     const int ahead = p.tile_group ? 0 : min(num_kb, S::STAGES);      // the ring's first fill: weights first
-    for (int i = 0; i < ahead; ++i) load_weights(i);
+    for (int i = 0; i < ahead; ++i)
+      if (i != p.skip_kb) load_weights(i);
     if (!p.tile_group) chain_wait();
-    for (int i = 0; i < ahead; ++i) load_tokens(i);
+    for (int i = 0; i < ahead; ++i)
+      if (i != p.skip_kb) load_tokens(i);
     issued = ahead;
     for (int i = ahead; i < num_kb; ++i) {
       const int s = i % S::STAGES;
@@ -230,13 +237,19 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
         break;
       }
       if (*aborted) break;
-      load_weights(i);
-      load_tokens(i);
+      if (i != p.skip_kb) {
+        load_weights(i);
+        load_tokens(i);
+      }
       issued = i + 1;
+    }
+    if (p.skip_kb >= 0) {       // a test's run: the consumers' wait for the left-out k-block has to run out before the drain
+      for (uint32_t spin = 0; spin < wait_limit && !*aborted; ++spin) __nanosleep(256);
     }
     if (*aborted) {
       // copies already started must land before the CTA's shared memory goes away
-      for (int i = max(0, issued - S::STAGES); i < issued; ++i) mbar_wait(&full[i % S::STAGES], (i / S::STAGES) & 1);
+      for (int i = max(0, issued - S::STAGES); i < issued; ++i)
+        if (i != p.skip_kb) mbar_wait(&full[i % S::STAGES], (i / S::STAGES) & 1);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
@@ -298,7 +311,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
             for (int j = 0; j < 16; ++j) {
               const int t = c0 + j;
               if (t < tok_rows) {
-                const float r = SWIGLU ? silu_mul(v[j], u[j]) : v[j] + b;
+                const float r = SWIGLU ? gated(v[j], u[j], p.act) : v[j] + b;
                 if (p.partial) p.partial[((long long)blockIdx.z * p.M + tok0 + t) * p.N + n] = r;
                 else store_out<TOut>(C + (long long)(tok0 + t) * p.ldc + n, r);
               }
@@ -312,7 +325,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int n = n0 + c0 + j;
-              r[j] = SWIGLU ? silu_mul(v[j], u[j]) : v[j] + ((p.bias && n < p.N) ? p.bias[n] : 0.f);
+              r[j] = SWIGLU ? gated(v[j], u[j], p.act) : v[j] + ((p.bias && n < p.N) ? p.bias[n] : 0.f);
             }
             // 16 consecutive outputs of one row: 16-byte stores when they are all there and aligned
             const bool whole = n0 + c0 + 16 <= p.N && (((uintptr_t)(row + n0 + c0)) & 15) == 0;
@@ -521,7 +534,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int col = n0 + c0 + j;
-            r[j] = SWIGLU ? silu_mul(v[j], u[j]) : v[j] + ((p.bias && col < p.N) ? p.bias[col] : 0.f);
+            r[j] = SWIGLU ? gated(v[j], u[j], p.act) : v[j] + ((p.bias && col < p.N) ? p.bias[col] : 0.f);
           }
           const bool whole = n0 + c0 + 16 <= p.N && (((uintptr_t)(row + n0 + c0)) & 15) == 0;
           if (whole) {
@@ -666,7 +679,8 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   TL_REQUIRE(out_dtype == TL_BF16 || out_dtype == TL_FP32, "tensor-core gemm: output dtype %d", out_dtype);
   TL_REQUIRE(splits >= 1 && (splits == 1 || (swap && !swiglu && partial && (!tile_group || !reduce))),
              "tensor-core gemm: split-K needs the swapped plain kernel and a workspace (grouped: the caller adds the sums)");
-  TL_REQUIRE(!bias || !swiglu, "tensor-core gemm: a bias with the SwiGLU epilogue is not implemented");
+  TL_REQUIRE(!bias || !swiglu, "tensor-core gemm: a bias with the gated epilogue is not implemented");
+  TL_REQUIRE(swiglu >= 0 && swiglu <= TL_ACT_LAST, "tensor-core gemm: gate activation %d is not one of 0..%d", swiglu, TL_ACT_LAST);
   TL_REQUIRE(!row_index || (swap && tile_group && row_div >= 1),
              "tensor-core gemm: a row index needs the swapped grouped kernel (divisor %d)", row_div);
   CUtensorMap tmW, tmX;
@@ -681,6 +695,8 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   p.rows_per_group = rows_per_group;
   p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles; p.status = status;
   p.row_index = row_index; p.row_div = row_index ? row_div : 1;
+  p.act = swiglu;
+  p.skip_kb = skip_kb_for_test();
   const int tok_tile = swap ? bn : TILE_M, n_tile = swap ? TILE_M : bn;
   // one CTA layer a split, also where rounding leaves the last splits without k-blocks: they write zeros
   dim3 grid(ceil_div(N, n_tile), tile_group ? max_tiles : ceil_div(M, tok_tile), splits);
@@ -725,6 +741,16 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
 }
 
 extern "C" void tl_tc_set_chained_launches(int enabled) { chained_launches() = enabled; }
+
+// For tests of the bounded waits: the polls after which an mbarrier wait of this file's kernels gives up (0 puts the
+// default back), and the k-block whose copies the plain (not persistent) kernel's producer leaves out (-1: none). With a
+// k-block left out the MMA issuer's wait for it runs out: the kernel records status 11, stores nothing, frees its tensor
+// memory and returns; nothing waits without a bound, so the next launch finds the GPU as it was.
+extern "C" int tl_tc_set_wait_limit(unsigned int polls) {
+  const uint32_t v = polls ? polls : (1u << 22);
+  return (int)cudaMemcpyToSymbol(wait_limit, &v, sizeof(v));
+}
+extern "C" void tl_tc_test_skip_k_block(int kb) { skip_kb_for_test() = kb; }
 
 extern "C" int tl_gather_rows(const void* x, long long ldx, const int* index, int div, void* out, int rows, int width,
                               cudaStream_t stream) {

@@ -13,7 +13,10 @@
 namespace tl {
 
 constexpr int TMA_BOX_COLS = 64;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;     // polls of an mbarrier before a wait gives up
+// Polls of an mbarrier before a wait gives up (every wait in these kernels is bounded: a wait that runs out records status
+// 11 and its kernel drains its copies, frees its tensor memory and returns). One copy a source file; tc_gemm.cu exports a
+// setter so that a test can make a wait run out in milliseconds instead of seconds.
+static __constant__ uint32_t wait_limit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -32,7 +35,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Waits for the phase with the given parity to complete; false when the bound ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+  const uint32_t limit = wait_limit;
+  for (uint32_t i = 0; i < limit; ++i) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"

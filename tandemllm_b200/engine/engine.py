@@ -177,6 +177,9 @@ class Engine:
             ff = layer.feed_forward
             if hasattr(ff, "count_into") and hasattr(ff, "num_experts"):
                 parts.append(ff)
+        if self._flight is not None:            # a step launched ahead belongs to the old setting: account it first
+            flight, self._flight = self._flight, None
+            self._account(flight)
         self.step_function.drop_graphs()
         self._routed_parts = parts if on else []
         self._routing = self._routing_seen = None
@@ -196,7 +199,7 @@ class Engine:
         rec = flight.record
         rec["ms"] = round((time.perf_counter() - flight.started) * 1e3, 3)
         rec["finished"] = finished
-        if flight.routed is not None:
+        if flight.routed is not None and self._routing_seen is not None and flight.routed.numel() == self._routing_seen.size:
             now = flight.routed.numpy().copy()
             delta, at, touched = now - self._routing_seen, 0, []
             self._routing_seen = now

@@ -16,6 +16,23 @@ from .build import load
 
 FP32, BF16 = 0, 1
 TL_BAD_ARGUMENT = 100001
+# the gate activations of gated products (TL_ACT_* of csrc/common.cuh) and the router's scoring functions (TL_SCORE_*
+# of csrc/route.cuh), by the names a part's spec gives them
+ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4}
+SCORINGS = {"sigmoid": 0, "softmax": 1}
+
+
+def activation_code(name: str) -> int:
+    if name not in ACTIVATIONS:
+        raise KernelError(f"gate activation {name!r}: one of {', '.join(ACTIVATIONS)}")
+    return ACTIVATIONS[name]
+
+
+def route_flags(normalize: bool, scoring: str = "sigmoid") -> int:
+    """The routers' `normalize` argument: bit 0 = divide the chosen weights by their sum, bits 1.. = the scoring function."""
+    if scoring not in SCORINGS:
+        raise KernelError(f"router scoring function {scoring!r}: one of {', '.join(SCORINGS)}")
+    return int(bool(normalize)) | (SCORINGS[scoring] << 1)
 
 
 class KernelError(RuntimeError):
@@ -36,7 +53,7 @@ _SIGNATURES = {
                        c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                        c_float, c_float, c_void_p, c_void_p, c_void_p],
-    "tl_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "tl_gated_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "tl_gemm_simt": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
                      c_int, c_int, c_void_p],
     "tl_gemm_simt_grouped": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
@@ -175,7 +192,7 @@ def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
     """residual += delta (32-bit); out = weight * rms_normalised(residual). `delta` is None, a float32 tensor, a
     `PartialSums` or an `ExpertRows`. With `gather` (int32 row indices) the output row i is computed from row
     gather[i] and the residual is left unchanged. `out32` also receives the normalised rows unrounded. `route`
-    (router weights float32 [E, hidden], bias, k, normalize, floor, scale, ids, wts) also runs the router on the
+    (router weights float32 [E, hidden], bias, k, normalize, scoring, floor, scale, ids, wts) also runs the router on the
     unrounded rows and fills ids int32 [rows, k] and wts float32 [rows, k]."""
     _need(residual, torch.float32, "residual"); _need(weight, torch.float32, "norm weight"); _need(out, None, "normed")
     if out32 is not None:
@@ -201,17 +218,23 @@ def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
         ptr(residual), dense or None, parts, stride, ptr(rows_ptr), eparts, estride, ptr(pos), ptr(ids), ptr(wts), top_k,
         ptr(weight),
         ptr(out), ptr(out32), ptr(gather), n_out, hidden, float(eps), dtype_code(out.dtype), ptr(r.get("weight")),
-        ptr(r.get("bias")), r["weight"].shape[0] if route else 0, int(r.get("k", 0)), int(r.get("normalize", 0)),
+        ptr(r.get("bias")), r["weight"].shape[0] if route else 0, int(r.get("k", 0)),
+        route_flags(r.get("normalize", 0), r.get("scoring", "sigmoid")),
         float(r.get("floor", 0.0)), float(r.get("scale", 1.0)), ptr(r.get("ids")), ptr(r.get("wts")), stream()),
         "add_rmsnorm")
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def gated_mul(gate_up: torch.Tensor, out: torch.Tensor, act: int = 1) -> torch.Tensor:
+    """out = act(gate_up[:, :inter]) * gate_up[:, inter:], `act` a code of ACTIVATIONS (1: SiLU)."""
     _need(gate_up, out.dtype, "gate_up"); _need(out, None, "out")
     rows, inter = out.shape
-    check(core().tl_silu_mul(ptr(gate_up), ptr(out), rows, inter, dtype_code(out.dtype), stream()), "silu_mul")
+    check(core().tl_gated_mul(ptr(gate_up), ptr(out), rows, inter, int(act), dtype_code(out.dtype), stream()), "gated_mul")
     return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    return gated_mul(gate_up, out, ACTIVATIONS["silu"])
 
 
 # ------------------------------------------------------------------------------------------ products
@@ -228,8 +251,9 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: 
 
 
 def gemm_simt_grouped(a: torch.Tensor, a_gather: torch.Tensor | None, a_div: int, w: torch.Tensor, out: torch.Tensor,
-                      plan: "MoePlan", swiglu: bool) -> torch.Tensor:
-    """Per sorted row i of the plan: out[i] = A[row(i)] @ w[expert(i)]^T, with w [E, N(*2 when swiglu), K]."""
+                      plan: "MoePlan", swiglu: bool | int) -> torch.Tensor:
+    """Per sorted row i of the plan: out[i] = A[row(i)] @ w[expert(i)]^T, with w [E, N(*2 when swiglu), K]. `swiglu`:
+    False for a plain product, True or a code of ACTIVATIONS for act(gate rows) * (up rows)."""
     _need(a, w.dtype, "a"); _need(w, None, "w"); _need(out, None, "out")
     E, n_rows_w, K = w.shape
     N = n_rows_w // 2 if swiglu else n_rows_w
@@ -355,10 +379,10 @@ def attention_join(scratch, positions, window, out, n_spans: int, span_keys: int
 
 
 # ------------------------------------------------------------------------------------------ experts
-def router_topk(logits, bias, k: int, normalize: bool, floor: float, scale: float, ids, wts) -> None:
+def router_topk(logits, bias, k: int, normalize: bool, floor: float, scale: float, ids, wts, scoring: str = "sigmoid") -> None:
     _need(logits, torch.float32, "router logits"); _need(ids, torch.int32, "ids"); _need(wts, torch.float32, "weights")
     rows, E = logits.shape
-    check(core().tl_router_topk(ptr(logits), logits.stride(0), ptr(bias), rows, E, k, int(normalize), float(floor),
+    check(core().tl_router_topk(ptr(logits), logits.stride(0), ptr(bias), rows, E, k, route_flags(normalize, scoring), float(floor),
                                 float(scale), ptr(ids), ptr(wts), stream()), "router_topk")
 
 

@@ -163,13 +163,14 @@ class TensorCore:
             return None
         return ops.PartialSums(partial, splits, M, N, None if out.dtype == torch.float32 else out.dtype)
 
-    def gated(self, x, w_gate_up, out) -> bool:
-        """out = silu(x gate^T) * (x up^T) for w_gate_up = [gate rows; up rows], in the persistent kernel with the SwiGLU
-        epilogue; False (nothing done) for a decode step's few rows or operands the kernels do not take."""
+    def gated(self, x, w_gate_up, out, act: int = 1) -> bool:
+        """out = act(x gate^T) * (x up^T) for w_gate_up = [gate rows; up rows], in the persistent kernel with the gated
+        epilogue (`act`: a code of ops.ACTIVATIONS, 1 = SiLU); False (nothing done) for a decode step's few rows or
+        operands the kernels do not take."""
         inter = w_gate_up.shape[0] // 2
         if x.shape[0] <= 128 or not usable(x, w_gate_up) or inter % 8 or out.stride(-1) != 1 or out.dtype != torch.bfloat16:
             return False
-        self.gemm(x, w_gate_up, None, out, swiglu=True, swap=False, n_out=inter)
+        self.gemm(x, w_gate_up, None, out, swiglu=act, swap=False, n_out=inter)
         return True
 
     def linear(self, x, w, bias, out, defer: bool = False):
@@ -239,7 +240,7 @@ class TensorCore:
                      plan.n_tiles.data_ptr(), plan.max_tiles, None, 0, E)
             gate_up_rows, pos, div = plan.sorted_pairs.data_ptr(), plan.pos_of_pair, k
         _check(lib().tl_gemm_skinny_grouped(x.data_ptr(), x.stride(0), gate_up_rows, div,
-                                            part.w_gate_up.data_ptr(), H, I2, act.data_ptr(), inter, inter, H, 1,
+                                            part.w_gate_up.data_ptr(), H, I2, act.data_ptr(), inter, inter, H, part.act,
                                             ops.dtype_code(act.dtype), *where, self.status.data_ptr(), ops.stream()),
                "gemm_skinny_grouped")
         _check(lib().tl_gemm_skinny_grouped(act.data_ptr(), inter, None, 1, part.w_down.data_ptr(), inter, H, y.data_ptr(), H,
@@ -285,10 +286,10 @@ class TensorCore:
         act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
         w_gate_up = part.w_gate_up.view(E * I2, H)
         if fetch:
-            self.gemm(x, w_gate_up, None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=True, bn=bn, n_out=inter,
+            self.gemm(x, w_gate_up, None, act, rows_per_group=I2, plan=plan, swiglu=part.act, swap=True, bn=bn, n_out=inter,
                       row_index=plan.sorted_pairs, row_div=k, rows=P)
         else:
-            self.gemm(xs, w_gate_up, None, act, rows_per_group=I2, plan=plan, swiglu=True, swap=swap, bn=bn, n_out=inter)
+            self.gemm(xs, w_gate_up, None, act, rows_per_group=I2, plan=plan, swiglu=part.act, swap=swap, bn=bn, n_out=inter)
         w_down = part.w_down.view(E * H, inter)
         ctas = min(P, E) * -(-H // 128)
         if fetch and ctas < self.sm_count and inter >= 512:

@@ -1,10 +1,14 @@
-"""Feed-forward parts: the dense SwiGLU and the sigmoid-routed top-k SwiGLU experts.
+"""Feed-forward parts: the dense gated feed-forward (SwiGLU) and the routed top-k gated experts.
 
-  dense    out = down( silu(gate n) * (up n) )                          engine/models/lfm2_moe/ref.py:180-183
+  dense    out = down( act(gate n) * (up n) ), act = silu             engine/models/lfm2_moe/ref.py:180-183
   experts  logits = router(n) in 32-bit; s = sigmoid(logits); the choice is the top-k of s + expert_bias
            (the bias for the choice only); w = s[chosen], divided by (sum w + norm_floor) when normalised,
            times scale; out = sum over the chosen experts in ascending expert id of w * expert(n)
                                                                          ref.py:185-214
+
+The gate's activation (`activation`: silu, gelu, relu2, identity) and the router's scoring function (`scoring`:
+sigmoid, or softmax over all experts) are parameters of the parts' specs, passed to the kernels as codes; LFM2 uses
+silu and sigmoid, and another architecture's gated or routed feed-forward reuses the same fused kernels by naming its own.
 
 Gate and up are fused into one matrix at bind time ([2I, H], gate first), per expert for the experts
 ([E, 2I, H] and [E, H, I], engine/models/lfm2_moe/load.py:136-161). Experts may be stored one by one
@@ -30,6 +34,7 @@ class SwiGLU(Part):
     def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
         super().__init__(spec, prefix, hidden_size)
         self.inter = int(spec["intermediate_size"])
+        self.act = ops.activation_code(spec.get("activation", "silu"))
         self.n = {k: prefix + v for k, v in spec["names"].items()}
 
     def weight_specs(self, present=None):
@@ -46,9 +51,9 @@ class SwiGLU(Part):
     def forward(self, x, step):
         act = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
         tc = self.runtime.tensorcore
-        if tc is None or not tc.gated(x, self.w_gate_up, act):      # prompts: gate, up and silu(gate) * up in one kernel
+        if tc is None or not tc.gated(x, self.w_gate_up, act, self.act):      # prompts: gate, up and act(gate) * up in one kernel
             gu = linear(self.runtime, x, self.w_gate_up)
-            ops.silu_mul(gu, act)
+            ops.gated_mul(gu, act, self.act)
         return linear(self.runtime, act, self.w_down, out_dtype=torch.float32, defer=True)
 
 
@@ -65,6 +70,9 @@ class SigmoidTopKExperts(Part):
         self.normalize = bool(spec.get("normalize", True))
         self.scale = float(spec.get("scale", 1.0))
         self.norm_floor = float(spec.get("norm_floor", 1e-6))
+        self.scoring = str(spec.get("scoring", "sigmoid"))
+        ops.route_flags(self.normalize, self.scoring)          # an unknown scoring function is refused here
+        self.act = ops.activation_code(spec.get("activation", "silu"))
         if not 0 < self.top_k <= self.num_experts:
             raise ValueError(f"top-{self.top_k} of {self.num_experts} experts")
         if self.num_experts > 1024 or self.top_k > 32:
@@ -143,7 +151,7 @@ class SigmoidTopKExperts(Part):
         """What the norm kernel in front of the layer needs to run this layer's router on its `rows` output rows
         (for many rows the kernel norms several rows per block, so the router's weights are read once per block)."""
         return {"weight": self.w_router, "bias": self.expert_bias, "k": self.top_k, "normalize": self.normalize,
-                "floor": self.norm_floor, "scale": self.scale,
+                "scoring": self.scoring, "floor": self.norm_floor, "scale": self.scale,
                 "ids": torch.empty(rows, self.top_k, dtype=torch.int32, device=device),
                 "wts": torch.empty(rows, self.top_k, dtype=torch.float32, device=device)}
 
@@ -154,7 +162,8 @@ class SigmoidTopKExperts(Part):
                                                                       device=x32.device))
         ids = torch.empty(R, self.top_k, dtype=torch.int32, device=x32.device)
         wts = torch.empty(R, self.top_k, dtype=torch.float32, device=x32.device)
-        ops.router_topk(logits, self.expert_bias, self.top_k, self.normalize, self.norm_floor, self.scale, ids, wts)
+        ops.router_topk(logits, self.expert_bias, self.top_k, self.normalize, self.norm_floor, self.scale, ids, wts,
+                        self.scoring)
         return ids, wts
 
     def plan_for(self, pairs: int, device, tile_rows: int | None = None) -> ops.MoePlan:
@@ -185,7 +194,7 @@ class SigmoidTopKExperts(Part):
         if self.load is not None:
             self.load.add_(plan.counts)
         act = torch.empty(R * self.top_k, self.inter, dtype=x.dtype, device=x.device)
-        ops.gemm_simt_grouped(x, plan.sorted_pairs, self.top_k, self.w_gate_up, act, plan, swiglu=True)
+        ops.gemm_simt_grouped(x, plan.sorted_pairs, self.top_k, self.w_gate_up, act, plan, swiglu=self.act)
         y = torch.empty(R * self.top_k, H, dtype=torch.float32, device=x.device)
         ops.gemm_simt_grouped(act, None, 1, self.w_down, y, plan, swiglu=False)
         return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)

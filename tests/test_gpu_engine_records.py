@@ -51,24 +51,25 @@ def test_every_step_leaves_a_record_and_a_log_line(tmp_path, dtype):
         assert line["experts_touched"] == r["experts_touched"] and line["pages_used"] == r["pages_used"]
         assert r["pages_used"][0] + r["pages_free"][0] == eng.cache.groups[0].pool.num_pages
     assert any(r["from_graph"] for r in records) and not records[0]["from_graph"]
-    # one step's count against the plain implementation's routing of the same rows: the first step is the first portion
-    # (16 tokens) of the first prompt alone
+    # one step's count against the plain implementation's routing of the same rows: the first step holds the first
+    # portion (16 tokens) of the first prompt and, with what is left of the budget of 24, 8 tokens of the second
     first = records[0]
-    assert first["rows"] == 16 and first["requests"] == 1
+    assert first["rows"] == 24 and first["requests"] == 2
     if dtype == "float32":
         routes = {}
         orig = P.route
 
         def spy(n, Wd, p, c, forced=None):
             ids, w = orig(n, Wd, p, c, forced)
-            routes[p] = ids
+            routes.setdefault(p, []).append(ids)
             return ids, w
         P.route = spy
         try:
             P.forward(cfg, W, prompts[0][:16])
+            P.forward(cfg, W, prompts[1][:8])
         finally:
             P.route = orig
-        want = [int(torch.unique(ids).numel()) for _, ids in sorted(routes.items())]
+        want = [int(torch.unique(torch.cat(ids)).numel()) for _, ids in sorted(routes.items())]
         assert first["experts_touched"] == want
     # switching the record off stops the counting and drops nothing else
     eng.set_routing_record(False)

@@ -166,6 +166,79 @@ def test_silu_mul(dtype):
     close(out, torch.nn.functional.silu(g) * u, dtype)
 
 
+def plain_activation(name, g):
+    """The gate activations a gated feed-forward may name, in plain torch."""
+    return {"silu": torch.nn.functional.silu, "gelu": lambda t: torch.nn.functional.gelu(t),
+            "relu2": lambda t: torch.relu(t) ** 2, "identity": lambda t: t}[name](g)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["silu", "gelu", "relu2", "identity"])
+def test_gate_activations(dtype, act):
+    o = ops()
+    gu = rnd(9, 2 * 150, seed=5, scale=1.5).to(dtype)
+    out = torch.empty(9, 150, dtype=dtype, device=DEV)
+    o.gated_mul(gu.to(DEV), out, o.activation_code(act))
+    g, u = gu.float()[:, :150], gu.float()[:, 150:]
+    close(out, plain_activation(act, g) * u, dtype, act)
+    with pytest.raises(o.KernelError, match="gate activation"):
+        o.activation_code("swish7")
+    with pytest.raises(o.KernelError, match="gate activation"):
+        o.gated_mul(gu.to(DEV), out, 9)
+
+
+@pytest.mark.parametrize("E,k,use_bias,normalize", [(12, 4, True, True), (12, 4, False, False), (70, 3, True, False),
+                                                     (300, 6, False, True)])
+def test_router_with_softmax_scores(E, k, use_bias, normalize):
+    """The other scoring function: scores are the softmax over all experts' logits (32-bit); the bias still only moves
+    the choice, the weights are the chosen scores, renormalised or not, times the scale. Alone and inside the norm kernel."""
+    o = ops()
+    R, H = 37, 136
+    res0, w = rnd(R, H, seed=1), 1 + rnd(H, seed=2, scale=0.2)
+    gate, bias = rnd(E, H, seed=7, scale=0.3), rnd(E, seed=8, scale=0.02)
+    n32 = P.rms_norm(res0, w, 1e-5)
+    logits = n32 @ gate.T
+    score = torch.softmax(logits, -1)
+    choice = score + bias if use_bias else score
+    want_ids = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :k]
+    want_w = torch.gather(score, 1, want_ids)
+    if normalize:
+        want_w = want_w / (want_w.sum(-1, keepdim=True) + 1e-6)
+    want_w = want_w * 1.5
+    ids = torch.empty(R, k, dtype=torch.int32, device=DEV)
+    wts = torch.empty(R, k, dtype=torch.float32, device=DEV)
+    o.router_topk(logits.to(DEV), bias.to(DEV) if use_bias else None, k, normalize, 1e-6, 1.5, ids, wts, scoring="softmax")
+    assert torch.equal(ids.cpu().long(), want_ids)
+    close(wts, want_w, torch.float32, "softmax routing weights")
+    route = {"weight": gate.to(DEV), "bias": bias.to(DEV) if use_bias else None, "k": k, "normalize": normalize,
+             "scoring": "softmax", "floor": 1e-6, "scale": 1.5,
+             "ids": torch.empty(R, k, dtype=torch.int32, device=DEV), "wts": torch.empty(R, k, dtype=torch.float32, device=DEV)}
+    out = torch.empty(R, H, dtype=torch.float32, device=DEV)
+    o.add_rmsnorm(res0.clone().to(DEV), None, w.to(DEV), 1e-5, out, None, None, route)
+    assert torch.equal(route["ids"].cpu().long(), want_ids)
+    close(route["wts"], want_w, torch.float32, "softmax routing weights from the norm kernel")
+    with pytest.raises(o.KernelError, match="scoring"):
+        o.router_topk(logits.to(DEV), None, k, normalize, 1e-6, 1.5, ids, wts, scoring="sparsemax")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("act", ["gelu", "relu2", "identity"])
+def test_grouped_products_with_other_gate_activations(dtype, act):
+    o = ops()
+    R, E, k, H, I = 40, 5, 2, 64, 24
+    x = rnd(R, H, seed=11).to(dtype)
+    w13 = rnd(E, 2 * I, H, seed=14, scale=0.3).to(dtype)
+    ids = torch.stack([torch.randperm(E, generator=torch.Generator().manual_seed(r))[:k] for r in range(R)]).int().to(DEV)
+    plan = o.MoePlan(R * k, E, o.simt_tile_rows(), DEV).build(ids)
+    got = torch.empty(R * k, I, dtype=dtype, device=DEV)
+    o.gemm_simt_grouped(x.to(DEV), plan.sorted_pairs, k, w13.to(DEV), got, plan, o.activation_code(act))
+    order = plan.sorted_pairs[:R * k].cpu().long()
+    xf, wf = x.float(), w13.float()
+    flat = ids.cpu().reshape(-1).long()
+    want = torch.stack([plain_activation(act, xf[p // k] @ wf[flat[p], :I].T) * (xf[p // k] @ wf[flat[p], I:].T) for p in order])
+    close(got, want, dtype, act)
+
+
 # ------------------------------------------------------------------------------------------ products
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M,N,K", [(1, 130, 77), (3, 64, 64), (8, 257, 100), (9, 130, 77), (70, 96, 200), (200, 33, 17),

@@ -407,3 +407,105 @@ def test_a_toy_architecture_registers_builds_and_steps(tmp_path):
         MIXERS.pop("toy_decay", None)
         FEED_FORWARDS.pop("toy_switch", None)
         POSITION_ENCODINGS.pop("toy_pairs", None)
+
+
+# ---- another architecture out of the product's own parts, with other constants: a GELU-gated dense feed-forward and
+# experts routed by a softmax over all experts with a squared-ReLU gate, in both precisions through the fused kernels
+def fused_toy_spec(raw):
+    from tandemllm_b200.config import ModelSpec, PartSpec, Site
+    from tandemllm_b200.config.spec import LayerSpec
+    H, eps = raw["width"], raw["eps"]
+    norm = lambda name: PartSpec("rmsnorm", {"eps": eps, "name": name})
+    conv = PartSpec("short_conv", {"taps": 3, "names": {"in": "mix.in", "taps": "mix.taps", "out": "mix.out"}})
+    attn = PartSpec("attention", {"num_heads": 4, "num_kv_heads": 1, "head_dim": 64, "qk_norm": PartSpec("rmsnorm", {"eps": eps}),
+                                  "position": PartSpec("rope_neox", {"theta": 1e4, "rotary_dim": 64}), "window": None,
+                                  "names": {"q": "att.q", "k": "att.k", "v": "att.v", "out": "att.o", "q_norm": "att.qn",
+                                            "k_norm": "att.kn"}})
+    dense = PartSpec("swiglu", {"intermediate_size": raw["inner"], "activation": "gelu",
+                                "names": {"gate": "ff.g", "up": "ff.u", "down": "ff.d"}})
+    routed = PartSpec("sigmoid_topk_experts", {"num_experts": raw["experts"], "top_k": 2, "intermediate_size": raw["expert_inner"],
+                                               "expert_bias": False, "normalize": True, "scale": 1.0, "norm_floor": 0.0,
+                                               "scoring": "softmax", "activation": "relu2",
+                                               "names": {"router": "moe.router", "bias": "moe.bias", "experts": "moe.e",
+                                                         "gate": "g", "up": "u", "down": "d"}})
+    layers = (LayerSpec("b.0.", conv, dense, norm("n1"), norm("n2")), LayerSpec("b.1.", attn, routed, norm("n1"), norm("n2")),
+              LayerSpec("b.2.", conv, routed, norm("n1"), norm("n2")))
+    return ModelSpec("FusedToyForCausalLM", H, raw["vocab"], layers, tuple(Site(i) for i in range(3)),
+                     PartSpec("rmsnorm", {"eps": eps}), embedding_name="tok.weight", final_norm_prefix="last.",
+                     head_name="head.weight", name_prefixes=("",))
+
+
+def fused_toy_plain(raw, W, tokens):
+    """(logits, routing margins) of the whole sequence in plain torch."""
+    eps, H, E = raw["eps"], raw["width"], raw["experts"]
+    cfg = dict(num_attention_heads=4, num_key_value_heads=1, head_dim=64, hidden_size=H, norm_eps=eps, rope_theta=1e4)
+    h = W["tok.weight"][torch.tensor(tokens)]
+    margins = []
+
+    def conv(h, p):
+        names = {"x.in_proj.weight": W[p + "mix.in.weight"], "x.conv.weight": W[p + "mix.taps.weight"],
+                 "x.out_proj.weight": W[p + "mix.out.weight"]}
+        return h + P.short_conv(P.rms_norm(h, W[p + "n1.weight"], eps), names, "x.", 3, False)
+
+    def routed(h, p):
+        n = P.rms_norm(h, W[p + "n2.weight"], eps)
+        score = torch.softmax(n @ W[p + "moe.router.weight"].T, -1)
+        top = torch.sort(score, dim=-1, descending=True, stable=True)
+        margins.append(top.values[:, 1] - top.values[:, 2])
+        ids, w = top.indices[:, :2], top.values[:, :2]
+        w = w / w.sum(-1, keepdim=True)
+        out = torch.zeros_like(n)
+        for e in range(E):
+            rows, slot = torch.where(ids == e)
+            if rows.numel():
+                q = f"{p}moe.e.{e}."
+                y = (torch.relu(n[rows] @ W[q + "g.weight"].T) ** 2 * (n[rows] @ W[q + "u.weight"].T)) @ W[q + "d.weight"].T
+                out.index_add_(0, rows, y * w[rows, slot, None])
+        return h + out
+    h = conv(h, "b.0.")
+    n = P.rms_norm(h, W["b.0.n2.weight"], eps)
+    h = h + (torch.nn.functional.gelu(n @ W["b.0.ff.g.weight"].T) * (n @ W["b.0.ff.u.weight"].T)) @ W["b.0.ff.d.weight"].T
+    names = {"x." + k: W[f"b.1.att.{v}.weight"] for k, v in (("q_proj.weight", "q"), ("k_proj.weight", "k"), ("v_proj.weight", "v"),
+                                                             ("out_proj.weight", "o"), ("q_layernorm.weight", "qn"),
+                                                             ("k_layernorm.weight", "kn"))}
+    h = h + P.attention(P.rms_norm(h, W["b.1.n1.weight"], eps), names, "x.", cfg)
+    h = routed(h, "b.1.")
+    h = routed(conv(h, "b.2."), "b.2.")
+    return P.rms_norm(h, W["last.weight"], eps) @ W["head.weight"].T, torch.stack(margins).min(0).values
+
+
+@pytest.mark.parametrize("dtype,tol,near", [("float32", 1e-4, 1e-6), ("bfloat16", 3e-2, 4e-3)])
+def test_another_architecture_reuses_the_fused_kernels_with_its_own_activation_and_scoring(tmp_path, dtype, tol, near):
+    from tandemllm_b200.config import Architecture, register, unregister
+    from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
+    from tandemllm_b200.parts import DecoderModel
+    from tandemllm_b200.weights.random_init import random_tensor
+    from tandemllm_b200.weights.safetensors_io import write_file
+    register(Architecture("fused_toy", ("FusedToyForCausalLM",), ("fused_toy",), lambda raw, folder, generation: fused_toy_spec(raw)))
+    try:
+        raw = {"architectures": ["FusedToyForCausalLM"], "width": 128, "inner": 192, "vocab": 200, "eps": 1e-5, "experts": 6,
+               "expert_inner": 64}
+        spec = fused_toy_spec(raw)
+        W = {s.name: random_tensor(s, 5, 0.08, 0.5, 0.1).to(torch.bfloat16).float() for s in DecoderModel(spec).weight_specs()}
+        for k in W:
+            if "router" in k:
+                W[k] = (W[k] * 8).to(torch.bfloat16).float()             # spread the routing scores
+        (tmp_path / "config.json").write_text(json.dumps(raw))
+        write_file(str(tmp_path / "model.safetensors"), {k: v.to(torch.bfloat16) if dtype == "bfloat16" else v for k, v in W.items()})
+        eng = Engine.from_folder(str(tmp_path), EngineArgs(dtype=dtype, max_len=512, parallel=2, kv_blocks=32, graph=True))
+        toks = torch.randint(0, 200, (170,), generator=torch.Generator().manual_seed(8)).tolist()
+        want, margin = fused_toy_plain(raw, W, toks)
+        eng.admit("t")
+        outs, at = [], 0
+        for n in (140, 9, 2) + (1,) * 19:                   # the persistent kernels, the swapped ones, the register-only ones, graphs
+            outs.append(eng.step([StepEntry("t", toks[at:at + n], list(range(n)))]).float().cpu())
+            at += n
+        assert at == 170 and (eng.step_function.graph_replays >= 10)
+        got = torch.cat(outs)
+        err = (got - want).abs().amax(-1) / want.abs().amax(-1)
+        clear = margin >= near
+        assert float(err[clear].max()) < tol, (float(err[clear].max()), int((~clear).sum()))
+        assert int((~clear).sum()) <= 17
+        eng.release("t")
+    finally:
+        unregister("fused_toy")

@@ -132,6 +132,21 @@ def test_every_tile_shape_in_both_orientations(swap, bn):
     assert rel(out, x.float() @ w.float().T) < 1e-3
 
 
+@pytest.mark.parametrize("act", ["gelu", "relu2", "identity"])
+def test_dense_gate_up_with_other_gate_activations(act):
+    from tandemllm_b200.kernels import ops
+    from tests.test_gpu_kernels import plain_activation
+    impl, rt = tc()
+    M, H, I = 300, 136, 200
+    x, w = rnd(M, H, seed=30), rnd(2 * I, H, seed=31, scale=0.2)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert impl.gated(x.to(DEV), w.to(DEV), out, ops.activation_code(act))
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    g, u = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
+    assert rel(out, plain_activation(act, g) * u) < 1e-2
+
+
 @pytest.mark.parametrize("M,H,I", [(300, 136, 200), (129, 64, 72), (2048, 256, 640)])
 def test_dense_gate_up_with_the_swiglu_epilogue(M, H, I):
     """A prompt's dense feed-forward: gate, up and silu(gate) * up in the persistent kernel (gate and up rows of the
@@ -145,6 +160,39 @@ def test_dense_gate_up_with_the_swiglu_epilogue(M, H, I):
     g, u = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
     assert rel(out, torch.nn.functional.silu(g) * u) < 1e-2
     assert not impl.gated(x[:8].to(DEV), w.to(DEV), out[:8])
+
+
+def test_a_pipeline_wait_that_runs_out_returns_and_leaves_the_gpu_as_it_was():
+    """Every mbarrier wait of the tensor-core kernels is bounded. Here one runs out on purpose, without any fault: the
+    producer is told to leave one k-block's copies out (a test hook of the launcher), so the MMA issuer waits for a
+    barrier that nothing completes. With the bound lowered the wait gives up after a few thousand polls: the kernel
+    records status 11, stores nothing, waits for the copies it did start, frees its tensor memory and returns by itself;
+    the same product launched again right after is correct."""
+    import ctypes
+
+    from tandemllm_b200.kernels import tensorcore
+    impl, rt = tc()
+    lib = tensorcore.lib()
+    lib.tl_tc_set_wait_limit.argtypes, lib.tl_tc_set_wait_limit.restype = [ctypes.c_uint], ctypes.c_int
+    lib.tl_tc_test_skip_k_block.argtypes, lib.tl_tc_test_skip_k_block.restype = [ctypes.c_int], None
+    M, N, K = 40, 128, 256                       # one CTA of the swapped kernel, four k-blocks, no split
+    x, w = rnd(M, K, seed=40).to(DEV), rnd(N, K, seed=41, scale=0.1).to(DEV)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    try:
+        assert lib.tl_tc_set_wait_limit(4096) == 0
+        lib.tl_tc_test_skip_k_block(2)
+        impl.gemm(x, w, None, out)
+        torch.cuda.synchronize()                 # returns: the kernel ended by its own bound
+        assert int(rt.status) == 11
+        assert bool(torch.isnan(out).all()), "a product that gave up must store nothing"
+    finally:
+        lib.tl_tc_test_skip_k_block(-1)
+        assert lib.tl_tc_set_wait_limit(0) == 0
+    rt.status.zero_()
+    impl.gemm(x, w, None, out)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    assert rel(out, x.float().cpu() @ w.float().cpu().T) < 1e-3
 
 
 def test_split_k_is_used_and_repeatable():
@@ -168,11 +216,24 @@ def test_split_k_is_used_and_repeatable():
                                        (16, 4, 2, 72, 40), (13, 3, 3, 88, 24), (16, 32, 4, 256, 192),  # experts with two tiles of 8
                                        (2048, 4, 2, 64, 128)])
 def test_grouped_experts_with_swiglu(R, E, k, H, I):
+    grouped_experts(R, E, k, H, I, "silu", "sigmoid")
+
+
+@pytest.mark.parametrize("act,scoring", [("gelu", "softmax"), ("relu2", "sigmoid"), ("identity", "softmax")])
+@pytest.mark.parametrize("R,E,k,H,I", [(4, 8, 2, 128, 64), (16, 32, 4, 256, 192), (64, 8, 3, 136, 72), (700, 6, 2, 128, 96)])
+def test_grouped_experts_with_other_activations_and_scoring(R, E, k, H, I, act, scoring):
+    """The fused expert kernels (the register-only grouped form, the swapped and the persistent tcgen05 forms) with the gate
+    activation and the router's scoring function a feed-forward other than LFM2's would name."""
+    grouped_experts(R, E, k, H, I, act, scoring)
+
+
+def grouped_experts(R, E, k, H, I, act, scoring):
     from tandemllm_b200.config import PartSpec
     from tandemllm_b200.parts import make_part
+    from tests.test_gpu_kernels import plain_activation
     impl, rt = tc()
     spec = PartSpec("sigmoid_topk_experts", {"num_experts": E, "top_k": k, "intermediate_size": I, "expert_bias": False,
-                                             "normalize": True, "scale": 1.0,
+                                             "normalize": True, "scale": 1.0, "activation": act, "scoring": scoring,
                                              "names": {"router": "gate", "bias": "expert_bias", "experts": "experts",
                                                        "gate": "w1", "up": "w3", "down": "w2"}})
     part = make_part("feed_forward", spec, prefix="m.", hidden_size=H)
@@ -185,6 +246,10 @@ def test_grouped_experts_with_swiglu(R, E, k, H, I):
     part.bind(lambda n: W[n], rt)
     x = rnd(R, H, seed=12)
     ids, wts = part.route(x.float().to(DEV))
+    score = x.float() @ W["m.gate.weight"].T
+    score = torch.softmax(score, -1) if scoring == "softmax" else torch.sigmoid(score)
+    want_ids = torch.sort(score, dim=-1, descending=True, stable=True).indices[:, :k]
+    assert torch.equal(ids.cpu().long(), want_ids)
     from tandemllm_b200.kernels import ops
     result = impl.experts(part, x.to(DEV), ids, wts)
     assert result is not None
@@ -206,7 +271,7 @@ def test_grouped_experts_with_swiglu(R, E, k, H, I):
     for e in range(E):
         rows, slot = torch.where(idc == e)
         if rows.numel():
-            h = torch.nn.functional.silu(xf[rows] @ w13[e, :I].float().T) * (xf[rows] @ w13[e, I:].float().T)
+            h = plain_activation(act, xf[rows] @ w13[e, :I].float().T) * (xf[rows] @ w13[e, I:].float().T)
             want.index_add_(0, rows, (h.to(torch.bfloat16).float() @ w2[e].float().T) * wc[rows, slot, None])
     assert rel(out, want) < 2e-2
 
