@@ -114,8 +114,9 @@ def attention(a) -> dict:
                                  host={"row_start": starts})
     cache = types.SimpleNamespace(k=kc, v=vc, page_size=page)
     out = torch.empty(R, Hq, D, dtype=torch.bfloat16, device=DEV)
-    if a.kernel == "mma":
+    if a.kernel in ("mma", "tc"):
         from tandemllm_b200.kernels import tensorcore
+        tensorcore.PROMPT_ATTENTION = "tcgen05" if a.kernel == "tc" else "mma"
         tensorcore.lib().tl_attention_mma_use_tma(int(a.copies == "tma"))
         fn = lambda: rt.tensorcore.attention(q, cache, table, step, D ** -0.5, None, out, rt)
     else:
@@ -164,7 +165,9 @@ def main(argv=None) -> int:
     t.add_argument("--heads", type=int, default=32)
     t.add_argument("--kv-heads", type=int, default=8)
     t.add_argument("--head-dim", type=int, default=64)
-    t.add_argument("--kernel", default="mma", choices=("mma", "split"))
+    t.add_argument("--kernel", default="tc", choices=("tc", "mma", "split"),
+                   help="tc: the tcgen05 kernel for prompt portions of head size 64 (decode rows go to the mma.sync kernel "
+                        "either way); mma: the mma.sync kernel for everything; split: the CUDA-core kernel")
     t.add_argument("--copies", default="tma", choices=("tma", "cp.async"),
                    help="decoding with the mma kernel: a producer warp's TMA copies, or cp.async from every thread")
     n = sub.add_parser("norm")

@@ -42,6 +42,8 @@ SKINNY_ROWS = 16                # rows of a step up to which the experts go to i
                                 # expert with more pairs has two tiles, and the second reads its weights from L2); measured
                                 # against the tcgen05 form: 8 % faster a step at 16 rows, even at 24, 4 % slower at 32
 SKINNY_PAIRS = 16               # routed pairs of such a step up to which its products run without a routing plan
+PROMPT_ATTENTION = "tcgen05"    # prompt portions of head size 64: the tcgen05 kernel (csrc/attention_tc.cu), or "mma" for the
+                                # mma.sync kernel that also takes them (kept for head size 128 and for comparison)
 _lib = None
 
 
@@ -62,6 +64,12 @@ def lib():
                                              c_void_p, ctypes.c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                              c_int, c_void_p, c_void_p]
         l.tl_paged_attention_mma.restype = c_int
+        l.tl_paged_attention_tc.argtypes = l.tl_paged_attention_mma.argtypes
+        l.tl_paged_attention_tc.restype = c_int
+        l.tl_attention_tc_tile_rows.argtypes = [c_int, c_int]
+        l.tl_attention_tc_tile_rows.restype = c_int
+        l.tl_attention_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
+        l.tl_attention_tc_supported.restype = c_int
         l.tl_attention_mma_use_tma.argtypes = [c_int]
         l.tl_attention_mma_use_tma.restype = None
         l.tl_attention_mma_tile_rows.argtypes = [c_int, c_int]
@@ -328,6 +336,10 @@ class TensorCore:
         Hk = cache.k.shape[1]
         if q.dtype != torch.bfloat16 or not lib().tl_attention_mma_supported(Hq, Hk, D):
             return False
+        G = Hq // Hk
+        if (PROMPT_ATTENTION == "tcgen05" and step.max_rows_per_request * G > 16
+                and lib().tl_attention_tc_supported(Hq, Hk, D, cache.page_size)):
+            return self._prompt_attention(q, cache, table, step, scale, window, out, runtime)
         tile_rows = lib().tl_attention_mma_tile_rows(Hq, Hk)
         tiles = self.query_tiles(step, tile_rows)
         n_tiles = tiles.shape[0]
@@ -354,6 +366,36 @@ class TensorCore:
         if span_keys:
             ops.attention_join(scratch, step.positions, window, out, spans, span_keys)
         return True
+
+
+def _prompt_attention(self, q, cache, table, step, scale, window, out, runtime) -> bool:
+    """Prompt portions (and whatever rows share their step) on the tcgen05 kernel: tiles of 128 M rows (128 / G query
+    rows), two CTAs an SM. The keys are split over spans only when the tiles alone would leave most of the GPU idle."""
+    R, Hq, D = q.shape
+    Hk = cache.k.shape[1]
+    tile_rows = lib().tl_attention_tc_tile_rows(Hq, Hk)
+    tiles = self.query_tiles(step, tile_rows)
+    n_tiles = tiles.shape[0]
+    ctas, slots = n_tiles * Hk, 2 * self.sm_count
+    span_keys, spans = 0, 1
+    if step.max_context > 1024 and 2 * ctas <= slots:
+        span_keys = max(512, -(-(-(-step.max_context // (slots // ctas))) // 128) * 128)
+        spans = -(-step.max_context // span_keys)
+        if spans <= 1:
+            span_keys, spans = 0, 1
+    scratch = runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans)) if span_keys else None
+    code = lib().tl_paged_attention_tc(
+        q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
+        cache.k.shape[0], tiles.data_ptr(), n_tiles, min(tile_rows, step.max_rows_per_request), step.positions.data_ptr(),
+        float(scale), int(window or 0), out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, span_keys,
+        self.status.data_ptr(), ops.stream())
+    _check(code, "attention_tc")
+    if span_keys:
+        ops.attention_join(scratch, step.positions, window, out, spans, span_keys)
+    return True
+
+
+TensorCore._prompt_attention = _prompt_attention
 
 
 def enable(runtime) -> TensorCore:

@@ -343,7 +343,27 @@ def test_attention_of_small_tiles_splits_the_keys_among_warps(split, Hq, Hk, D, 
     attention_against_plain([700, 90, 16, 300, 513, 64, 65], news, split, Hq, Hk, D, page, window)
 
 
-def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window):
+@pytest.mark.parametrize("split", [0, 256, 512])
+@pytest.mark.parametrize("Hq,Hk,page,window", [(8, 2, 16, None), (4, 4, 16, None), (8, 1, 16, 100), (32, 8, 16, None),
+                                               (3, 1, 64, None), (8, 2, 128, None), (4, 1, 128, 200), (6, 2, 8, 300),
+                                               (16, 4, 32, None), (5, 1, 256, None), (7, 7, 16, 130)])
+def test_prompt_attention_on_tcgen05(split, Hq, Hk, page, window):
+    """The tcgen05 kernel (scores and values in tensor memory, tiles of 128 M rows and 128 keys): prompt portions of
+    several lengths, a sequence's first rows, portions that end at a tile's edge and decode rows at short and long
+    contexts in one call, unsplit and split over key spans, group sizes that do not divide 128, pages of 8 to 256."""
+    attention_against_plain([700, 90, 7, 300, 513, 128, 256], [1, 23, 7, 150, 1, 128, 129], split, Hq, Hk, 64, page, window,
+                            kernel="tc")
+
+
+@pytest.mark.parametrize("rows,context", [(2048, 2048), (512, 4096), (1000, 1000)])
+def test_prompt_attention_on_tcgen05_over_many_key_tiles(rows, context):
+    """Whole prompts and a portion at the end of a long context: a tile walks up to 32 key tiles, the ring of key and
+    value slots turns many times, and the running maximum and the rescaling of O are exercised over long rows."""
+    attention_against_plain([context], [rows], 0, 32, 8, 64, 16, None, kernel="tc")
+    attention_against_plain([context], [rows], 1024, 8, 2, 64, 16, 600, kernel="tc")
+
+
+def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window, kernel="mma"):
     import types
 
     from tandemllm_b200.kernels import ops, tensorcore
@@ -360,7 +380,10 @@ def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window):
     step = types.SimpleNamespace(n_requests=len(seqs), max_rows_per_request=max(news), max_context=max(seqs),
                                  positions=pos_dev, host={"row_start": starts})
     lib = tensorcore.lib()
-    tile_rows = lib.tl_attention_mma_tile_rows(Hq, Hk)
+    if kernel == "tc":
+        assert lib.tl_attention_tc_supported(Hq, Hk, D, page)
+    tile_rows = lib.tl_attention_tc_tile_rows(Hq, Hk) if kernel == "tc" else lib.tl_attention_mma_tile_rows(Hq, Hk)
+    launch = lib.tl_paged_attention_tc if kernel == "tc" else lib.tl_paged_attention_mma
     tiles = impl.query_tiles(step, tile_rows)
     assert int(tiles[:, 2].sum()) == R and int(tiles[:, 2].max()) <= tile_rows
     spans = -(-max(seqs) // split) if split else 1          # `split`: key positions per span, 0 for one pass
@@ -368,12 +391,12 @@ def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window):
     out = torch.full((R, Hq, D), float("nan"), dtype=torch.bfloat16, device=DEV)
     scale = 0.9 / D ** 0.5
     qd, kd, vd, td = q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV)      # kept alive until the kernel has run
-    code = lib.tl_paged_attention_mma(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(),
-                                      table.shape[1], page, kd.shape[0], tiles.data_ptr(), tiles.shape[0], int(tiles[:, 2].max()),
-                                      pos_dev.data_ptr(), scale,
-                                      window or 0, out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, int(split),
-                                      rt.status.data_ptr(), ops.stream())
-    assert code == 0
+    code = launch(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(),
+                  table.shape[1], page, kd.shape[0], tiles.data_ptr(), tiles.shape[0], int(tiles[:, 2].max()),
+                  pos_dev.data_ptr(), scale,
+                  window or 0, out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, int(split),
+                  rt.status.data_ptr(), ops.stream())
+    assert code == 0, lib.tl_tc_last_error().decode()
     if split:
         ops.attention_join(scratch, pos_dev, window, out, spans, split)
     torch.cuda.synchronize()
@@ -385,10 +408,17 @@ def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window):
         at += n
 
 
+@pytest.mark.parametrize("split", [0, 256])
+@pytest.mark.parametrize("page", [16, 128])
+def test_window_edge_on_tcgen05(page, split):
+    """The same planted key at the window's edge through the tcgen05 prompt kernel."""
+    test_window_edge_on_tensor_cores(64, page, split, 1, kernel="tc")
+
+
 @pytest.mark.parametrize("use_tma", [1, 0])
 @pytest.mark.parametrize("split", [0, 256])
 @pytest.mark.parametrize("D,page", [(64, 16), (64, 48), (64, 128), (128, 16), (128, 48), (128, 128)])
-def test_window_edge_on_tensor_cores(D, page, split, use_tma):
+def test_window_edge_on_tensor_cores(D, page, split, use_tma, kernel="mma"):
     """The tensor-core kernel's window: with a window of w the key w positions behind a row is out and the one w - 1
     behind it is in. One key is made to match the queries so strongly that the output is its value when it is visible:
     at the first position inside the window of the checked row (in), and one before it (out). A decode row, and a prompt
@@ -421,16 +451,18 @@ def test_window_edge_on_tensor_cores(D, page, split, use_tma):
             pos_dev = torch.tensor(positions, dtype=torch.int32, device=DEV)
             step = types.SimpleNamespace(n_requests=2, max_rows_per_request=max(news), max_context=max(seqs),
                                          positions=pos_dev, host={"row_start": [0, 1, 41]})
-            tiles = impl.query_tiles(step, lib.tl_attention_mma_tile_rows(Hq, Hk))
+            tile_rows = lib.tl_attention_tc_tile_rows(Hq, Hk) if kernel == "tc" else lib.tl_attention_mma_tile_rows(Hq, Hk)
+            launch = lib.tl_paged_attention_tc if kernel == "tc" else lib.tl_paged_attention_mma
+            tiles = impl.query_tiles(step, tile_rows)
             spans = -(-max(seqs) // split) if split else 1
             R = sum(news)
             scratch = torch.full((ops.attention_scratch_floats(R, Hq, D, spans),), float("nan"), device=DEV) if split else None
             out = torch.full((R, Hq, D), float("nan"), dtype=torch.bfloat16, device=DEV)
             qd, kd, vd, td = q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV)
-            code = lib.tl_paged_attention_mma(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(), table.shape[1], page,
-                                              kd.shape[0], tiles.data_ptr(), tiles.shape[0], int(tiles[:, 2].max()),
-                                              pos_dev.data_ptr(), 1.0, w, out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans,
-                                              int(split), rt.status.data_ptr(), ops.stream())
+            code = launch(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(), table.shape[1], page,
+                          kd.shape[0], tiles.data_ptr(), tiles.shape[0], int(tiles[:, 2].max()),
+                          pos_dev.data_ptr(), 1.0, w, out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans,
+                          int(split), rt.status.data_ptr(), ops.stream())
             assert code == 0
             if split:
                 ops.attention_join(scratch, pos_dev, w, out, spans, split)
