@@ -118,6 +118,7 @@ def attention(a) -> dict:
         from tandemllm_b200.kernels import tensorcore
         tensorcore.PROMPT_ATTENTION = "tcgen05" if a.kernel == "tc" else "mma"
         tensorcore.lib().tl_attention_mma_use_tma(int(a.copies == "tma"))
+        tensorcore.lib().tl_attention_tc_p_in_tensor_memory(int(a.p == "tmem"))
         fn = lambda: rt.tensorcore.attention(q, cache, table, step, D ** -0.5, None, out, rt)
     else:
         spans = ops.attention_spans(L)
@@ -168,6 +169,8 @@ def main(argv=None) -> int:
     t.add_argument("--kernel", default="tc", choices=("tc", "mma", "split"),
                    help="tc: the tcgen05 kernel for prompt portions of head size 64 (decode rows go to the mma.sync kernel "
                         "either way); mma: the mma.sync kernel for everything; split: the CUDA-core kernel")
+    t.add_argument("--p", default="tmem", choices=("tmem", "smem"),
+                   help="the tcgen05 kernel: P as the MMA's operand from tensor memory, or through shared memory")
     t.add_argument("--copies", default="tma", choices=("tma", "cp.async"),
                    help="decoding with the mma kernel: a producer warp's TMA copies, or cp.async from every thread")
     n = sub.add_parser("norm")

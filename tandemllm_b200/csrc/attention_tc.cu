@@ -13,14 +13,15 @@
 //               (a page's rows of the KV head, 64 columns, 128-byte swizzle) into a ring of three 16 KB slots that holds
 //               keys and values in turn (K0 V0 K1 V1 ...); a slot is reused when the product that read it has completed
 //   warp 1      one thread issues S = Q K^T (M 128, N 128, k = the head size; Q and K K-major) into tensor-memory columns
-//               0..127, commits, and, once the softmax warps have written P, O += P V (M 128, N = head size, k = 128 keys;
-//               P K-major from shared memory, V as it lies in the cache: N-major, "MN-major" in the descriptor) into
-//               columns 128.., and commits
-//   warps 2..5  the softmax: thread i owns M row i (tensor-memory lane i). It reads its row of S twice with tcgen05.ld:
-//               once for the maximum, once to form p = exp2(s * scale * log2 e - max), which it sums in 32-bit, rounds to
-//               bfloat16 and stores to shared memory in the layout the MMA reads (128-byte swizzle). When a row's maximum
-//               rose, its O row in tensor memory is rescaled first (tcgen05.ld, multiply, tcgen05.st). At the end the
-//               same threads read O, divide by the row sums and store.
+//               0..127 and commits; it issues the next tile's S as soon as the softmax warps hold this tile's S in their
+//               registers, so that product runs under their exponentials; once they have written P it issues O += P V
+//               (M 128, N = head size, k = 128 keys; P K-major from shared memory, V as it lies in the cache: N-major,
+//               "MN-major" in the descriptor) into columns 128.., and commits
+//   warps 2..5  the softmax: thread i owns M row i (tensor-memory lane i). It reads its row of S with tcgen05.ld (all
+//               128 columns in flight, one wait), gives S back, takes the maximum, forms p = exp2(s * scale * log2 e -
+//               max), sums it in 32-bit, rounds it to bfloat16 and stores it to shared memory in the layout the MMA reads
+//               (128-byte swizzle). When a row's maximum rose, its O row in tensor memory is rescaled first (tcgen05.ld,
+//               multiply, tcgen05.st). At the end the same threads read O, divide by the row sums and store.
 //
 // S and O together take 192 of a CTA's 256 tensor-memory columns and the CTA 98 KB of shared memory, so two CTAs share an
 // SM: one's softmax runs beside the other's products. With `split` the keys are cut into spans exactly as in
@@ -32,7 +33,6 @@ namespace tl {
 
 constexpr int TC_KT = 128;        // keys per tile
 constexpr int TC_M = 128;         // M rows per tile
-constexpr int TC_RING = 3;        // 16 KB slots of the key/value ring
 constexpr int TC_THREADS = 192;
 
 // K-major operand tile with 128-byte rows and 128-byte swizzle (Q, K and P): 8-row groups 1024 bytes apart.
@@ -90,6 +90,19 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// The same without the wait: several loads may be in flight before one tc_ld_wait().
+__device__ __forceinline__ void tc_ld32_async(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+      "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
@@ -98,6 +111,24 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
         "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
         "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// A from tensor memory (P: lane = M row, a column holds two consecutive bfloat16 of the row), B from shared memory.
+__device__ __forceinline__ void tc_mma_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -116,7 +147,9 @@ struct TcKvMaps {
   CUtensorMap k, v;       // the key and value caches as [pages * KV heads * page size, D], boxes of box_rows x 64 columns
 };
 
-template <int D>
+// P_TMEM: P goes back to tensor memory (columns 192..255) and is the MMA's A operand from there, which leaves shared
+// memory for a ring of RING key/value slots; else P goes through 32 KB of shared memory.
+template <int D, bool P_TMEM, int RING>
 __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
     const bf16* __restrict__ q, const int* __restrict__ block_table, int max_pages, int page_size, int page_shift,
     int num_pages, const int* __restrict__ tiles, int n_tiles, const int* __restrict__ positions, float scale, int window,
@@ -125,9 +158,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
   static_assert(D == 64, "the tensor-core prompt attention is built for a head size of 64");
   constexpr int SLOT_BYTES = TC_KT * 128;          // 16 KB: 128 keys x 64 columns
   constexpr int Q_BYTES = TC_M * D * 2;            // 16 KB
-  constexpr int P_BYTES = TC_M * TC_KT * 2;        // 32 KB: two halves of 64 keys, each [128 rows][128 bytes]
+  constexpr int P_BYTES = P_TMEM ? 0 : TC_M * TC_KT * 2;        // 32 KB: two halves of 64 keys, each [128 rows][128 bytes]
   constexpr uint32_t TMEM_COLS = 256;
-  constexpr uint32_t O_COL = 128;
+  constexpr uint32_t O_COL = 128, P_COL = 192;
+  constexpr int TC_RING = RING;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sq = smem;
@@ -138,7 +172,9 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
   uint64_t* s_ready = empty + TC_RING;
   uint64_t* p_ready = s_ready + 1;
   uint64_t* o_done = p_ready + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+  uint64_t* s_free = o_done + 1;
+  uint64_t* o_ready = s_free + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
   volatile uint32_t* aborted = tmem_slot + 1;
 
   chain_next();
@@ -173,6 +209,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
     mbar_init(s_ready, 1);
     mbar_init(p_ready, 4);            // one arrival a softmax warp
     mbar_init(o_done, 1);
+    mbar_init(s_free, 4);             // one arrival a softmax warp: S is in their registers
+    mbar_init(o_ready, 1);            // the commit behind a tile's O += P V
     *aborted = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -263,10 +301,9 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
       constexpr uint32_t idesc_o = tc_idesc(D, true);
       const uint32_t q_addr = smem_u32(sq), p_addr = smem_u32(sp);
       bool ok = true;
-      for (int j = 0; j < n_kt && ok; ++j) {
-        const int ik = 2 * j, iv = 2 * j + 1;
-        const int slot_k = ik % TC_RING, slot_v = iv % TC_RING;
-        if (!mbar_wait(&full[slot_k], (ik / TC_RING) & 1)) { ok = false; break; }
+      auto scores = [&](int j) -> bool {         // S = Q K^T of key tile j into columns 0..127
+        const int ik = 2 * j, slot_k = ik % TC_RING;
+        if (!mbar_wait(&full[slot_k], (ik / TC_RING) & 1)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t k_addr = smem_u32(ring + slot_k * SLOT_BYTES);
 #pragma unroll
@@ -274,6 +311,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
           tc_mma(tmem_base, tc_desc_k_major(q_addr + kk * 32), tc_desc_k_major(k_addr + kk * 32), idesc_s, kk > 0 ? 1u : 0u);
         tc_commit(&empty[slot_k]);                       // the keys' slot is free once the scores are done
         tc_commit(s_ready);
+        return true;
+      };
+      ok = scores(0);
+      for (int j = 0; j < n_kt && ok; ++j) {
+        // the next tile's scores as soon as this tile's S has been read out: they run under the softmax
+        if (j + 1 < n_kt) {
+          if (!mbar_wait(s_free, j & 1)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (!scores(j + 1)) { ok = false; break; }
+        }
+        const int iv = 2 * j + 1, slot_v = iv % TC_RING;
         if (!mbar_wait(p_ready, j & 1)) { ok = false; break; }       // P is in shared memory, O is rescaled
         if (!mbar_wait(&full[slot_v], (iv / TC_RING) & 1)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -281,11 +329,17 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
 #pragma unroll
         for (int kk = 0; kk < TC_KT / 16; ++kk) {
           // 16 keys: P's columns 16 kk .. (half kk / 4, 32 bytes a step inside the 128-byte row), V's rows 16 kk ..
-          const uint32_t pa = p_addr + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32;
-          tc_mma(tmem_base + O_COL, tc_desc_k_major(pa), tc_desc_mn_major(v_addr + kk * 2048, SLOT_BYTES), idesc_o,
-                 (j > 0 || kk > 0) ? 1u : 0u);
+          if constexpr (P_TMEM) {
+            tc_mma_a_tmem(tmem_base + O_COL, tmem_base + P_COL + kk * 8, tc_desc_mn_major(v_addr + kk * 2048, SLOT_BYTES),
+                          idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          } else {
+            const uint32_t pa = p_addr + (kk >> 2) * (TC_M * 128) + (kk & 3) * 32;
+            tc_mma(tmem_base + O_COL, tc_desc_k_major(pa), tc_desc_mn_major(v_addr + kk * 2048, SLOT_BYTES), idesc_o,
+                   (j > 0 || kk > 0) ? 1u : 0u);
+          }
         }
         tc_commit(&empty[slot_v]);
+        tc_commit(o_ready);
         if (j == n_kt - 1) tc_commit(o_done);
       }
       if (!ok) {
@@ -318,24 +372,30 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int key_base = kt * TC_KT;
       const bool open = rows_all_valid && key_base >= k_lo && key_base + TC_KT - 1 <= min(k_hi, first_pos) && key_base >= last_w_lo;
-      // ---- pass 1: the row's maximum ----
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < TC_KT / 32; ++c) {
-        uint32_t r[32];
-        tc_ld32(t_row + c * 32, r);
-        if (open) {
+      // ---- the row of S into registers (four loads in flight, one wait), and S is free for the next tile's scores ----
+      uint32_t r[TC_KT];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-        } else {
+      for (int c = 0; c < TC_KT / 32; ++c) tc_ld32_async(t_row + c * 32, r + c * 32);
+      tc_ld_wait();
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+      // ---- the row's maximum ----
+      if (!open) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int kp = key_base + c * 32 + e;
-            const bool in = v_row && kp >= k_lo && kp <= k_hi && kp <= p_row && kp >= w_row;
-            mx = fmaxf(mx, in ? __uint_as_float(r[e]) : -INFINITY);
-          }
+        for (int e = 0; e < TC_KT; ++e) {
+          const int kp = key_base + e;
+          const bool in = v_row && kp >= k_lo && kp <= k_hi && kp <= p_row && kp >= w_row;
+          r[e] = in ? r[e] : 0xff800000u;                 // -inf: exp2 of it is 0
         }
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains: a single one is 128 dependent steps
+#pragma unroll
+      for (int e = 0; e < TC_KT; e += 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx4[i] = fmaxf(mx4[i], __uint_as_float(r[e + i]));
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx = mx == -INFINITY ? mx : mx * scale2;
       const float m_new = fmaxf(m_run, mx);
       // a row that has seen no key yet keeps 0 as its reference, so that exp2(-inf - reference) is 0, not NaN
@@ -343,55 +403,49 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
       const float alpha = tc_exp2(m_run - ref);             // 0 where the row had no key before
       m_run = m_new;
       l_run *= alpha;
-      // ---- rescale O where a maximum rose (the products into O up to the last tile's are complete: the commit that
-      // announced S came after them) ----
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+      // ---- rescale O where a maximum rose, once the products into O up to the last tile's are complete ----
+      if (j > 0) {
+        if (!__all_sync(0xffffffffu, mbar_wait(o_ready, (j - 1) & 1))) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tc_ld32(t_row + O_COL + c * 32, r);
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tc_ld32(t_row + O_COL + c * 32, o);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-          tc_st32(t_row + O_COL + c * 32, r);
-        }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      }
-      // ---- pass 2: p = exp2(s - max), summed in 32-bit, rounded to bfloat16 into shared memory ----
-      float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < TC_KT / 32; ++c) {
-        uint32_t r[32];
-        tc_ld32(t_row + c * 32, r);
-        uint32_t pk[16];
-        if (open) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float p0 = tc_exp2(fmaf(__uint_as_float(r[e]), scale2, -ref));
-            const float p1 = tc_exp2(fmaf(__uint_as_float(r[e + 1]), scale2, -ref));
-            sum += p0 + p1;
-            pk[e >> 1] = tc_pack(p0, p1);
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tc_st32(t_row + O_COL + c * 32, o);
           }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      // ---- p = exp2(s - max), summed in 32-bit, rounded to bfloat16 into shared memory: 32 keys = four 16-byte pieces
+      // of this row, piece index 4 c + i, in half (4 c + i) / 8 ----
+      float sum = 0.f, sum_b = 0.f;
+#pragma unroll
+      for (int c = 0; c < TC_KT / 32; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = tc_exp2(fmaf(__uint_as_float(r[c * 32 + 2 * e]), scale2, -ref));
+          const float p1 = tc_exp2(fmaf(__uint_as_float(r[c * 32 + 2 * e + 1]), scale2, -ref));
+          sum += p0;
+          sum_b += p1;
+          pk[e] = tc_pack(p0, p1);
+        }
+        if constexpr (P_TMEM) {
+          tc_st16(t_row + P_COL + c * 16, pk);
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const int kp = key_base + c * 32 + e;
-            const bool in0 = v_row && kp >= k_lo && kp <= k_hi && kp <= p_row && kp >= w_row;
-            const bool in1 = v_row && kp + 1 >= k_lo && kp + 1 <= k_hi && kp + 1 <= p_row && kp + 1 >= w_row;
-            const float p0 = in0 ? tc_exp2(fmaf(__uint_as_float(r[e]), scale2, -ref)) : 0.f;
-            const float p1 = in1 ? tc_exp2(fmaf(__uint_as_float(r[e + 1]), scale2, -ref)) : 0.f;
-            sum += p0 + p1;
-            pk[e >> 1] = tc_pack(p0, p1);
+          for (int i = 0; i < 4; ++i) {
+            const int piece = c * 4 + i;
+            uint8_t* dst = sp + (piece >> 3) * (TC_M * 128) + m * 128 + (((piece & 7) ^ (m & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
           }
         }
-        // 32 keys = four 16-byte pieces of this row: piece index 4 c + i, in half (4 c + i) / 8
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int piece = c * 4 + i;
-          uint8_t* dst = sp + (piece >> 3) * (TC_M * 128) + m * 128 + (((piece & 7) ^ (m & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-        }
       }
-      l_run += sum;
+      if constexpr (P_TMEM) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      l_run += sum + sum_b;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");     // this thread's tensor-memory reads and writes
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");         // its P row, for the MMA's async reads
       __syncwarp();
@@ -449,6 +503,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
   }
 }
 
+static int& p_in_tensor_memory() {
+  static int on = 1;
+  return on;
+}
+
 }  // namespace tl
 
 using namespace tl;
@@ -487,10 +546,16 @@ extern "C" int tl_paged_attention_tc(const void* q, const void* k_cache, const v
                  ((uintptr_t)v_cache % 16) == 0 && (!scratch || ((uintptr_t)scratch % 16) == 0),
              "attention (tcgen05): operands must be 16-byte aligned (%d)", 0);
   TL_REQUIRE((long long)num_pages * Hk * page_size < (1LL << 31), "attention (tcgen05): a cache of %d pages is too large", num_pages);
-  constexpr int SMEM = TC_M * 64 * 2 + TC_M * TC_KT * 2 + TC_RING * TC_KT * 128 + 256 + 1024;
+  const bool p_tmem = p_in_tensor_memory() != 0;
+  constexpr int RING_S = 3, RING_T = 5;
+  constexpr int SMEM_S = TC_M * 64 * 2 + TC_M * TC_KT * 2 + RING_S * TC_KT * 128 + 256 + 1024;
+  constexpr int SMEM_T = TC_M * 64 * 2 + RING_T * TC_KT * 128 + 256 + 1024;
+  const int SMEM = p_tmem ? SMEM_T : SMEM_S;
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<64, false, RING_S>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_S);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_tc_kernel<64, true, RING_T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_T);
     if (e != cudaSuccess) return (int)e;
     set = true;
   }
@@ -507,7 +572,14 @@ extern "C" int tl_paged_attention_tc(const void* q, const void* k_cache, const v
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (long long)rows * Hq * n_spans * D : nullptr;
   dim3 grid(n_tiles, Hk, split ? n_spans : 1);
-  return (int)launch_chained(attention_tc_kernel<64>, grid, dim3(TC_THREADS), SMEM, stream, (const bf16*)q, block_table,
-                             max_pages, page_size, page_shift, num_pages, tiles, n_tiles, positions, scale, window, (bf16*)out,
-                             part_o, part_ml, n_spans, split, Hq, Hk, status, maps, box_rows);
+  if (p_tmem)
+    return (int)launch_chained(attention_tc_kernel<64, true, RING_T>, grid, dim3(TC_THREADS), SMEM, stream, (const bf16*)q,
+                               block_table, max_pages, page_size, page_shift, num_pages, tiles, n_tiles, positions, scale, window,
+                               (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status, maps, box_rows);
+  return (int)launch_chained(attention_tc_kernel<64, false, RING_S>, grid, dim3(TC_THREADS), SMEM, stream, (const bf16*)q,
+                             block_table, max_pages, page_size, page_shift, num_pages, tiles, n_tiles, positions, scale, window,
+                             (bf16*)out, part_o, part_ml, n_spans, split, Hq, Hk, status, maps, box_rows);
 }
+
+// 1 (the default): P is the MMA's operand from tensor memory; 0: P goes through shared memory (kept for comparison).
+extern "C" void tl_attention_tc_p_in_tensor_memory(int on) { p_in_tensor_memory() = on; }

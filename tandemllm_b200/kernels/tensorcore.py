@@ -70,6 +70,8 @@ def lib():
         l.tl_attention_tc_tile_rows.restype = c_int
         l.tl_attention_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
         l.tl_attention_tc_supported.restype = c_int
+        l.tl_attention_tc_p_in_tensor_memory.argtypes = [c_int]
+        l.tl_attention_tc_p_in_tensor_memory.restype = None
         l.tl_attention_mma_use_tma.argtypes = [c_int]
         l.tl_attention_mma_use_tma.restype = None
         l.tl_attention_mma_tile_rows.argtypes = [c_int, c_int]

@@ -435,8 +435,9 @@ def fused_toy_spec(raw):
                      head_name="head.weight", name_prefixes=("",))
 
 
-def fused_toy_plain(raw, W, tokens):
-    """(logits, routing margins) of the whole sequence in plain torch."""
+def fused_toy_plain(raw, W, tokens, forced=None):
+    """(logits, routing margins) of the whole sequence in plain torch. `forced` {layer prefix: ids [T, 2]} replaces a
+    routed layer's choice of experts (the weights are still this function's own)."""
     eps, H, E = raw["eps"], raw["width"], raw["experts"]
     cfg = dict(num_attention_heads=4, num_key_value_heads=1, head_dim=64, hidden_size=H, norm_eps=eps, rope_theta=1e4)
     h = W["tok.weight"][torch.tensor(tokens)]
@@ -455,6 +456,9 @@ def fused_toy_plain(raw, W, tokens):
         ordered = torch.sort(logits, dim=-1, descending=True).values
         margins.append(ordered[:, 1] - ordered[:, 2])          # how far, in logits, the choice is from another
         ids, w = top.indices[:, :2], top.values[:, :2]
+        if forced is not None:
+            ids = forced[p].long()
+            w = torch.gather(score, 1, ids)
         w = w / w.sum(-1, keepdim=True)
         out = torch.zeros_like(n)
         for e in range(E):
@@ -476,9 +480,13 @@ def fused_toy_plain(raw, W, tokens):
     return P.rms_norm(h, W["last.weight"], eps) @ W["head.weight"].T, torch.stack(margins).min(0).values
 
 
-@pytest.mark.parametrize("dtype,tol,near", [("float32", 1e-4, 1e-4), ("bfloat16", 5e-2, 0.3)])   # (a squared gate doubles
-# the relative rounding error of what it squares: the bfloat16 tolerance is wider here than for the SiLU models)
-def test_another_architecture_reuses_the_fused_kernels_with_its_own_activation_and_scoring(tmp_path, dtype, tol, near):
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_another_architecture_reuses_the_fused_kernels_with_its_own_activation_and_scoring(tmp_path, dtype, tol):
+    """A routed model out of the product's own parts with a GELU-gated dense feed-forward and experts scored by a softmax
+    over all experts with a squared-ReLU gate, registered from here. In bfloat16 it runs the fused tensor-core kernels (the
+    persistent, the swapped and the register-only forms, decode steps from graphs). Every position is held to the plain
+    implementation run with the engine's own choice of experts (read from a traced second run), so that a routing near tie
+    is no excuse; in 32-bit the choice itself must be the plain implementation's."""
     from tandemllm_b200.config import Architecture, register, unregister
     from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
     from tandemllm_b200.parts import DecoderModel
@@ -495,20 +503,38 @@ def test_another_architecture_reuses_the_fused_kernels_with_its_own_activation_a
                 W[k] = (W[k] * 6).to(torch.bfloat16).float()             # spread the routing scores
         (tmp_path / "config.json").write_text(json.dumps(raw))
         write_file(str(tmp_path / "model.safetensors"), {k: v.to(torch.bfloat16) if dtype == "bfloat16" else v for k, v in W.items()})
-        eng = Engine.from_folder(str(tmp_path), EngineArgs(dtype=dtype, max_len=512, parallel=2, kv_blocks=32, graph=True))
         toks = torch.randint(0, 200, (170,), generator=torch.Generator().manual_seed(8)).tolist()
-        want, margin = fused_toy_plain(raw, W, toks)
-        eng.admit("t")
-        outs, at = [], 0
-        for n in (140, 9, 2) + (1,) * 19:                   # the persistent kernels, the swapped ones, the register-only ones, graphs
-            outs.append(eng.step([StepEntry("t", toks[at:at + n], list(range(n)))]).float().cpu())
-            at += n
-        assert at == 170 and (eng.step_function.graph_replays >= 10)
-        got = torch.cat(outs)
+        portions = (140, 9, 2) + (1,) * 19          # the persistent kernels, the swapped ones, the register-only ones, graphs
+
+        def run(traced):
+            eng = Engine.from_folder(str(tmp_path), EngineArgs(dtype=dtype, max_len=512, parallel=2, kv_blocks=32, graph=True))
+            routes = {}
+            if traced:
+                eng.step_function.trace = {}
+            eng.admit("t")
+            outs, at = [], 0
+            for n in portions:
+                outs.append(eng.step([StepEntry("t", toks[at:at + n], list(range(n)))]).float().cpu())
+                for prefix, ids in (eng.step_function.trace or {}).get("routes", []):
+                    routes.setdefault(prefix, []).append(ids.cpu())
+                at += n
+            assert at == 170 and (traced or eng.step_function.graph_replays >= 10)
+            eng.release("t")
+            return torch.cat(outs), {p: torch.cat(v) for p, v in routes.items()}
+        got, _ = run(False)
+        again, routes = run(True)
+        assert torch.equal(got, again), "a traced (eager) run gives the bits of the run with graphs"
+        assert set(routes) == {"b.1.", "b.2."} and all(v.shape == (170, 2) for v in routes.values())
+        plain_logits, margin = fused_toy_plain(raw, W, toks)
+        if dtype == "float32":
+            own = fused_toy_plain(raw, W, toks, forced=routes)[0]
+            assert torch.equal(own, plain_logits) or float((own - plain_logits).abs().max()) < 1e-6, "32-bit: the same experts"
+        want = fused_toy_plain(raw, W, toks, forced=routes)[0]
         err = (got - want).abs().amax(-1) / want.abs().amax(-1)
-        clear = margin >= near
-        assert float(err[clear].max()) < tol, (float(err[clear].max()), int((~clear).sum()))
-        assert int((~clear).sum()) <= 60, int((~clear).sum())
-        eng.release("t")
+        assert float(err.max()) < tol, (float(err.max()), int(err.argmax()))
+        # and the engine's choice differs from the plain one only where the plain margin (in logits) is small
+        differs = (got - plain_logits).abs().amax(-1) / plain_logits.abs().amax(-1) > tol
+        assert int(differs.sum()) <= 40 and (not bool(differs.any()) or float(margin[differs].max()) < 1.0), \
+            (int(differs.sum()), float(margin[differs].max()) if bool(differs.any()) else 0.0)
     finally:
         unregister("fused_toy")

@@ -364,6 +364,18 @@ def test_prompt_attention_on_tcgen05_over_many_key_tiles(rows, context):
 
 
 def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window, kernel="mma"):
+    if kernel == "tc":
+        # both forms of the tcgen05 kernel: P back in tensor memory (the default), and P through shared memory
+        from tandemllm_b200.kernels import tensorcore
+        lib = tensorcore.lib()
+        try:
+            for p_in_tmem in (0, 1):
+                lib.tl_attention_tc_p_in_tensor_memory(p_in_tmem)
+                attention_against_plain(seqs, news, split, Hq, Hk, D, page, window, kernel="tc, as set")
+        finally:
+            lib.tl_attention_tc_p_in_tensor_memory(1)
+        return
+    kernel = kernel.split(",")[0]
     import types
 
     from tandemllm_b200.kernels import ops, tensorcore
