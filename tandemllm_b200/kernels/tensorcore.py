@@ -370,33 +370,62 @@ class TensorCore:
         return True
 
 
+def _split_tiles(self, step, big_rows: int, small_rows: int):
+    """(tiles of requests that bring more than `small_rows` rows, cut into `big_rows` rows; one tile for each of the other
+    requests), each int32 [n, 3] = (request, first row, rows) on the device, or None. Kept on the step."""
+    key = ("split_tiles", big_rows, small_rows)
+    if key not in step.host:
+        starts = step.host["row_start"]
+        big, small = [], []
+        for b in range(step.n_requests):
+            n = starts[b + 1] - starts[b]
+            if n <= small_rows:
+                small.append((b, starts[b], n))
+            else:
+                big += [(b, r0, min(big_rows, starts[b + 1] - r0)) for r0 in range(starts[b], starts[b + 1], big_rows)]
+        both = torch.tensor(big + small, dtype=torch.int32).reshape(-1, 3).to(self.device, non_blocking=True)
+        step.host[key] = (both[:len(big)] if big else None, both[len(big):] if small else None,
+                          max((t[2] for t in small), default=0))
+    return step.host[key]
+
+
 def _prompt_attention(self, q, cache, table, step, scale, window, out, runtime) -> bool:
-    """Prompt portions (and whatever rows share their step) on the tcgen05 kernel: tiles of 128 M rows (128 / G query
-    rows), two CTAs an SM. The keys are split over spans only when the tiles alone would leave most of the GPU idle."""
+    """A step with prompt portions. Requests that bring many rows go to the tcgen05 kernel in tiles of 128 M rows (128 / G
+    query rows), two CTAs an SM; requests that bring a row or a few (the decode rows of a mixed step) go to the mma.sync
+    kernel's form for small tiles, which splits each key tile among its warps. Both cut the keys into the same spans, so
+    one join serves the step; the keys are split when the tiles alone would leave the GPU idle or the contexts are long
+    enough that a tile's walk over all its keys would be the step's tail."""
     R, Hq, D = q.shape
     Hk = cache.k.shape[1]
+    G = Hq // Hk
     tile_rows = lib().tl_attention_tc_tile_rows(Hq, Hk)
-    tiles = self.query_tiles(step, tile_rows)
-    n_tiles = tiles.shape[0]
-    ctas, slots = n_tiles * Hk, 2 * self.sm_count
+    big, small, small_max = self._split_tiles(step, tile_rows, 16 // G)
+    n_big = 0 if big is None else big.shape[0]
+    n_small = 0 if small is None else small.shape[0]
+    ctas, slots = (n_big + n_small) * Hk, 2 * self.sm_count
     span_keys, spans = 0, 1
-    if step.max_context > 1024 and 2 * ctas <= slots:
-        span_keys = max(512, -(-(-(-step.max_context // (slots // ctas))) // 128) * 128)
+    if step.max_context > 1024 and ctas < 2 * slots:
+        want = -(-2 * slots // ctas)                                   # spans that give every slot two CTAs
+        span_keys = max(1024, -(-(-(-step.max_context // want)) // 128) * 128)
         spans = -(-step.max_context // span_keys)
         if spans <= 1:
             span_keys, spans = 0, 1
     scratch = runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans)) if span_keys else None
-    code = lib().tl_paged_attention_tc(
-        q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
-        cache.k.shape[0], tiles.data_ptr(), n_tiles, min(tile_rows, step.max_rows_per_request), step.positions.data_ptr(),
-        float(scale), int(window or 0), out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans, span_keys,
-        self.status.data_ptr(), ops.stream())
-    _check(code, "attention_tc")
+    common = (step.positions.data_ptr(), float(scale), int(window or 0), out.data_ptr(), ops.ptr(scratch), R, Hq, Hk, D, spans,
+              span_keys, self.status.data_ptr(), ops.stream())
+    head = (q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
+            cache.k.shape[0])
+    if n_big:
+        _check(lib().tl_paged_attention_tc(*head, big.data_ptr(), n_big, min(tile_rows, step.max_rows_per_request), *common),
+               "attention_tc")
+    if n_small:
+        _check(lib().tl_paged_attention_mma(*head, small.data_ptr(), n_small, small_max, *common), "attention_mma")
     if span_keys:
         ops.attention_join(scratch, step.positions, window, out, spans, span_keys)
     return True
 
 
+TensorCore._split_tiles = _split_tiles
 TensorCore._prompt_attention = _prompt_attention
 
 

@@ -363,6 +363,41 @@ def test_prompt_attention_on_tcgen05_over_many_key_tiles(rows, context):
     attention_against_plain([context], [rows], 1024, 8, 2, 64, 16, 600, kernel="tc")
 
 
+@pytest.mark.parametrize("Hq,Hk,window", [(32, 8, None), (8, 2, 900), (4, 4, None)])
+def test_a_mixed_step_sends_portions_and_decode_rows_to_their_kernels_over_the_same_spans(Hq, Hk, window):
+    """What the dispatcher does for a step with prompt portions: long portions on the tcgen05 kernel, single decode rows
+    and portions of a few rows on the mma.sync kernel's small-tile form, both over the same key spans (contexts of
+    thousands of keys), one join."""
+    import types
+
+    from tests.test_gpu_kernels import paged_setup, plain_attention
+    impl, rt = tc()
+    D, page = 64, 16
+    seqs, news = [3000, 2000, 5000, 90, 4100, 130], [1, 300, 2, 40, 1, 130]
+    kc, vc, table, ks, vs = paged_setup(seqs, Hk, D, page, torch.bfloat16, seed=80)
+    R = sum(news)
+    q = rnd(R, Hq, D, seed=81)
+    positions = sum((list(range(L - n, L)) for L, n in zip(seqs, news)), [])
+    starts = [0]
+    for n in news:
+        starts.append(starts[-1] + n)
+    step = types.SimpleNamespace(n_requests=len(seqs), max_rows_per_request=max(news), max_context=max(seqs),
+                                 positions=torch.tensor(positions, dtype=torch.int32, device=DEV), host={"row_start": starts})
+    cache = types.SimpleNamespace(k=kc.to(DEV), v=vc.to(DEV), page_size=page)
+    out = torch.full((R, Hq, D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scale = 0.9 / D ** 0.5
+    assert impl.attention(q.to(DEV), cache, table.to(DEV), step, scale, window, out, rt)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    big, small, small_max = impl._split_tiles(step, 128 // (Hq // Hk), 16 // (Hq // Hk))
+    assert big is not None and small is not None and int(small[:, 2].max()) == small_max <= 16 // (Hq // Hk)
+    at = 0
+    for b, (L, n) in enumerate(zip(seqs, news)):
+        want = plain_attention(q[at:at + n].float(), ks[b], vs[b], scale, window)
+        assert rel(out[at:at + n], want) < 2e-2, f"sequence {b}"
+        at += n
+
+
 def attention_against_plain(seqs, news, split, Hq, Hk, D, page, window, kernel="mma"):
     if kernel == "tc":
         # both forms of the tcgen05 kernel: P back in tensor memory (the default), and P through shared memory
