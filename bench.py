@@ -343,7 +343,7 @@ class LaunchTimer:
         if name == "tl_gemm_skinny_grouped":
             return "experts gate/up + SwiGLU (register-only)" if args[11] else "experts down (register-only)"
         return {"tl_gemm_skinny_mma": "dense products (register-only)", "tl_gemm_skinny_conv": "in-projection + short conv",
-                "tl_add_rmsnorm": "residual add + norm (+ router, + deferred sums)", "tl_paged_attention_mma": "attention",
+                "tl_add_rmsnorm": "residual add + norm (+ router, + deferred sums)", "tl_paged_attention_mma": "attention", "tl_paged_attention_tc": "attention",
                 "tl_paged_attention_split": "attention", "tl_paged_attention_simt": "attention",
                 "tl_attention_join": "attention join", "tl_qk_prepare": "q/k norm + rotary + cache write",
                 "tl_moe_plan": "routing plan", "tl_gather_rows": "rows into expert order", "tl_short_conv": "short conv",

@@ -393,8 +393,7 @@ def _prompt_attention(self, q, cache, table, step, scale, window, out, runtime) 
     """A step with prompt portions. Requests that bring many rows go to the tcgen05 kernel in tiles of 128 M rows (128 / G
     query rows), two CTAs an SM; requests that bring a row or a few (the decode rows of a mixed step) go to the mma.sync
     kernel's form for small tiles, which splits each key tile among its warps. Both cut the keys into the same spans, so
-    one join serves the step; the keys are split when the tiles alone would leave the GPU idle or the contexts are long
-    enough that a tile's walk over all its keys would be the step's tail."""
+    one join serves the step; the keys are split only when the tiles alone would leave half of the GPU idle."""
     R, Hq, D = q.shape
     Hk = cache.k.shape[1]
     G = Hq // Hk
@@ -404,8 +403,10 @@ def _prompt_attention(self, q, cache, table, step, scale, window, out, runtime) 
     n_small = 0 if small is None else small.shape[0]
     ctas, slots = (n_big + n_small) * Hk, 2 * self.sm_count
     span_keys, spans = 0, 1
-    if step.max_context > 1024 and ctas < 2 * slots:
-        want = -(-2 * slots // ctas)                                   # spans that give every slot two CTAs
+    if step.max_context > 1024 and 2 * ctas <= slots:
+        # (only then: the join reads and writes every row's partial results, which for a prompt's many rows costs as
+        # much as the attention of a short context itself)
+        want = slots // ctas                                           # spans that fill the GPU once
         span_keys = max(1024, -(-(-(-step.max_context // want)) // 128) * 128)
         spans = -(-step.max_context // span_keys)
         if spans <= 1:
