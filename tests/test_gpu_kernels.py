@@ -115,6 +115,37 @@ def test_add_rmsnorm_adds_deferred_branch_outputs_and_routes(dtype, R):
     close(out, n32, dtype, "normed rows beside the router")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,E,k", [(2048, 32, 4), (2048, 64, 4), (136, 12, 3), (4100, 40, 5), (2048, 96, 4)])
+def test_the_router_inside_the_norm_routes_a_row_the_same_alone_and_among_many(dtype, H, E, k):
+    """A prompt's rows are normed and routed several a block, a decode step's one a block: the same experts must be
+    chosen, and the weights and the normed rows may differ by rounding only (the sum of squares of a row is added up by 64
+    threads in one form and by 512 in the other), or a row would route differently depending on what else is in its step."""
+    o = ops()
+    R = 150
+    res0, w = rnd(R, H, seed=1), 1 + rnd(H, seed=2, scale=0.2)
+    gate, bias = rnd(E, H, seed=7, scale=0.3), rnd(E, seed=8, scale=0.2)
+
+    def run(lo, hi):
+        n = hi - lo
+        route = {"weight": gate.to(DEV), "bias": bias.to(DEV), "k": k, "normalize": True, "floor": 1e-6, "scale": 1.0,
+                 "ids": torch.empty(n, k, dtype=torch.int32, device=DEV), "wts": torch.empty(n, k, dtype=torch.float32, device=DEV)}
+        out = torch.empty(n, H, dtype=dtype, device=DEV)
+        o.add_rmsnorm(res0[lo:hi].clone().to(DEV), None, w.to(DEV), 1e-5, out, None, None, route)
+        return route["ids"].cpu(), route["wts"].cpu(), out.float().cpu()
+    many = run(0, R)                                       # more than 64 rows: several rows a block
+    few = [run(lo, min(lo + 50, R)) for lo in range(0, R, 50)]      # at most 64: one row a block
+    alone = [torch.cat([f[j] for f in few]) for j in range(3)]
+    assert torch.equal(many[0], alone[0]), "the chosen experts, in order"
+    assert float((many[1] - alone[1]).abs().max()) <= 2e-6, "weights"
+    assert float((many[2] - alone[2]).abs().max()) <= (1e-5 if dtype == torch.float32 else 2e-2) * float(alone[2].abs().max())
+    n32 = P.rms_norm(res0, w, 1e-5)
+    cfg = dict(num_experts_per_tok=k, use_expert_bias=True, norm_topk_prob=True, routed_scaling_factor=1.0)
+    want_ids, want_w = P.route(n32, {"gate.weight": gate, "expert_bias": bias}, "", cfg)
+    assert torch.equal(many[0].long(), want_ids)
+    close(many[1], want_w, torch.float32, "routing weights")
+
+
 @pytest.mark.parametrize("P_rows,E,k", [(8, 32, 4), (64, 6, 3), (1500, 8, 4), (3000, 200, 3), (1025, 1000, 5), (4096, 32, 4),
                                         (6000, 8, 3), (4500, 64, 4)])
 def test_plan_forms_agree_and_copy_rows(P_rows, E, k):
