@@ -234,8 +234,9 @@ class TensorCore:
         P = R * k
         act = torch.empty(P, inter, dtype=x.dtype, device=x.device)
         y = torch.empty(P, H, dtype=torch.float32, device=x.device)
-        if plan is None and part.load is None and P <= SKINNY_PAIRS and ids.is_contiguous():
-            # No plan: the products' CTAs find each expert's pairs in the ids themselves, rows stay in pair order. A
+        if plan is None and part.load is None and P <= SKINNY_PAIRS and R <= 8 and ids.is_contiguous():
+            # No plan: the products' CTAs find each expert's pairs in the ids themselves, rows stay in pair order (a CTA
+            # takes all of an expert's pairs, at most 8 rows: a row chooses an expert once, so up to 8 rows of a step). A
             # pair whose expert an earlier pair has costs CTAs that start, look and leave in between the working ones.
             # Measured a step of 22 expert layers, top-4 of 32 experts: 97 us gained with 4 pairs, 82 with 8, 33 with 16;
             # 26 lost with 24, 74 with 32 (and 45 lost with 32 pairs over 64 experts).

@@ -11,7 +11,8 @@ allowed exception is a position whose routing is a near tie in the plain impleme
 in bfloat16, where activations carry errors of about a hundredth of their size), the engine may choose the other
 expert, and that token's logits then differ by much more than rounding. The reference sets near ties aside the
 same way when it compares engines (tools/lfm_check.py:100-125). Such positions must be few (a tenth at most),
-and a position with a clear routing margin must be within the tolerance whatever the others do. A position set
+and a position with a clear routing margin must be within the tolerance, unless an earlier position of its own request
+was set aside (it attends to that position's keys and values): then it must pass the check below. A position set
 aside is not left unchecked: the trace is replayed once more with the engine recording the experts it chose
 (`StepFunction.trace`), the plain implementation is run again with exactly that choice forced in every layer and
 at every position of the request, and the position must then be within the tolerance.
@@ -124,7 +125,8 @@ class Case:
         return checked
 
     def compare(self, got: dict, what: str) -> None:
-        worst, rerouted, first_bad = 0.0, [], None
+        worst, rerouted, downstream, first_bad = 0.0, [], [], None
+        touched = set()             # requests in which an earlier position went the other way at a routing near tie
         for (rid, pos), row in sorted(got.items()):
             ref = self.ref[rid][pos]
             err = float((row - ref).abs().max() / ref.abs().max())
@@ -132,6 +134,11 @@ class Case:
                 worst = max(worst, err)
             elif float(self.margin[rid][pos]) < NEAR_TIE[self.dtype]:
                 rerouted.append((rid, pos, round(err, 3)))          # a routing near tie went the other way
+                touched.add(rid)
+            elif rid in touched:
+                # its own routing is clear, but it reads (keys, values, conv state) what a rerouted earlier position of
+                # its request left: no excuse by itself, it must pass the check with the engine's routes forced below
+                downstream.append((rid, pos, round(err, 3)))
             elif first_bad is None:
                 first_bad = (rid, pos, err, float(self.margin[rid][pos]))
         assert first_bad is None, (f"{what} [{self.name} {self.dtype}]: first wrong token is {first_bad[0]} position "
@@ -139,10 +146,15 @@ class Case:
                                    f"routing margin {first_bad[3]:.3g}; tolerance {TOL[self.dtype]:.1g}")
         assert len(rerouted) <= max(1, len(got) // 10), (f"{what} [{self.name} {self.dtype}]: {len(rerouted)} of {len(got)} "
                                                          f"positions differ as routing near ties: {rerouted[:8]}")
-        if rerouted and getattr(self, "_last", (None, None, None))[2] == id(got):
-            checked = self.recheck_with_the_engines_routes(rerouted, what)
+        can_recheck = getattr(self, "_last", (None, None, None))[2] == id(got)
+        assert not downstream or can_recheck, (f"{what} [{self.name} {self.dtype}]: positions behind a rerouted one differ "
+                                               f"and cannot be rechecked here: {downstream[:8]}")
+        if rerouted and can_recheck:
+            checked = self.recheck_with_the_engines_routes(rerouted + downstream, what)
+            assert checked >= len(downstream), "every position behind a rerouted one was held to the forced-route run"
             print(f"{what} [{self.name} {self.dtype}]: {len(rerouted)} of {len(got)} positions set aside as routing near "
-                  f"ties, {checked} of them held to the plain implementation with the engine's choice forced")
+                  f"ties and {len(downstream)} behind them, {checked} held to the plain implementation with the engine's "
+                  f"choice forced")
 
 
 def greedy_like_plain(case, prompt, out) -> None:

@@ -214,6 +214,7 @@ def test_split_k_is_used_and_repeatable():
                                        (1, 32, 4, 256, 1024), (2, 16, 3, 200, 520), (5, 6, 2, 136, 72),
                                        (8, 4, 4, 72, 40), (7, 3, 3, 88, 24), (8, 2, 2, 72, 40),     # every expert holds every row
                                        (16, 4, 2, 72, 40), (13, 3, 3, 88, 24), (16, 32, 4, 256, 192),  # experts with two tiles of 8
+                                       (12, 5, 1, 72, 40), (16, 2, 1, 72, 40), (9, 1, 1, 72, 40),   # top-1: up to 16 pairs, yet an expert with more than 8 rows
                                        (2048, 4, 2, 64, 128)])
 def test_grouped_experts_with_swiglu(R, E, k, H, I):
     grouped_experts(R, E, k, H, I, "silu", "sigmoid")

@@ -42,12 +42,37 @@ TINY_C = dict(
     rope_parameters={"rope_type": "default", "rope_theta": 1000000.0}, eos_token_id=2, bos_token_id=1, pad_token_id=0,
 )
 
+# Two more with sizes no kernel is tuned for. D: a head size of 48 (a multiple of 16 that is no power of two), as many KV
+# heads as query heads, two conv taps, top-1 of 5 experts, no dense layer, an odd vocabulary, attention first. E: a head
+# size of 80, three query heads a KV head, five conv taps with bias, every expert chosen (top-7 of 7), an expert width that
+# is no multiple of 8 (the tensor-core kernels cannot take it and must say so to their caller, not compute wrongly), a
+# scaling factor, an untied head.
+TINY_D = dict(
+    model_type="lfm2_moe", architectures=["Lfm2MoeForCausalLM"], vocab_size=1001, hidden_size=80,
+    intermediate_size=144, moe_intermediate_size=40, num_hidden_layers=3, num_attention_heads=5,
+    num_key_value_heads=5, head_dim=48, norm_eps=1e-5, max_position_embeddings=4096, conv_bias=False,
+    conv_L_cache=2, num_dense_layers=0, num_experts=5, num_experts_per_tok=1, use_expert_bias=True,
+    routed_scaling_factor=1.0, norm_topk_prob=True, tie_word_embeddings=True,
+    layer_types=["full_attention", "full_attention", "conv"],
+    rope_parameters={"rope_type": "default", "rope_theta": 50000.0}, eos_token_id=2, bos_token_id=1, pad_token_id=0,
+)
+
+TINY_E = dict(
+    model_type="lfm2_moe", architectures=["Lfm2MoeForCausalLM"], vocab_size=517, hidden_size=136,
+    intermediate_size=100, moe_intermediate_size=28, num_hidden_layers=5, num_attention_heads=6,
+    num_key_value_heads=2, head_dim=80, norm_eps=3e-6, max_position_embeddings=4096, conv_bias=True,
+    conv_L_cache=5, num_dense_layers=1, num_experts=7, num_experts_per_tok=7, use_expert_bias=False,
+    routed_scaling_factor=0.7, norm_topk_prob=False, tie_word_embeddings=False,
+    layer_types=["conv", "full_attention", "conv", "conv", "full_attention"],
+    rope_parameters={"rope_type": "default", "rope_theta": 1000000.0}, eos_token_id=2, bos_token_id=1, pad_token_id=0,
+)
+
 # B without the three options the reference refuses, so the reference itself can run it
 TINY_B_REFERENCE = {**TINY_B, "conv_bias": False, "norm_topk_prob": True}
 
-SEEDS = {"a": 0, "b": 1, "c": 2}
-STD = {"a": 0.02, "b": 0.05, "c": 0.02}
-CONFIGS = {"a": TINY_A, "b": TINY_B, "c": TINY_C}
+SEEDS = {"a": 0, "b": 1, "c": 2, "d": 3, "e": 4}
+STD = {"a": 0.02, "b": 0.05, "c": 0.02, "d": 0.04, "e": 0.03}
+CONFIGS = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D, "e": TINY_E}
 
 
 def prompts(name: str) -> list[list[int]]:
