@@ -55,7 +55,8 @@ class Case:
         for rid, toks in self.requests.items():
             margins = []
             self.ref[rid] = P.forward(self.cfg, self.W, toks, margins=margins)
-            self.margin[rid] = torch.stack(margins).min(0).values      # per position, the tightest routing margin
+            # per position, the tightest routing margin (a model without a routed layer has none to be near)
+            self.margin[rid] = torch.stack(margins).min(0).values if margins else torch.full((len(toks),), float("inf"))
 
     def engine(self, max_tokens: int, parallel: int = 4, block_size: int = 16, **kw):
         from tandemllm_b200.engine import Engine, EngineArgs

@@ -228,6 +228,25 @@ def test_grouped_experts_with_other_activations_and_scoring(R, E, k, H, I, act, 
     grouped_experts(R, E, k, H, I, act, scoring)
 
 
+def _drawn_expert_shapes():
+    import random
+    rng = random.Random(5)
+    shapes = []
+    for _ in range(36):
+        E = rng.choice([1, 2, 3, 5, 8, 9, 16, 33, 40, 70])
+        k = rng.randint(1, min(E, 8))
+        R = rng.choice([1, 2, 3, 7, 8, 9, 12, 15, 16, 17, 24, 31, 32, 33, 47, 64, 65, 100, 128, 129, 200, 300])
+        shapes.append((R, E, k, rng.choice([72, 136]), rng.choice([40, 72])))
+    return shapes
+
+
+@pytest.mark.parametrize("R,E,k,H,I", _drawn_expert_shapes())
+def test_grouped_experts_at_drawn_rows_experts_and_top_k(R, E, k, H, I):
+    """The experts' dispatch picks a kernel form by the step's rows, the pairs and the experts (no plan, plan tiles of 8,
+    fetched rows, the swapped tile widths, the persistent kernel): drawn combinations around every threshold."""
+    grouped_experts(R, E, k, H, I, "silu", "sigmoid")
+
+
 def grouped_experts(R, E, k, H, I, act, scoring):
     from tandemllm_b200.config import PartSpec
     from tandemllm_b200.parts import make_part
