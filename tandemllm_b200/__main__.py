@@ -6,8 +6,8 @@
   bench           the measurement program (the same as bench.py at the repository's root)
 
 Option names follow the reference's command lines where it has them: `--model`, `--max-len`, `--tokens`,
-`--graph on|off`, `--json` (tools/lfm_check.py:374-418), `--temperature`, `--top-p`, `--top-k`, `--parallel`
-(server/app.py:12893-12940). No tokenizer is involved: prompts are token ids.
+`--graph on|off`, `--json` (tools/lfm_check.py:374-418), `--temperature`, `--top-p`, `--top-k`, `--parallel`,
+`--rep-penalty`, `--presence-penalty`, `--frequency-penalty` (server/app.py:12893-12940). No tokenizer is involved: prompts are token ids.
 """
 
 from __future__ import annotations
@@ -67,7 +67,9 @@ def cmd_generate(a) -> int:
         g = torch.Generator().manual_seed(a.prompt_seed)
         prompts = [torch.randint(0, vocab, (a.prompt_len,), generator=g).tolist() for _ in range(a.prompts)]
     params = SamplingParams(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, min_p=a.min_p, seed=a.seed,
-                            max_tokens=a.tokens, ignore_eos=a.ignore_eos)
+                            max_tokens=a.tokens, ignore_eos=a.ignore_eos, repetition_penalty=a.rep_penalty,
+                            presence_penalty=a.presence_penalty, frequency_penalty=a.frequency_penalty,
+                            logit_bias=_logit_bias(a.logit_bias))
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = engine.generate(prompts, params)
@@ -117,6 +119,20 @@ def cmd_bench(a) -> int:
     return 0
 
 
+def _logit_bias(items) -> dict | None:
+    """{token: added logit} from TOKEN:VALUE arguments."""
+    bias = {}
+    for item in items or ():
+        token, sep, value = item.partition(":")
+        try:
+            if not sep:
+                raise ValueError
+            bias[int(token)] = float(value)
+        except ValueError:
+            raise SystemExit(f"--logit-bias takes TOKEN:VALUE, as in 17:-4.5; got {item!r}")
+    return bias or None
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m tandemllm_b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -132,6 +148,13 @@ def main(argv=None) -> int:
     g.add_argument("--top-p", type=float, default=1.0)
     g.add_argument("--top-k", type=int, default=0)
     g.add_argument("--min-p", type=float, default=0.0)
+    g.add_argument("--rep-penalty", type=float, default=1.0,
+                   help="repetition penalty: a logit of a token seen in the prompt or the output is divided by this if "
+                        "positive, multiplied if negative (1.0: off)")
+    g.add_argument("--presence-penalty", type=float, default=0.0, help="subtracted once from the logit of a seen token")
+    g.add_argument("--frequency-penalty", type=float, default=0.0,
+                   help="subtracted from the logit of a seen token, times the number of times it was seen")
+    g.add_argument("--logit-bias", action="append", metavar="TOKEN:VALUE", help="added to this token's logit (repeatable)")
     g.add_argument("--seed", type=int, help="sampling seed (default: from the operating system)")
     g.add_argument("--ignore-eos", action="store_true")
     g.add_argument("--json", help="write prompts, outputs and timing here")

@@ -210,6 +210,54 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* __restrict__ 
   if (threadIdx.x == 0) out[n] = b.i == 0x7fffffff ? 0 : b.i;
 }
 
+// Penalties and added logits (engine/penalty.py of the reference), in place on the rows that ask for them, before the
+// choice. A row first takes its `logit_bias` entries (penalty.py:189-204: added before everything else); then, where
+// the row's request has seen a token (its count row: prompt and generated tokens, penalty.py:206-232), the logit is
+// multiplied by the repetition penalty if negative and divided by it if not, loses the presence penalty once and the
+// frequency penalty times the count (penalty.py:320-331). slot < 0: a row without penalties (it may still have a bias).
+__global__ void penalize_kernel(float* __restrict__ logits, long long ld, int V, const int* __restrict__ counts,
+                                long long counts_ld, int slots, const int* __restrict__ slot,
+                                const float* __restrict__ repetition,
+                                const float* __restrict__ presence, const float* __restrict__ frequency,
+                                const int* __restrict__ bias_begin, const int* __restrict__ bias_token,
+                                const float* __restrict__ bias_value) {
+  const int r = blockIdx.x;
+  float* row = logits + (long long)r * ld;
+  if (bias_begin != nullptr) {
+    const int b1 = bias_begin[r + 1];
+    for (int i = bias_begin[r] + threadIdx.x; i < b1; i += blockDim.x) {
+      const int t = bias_token[i];
+      if (t >= 0 && t < V) row[t] += bias_value[i];      // a request's bias names a token once
+    }
+    __syncthreads();
+  }
+  const int s = slot[r];
+  if (s < 0 || s >= slots) return;
+  const int* seen = counts + (long long)s * counts_ld;
+  const float rp = repetition[r], pr = presence[r], fq = frequency[r];
+  for (int v = threadIdx.x; v < V; v += blockDim.x) {
+    const int n = seen[v];
+    if (n <= 0) continue;
+    float x = row[v];
+    if (rp != 1.f) x = x < 0.f ? x * rp : x / rp;
+    if (pr != 0.f) x -= pr;
+    if (fq != 0.f) x -= fq * (float)n;
+    row[v] = x;
+  }
+}
+
+// counts[slot, token] += 1 for every (slot, token) given; `slot` null: all go to `one_slot` (a request's history at
+// its start). Tokens repeat within a history, so the additions are atomic; a negative slot or token is passed over.
+__global__ void count_tokens_kernel(int* __restrict__ counts, long long ld, int slots, int V,
+                                    const int* __restrict__ slot,
+                                    int one_slot, const int* __restrict__ token, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int s = slot != nullptr ? slot[i] : one_slot, t = token[i];
+  if (s < 0 || s >= slots || t < 0 || t >= V) return;
+  atomicAdd(counts + (long long)s * ld + t, 1);
+}
+
 }  // namespace tl
 
 using namespace tl;
@@ -229,6 +277,33 @@ extern "C" int tl_sample(const float* logits, long long ld, int rows, int V, con
   TL_REQUIRE(V > 0 && V < (1 << 24) && ld >= V, "sample: vocabulary %d, row stride %lld", V, ld);
   sample_kernel<<<rows, V >= 4096 ? 1024 : 256, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p, seed,
                                                              position, out);
+  TL_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int tl_penalize(float* logits, long long ld, int rows, int V, const int* counts, long long counts_ld,
+                           int slots, const int* slot, const float* repetition, const float* presence,
+                           const float* frequency, const int* bias_begin, const int* bias_token,
+                           const float* bias_value, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  TL_REQUIRE(V > 0 && ld >= V, "penalize: vocabulary %d, row stride %lld", V, ld);
+  TL_REQUIRE(slots == 0 || (counts != nullptr && counts_ld >= V), "penalize: %d count rows with stride %lld", slots,
+             counts_ld);
+  TL_REQUIRE((bias_begin == nullptr) == (bias_token == nullptr) && (bias_begin == nullptr) == (bias_value == nullptr),
+             "penalize: the bias needs its offsets, tokens and values together (%d)", 0);
+  penalize_kernel<<<rows, V >= 4096 ? 1024 : 256, 0, stream>>>(logits, ld, V, counts, counts_ld, slots, slot,
+                                                               repetition, presence, frequency, bias_begin, bias_token,
+                                                               bias_value);
+  TL_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int tl_count_tokens(int* counts, long long ld, int slots, int V, const int* slot, int one_slot,
+                               const int* token, int n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  TL_REQUIRE(V > 0 && ld >= V && slots > 0, "count tokens: vocabulary %d, row stride %lld", V, ld);
+  TL_REQUIRE(slot != nullptr || (one_slot >= 0 && one_slot < slots), "count tokens: slot %d of %d", one_slot, slots);
+  count_tokens_kernel<<<(n + 255) / 256, 256, 0, stream>>>(counts, ld, slots, V, slot, one_slot, token, n);
   TL_LAUNCH_CHECK();
   return 0;
 }

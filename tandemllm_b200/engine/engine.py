@@ -25,7 +25,7 @@ from ..cache.manager import CacheManager
 from ..config.registry import read_model_config, resolve_model_folder, spec_of
 from ..parts.base import Runtime
 from ..parts.model import DecoderModel
-from ..sampling.sampler import Sampler, SamplingParams
+from ..sampling.sampler import Sampler, SampleRow, SamplingParams
 from ..settings import SETTINGS
 from ..weights.loader import DictWeights, FolderWeights
 from ..weights.random_init import random_weights
@@ -88,7 +88,7 @@ class Engine:
         self._flight = None             # a step that is launched and not yet accounted
         self.step_function = StepFunction(model, self.cache, use_graphs=args.graph and model.graph_safe,
                                           max_graph_batch=args.parallel)
-        self.sampler = Sampler(self.device)
+        self.sampler = Sampler(self.device, slots=args.parallel)
         self.scheduler = Scheduler(self.cache, max_num_seqs=args.parallel, max_num_batched_tokens=args.max_batched_tokens,
                                    chunk_size=args.chunk_size, max_model_len=args.max_len,
                                    stop_token_ids=model.spec.stop_token_ids)
@@ -163,6 +163,9 @@ class Engine:
         bad = [t for t in prompt if not 0 <= int(t) < vocab]
         if bad:
             raise ValueError(f"request {request_id!r}: token id {bad[0]} is outside the vocabulary of {vocab}")
+        bad = [t for t in (params.logit_bias or ()) if t >= vocab]
+        if bad:
+            raise ValueError(f"request {request_id!r}: logit_bias names token {bad[0]}; the vocabulary has {vocab}")
         req = Request(request_id, [int(t) for t in prompt], params)
         self.scheduler.add(req)
         return req
@@ -274,6 +277,16 @@ class Engine:
             return False
         return not sch._pages_short([(r, 1) for r in sch.running])
 
+    def _sample_row(self, r: Request) -> SampleRow:
+        """What the sampler needs of a request whose next token is drawn now. A request with penalties also names its
+        row of counts (its slot in the cache) and how to read its history; (id, arrival, preemptions) tells the sampler
+        when that row holds another request's counts, or this one's from before it lost its place."""
+        position = len(r.prompt) + len(r.output)
+        if not r.params.penalizes:
+            return SampleRow(r.params, position)
+        return SampleRow(r.params, position, self.cache.slot_of(r.request_id), (r.request_id, r.order, r.preemptions),
+                         lambda: r.span(0, position))
+
     def _launch(self, batch, before: "_Flight | None") -> "_Flight":
         """Run `batch` and its sampling without waiting for them. `before`: the step whose tokens this one's rows
         take from the device."""
@@ -291,7 +304,7 @@ class Engine:
                 logits = fn.run(entries, feedback)
             finally:
                 fn.check_status = checks
-            rows = [(s.request.params, len(s.request.prompt) + len(s.request.output)) for s in batch if s.samples]
+            rows = [self._sample_row(s.request) for s in batch if s.samples]
             n = len(rows)
             self._turn ^= 1
             host = self._results[self._turn]

@@ -86,6 +86,9 @@ _SIGNATURES = {
     "tl_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_void_p, c_void_p],
+    "tl_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
+                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "tl_count_tokens": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p],
 }
 
 _core = None
@@ -450,3 +453,44 @@ def sample(logits, temperature, top_k, top_p, min_p, seed, position, out) -> tor
     check(core().tl_sample(ptr(logits), logits.stride(0), rows, V, ptr(temperature), ptr(top_k), ptr(top_p), ptr(min_p),
                            ptr(seed), ptr(position), ptr(out), stream()), "sample")
     return out
+
+
+def penalize(logits, counts, slot, repetition, presence, frequency, bias=None) -> torch.Tensor:
+    """Penalties and added logits, in place on float32 logits [n, V]. `counts` int32 [slots, V] (None when no row
+    has penalties); `slot` int32 [n], negative for a row without penalties; `repetition`, `presence`, `frequency`
+    float32 [n]; `bias` None or (begin int32 [n + 1], token int32 [m], value float32 [m])."""
+    _need(logits, torch.float32, "logits"); _need(slot, torch.int32, "slot")
+    _need(repetition, torch.float32, "repetition"); _need(presence, torch.float32, "presence")
+    _need(frequency, torch.float32, "frequency")
+    rows, V = logits.shape
+    slots, counts_ld, counts_ptr = 0, 0, None
+    if counts is not None:
+        _need(counts, torch.int32, "counts")
+        slots, counts_ld, counts_ptr = counts.shape[0], counts.stride(0), ptr(counts)
+        if counts.shape[1] != V:
+            raise ValueError(f"counts over {counts.shape[1]} tokens for logits over {V}")
+    begin = token = value = None
+    if bias is not None:
+        _need(bias[0], torch.int32, "bias begin"); _need(bias[1], torch.int32, "bias token")
+        _need(bias[2], torch.float32, "bias value")
+        if bias[0].numel() != rows + 1 or bias[1].numel() != bias[2].numel():
+            raise ValueError("bias: begin needs one entry a row and one more, and a value for every token")
+        begin, token, value = ptr(bias[0]), ptr(bias[1]), ptr(bias[2])
+    check(core().tl_penalize(ptr(logits), logits.stride(0), rows, V, counts_ptr, counts_ld, slots, ptr(slot),
+                             ptr(repetition), ptr(presence), ptr(frequency), begin, token, value, stream()), "penalize")
+    return logits
+
+
+def count_tokens(counts: torch.Tensor, tokens: torch.Tensor, slot) -> None:
+    """counts[slot, token] += 1 for int32 tokens [n]; `slot` is an int32 tensor [n] or one row's index."""
+    _need(counts, torch.int32, "counts"); _need(tokens, torch.int32, "tokens")
+    slots, V = counts.shape
+    if isinstance(slot, torch.Tensor):
+        _need(slot, torch.int32, "slot")
+        if slot.numel() != tokens.numel():
+            raise ValueError(f"{slot.numel()} slots for {tokens.numel()} tokens")
+        slot_ptr, one = ptr(slot), -1
+    else:
+        slot_ptr, one = None, int(slot)
+    check(core().tl_count_tokens(ptr(counts), counts.stride(0), slots, V, slot_ptr, one, ptr(tokens), tokens.numel(),
+                                 stream()), "count_tokens")

@@ -6,14 +6,20 @@ greedy whatever the filters say (sample.py:134-141); otherwise logits / temperat
 (seed, sequence position) (sample.py:311-322), so a seeded request yields the same tokens whatever shares
 its batch; a request without a seed takes one from the operating system when it is made (sample.py:164-169).
 
+Before the choice a request's logits take its `logit_bias` and its repetition, presence and frequency
+penalties, with the reference's meanings (`PenaltySpec` and `PenaltyState`, engine/penalty.py:44-67,
+189-232, 320-331): the history that the penalties read is the prompt and every token generated since, kept
+as one row of counts a request on the device.
+
 One kernel launch draws for every row of a step (`kernels.ops.sample`); a step of greedy rows only uses
-the argmax kernel.
+the argmax kernel; a step in which no request asks for penalties or a bias launches nothing more.
 """
 
 from __future__ import annotations
 
 import os
 from dataclasses import dataclass
+from typing import Callable
 
 import torch
 
@@ -30,6 +36,10 @@ class SamplingParams:
     max_tokens: int = 128           # new tokens at most
     stop_token_ids: tuple[int, ...] | None = None    # None: the model's own stop ids
     ignore_eos: bool = False
+    repetition_penalty: float = 1.0     # seen tokens: negative logits times this, the others divided by it
+    presence_penalty: float = 0.0       # seen tokens lose this once
+    frequency_penalty: float = 0.0      # seen tokens lose this times their count
+    logit_bias: dict[int, float] | None = None      # {token id: added logit}
 
     def __post_init__(self) -> None:
         if self.temperature < 0.0 or self.temperature != self.temperature:
@@ -42,10 +52,40 @@ class SamplingParams:
             raise ValueError(f"min_p must be in [0, 1], got {self.min_p}")
         if self.max_tokens < 1:
             raise ValueError(f"max_tokens must be at least 1, got {self.max_tokens}")
+        if not self.repetition_penalty > 0.0:
+            raise ValueError(f"repetition_penalty must be > 0, got {self.repetition_penalty}")
+        if not -2.0 <= self.presence_penalty <= 2.0:
+            raise ValueError(f"presence_penalty must be in [-2, 2], got {self.presence_penalty}")
+        if not -2.0 <= self.frequency_penalty <= 2.0:
+            raise ValueError(f"frequency_penalty must be in [-2, 2], got {self.frequency_penalty}")
+        if self.logit_bias:
+            bias = {}
+            for k, v in self.logit_bias.items():         # keys may be strings of digits, as they are in JSON
+                try:
+                    t, v = int(k), float(v)
+                    whole = isinstance(k, str) or t == k
+                except (TypeError, ValueError):
+                    whole = False
+                if not whole or t < 0 or v != v:
+                    raise ValueError(f"logit_bias maps token ids to numbers, got {k!r}: {v!r}")
+                if v:
+                    bias[t] = v
+            self.logit_bias = bias or None
+        else:
+            self.logit_bias = None
 
     @property
     def greedy(self) -> bool:
         return self.temperature <= 0.0
+
+    @property
+    def penalizes(self) -> bool:
+        """Some rule reads the request's history: it needs a row of counts."""
+        return self.repetition_penalty != 1.0 or self.presence_penalty != 0.0 or self.frequency_penalty != 0.0
+
+    @property
+    def changes_logits(self) -> bool:
+        return self.penalizes or self.logit_bias is not None
 
     def resolved_seed(self) -> int:
         """The request's seed as a 63-bit integer; an unseeded request draws one now."""
@@ -54,12 +94,33 @@ class SamplingParams:
         return int(self.seed) & ((1 << 63) - 1)
 
 
-class Sampler:
-    """Draws one token per logits row on the device. Rows are (params, position) pairs: `position` is the
-    index in the sequence of the token being drawn."""
+@dataclass
+class SampleRow:
+    """One logits row's request as the sampler sees it. `position` is the index in the sequence of the token being
+    drawn. The last three matter to a request with penalties only: `slot`, the request's row among the counts (its slot
+    in the cache); `owner`, a value that no other request in that slot ever has; `history`, a call that returns the
+    `position` tokens before the drawn one, made only when the request's counts have to be built (its first draw, and
+    the first after it lost its place)."""
+    params: SamplingParams
+    position: int
+    slot: int = -1
+    owner: object = None
+    history: Callable[[], list[int]] | None = None
 
-    def __init__(self, device):
+
+class Sampler:
+    """Draws one token per logits row on the device. Rows are `SampleRow`s, or (params, position) pairs for requests
+    without penalties. `slots` is how many requests can be live at a time: the rows of the count table, which is made
+    when the first request with penalties draws."""
+
+    # float32: temperature, top_p, min_p, repetition, presence, frequency | int32: top_k, position, slot | int64: seed
+    FIELDS = 11
+
+    def __init__(self, device, slots: int = 0):
         self.device = device
+        self.slots = int(slots)
+        self.counts: torch.Tensor | None = None     # int32 [slots, vocabulary]
+        self._counted: dict[int, tuple] = {}        # slot -> (owner, tokens counted)
         self._cap = 0
 
     def _staging(self, n: int):
@@ -67,9 +128,8 @@ class Sampler:
         read it, so that a step can be launched while the one before it still runs."""
         if n > self._cap:
             self._cap = max(64, 2 * n)
-            # one pinned block: temperature, top_p, min_p (float32) | top_k, position (int32) | seed (int64)
-            self._hosts = [torch.empty(7 * self._cap, dtype=torch.int32, pin_memory=True) for _ in range(3)]
-            self._devs = [torch.empty(7 * self._cap, dtype=torch.int32, device=self.device) for _ in range(3)]
+            self._hosts = [torch.empty(self.FIELDS * self._cap, dtype=torch.int32, pin_memory=True) for _ in range(3)]
+            self._devs = [torch.empty(self.FIELDS * self._cap, dtype=torch.int32, device=self.device) for _ in range(3)]
             self._events = [None, None, None]
             self._turn = 0
         self._turn = (self._turn + 1) % 3
@@ -77,31 +137,92 @@ class Sampler:
             self._events[self._turn].synchronize()
         return self._hosts[self._turn], self._devs[self._turn]
 
-    def __call__(self, logits: torch.Tensor, rows: list[tuple[SamplingParams, int]]) -> torch.Tensor:
-        """int32 [n] token ids for float32 logits [n, V]."""
-        n = logits.shape[0]
+    def _count_history(self, row: SampleRow, vocab: int) -> None:
+        """Makes the request's row of counts hold its `position` tokens, if it does not already."""
+        if not 0 <= row.slot < self.slots:
+            raise ValueError(f"a request with penalties needs a slot below {self.slots}, got {row.slot}")
+        if self.counts is None:
+            self.counts = torch.zeros(self.slots, vocab, dtype=torch.int32, device=self.device)
+        if self._counted.get(row.slot) == (row.owner, row.position):
+            return
+        if row.history is None:
+            raise ValueError("a request with penalties needs its history at its first draw")
+        tokens = row.history()
+        if len(tokens) != row.position or any(t < 0 for t in tokens):
+            raise ValueError(f"history of {len(tokens)} tokens for a draw at position {row.position}")
+        self.counts[row.slot].zero_()
+        if tokens:
+            staged = torch.tensor(tokens, dtype=torch.int32).pin_memory()
+            ops.count_tokens(self.counts, staged.to(self.device, non_blocking=True), row.slot)
+
+    def _bias(self, rows: list[SampleRow], vocab: int):
+        """(begin, token, value) on the device for the rows' added logits; None when no row has any."""
+        if not any(r.params.logit_bias for r in rows):
+            return None
+        begin, token, value = [0], [], []
+        for r in rows:
+            for t, v in sorted((r.params.logit_bias or {}).items()):
+                if t >= vocab:
+                    raise ValueError(f"logit_bias names token {t}; the vocabulary has {vocab}")
+                token.append(t)
+                value.append(v)
+            begin.append(len(token))
+        ints = torch.tensor(begin + token, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        vals = torch.tensor(value, dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
+        return ints[:len(begin)], ints[len(begin):], vals
+
+    def forget(self, slot: int) -> None:
+        """The slot's request is gone: whoever draws from it next starts its counts anew."""
+        self._counted.pop(slot, None)
+
+    def __call__(self, logits: torch.Tensor, rows: list) -> torch.Tensor:
+        """int32 [n] token ids for float32 logits [n, V]. Logits of requests with penalties or a bias are changed in place."""
+        n, vocab = logits.shape
         if n != len(rows):
             raise ValueError(f"{n} logits rows for {len(rows)} requests")
         out = torch.empty(n, dtype=torch.int32, device=logits.device)
         if n == 0:
             return out
-        if all(p.greedy for p, _ in rows):
+        rows = [r if isinstance(r, SampleRow) else SampleRow(*r) for r in rows]
+        greedy = all(r.params.greedy for r in rows)
+        changed = any(r.params.changes_logits for r in rows)
+        if greedy and not changed:
             return ops.argmax(logits, out)
+        counted = [r for r in rows if r.params.penalizes]
+        for r in counted:
+            self._count_history(r, vocab)
         host, dev = self._staging(n)
         c = self._cap
         f = host.view(torch.float32)
-        seeds = host[5 * c:7 * c].view(torch.int64)
-        for i, (p, pos) in enumerate(rows):
+        seeds = host[9 * c:11 * c].view(torch.int64)
+        for i, r in enumerate(rows):
+            p = r.params
             f[i] = p.temperature
             f[c + i] = p.top_p
             f[2 * c + i] = p.min_p
-            host[3 * c + i] = p.top_k
-            host[4 * c + i] = pos
+            f[3 * c + i] = p.repetition_penalty
+            f[4 * c + i] = p.presence_penalty
+            f[5 * c + i] = p.frequency_penalty
+            host[6 * c + i] = p.top_k
+            host[7 * c + i] = r.position
+            host[8 * c + i] = r.slot if p.penalizes else -1
             seeds[i] = p.resolved_seed() if not p.greedy else 0
         dev.copy_(host, non_blocking=True)
         event = self._events[self._turn] or torch.cuda.Event()
         event.record()
         self._events[self._turn] = event
         df = dev.view(torch.float32)
-        return ops.sample(logits, df[0:n], dev[3 * c:3 * c + n], df[c:c + n], df[2 * c:2 * c + n],
-                          dev[5 * c:7 * c].view(torch.int64)[:n], dev[4 * c:4 * c + n], out)
+        slot = dev[8 * c:8 * c + n]
+        if changed:
+            ops.penalize(logits, self.counts if counted else None, slot, df[3 * c:3 * c + n], df[4 * c:4 * c + n],
+                         df[5 * c:5 * c + n], self._bias(rows, vocab))
+        if greedy:
+            ops.argmax(logits, out)
+        else:
+            ops.sample(logits, df[0:n], dev[6 * c:6 * c + n], df[c:c + n], df[2 * c:2 * c + n],
+                       dev[9 * c:11 * c].view(torch.int64)[:n], dev[7 * c:7 * c + n], out)
+        if counted:
+            ops.count_tokens(self.counts, out, slot)
+            for r in counted:
+                self._counted[r.slot] = (r.owner, r.position + 1)
+        return out

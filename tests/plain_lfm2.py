@@ -274,3 +274,26 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, m
         if v > best_v:
             best, best_v = i, v
     return best
+
+
+def penalize(logits: torch.Tensor, history: list[int], repetition: float = 1.0, presence: float = 0.0,
+             frequency: float = 0.0, bias: dict | None = None) -> torch.Tensor:
+    """A row of logits after `logit_bias` and the three penalties, given the tokens before it (prompt and generated):
+    the bias is added first (engine/penalty.py:189-204, :291); then a token that the history holds has its logit
+    multiplied by the repetition penalty if negative and divided by it otherwise, loses the presence penalty once,
+    and the frequency penalty times its count (penalty.py:320-331; the counts are seeded from the prompt and grow
+    with every committed token, penalty.py:206-232)."""
+    out = logits.clone().float()
+    for t, v in sorted((bias or {}).items()):
+        out[t] += v
+    counts = torch.zeros(out.numel(), dtype=torch.int64)
+    for t in history:
+        counts[t] += 1
+    seen = counts > 0
+    if repetition != 1.0:
+        out = torch.where(seen, torch.where(out < 0, out * repetition, out / repetition), out)
+    if presence != 0.0:
+        out = out - presence * seen
+    if frequency != 0.0:
+        out = out - frequency * counts.float() * seen
+    return out

@@ -75,3 +75,16 @@ def test_sampling_filters_and_keyed_draws():
     assert len(draws) > 5
     assert P.sample(logits, 0.0, 5, 0.5, 0.1, seed=1, position=0) == int(logits.argmax())
     assert 0.0 < P.keyed_uniform(1, 2, 3) < 1.0
+
+
+def test_penalties_on_a_hand_made_row():
+    logits = torch.tensor([2.0, -2.0, 1.0, -1.0, 0.5, 3.0])
+    history = [0, 1, 1, 5, 5, 5]
+    out = P.penalize(logits, history, repetition=2.0)
+    assert out.tolist() == [1.0, -4.0, 1.0, -1.0, 0.5, 1.5]           # seen and positive: halved; seen and negative: doubled
+    out = P.penalize(logits, history, presence=0.5, frequency=0.25)
+    assert out.tolist() == [2.0 - 0.5 - 0.25, -2.0 - 0.5 - 0.5, 1.0, -1.0, 0.5, 3.0 - 0.5 - 0.75]
+    # the bias comes first: token 2 is unseen, so only the bias moves it; token 1 turns positive before the repetition rule
+    out = P.penalize(logits, history, repetition=2.0, bias={1: 3.0, 2: -4.0})
+    assert out.tolist() == [1.0, 0.5, -3.0, -1.0, 0.5, 1.5]
+    assert torch.equal(P.penalize(logits, history), logits)

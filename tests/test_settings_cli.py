@@ -137,3 +137,29 @@ def test_the_model_accounts_the_bytes_of_a_decode_step_from_its_parts():
     # without a count: what uniform routing would read
     uniform = model.decode_bytes(batch=3)["experts"]
     assert uniform == 3 * int(E * (1 - (1 - k / E) ** 3) * 3 * H * Im * 2)
+
+
+def test_penalty_options_are_checked_when_the_parameters_are_made():
+    from tandemllm_b200.sampling import SamplingParams
+    p = SamplingParams()
+    assert not p.penalizes and not p.changes_logits and p.logit_bias is None
+    assert SamplingParams(repetition_penalty=1.1).penalizes and SamplingParams(frequency_penalty=-0.5).penalizes
+    q = SamplingParams(logit_bias={"7": 1.5, 9: 0.0})
+    assert q.logit_bias == {7: 1.5} and q.changes_logits and not q.penalizes       # a zero entry is no entry
+    assert SamplingParams(logit_bias={3: 0.0}).logit_bias is None
+    for bad in (dict(repetition_penalty=0.0), dict(repetition_penalty=float("nan")), dict(presence_penalty=2.5),
+                dict(frequency_penalty=-2.5), dict(logit_bias={-1: 1.0}), dict(logit_bias={2.5: 1.0}),
+                dict(logit_bias={2: float("nan")})):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
+
+
+def test_the_command_line_reads_penalties_and_added_logits():
+    from tandemllm_b200.__main__ import _logit_bias
+    assert _logit_bias(["17:-4.5", "3:2"]) == {17: -4.5, 3: 2.0} and _logit_bias(None) is None
+    with pytest.raises(SystemExit, match="TOKEN:VALUE"):
+        _logit_bias(["17"])
+    out = subprocess.run([sys.executable, "-m", "tandemllm_b200", "generate", "--help"], capture_output=True, text=True,
+                         cwd=ROOT).stdout
+    for name in ("--rep-penalty", "--presence-penalty", "--frequency-penalty", "--logit-bias"):
+        assert name in out
