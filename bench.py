@@ -340,6 +340,11 @@ class LaunchTimer:
             if grouped:
                 return "experts gate/up + SwiGLU (tcgen05)" if swiglu else "experts down (tcgen05)"
             return "dense products (tcgen05" + (", persistent)" if persistent else ", swapped)")
+        if name == "tl_gemm_tc_pair":            # args: ..., gated at 13, ..., tile_group at 15
+            grouped, gated = bool(args[15]), bool(args[13])
+            if grouped:
+                return "experts gate/up + SwiGLU (tcgen05)" if gated else "experts down (tcgen05)"
+            return "dense products (tcgen05, pairs of SMs)"
         if name == "tl_gemm_skinny_grouped":
             return "experts gate/up + SwiGLU (register-only)" if args[11] else "experts down (register-only)"
         return {"tl_gemm_skinny_mma": "dense products (register-only)", "tl_gemm_skinny_conv": "in-projection + short conv",

@@ -37,7 +37,7 @@ LIBRARIES: dict[str, list[str]] = {
     "core": ["rows.cu", "gemm_simt.cu", "conv.cu", "attention_simt.cu", "attention_split.cu", "moe_route.cu",
              "sampling.cu"],
     # the tcgen05 / TMA kernels of the bfloat16 path; a 32-bit run never builds or loads them
-    "tensorcore": ["tc_gemm.cu", "attention_mma.cu", "attention_tc.cu", "gemm_skinny_mma.cu"],
+    "tensorcore": ["tc_gemm.cu", "tc_gemm_pair.cu", "attention_mma.cu", "attention_tc.cu", "gemm_skinny_mma.cu"],
 }
 HEADERS = ["common.cuh", "route.cuh", "attention_noalloc.h", "tma.cuh"]
 
