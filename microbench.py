@@ -49,11 +49,13 @@ def timed(fn, iters: int, flush: bool = True) -> float:
     return statistics.median(times)
 
 
-def runtime():
+def runtime(prompt_product: str | None = None):
     from tandemllm_b200.parts import Runtime
     from tandemllm_b200.kernels import tensorcore
     rt = Runtime(torch.device(DEV), torch.bfloat16)
     tensorcore.enable(rt)
+    if prompt_product:
+        tensorcore.PROMPT_PRODUCT = prompt_product
     return rt
 
 
@@ -61,7 +63,7 @@ def expert_gemm(a) -> dict:
     """The routed experts of one layer: plan + gate/up with SwiGLU + down, for `tokens` rows."""
     from tandemllm_b200.config import PartSpec
     from tandemllm_b200.parts import make_part
-    rt = runtime()
+    rt = runtime(a.product)
     E, H, I, k, R = a.experts, a.hidden, a.inter, a.top_k, a.tokens
     spec = PartSpec("sigmoid_topk_experts", {"num_experts": E, "top_k": k, "intermediate_size": I, "expert_bias": False,
                                              "normalize": True, "scale": 1.0,
@@ -84,7 +86,7 @@ def expert_gemm(a) -> dict:
 
 
 def dense_gemm(a) -> dict:
-    rt = runtime()
+    rt = runtime(a.product)
     x = torch.randn(a.rows, a.k, device=DEV).to(torch.bfloat16)
     w = (torch.randn(a.n, a.k, device=DEV) * 0.02).to(torch.bfloat16)
     out = torch.empty(a.rows, a.n, dtype=torch.bfloat16 if a.out == "bf16" else torch.float32, device=DEV)
@@ -176,6 +178,9 @@ def main(argv=None) -> int:
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)
     n.add_argument("--hidden", type=int, default=2048)
+    for p in (e, d):
+        p.add_argument("--product", default="pair", choices=("pair", "single"),
+                       help="prompt-sized products: the kernel on pairs of SMs (cta_group::2), or the one-CTA persistent kernel")
     for p in (e, d, t, n):
         p.add_argument("--iters", type=int, default=20)
     a = ap.parse_args(argv)

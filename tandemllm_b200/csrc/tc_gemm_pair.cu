@@ -48,8 +48,14 @@ struct Params {
   const int* n_tiles;
   int plan_rows;              // the height of the tile map's tiles, at most TOKENS
   int act;                    // the gate's activation (TL_ACT_*), 0 for a plain product
+  int skip_kb;                // -1; a test sets the k-block (counted over a cluster's tiles) whose copies both producers leave out
   int* status;
 };
+
+inline int& skip_kb_for_test() {
+  static int kb = -1;
+  return kb;
+}
 
 template <bool GATED>
 struct Smem {
@@ -242,19 +248,22 @@ __global__ void __launch_bounds__(Smem<GATED>::THREADS) gemm_tc_pair_kernel(cons
         const int s = it % S::STAGES;
         if (it >= S::STAGES && !mbar_wait(&empty[s], ((it / S::STAGES) - 1) & 1)) give_up();
         if (*aborted) break;
-        uint8_t* st = tiles + s * S::STAGE_BYTES;
-        const uint32_t bar = in_cta(&full[s], 0);
-        if (first) mbar_expect_tx(&full[s], 2 * cta_bytes);
-        const int kx = kb * TILE_K;
-        load_2d(st, &tmW, bar, kx, my_row);
-        if (GATED) load_2d(st + S::A_BYTES, &tmW, bar, kx, my_row + p.N);
-        load_2d(st + S::W_TILES * S::A_BYTES, tmX, bar, kx, my_tok);
+        if (it != p.skip_kb) {
+          uint8_t* st = tiles + s * S::STAGE_BYTES;
+          const uint32_t bar = in_cta(&full[s], 0);
+          if (first) mbar_expect_tx(&full[s], 2 * cta_bytes);
+          const int kx = kb * TILE_K;
+          load_2d(st, &tmW, bar, kx, my_row);
+          if (GATED) load_2d(st + S::A_BYTES, &tmW, bar, kx, my_row + p.N);
+          load_2d(st + S::W_TILES * S::A_BYTES, tmX, bar, kx, my_tok);
+        }
         issued = it + 1;
       }
     }
     if (*aborted && first) {
       // copies already started (the peer's are counted here too) must land before the shared memory goes away
-      for (int i = max(0, issued - S::STAGES); i < issued; ++i) mbar_wait(&full[i % S::STAGES], (i / S::STAGES) & 1);
+      for (int i = max(0, issued - S::STAGES); i < issued; ++i)
+        if (i != p.skip_kb) mbar_wait(&full[i % S::STAGES], (i / S::STAGES) & 1);
     }
   } else if (warp == 1 && lane == 0 && first) {
     // ---- MMA issuer (the first CTA for the pair) ----
@@ -489,9 +498,20 @@ extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, c
   p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles;
   p.plan_rows = plan_rows;
   p.act = gated; p.status = status;
+  p.skip_kb = pair::skip_kb_for_test();
   const long long work = (long long)ceil_div(N, 2 * pair::ROWS) * (tile_group ? max_tiles : ceil_div(M, tokens));
   if (gated) return out_dtype == TL_BF16 ? pair::launch<true, bf16>(tmW, tmX, p, work, stream)
                                          : pair::launch<true, float>(tmW, tmX, p, work, stream);
   return out_dtype == TL_BF16 ? pair::launch<false, bf16>(tmW, tmX, p, work, stream)
                               : pair::launch<false, float>(tmW, tmX, p, work, stream);
 }
+
+// For tests of the bounded waits, as in tc_gemm.cu: the polls after which an mbarrier wait of this file's kernel gives up
+// (0 puts the default back), and the k-block whose copies the producers of both CTAs leave out (-1: none). The MMA
+// issuer's wait for it then runs out: the pair records status 11, each CTA tells the other, every role stops at its
+// next wait, the pair meets at the cluster barrier, frees its tensor memory and returns.
+extern "C" int tl_tc_pair_set_wait_limit(unsigned int polls) {
+  const uint32_t v = polls ? polls : (1u << 22);
+  return (int)cudaMemcpyToSymbol(wait_limit, &v, sizeof(v));
+}
+extern "C" void tl_tc_pair_test_skip_k_block(int kb) { pair::skip_kb_for_test() = kb; }

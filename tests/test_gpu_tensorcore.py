@@ -568,3 +568,148 @@ def test_shapes_tma_cannot_take_fall_back():
     from tandemllm_b200.parts.linear import linear
     got = linear(rt, x.to(DEV), w.to(DEV))
     assert rel(got, x.float() @ w.float().T) < 1e-2
+
+
+# ---- the product on pairs of SMs (csrc/tc_gemm_pair.cu) ----
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1, 256, 64), (17, 40, 72), (300, 520, 192), (255, 257, 264), (1000, 136, 520),
+                                   (2048, 768, 1024)])
+def test_pair_product_at_every_kind_of_tail(M, N, K):
+    """Token rows that end a 16-row step of the MMA's N side early, outputs that end a CTA's 128 rows (or the pair's 256)
+    early, a k that ends a 64-element block early; bias, both output types; run twice, the same bits."""
+    impl, rt = tc()
+    x, w = rnd(M, K, seed=61), rnd(N, K, seed=62, scale=0.1)
+    b = torch.randn(N, generator=torch.Generator().manual_seed(63))
+    want = x.float() @ w.float().T
+    for out_dtype, bias in ((torch.bfloat16, None), (torch.float32, b)):
+        outs = []
+        for _ in range(2):
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+            impl.gemm_pair(x.to(DEV), w.to(DEV), None if bias is None else bias.to(DEV), out)
+            torch.cuda.synchronize()
+            assert int(rt.status) == 0
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1])
+        assert rel(outs[0], want + (0 if bias is None else bias)) < (1e-2 if out_dtype == torch.bfloat16 else 1e-4), (M, N, K)
+
+
+def test_pair_product_into_a_wider_output_with_strided_token_rows():
+    impl, rt = tc()
+    M, N, K = 130, 264, 136
+    xw = rnd(M, K + 24, seed=64).to(DEV)
+    x, w = xw[:, 8:8 + K], rnd(N, K, seed=65, scale=0.1).to(DEV)          # rows 16-byte aligned, stride K + 24
+    wide = torch.full((M, N + 40), float("nan"), dtype=torch.bfloat16, device=DEV)
+    impl.gemm_pair(x, w, None, wide[:, 8:8 + N])
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    assert rel(wide[:, 8:8 + N], x.float().cpu() @ w.float().cpu().T) < 1e-2
+    assert bool(torch.isnan(wide[:, :8]).all()) and bool(torch.isnan(wide[:, 8 + N:]).all())
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu", "relu2", "identity"])
+@pytest.mark.parametrize("M,H,I", [(300, 136, 200), (40, 64, 72), (1024, 256, 640)])
+def test_pair_product_with_the_gated_epilogue(M, H, I, act):
+    from tandemllm_b200.kernels import ops
+    from tests.test_gpu_kernels import plain_activation
+    impl, rt = tc()
+    x, w = rnd(M, H, seed=66), rnd(2 * I, H, seed=67, scale=0.2)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    impl.gemm_pair(x.to(DEV), w.to(DEV), None, out, gated=ops.activation_code(act), n_out=I)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    g, u = x.float() @ w[:I].float().T, x.float() @ w[I:].float().T
+    assert rel(out, plain_activation(act, g) * u) < 1e-2
+
+
+@pytest.mark.parametrize("tile", [256, 128, 48])
+@pytest.mark.parametrize("R,E,k,H,I", [(64, 8, 4, 128, 256), (700, 32, 4, 256, 264), (512, 5, 2, 136, 72), (1500, 3, 1, 64, 136)])
+def test_pair_product_over_a_routing_plan_of_ragged_tiles(R, E, k, H, I, tile):
+    """The routed experts' two products over plans of several tile heights: experts with no rows, with a few, with
+    more than a tile; every tile's MMAs are as wide as the tile has rows."""
+    from tandemllm_b200.kernels import ops
+    impl, rt = tc()
+    g = torch.Generator().manual_seed(R + E)
+    skew = torch.rand(E, generator=g) ** 3 + 1e-3                       # some experts get most of the rows
+    ids = torch.stack([torch.multinomial(skew, k, generator=g) for _ in range(R)]).int().to(DEV)
+    plan = ops.MoePlan(R * k, E, tile, torch.device(DEV)).build(ids)
+    x = rnd(R, H, seed=68).to(DEV)
+    order = plan.sorted_pairs[:R * k].long()
+    xs = x[order // k].contiguous()
+    wgu, wd = rnd(E, 2 * I, H, seed=69, scale=0.1).to(DEV), rnd(E, H, I, seed=70, scale=0.1).to(DEV)
+    act = torch.full((R * k, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    impl.gemm_pair(xs, wgu.view(E * 2 * I, H), None, act, rows_per_group=2 * I, plan=plan, gated=1, n_out=I)
+    y = torch.full((R * k, H), float("nan"), dtype=torch.float32, device=DEV)
+    impl.gemm_pair(act, wd.view(E * H, I), None, y, rows_per_group=H, plan=plan, n_out=H)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    expert = ids.flatten()[order].long()
+    for e in range(E):
+        m = expert == e
+        if not bool(m.any()):
+            continue
+        gu = xs[m].float() @ wgu[e].float().T
+        want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+        assert rel(act[m], want.cpu()) < 1e-2, e
+        assert rel(y[m], (act[m].float() @ wd[e].float().T).cpu()) < 1e-3, e
+
+
+def test_pair_product_refuses_a_plan_of_taller_tiles_than_it_takes():
+    from tandemllm_b200.kernels import ops
+    impl, rt = tc()
+    ids = torch.zeros(600, 1, dtype=torch.int32, device=DEV)
+    plan = ops.MoePlan(600, 2, 512, torch.device(DEV)).build(ids)
+    x, w = rnd(600, 64, seed=71).to(DEV), rnd(2 * 128, 64, seed=72).to(DEV)
+    out = torch.zeros(600, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.KernelError, match="tiles of 512 rows"):
+        impl.gemm_pair(x, w, None, out, rows_per_group=128, plan=plan, n_out=128)
+
+
+@pytest.mark.parametrize("gated", [0, 1])
+def test_a_wait_of_the_pair_product_that_runs_out_ends_both_ctas_and_leaves_the_gpu_as_it_was(gated):
+    """As for the one-CTA kernels: both producers leave one k-block's copies out, so the MMA issuer of the pair's first
+    CTA waits for a barrier that nothing completes. With the bound lowered the wait gives up: status 11, nothing stored,
+    each CTA tells the other, the pair meets at its cluster barrier, frees its tensor memory and returns; the same
+    product launched again right after is correct."""
+    import ctypes
+
+    from tandemllm_b200.kernels import tensorcore
+    impl, rt = tc()
+    lib = tensorcore.lib()
+    lib.tl_tc_pair_set_wait_limit.argtypes, lib.tl_tc_pair_set_wait_limit.restype = [ctypes.c_uint], ctypes.c_int
+    lib.tl_tc_pair_test_skip_k_block.argtypes, lib.tl_tc_pair_test_skip_k_block.restype = [ctypes.c_int], None
+    M, N, K = 200, 256, 256                      # one pair, one tile, four k-blocks
+    x, w = rnd(M, K, seed=73).to(DEV), rnd((2 if gated else 1) * N, K, seed=74, scale=0.1).to(DEV)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    try:
+        assert lib.tl_tc_pair_set_wait_limit(4096) == 0
+        lib.tl_tc_pair_test_skip_k_block(2)
+        impl.gemm_pair(x, w, None, out, gated=gated, n_out=N)
+        torch.cuda.synchronize()                 # returns: the kernel ended by its own bound
+        assert int(rt.status) == 11
+        assert bool(torch.isnan(out).all()), "a product that gave up must store nothing"
+    finally:
+        lib.tl_tc_pair_test_skip_k_block(-1)
+        assert lib.tl_tc_pair_set_wait_limit(0) == 0
+    rt.status.zero_()
+    impl.gemm_pair(x, w, None, out, gated=gated, n_out=N)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    xf, wf = x.float().cpu(), w.float().cpu()
+    want = torch.nn.functional.silu(xf @ wf[:N].T) * (xf @ wf[N:].T) if gated else xf @ wf.T
+    assert rel(out, want) < 1e-3
+
+
+@pytest.mark.parametrize("which", ["pair", "single"])
+def test_prompt_products_through_either_kernel(which, monkeypatch):
+    """`gemm` sends the prompt-sized form to the pair kernel or, when told so, to the one-CTA persistent kernel."""
+    from tandemllm_b200.kernels import ops, tensorcore
+    monkeypatch.setattr(tensorcore, "PROMPT_PRODUCT", which)
+    impl, rt = tc()
+    M, N, K = 700, 330, 520
+    x, w = rnd(M, K, seed=75), rnd(N, K, seed=76, scale=0.1)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    before = ops.launches
+    impl.gemm(x.to(DEV), w.to(DEV), None, out, swap=False, bn=256)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0 and ops.launches == before + 1
+    assert rel(out, x.float() @ w.float().T) < 1e-3
+    assert impl.expert_tile(8192, 32)[2] == (256 if which == "pair" else 128)
