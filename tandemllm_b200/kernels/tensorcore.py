@@ -32,6 +32,7 @@ from ctypes import c_int, c_longlong, c_void_p
 
 import torch
 
+from ..settings import SETTINGS
 from . import ops
 from .build import load
 
@@ -44,8 +45,11 @@ SKINNY_ROWS = 16                # rows of a step up to which the experts go to i
 SKINNY_PAIRS = 16               # routed pairs of such a step up to which its products run without a routing plan
 PROMPT_ATTENTION = "tcgen05"    # prompt portions of head size 64: the tcgen05 kernel (csrc/attention_tc.cu), or "mma" for the
                                 # mma.sync kernel that also takes them (kept for head size 128 and for comparison)
-PROMPT_PRODUCT = "pair"         # prompt-sized products on pairs of SMs (csrc/tc_gemm_pair.cu); "single": the one-CTA
-                                # persistent kernel of csrc/tc_gemm.cu (kept for comparison and as the pair's reference)
+# prompt-sized products on pairs of SMs (csrc/tc_gemm_pair.cu), or "single": the one-CTA persistent kernel of
+# csrc/tc_gemm.cu (kept for comparison and as the pair's reference)
+PROMPT_PRODUCT = SETTINGS.get("PROMPT_PRODUCT")
+if PROMPT_PRODUCT not in ("pair", "single"):
+    raise ValueError(f"TANDEMLLM_PROMPT_PRODUCT={PROMPT_PRODUCT!r}: pair or single")
 _lib = None
 
 
