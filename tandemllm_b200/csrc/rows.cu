@@ -64,10 +64,13 @@ struct NormParams {
   float* route_wts;
   int rows_per_block, out_rows;
   unsigned zero;             // 0 (see router_logits_one_row)
+  int split;                 // CTAs a row (a cluster; one row a block with a router): each takes every split-th expert
 };
 
 // With a router and many rows, a block norms this many rows before it multiplies them by the router's weights,
 // so that the weights are read once per block and not once per row.
+constexpr int ROUTER_SPLIT = 8;            // CTAs a row (a cluster) for a decode step's router
+constexpr int ROUTER_SPLIT_ROWS = 16;      // rows of a step up to which the router's rows are split
 constexpr int MAX_ROWS_PER_BLOCK = 8;
 constexpr int PLAIN_ROWS_PER_BLOCK = 4;   // without a router
 
@@ -155,11 +158,17 @@ __device__ __forceinline__ void router_logits(const NormParams& p, const float* 
 // the warp, which issues in order, would wait there with the other loads unsent. The sum is built in the same order
 // as above.
 __device__ __forceinline__ void router_logits_one_row(const NormParams& p, const float* row, float* logits, int lane,
-                                                      int warp, int nwarps) {
+                                                      int warp, int nwarps, int rank) {
   constexpr int CH = 16;
   const int hidden = p.hidden, h4 = hidden >> 2;
   const float4* row4 = reinterpret_cast<const float4*>(row);
-  for (int e = warp; e < p.E; e += nwarps) {
+  // With `split` CTAs a row (a cluster), this one takes experts rank, rank + split, ..., a warp an expert as ever, and
+  // hands each logit to the cluster's first CTA, which makes the choice.
+  uint32_t first_cta_logits = 0;
+  if (p.split > 1)
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(first_cta_logits) : "r"((uint32_t)__cvta_generic_to_shared(logits)), "r"(0));
+  for (int j = warp; j * p.split + rank < p.E; j += nwarps) {
+    const int e = j * p.split + rank;
     const float4* w4 = reinterpret_cast<const float4*>(p.router_w + (size_t)e * hidden);
     float acc = 0.f;
     for (int c0 = lane; c0 < h4; c0 += 32 * CH) {
@@ -182,7 +191,10 @@ __device__ __forceinline__ void router_logits_one_row(const NormParams& p, const
       }
     }
     const float v = warp_sum(acc);
-    if (lane == 0) logits[e] = v;
+    if (lane == 0) {
+      if (p.split > 1) asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(first_cta_logits + 4u * (uint32_t)e), "f"(v) : "memory");
+      else logits[e] = v;
+    }
   }
 }
 
@@ -207,7 +219,10 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
   chain_next();
   chain_wait();
   const int hidden = p.hidden;
-  const int first_row = blockIdx.x * p.rows_per_block;
+  // (a router's one-row form may run `split` CTAs a row: all of them put the row together, the first one stores it)
+  const int split = (ONE_ROW && ROUTE_PER > 0) ? p.split : 1;
+  const int rank = split > 1 ? (int)(blockIdx.x % split) : 0;
+  const int first_row = (int)(blockIdx.x / split) * p.rows_per_block;
   const int n_rows = min(p.rows_per_block, p.out_rows - first_row);
   const int G = blockDim.x / p.rows_per_block;           // threads a row
   const int rr = threadIdx.x / G, t = threadIdx.x - rr * G;
@@ -347,19 +362,21 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
     if (vec) {
       const int h4 = hidden >> 2;
       auto finish = [&](int c, const float4 x) {
-        if (!p.gather && adds) reinterpret_cast<float4*>(res)[c] = x;
+        if (!p.gather && adds && rank == 0) reinterpret_cast<float4*>(res)[c] = x;
         const float4 w = reinterpret_cast<const float4*>(p.weight)[c];
         const float4 y = make_float4(w.x * (x.x * inv), w.y * (x.y * inv), w.z * (x.z * inv), w.w * (x.w * inv));
-        if constexpr (sizeof(T) == 2) {
-          __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
-          uint2 packed;
-          packed.x = *reinterpret_cast<uint32_t*>(&lo);
-          packed.y = *reinterpret_cast<uint32_t*>(&hi);
-          reinterpret_cast<uint2*>(out)[c] = packed;
-        } else {
-          reinterpret_cast<float4*>(out)[c] = y;
+        if (rank == 0) {
+          if constexpr (sizeof(T) == 2) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(out)[c] = packed;
+          } else {
+            reinterpret_cast<float4*>(out)[c] = y;
+          }
+          if (out32) reinterpret_cast<float4*>(out32)[c] = y;
         }
-        if (out32) reinterpret_cast<float4*>(out32)[c] = y;
         if (ROUTE_PER > 0) reinterpret_cast<float4*>(row)[c] = y;      // the router reads the normed rows from here
       };
       if (in_regs) {
@@ -372,10 +389,12 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
     } else {
       for (int c = t; c < hidden; c += G) {
         const float x = row[c];
-        if (!p.gather && adds) res[c] = x;
         const float y = p.weight[c] * (x * inv);
-        out[c] = from_f32<T>(y);
-        if (out32) out32[c] = y;
+        if (rank == 0) {
+          if (!p.gather && adds) res[c] = x;
+          out[c] = from_f32<T>(y);
+          if (out32) out32[c] = y;
+        }
         row[c] = y;
       }
     }
@@ -386,9 +405,15 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
     // columns; an expert's weights are read once for all rows of the block. A row's sum is built in the same order
     // whether the block holds one row or several.
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    if (ONE_ROW && (p.hidden & 3) == 0) router_logits_one_row(p, rows_buf, logits, lane, warp, nwarps);
+    if (ONE_ROW && (p.hidden & 3) == 0) router_logits_one_row(p, rows_buf, logits, lane, warp, nwarps, rank);
     else if (n_rows == 1) router_logits<1>(p, rows_buf, logits, 1, lane, warp, nwarps);
     else router_logits<MAX_ROWS_PER_BLOCK>(p, rows_buf, logits, n_rows, lane, warp, nwarps);
+    if (split > 1) {
+      // every CTA of the row has sent its logits to the first one
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      if (rank != 0) return;
+    }
     __syncthreads();
     for (int rr = warp; rr < n_rows; rr += nwarps)
       warp_route_sized<ROUTE_PER>(logits + rr * p.E, p.router_bias, p.E, p.route_k, p.normalize, p.floor_, p.scale,
@@ -434,6 +459,25 @@ extern "C" int tl_embed_rows(const void* table, const int* tokens, float* residu
 extern "C" void tl_set_chained_launches(int enabled) { chained_launches() = enabled; }
 
 // See NormParams for the forms of what is added. Null pointers switch a form or the router off.
+// An ordinary launch in clusters of `cluster` CTAs along x.
+template <typename... KernelArgs, typename... Args>
+static cudaError_t launch_clustered(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    int cluster, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KernelArgs>(args)...);
+}
+
 extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, long long part_stride,
                               const float* expert_rows, int expert_parts, long long expert_part_stride,
                               const int* pos_of_pair, const int* ids, const float* wts, int top_k,
@@ -469,12 +513,18 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
   p.rows_per_block = rows_per_block; p.out_rows = out_rows; p.zero = 0u;
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (threads < 32 * rows_per_block) threads = 32 * rows_per_block;       // whole warps a row
-  const dim3 grid(ceil_div(out_rows, rows_per_block));
+  // A decode step's router: one block a row would pull all of the router's weights through one SM (256 KB for 32
+  // experts of 2048: a third of the kernel's time). A cluster of CTAs a row shares them out; every CTA of the cluster
+  // puts the row together for itself, which a step of many rows no longer pays (measured: 2.415 -> 2.374 ms a step at
+  // batch 8, 773 -> 797 tok/s at batch 1, but 13.2 k -> 12.5 k tok/s at batch 64).
+  p.split = (rows_per_block == 1 && out_rows <= ROUTER_SPLIT_ROWS && router_w && E >= 16 && (hidden & 3) == 0) ? ROUTER_SPLIT : 1;
+  const dim3 grid(ceil_div(out_rows, rows_per_block) * p.split);
   const int per = !router_w ? 0 : (E <= 32 ? 1 : (E <= 128 ? 4 : MAX_EXPERTS / 32));
 #define TL_NORM1(T_, PER_, ONE_)                                                                                          \
   do {                                                                                                                    \
     if (smem > 48 * 1024)                                                                                                 \
       cudaFuncSetAttribute(add_rmsnorm_kernel<T_, PER_, ONE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+    if (p.split > 1) return (int)launch_clustered(add_rmsnorm_kernel<T_, PER_, ONE_>, grid, dim3(threads), smem, stream, p.split, p); \
     return (int)launch_chained(add_rmsnorm_kernel<T_, PER_, ONE_>, grid, dim3(threads), smem, stream, p);                 \
   } while (0)
 #define TL_NORM(T_, PER_)                          \

@@ -139,6 +139,10 @@ def test_the_router_inside_the_norm_routes_a_row_the_same_alone_and_among_many(d
     assert torch.equal(many[0], alone[0]), "the chosen experts, in order"
     assert float((many[1] - alone[1]).abs().max()) <= 2e-6, "weights"
     assert float((many[2] - alone[2]).abs().max()) <= (1e-5 if dtype == torch.float32 else 2e-2) * float(alone[2].abs().max())
+    # a step of a few rows: a cluster of CTAs a row shares the experts out (from 16 experts on); the same bits as one block a row
+    tiny = [run(lo, lo + n) for lo, n in ((0, 11), (11, 1), (12, 16), (28, 5))]
+    for j in range(3):
+        assert torch.equal(torch.cat([t[j] for t in tiny]), alone[j][:33]), ("a few rows", j)
     n32 = P.rms_norm(res0, w, 1e-5)
     cfg = dict(num_experts_per_tok=k, use_expert_bias=True, norm_topk_prob=True, routed_scaling_factor=1.0)
     want_ids, want_w = P.route(n32, {"gate.weight": gate, "expert_bias": bias}, "", cfg)
