@@ -219,6 +219,11 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
   chain_next();
   chain_wait();
   const int hidden = p.hidden;
+  // One row a block: the thread's piece of the norm's weight does not depend on the row and is asked for first, or its
+  // round trip would come after the row's sum of squares, at the end of the kernel's chain.
+  float4 norm_w = make_float4(0.f, 0.f, 0.f, 0.f);
+  const bool has_norm_w = ONE_ROW && (hidden & 3) == 0 && (int)threadIdx.x < (hidden >> 2);
+  if (has_norm_w) norm_w = reinterpret_cast<const float4*>(p.weight)[threadIdx.x];
   // (a router's one-row form may run `split` CTAs a row: all of them put the row together, the first one stores it)
   const int split = (ONE_ROW && ROUTE_PER > 0) ? p.split : 1;
   const int rank = split > 1 ? (int)(blockIdx.x % split) : 0;
@@ -363,7 +368,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
       const int h4 = hidden >> 2;
       auto finish = [&](int c, const float4 x) {
         if (!p.gather && adds && rank == 0) reinterpret_cast<float4*>(res)[c] = x;
-        const float4 w = reinterpret_cast<const float4*>(p.weight)[c];
+        const float4 w = (has_norm_w && c == (int)threadIdx.x) ? norm_w : reinterpret_cast<const float4*>(p.weight)[c];
         const float4 y = make_float4(w.x * (x.x * inv), w.y * (x.y * inv), w.z * (x.z * inv), w.w * (x.w * inv));
         if (rank == 0) {
           if constexpr (sizeof(T) == 2) {
