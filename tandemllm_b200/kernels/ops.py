@@ -124,7 +124,15 @@ def check(code: int, what: str, lib=None, kernels: int = 1) -> None:
     raise KernelError(f"{what}: CUDA error {code}: {core().tl_cuda_error_string(code).decode()}")
 
 
+# The current stream's handle is asked for once a launch: through torch's own C entry points where it has them (a
+# fraction of a microsecond), else through `torch.cuda.current_stream()`, whose Python checks cost more than the launch.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def stream() -> int:
+    if _raw_stream is not None and _current_device is not None:
+        return _raw_stream(_current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
