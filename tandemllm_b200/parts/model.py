@@ -13,6 +13,7 @@ import torch
 
 from ..config.spec import ModelSpec
 from ..kernels import ops
+from ..settings import SETTINGS
 from ..weights.loader import TensorSpec
 from .base import Runtime, StepContext, make_part
 from .block import Layer
@@ -112,11 +113,29 @@ class DecoderModel:
         residual = torch.empty(step.n_rows, self.hidden_size, dtype=torch.float32, device=rt.device)
         ops.embed_rows(self.embedding, step.token_ids, residual, rt.status)
         pending = None
-        for i, site in enumerate(self.spec.schedule):
-            own = site.cache_of is None
-            cache = site_caches[i if own else site.cache_of]
-            pending = self.layers[site.layer].run(residual, pending, step, cache, writes_cache=own)
-        if step.n_out == 0:
-            return torch.empty(0, self.vocab_size, dtype=torch.float32, device=rt.device)
-        n = self.final_norm.add_norm(residual, pending, gather=step.out_rows, n_out=step.n_out)
-        return linear(rt, n, self.head, out_dtype=torch.float32)
+        ranges = SETTINGS.is_set("NVTX")             # named ranges for profilers: the step, and each layer in run order
+        if ranges:
+            torch.cuda.nvtx.range_push(f"step rows={step.n_rows} requests={step.n_requests}")
+        try:
+            for i, site in enumerate(self.spec.schedule):
+                own = site.cache_of is None
+                cache = site_caches[i if own else site.cache_of]
+                if ranges:
+                    layer = self.layers[site.layer]
+                    torch.cuda.nvtx.range_push(f"site {i} layer {site.layer} {type(layer.mixer).__name__} + "
+                                               f"{type(layer.feed_forward).__name__}")
+                pending = self.layers[site.layer].run(residual, pending, step, cache, writes_cache=own)
+                if ranges:
+                    torch.cuda.nvtx.range_pop()
+            if step.n_out == 0:
+                return torch.empty(0, self.vocab_size, dtype=torch.float32, device=rt.device)
+            if ranges:
+                torch.cuda.nvtx.range_push("final norm + head")
+            n = self.final_norm.add_norm(residual, pending, gather=step.out_rows, n_out=step.n_out)
+            out = linear(rt, n, self.head, out_dtype=torch.float32)
+            if ranges:
+                torch.cuda.nvtx.range_pop()
+            return out
+        finally:
+            if ranges:
+                torch.cuda.nvtx.range_pop()

@@ -24,6 +24,8 @@ KNOBS: dict[str, tuple] = {
                         "the temp dir)", "kernels/build.py"),
     "GRAPHS": ("32", "decode graphs kept at a time by a step function; the least recently replayed is dropped beyond it",
                "engine/step.py"),
+    "NVTX": (None, "when set, every step and every layer of it is an NVTX range (for `ncu --nvtx --nvtx-include` and other "
+                   "tools that read them); off by default: a range costs a host call", "parts/model.py"),
     "PROMPT_PRODUCT": ("pair", "prompt-sized bfloat16 products: `pair` (two SMs a tile, tcgen05 cta_group::2) or `single` "
                                "(one CTA a tile)", "kernels/tensorcore.py"),
     "STEP_LOG": (None, "a file to which every engine appends one JSON line a scheduler step (rows, pages, milliseconds)",

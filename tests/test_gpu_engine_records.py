@@ -144,3 +144,19 @@ def test_random_weights_then_generate_as_subprocesses(tmp_path):
     assert saved["outputs"] == printed and saved["generated"] == 16
     lines = [json.loads(ln) for ln in log.read_text().splitlines()]
     assert lines and all("experts_touched" in ln and "ms" in ln for ln in lines)
+
+
+def test_named_ranges_for_profilers_change_nothing(tmp_path, monkeypatch):
+    """With TANDEMLLM_NVTX set every step and layer is an NVTX range (eager steps and the capture of decode graphs alike);
+    the tokens are the same bits as without."""
+    from tandemllm_b200.engine import Engine, EngineArgs
+    from tandemllm_b200.sampling import SamplingParams
+    folder, cfg, W = folder_of("a", tmp_path)
+    prompts = [T.long_tokens("a", n, seed=5 + n) for n in (19, 6)]
+
+    def run():
+        eng = Engine.from_folder(folder, EngineArgs(dtype="float32", max_len=128, parallel=2, chunk_size=8))
+        return eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    plain = run()
+    monkeypatch.setenv("TANDEMLLM_NVTX", "1")
+    assert run() == plain
