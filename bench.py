@@ -460,6 +460,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
     ap.add_argument("--graph", default="on", choices=("on", "off"))
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="with --only prefill: a prompt of this many tokens in one step (the headline line keeps 2048)")
     ap.add_argument("--only", choices=("prefill",), help="measure only this part and print it (a profiling aid)")
     ap.add_argument("--scenario", choices=("mixed",),
                     help="mixed: 64 requests with prompts of 128 to 32768 tokens (log-uniform) under a cache budget that makes "
@@ -501,11 +503,12 @@ def main() -> int:
     pk = peaks()
     bf16 = a.dtype == "bfloat16"
     max_batch = 64 if not a.skip_points else a.batch
-    room = a.context + REPEATS * a.steps + a.warmup + 80
+    only_tokens = a.prefill_tokens if a.only == "prefill" else PREFILL_TOKENS
+    room = max(a.context, only_tokens) + REPEATS * a.steps + a.warmup + 80
     t0 = time.time()
     engine = Engine.from_config(cfg, seed=0, args=EngineArgs(
         dtype=a.dtype, max_len=room, parallel=max(max_batch, a.batch), block_size=16,
-        max_batched_tokens=max(PREFILL_TOKENS, max_batch), chunk_size=PREFILL_TOKENS, graph=a.graph == "on"))
+        max_batched_tokens=max(only_tokens, max_batch), chunk_size=only_tokens, graph=a.graph == "on"))
     torch.cuda.synchronize()
     load_s = time.time() - t0
     if a.chain == "on":
@@ -715,7 +718,7 @@ def main() -> int:
         return 0
 
     if a.only == "prefill":          # a profiling aid: the prefill alone, its last repetition between profiler marks
-        print(json.dumps({"prefill": prefill(PREFILL_TOKENS, reps=2)}))
+        print(json.dumps({"prefill": prefill(only_tokens, reps=2)}))
         return 0
     if a.profile_table:
         return profile_table()

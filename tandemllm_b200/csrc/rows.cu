@@ -503,7 +503,11 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
                normalize >> 1, TL_SCORE_LAST);
   }
   // prompts: several rows a block (eight beside a router, whose weights are then read once for eight rows)
-  int rows_per_block = out_rows > 64 ? (router_w ? MAX_ROWS_PER_BLOCK : PLAIN_ROWS_PER_BLOCK) : 1;
+  // (a few hundred rows: fewer rows a block, so that there are about as many blocks as SMs: at 128 rows eight rows a
+  // block were 16 blocks, 22 us a norm where one row a block takes 7)
+  const int most = router_w ? MAX_ROWS_PER_BLOCK : PLAIN_ROWS_PER_BLOCK;
+  int rows_per_block = 1;
+  while (rows_per_block < most && out_rows > 160 * rows_per_block) rows_per_block *= 2;
   while (rows_per_block > 1 && (size_t)rows_per_block * (hidden + E) * sizeof(float) > 96 * 1024) rows_per_block /= 2;
   const size_t smem = ((size_t)rows_per_block * hidden + 33 + (router_w ? (size_t)rows_per_block * E : 0)) * sizeof(float);
   TL_REQUIRE(smem <= 200 * 1024, "add_rmsnorm: hidden size %d needs %zu bytes of shared memory, the limit is 204800",
