@@ -284,7 +284,9 @@ extern "C" int tl_qk_prepare(const void* qkv, long long ld_qkv, const float* q_w
              "qk_prepare: rotary size %d for head size %d", rotary_dim, D);
   TL_REQUIRE((k_cache && v_cache && page_size > 0 && max_pages > 0) || (k_out && v_out),
              "qk_prepare: neither cache pages nor plain outputs for k and v");
-  const int heads_per_block = max(1, min(Hq + 2 * Hk, QK_GROUP_FLOATS / D));
+  // a decode step's few rows: a few heads a block, so that a row's heads run side by side and not twelve after one another a warp
+  int heads_per_block = max(1, min(Hq + 2 * Hk, QK_GROUP_FLOATS / D));
+  if (rows <= 64 && heads_per_block > 8) heads_per_block = 8;
   dim3 grid(rows, ceil_div(Hq + 2 * Hk, heads_per_block));
   TL_REQUIRE(grid.y <= 65535, "qk_prepare: %d heads exceed the grid limit", Hq + 2 * Hk);
   // the unrolled form: the whole head is rotated (or nothing is) and a lane's pairs are (f, f + D / 2)
