@@ -275,6 +275,19 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_conv_kernel(
   float acc[2][4];
 #pragma unroll
   for (int j = 0; j < 2; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  // What the epilogue needs beside the sums does not depend on them: the row's position and state slot, then the state
+  // and the taps of its channel. They are asked for behind the first round of weight loads (up to PRE_TAPS taps), so
+  // that their round trips run under the product and not after it, at the end of the kernel's chain.
+  constexpr int PRE_TAPS = 4;
+  const int e_ep = threadIdx.x & 7, m_ep = threadIdx.x >> 3, c_ep = c0 + e_ep;
+  const bool ep = threadIdx.x < 64 && m_ep < M && c_ep < hidden;
+  const bool pre = n_taps <= PRE_TAPS;
+  int pre_pos = 0, pre_slot = 0;
+  float pre_old[PRE_TAPS - 1], pre_tap[PRE_TAPS], pre_cb = 0.f;
+#pragma unroll
+  for (int i = 0; i < PRE_TAPS - 1; ++i) pre_old[i] = 0.f;
+#pragma unroll
+  for (int i = 0; i < PRE_TAPS; ++i) pre_tap[i] = 0.f;
   const int chunks = (K + 31) / 32;
   for (int k0 = warp; k0 < chunks; k0 += SKINNY_WARPS * UNROLL) {
     uint4 a_b[UNROLL], a_c[UNROLL], a_x[UNROLL], b[UNROLL];
@@ -289,6 +302,14 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_conv_kernel(
       b[u] = load16(x_row + c * 32, in && x_ok);
       all ^= a_b[u].w ^ a_c[u].w ^ a_x[u].w ^ b[u].w;
     }
+    if (k0 == warp && ep && pre) {              // behind the first round's loads
+      pre_pos = positions[m_ep];
+      pre_slot = state_slot[req_of_row[m_ep]];
+#pragma unroll
+      for (int j = 0; j < PRE_TAPS; ++j)
+        if (j < n_taps) pre_tap[j] = taps[(long long)c_ep * n_taps + j];
+      if (conv_bias) pre_cb = conv_bias[c_ep];
+    }
     a_b[0].x ^= all & zero;                     // the round's first MMA waits for all of the round's loads (zero is 0)
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -296,6 +317,12 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_conv_kernel(
       mma_16816(acc[0], a_b[u].z, a_c[u].z, a_b[u].w, a_c[u].w, b[u].z, b[u].w);
       mma_16816(acc[1], a_x[u].x, 0u, a_x[u].y, 0u, b[u].x, b[u].y);
       mma_16816(acc[1], a_x[u].z, 0u, a_x[u].w, 0u, b[u].z, b[u].w);
+    }
+    if (k0 == warp && ep && pre) {              // the slot is here by now: the channel's state
+      const float* st0 = state + ((long long)pre_slot * (n_taps - 1)) * hidden + c_ep;
+#pragma unroll
+      for (int i = 0; i < PRE_TAPS - 1; ++i)
+        if (i < n_taps - 1) pre_old[i] = st0[(long long)i * hidden];
     }
   }
 #pragma unroll
@@ -320,20 +347,37 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_conv_kernel(
     in[j] = to_f32(from_f32<bf16>(v));
   }
   // from here on: short_conv_decode_kernel, line by line
-  const int pos = positions[m];
   const float bx = in[0] * in[2];
   const int S = n_taps - 1;
-  float* st = state + ((long long)state_slot[req_of_row[m]] * S) * hidden;
+  const int pos = pre ? pre_pos : positions[m];
+  float* st = state + ((long long)(pre ? pre_slot : state_slot[req_of_row[m]]) * S) * hidden;
   float old[CONV_MAX_TAPS];
+  float sum;
+  if (pre) {
+#pragma unroll
+    for (int s = 0; s < PRE_TAPS - 1; ++s) old[s] = pre_old[s];
+    sum = conv_bias ? pre_cb : 0.f;
+#pragma unroll
+    for (int j = 0; j < PRE_TAPS; ++j) {
+      const int back = n_taps - 1 - j;
+      if (j >= n_taps || pos - back < 0) continue;       // before the sequence's first token: zero
+      float v = bx;
+#pragma unroll
+      for (int s = 0; s < PRE_TAPS - 1; ++s)
+        if (back != 0 && s == S - back) v = pre_old[s];
+      sum = fmaf(pre_tap[j], v, sum);
+    }
+  } else {
 #pragma unroll 1
-  for (int s = 0; s < S; ++s) old[s] = st[(long long)s * hidden + c];
-  float sum = conv_bias ? conv_bias[c] : 0.f;
+    for (int s = 0; s < S; ++s) old[s] = st[(long long)s * hidden + c];
+    sum = conv_bias ? conv_bias[c] : 0.f;
 #pragma unroll 1
-  for (int j = 0; j < n_taps; ++j) {
-    const int back = n_taps - 1 - j;
-    if (pos - back < 0) continue;                // before the sequence's first token: zero
-    const float v = back == 0 ? bx : old[S - back];
-    sum = fmaf(taps[(long long)c * n_taps + j], v, sum);
+    for (int j = 0; j < n_taps; ++j) {
+      const int back = n_taps - 1 - j;
+      if (pos - back < 0) continue;                // before the sequence's first token: zero
+      const float v = back == 0 ? bx : old[S - back];
+      sum = fmaf(taps[(long long)c * n_taps + j], v, sum);
+    }
   }
   y[(long long)m * hidden + c] = from_f32<bf16>(in[1] * sum);
   if (write_state) {
