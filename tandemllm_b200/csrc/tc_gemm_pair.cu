@@ -57,21 +57,31 @@ inline int& skip_kb_for_test() {
   return kb;
 }
 
-template <bool GATED>
+// PER_SM: CTAs an SM. One: the forms described above. Two: half the shared memory and half the tensor memory each (the
+// gated product then takes tiles of 128 token rows, gate and up accumulators of 128 columns; one accumulator set, so the
+// other CTA of the SM is what runs under an epilogue). Twice the pairs are resident, which is what a product bound by
+// its weights wants: its work items all cost the same (what their weight tiles take to load), and when the last round
+// leaves an SM with one CTA instead of two, that CTA loads at the SM's full rate. Measured on the experts' two products
+// of 128 to 512 tokens (32 experts, 16 to 64 rows each): 170 to 176 us -> 158 to 164 us; from 128 rows an expert on the
+// form with one CTA an SM and its deeper ring is faster again.
+template <bool GATED, int PER_SM>
 struct Smem {
-  static constexpr int TOKENS = 256;                               // token rows a tile at most
+  static constexpr int TOKENS = (GATED && PER_SM == 2) ? 128 : 256;  // token rows a tile at most
   static constexpr int W_TILES = GATED ? 2 : 1;
-  static constexpr int ACC_BUFS = GATED ? 1 : 2;                   // accumulators (sets of them) in tensor memory
+  static constexpr int ACC_BUFS = (GATED || PER_SM == 2) ? 1 : 2;  // accumulators (sets of them) in tensor memory
+  static constexpr int TMEM_COLS = PER_SM == 2 ? 256 : 512;
+  static constexpr int UP_COL = TOKENS;                            // the gated product's second accumulator
   // Epilogue warps: one a quarter of the accumulator's lanes, or, where the MMAs wait for the epilogue, two that take
   // every other block of 16 tokens (measured: the plain product is a little slower with eight)
   static constexpr int EPI_WARPS = GATED ? 8 : 4;
   static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int A_BYTES = ROWS * TILE_K * 2;                // one box of weights
   static constexpr int B_BYTES = (TOKENS / 2) * TILE_K * 2;        // this CTA's half of the token rows, at most
-  static constexpr int STAGE_BYTES = W_TILES * A_BYTES + B_BYTES;  // 48 KB gated, 32 KB plain
-  static constexpr int STAGES = GATED ? 4 : 6;
+  static constexpr int STAGE_BYTES = W_TILES * A_BYTES + B_BYTES;
+  static constexpr int STAGES = PER_SM == 2 ? (GATED ? 2 : 3) : (GATED ? 4 : 6);
   static constexpr int TURN_BYTES = EPI_WARPS * 16 * 32 * 4;       // the epilogue warps' blocks
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */ + TURN_BYTES;
+  static_assert(PER_SM * TOTAL <= 227 * 1024, "the CTAs of an SM share its shared memory");
 };
 
 // K-major tile with 128-byte rows and the 128-byte swizzle: 8-row groups 1024 bytes apart, descriptor version 1.
@@ -158,12 +168,12 @@ template <typename TOut> __device__ __forceinline__ void put(TOut* p, float v);
 template <> __device__ __forceinline__ void put<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void put<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-template <bool GATED, typename TOut>
-__global__ void __launch_bounds__(Smem<GATED>::THREADS) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW,
+template <bool GATED, int PER_SM, typename TOut>
+__global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmW,
                                                            const __grid_constant__ CUtensorMap tmX16,
                                                            const __grid_constant__ CUtensorMap tmX64,
                                                            const __grid_constant__ CUtensorMap tmX128, Params p) {
-  using S = Smem<GATED>;
+  using S = Smem<GATED, PER_SM>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full = (uint64_t*)(tiles + S::STAGES * S::STAGE_BYTES);   // used in the first CTA: both CTAs' bytes
@@ -191,7 +201,8 @@ __global__ void __launch_bounds__(Smem<GATED>::THREADS) gemm_tc_pair_kernel(cons
   }
   if (warp == 1) {
     // the same warp of both CTAs: the pair's tensor memory is given out, and later freed, together
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u));
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"((uint32_t)S::TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -241,7 +252,7 @@ __global__ void __launch_bounds__(Smem<GATED>::THREADS) gemm_tc_pair_kernel(cons
       const int my_tok = tok0 + (int)rank * half;                    // this CTA's half of the N side
       const int my_row = (int)(w_base + n0) + (int)rank * ROWS;      // this CTA's 128 outputs
       // the smallest box that holds the half; rows of it behind the half are read and never used
-      const int box = half <= 16 ? 16 : (half <= 64 ? 64 : 128);
+      const int box = half <= 16 ? 16 : (half <= 64 ? 64 : 128);      // (a half is at most TOKENS / 2 rows)
       const CUtensorMap* tmX = box == 16 ? &tmX16 : (box == 64 ? &tmX64 : &tmX128);
       const uint32_t cta_bytes = (uint32_t)(S::W_TILES * S::A_BYTES + box * TILE_K * 2);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -294,7 +305,7 @@ __global__ void __launch_bounds__(Smem<GATED>::THREADS) gemm_tc_pair_kernel(cons
         for (int k = 0; k < TILE_K / UMMA_K; ++k) {
           const uint32_t more = (kb > 0 || k > 0) ? 1u : 0u, koff = k * UMMA_K * 2;
           mma2(acc, desc(a0 + koff), desc(b0 + koff), id, more);
-          if (GATED) mma2(acc + 256, desc(a0 + S::A_BYTES + koff), desc(b0 + koff), id, more);
+          if (GATED) mma2(acc + S::UP_COL, desc(a0 + S::A_BYTES + koff), desc(b0 + koff), id, more);
         }
         commit_both(&empty[s]);
       }
@@ -333,7 +344,7 @@ __global__ void __launch_bounds__(Smem<GATED>::THREADS) gemm_tc_pair_kernel(cons
         float v[16], u[16];
         if (num_kb > 0) {
           ld16(taddr + c0, v);
-          if (GATED) ld16(taddr + 256 + c0, u);
+          if (GATED) ld16(taddr + S::UP_COL + c0, u);
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = u[j] = 0.f;
@@ -403,18 +414,21 @@ __global__ void __launch_bounds__(Smem<GATED>::THREADS) gemm_tc_pair_kernel(cons
   cluster_sync();                                      // neither CTA leaves while the other may still signal it or read its tiles
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u));
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS));
   }
 }
 
 // How many pairs of this kernel the GPU holds at a time (asked once a kernel); negative: a CUDA error code, negated.
-template <bool GATED, typename TOut>
+template <bool GATED, int PER_SM, typename TOut>
 static int resident_pairs() {
-  using S = Smem<GATED>;
+  using S = Smem<GATED, PER_SM>;
   static int clusters = 0;
   if (clusters != 0) return clusters;
-  auto kernel = gemm_tc_pair_kernel<GATED, TOut>;
+  auto kernel = gemm_tc_pair_kernel<GATED, PER_SM, TOut>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+  if (e != cudaSuccess) return -(int)e;
+  // all of the SM's configurable memory as shared memory: two CTAs an SM need it
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return -(int)e;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -422,7 +436,7 @@ static int resident_pairs() {
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  cfg.gridDim = dim3(2 * (sm_count() / 2));
+  cfg.gridDim = dim3(2 * PER_SM * (sm_count() / 2));
   cfg.blockDim = dim3(S::THREADS);
   cfg.dynamicSmemBytes = S::TOTAL;
   cfg.attrs = attr;
@@ -431,13 +445,17 @@ static int resident_pairs() {
   e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
   if (e != cudaSuccess) return -(int)e;
   clusters = n;
-  return n;
+  // Two CTAs an SM: the query answers as if a pair had the two SMs to itself (74), yet two pairs do share them
+  // (ncu: 296 CTAs are one wave, 20 warps active an SM). No pair waits for another in this kernel, so a grid of twice
+  // the pairs is safe either way: on a GPU that held only one CTA an SM the others would simply start later.
+  if (PER_SM == 2 && n >= 1) clusters = 2 * (sm_count() / 2);
+  return clusters;
 }
 
-template <bool GATED, typename TOut>
+template <bool GATED, int PER_SM, typename TOut>
 static int launch(const CUtensorMap& tmW, const CUtensorMap* tmX, const Params& p, long long work, cudaStream_t stream) {
-  using S = Smem<GATED>;
-  const int clusters = resident_pairs<GATED, TOut>();
+  using S = Smem<GATED, PER_SM>;
+  const int clusters = resident_pairs<GATED, PER_SM, TOut>();
   if (clusters < 0) return -clusters;
   TL_REQUIRE(clusters >= 1, "pair product: no cluster of two CTAs with %d bytes of shared memory fits this GPU", S::TOTAL);
   cudaLaunchConfig_t cfg = {};
@@ -452,7 +470,7 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap* tmX, const Params& 
   cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<GATED, TOut>, tmW, tmX[0], tmX[1], tmX[2], p);
+  return (int)cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<GATED, PER_SM, TOut>, tmW, tmX[0], tmX[1], tmX[2], p);
 }
 
 }  // namespace pair
@@ -461,20 +479,24 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap* tmX, const Params& 
 using namespace tl;
 
 // The token rows a tile of the pair kernel holds at most (a routing plan for it is built with tiles of this height).
-extern "C" int tl_tc_pair_token_tile() { return pair::Smem<false>::TOKENS; }
+extern "C" int tl_tc_pair_token_tile(int per_sm) {
+  return per_sm == 2 ? pair::Smem<true, 2>::TOKENS : pair::Smem<true, 1>::TOKENS;      // what the gated product takes
+}
 
-extern "C" int tl_tc_pair_resident(int gated) {
-  return gated ? pair::resident_pairs<true, bf16>() : pair::resident_pairs<false, bf16>();
+extern "C" int tl_tc_pair_resident(int gated, int per_sm) {
+  if (per_sm == 2) return gated ? pair::resident_pairs<true, 2, bf16>() : pair::resident_pairs<false, 2, bf16>();
+  return gated ? pair::resident_pairs<true, 1, bf16>() : pair::resident_pairs<false, 1, bf16>();
 }
 
 // X [M, K] (row stride ldx, x_rows rows in the tensor), W [groups * rows_per_group, K] (row stride ldw). Plain: groups = 1,
 // tile_group = nullptr. gated (an activation code TL_ACT_*, or 0): W holds 2 N rows per group (gate then up) and
 // C = act(gate) * up. out_dtype: TL_BF16 or TL_FP32. Grouped: the tile map's tiles hold at most tl_tc_pair_token_tile()
-// rows (plan_rows: the height the map was built with).
+// rows (plan_rows: the height the map was built with). per_sm: 1 or 2 CTAs an SM (see Smem).
 extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
                                long long rows_per_group, const float* bias, void* C, long long ldc, int M, int N, int K,
                                int gated, int out_dtype, const int* tile_group, const int* tile_row0, const int* tile_rows,
-                               const int* n_tiles, int max_tiles, int plan_rows, int* status, cudaStream_t stream) {
+                               const int* n_tiles, int max_tiles, int plan_rows, int per_sm, int* status,
+                               cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   TL_REQUIRE(M > 0 && N > 0 && K > 0, "pair product: M %d N %d K %d", M, N, K);
   TL_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
@@ -485,7 +507,8 @@ extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, c
   TL_REQUIRE(gated >= 0 && gated <= TL_ACT_LAST, "pair product: gate activation %d is not one of 0..%d", gated, TL_ACT_LAST);
   TL_REQUIRE(!tile_group || (tile_row0 && tile_rows && n_tiles && max_tiles > 0 && plan_rows > 0),
              "pair product: incomplete tile map (tiles of %d rows)", plan_rows);
-  const int tokens = tl_tc_pair_token_tile();
+  TL_REQUIRE(per_sm == 1 || per_sm == 2, "pair product: %d CTAs an SM; 1 or 2", per_sm);
+  const int tokens = (gated && per_sm == 2) ? 128 : 256;
   TL_REQUIRE(!tile_group || plan_rows <= tokens, "pair product: a tile map with tiles of %d rows; at most %d", plan_rows, tokens);
   CUtensorMap tmW, tmX[3];
   if (int e = tensor_map(W, w_rows, K, ldw, pair::ROWS, &tmW)) return e;
@@ -500,10 +523,11 @@ extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, c
   p.act = gated; p.status = status;
   p.skip_kb = pair::skip_kb_for_test();
   const long long work = (long long)ceil_div(N, 2 * pair::ROWS) * (tile_group ? max_tiles : ceil_div(M, tokens));
-  if (gated) return out_dtype == TL_BF16 ? pair::launch<true, bf16>(tmW, tmX, p, work, stream)
-                                         : pair::launch<true, float>(tmW, tmX, p, work, stream);
-  return out_dtype == TL_BF16 ? pair::launch<false, bf16>(tmW, tmX, p, work, stream)
-                              : pair::launch<false, float>(tmW, tmX, p, work, stream);
+#define TL_PAIR(G_, P_) \
+  (out_dtype == TL_BF16 ? pair::launch<G_, P_, bf16>(tmW, tmX, p, work, stream) : pair::launch<G_, P_, float>(tmW, tmX, p, work, stream))
+  if (per_sm == 2) return gated ? TL_PAIR(true, 2) : TL_PAIR(false, 2);
+  return gated ? TL_PAIR(true, 1) : TL_PAIR(false, 1);
+#undef TL_PAIR
 }
 
 // For tests of the bounded waits, as in tc_gemm.cu: the polls after which an mbarrier wait of this file's kernel gives up

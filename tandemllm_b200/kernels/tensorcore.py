@@ -50,6 +50,7 @@ PROMPT_ATTENTION = "tcgen05"    # prompt portions of head size 64: the tcgen05 k
 PROMPT_PRODUCT = SETTINGS.get("PROMPT_PRODUCT")
 if PROMPT_PRODUCT not in ("pair", "single"):
     raise ValueError(f"TANDEMLLM_PROMPT_PRODUCT={PROMPT_PRODUCT!r}: pair or single")
+PAIR_HALF_ROWS = 64             # rows an expert (on average) up to which the experts' pair products run two CTAs an SM
 _lib = None
 
 
@@ -63,9 +64,9 @@ def lib():
         l.tl_gemm_tc.restype = c_int
         l.tl_gemm_tc_pair.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p,
                                       c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                      c_void_p, c_int, c_int, c_void_p, c_void_p]
+                                      c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
         l.tl_gemm_tc_pair.restype = c_int
-        l.tl_tc_pair_token_tile.argtypes = []
+        l.tl_tc_pair_token_tile.argtypes = [c_int]
         l.tl_tc_pair_token_tile.restype = c_int
         l.tl_gather_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         l.tl_gather_rows.restype = c_int
@@ -158,7 +159,7 @@ class TensorCore:
         if bn is None:
             bn = _pow2_at_least(M) if swap else 256        # 256 without swap: the persistent kernel
         if (PROMPT_PRODUCT == "pair" and not swap and bn == 256 and splits == 1 and row_index is None
-                and (plan is None or plan.tile_m <= lib().tl_tc_pair_token_tile())):
+                and (plan is None or plan.tile_m <= lib().tl_tc_pair_token_tile(1))):
             self.gemm_pair(x, w2d, bias, out, rows_per_group=rows_per_group, plan=plan, gated=int(swiglu), n_out=n_out,
                            rows=rows)
             return None
@@ -191,9 +192,11 @@ class TensorCore:
         return ops.PartialSums(partial, splits, M, N, None if out.dtype == torch.float32 else out.dtype)
 
     def gemm_pair(self, x, w2d, bias, out, *, rows_per_group=0, plan=None, gated: int = 0, n_out=None,
-                  rows: int | None = None) -> None:
+                  rows: int | None = None, per_sm: int | None = None) -> None:
         """The product on pairs of SMs (csrc/tc_gemm_pair.cu): 256 outputs by up to 256 token rows a pair, the N side
-        of its MMAs as many rows as a tile holds. `plan`: tiles of any height up to 256 rows."""
+        of its MMAs as many rows as a tile holds. `plan`: tiles of any height up to 256 rows. `per_sm` 2: two CTAs an
+        SM, each with half the shared and tensor memory (gated: tiles of up to 128 rows), the form for products bound
+        by their weights; default: 2 for a plan with tiles of up to 128 rows, else 1."""
         M, K = (rows if rows is not None else x.shape[0]), x.shape[1]
         N = n_out if n_out is not None else w2d.shape[0]
         tg = tr0 = trs = nt = None
@@ -201,10 +204,12 @@ class TensorCore:
         if plan is not None:
             tg, tr0, trs, nt, max_tiles, plan_rows = (plan.tile_group, plan.tile_row0, plan.tile_rows, plan.n_tiles,
                                                       plan.max_tiles, plan.tile_m)
+        if per_sm is None:
+            per_sm = 2 if plan is not None and plan.tile_m <= 128 else 1
         _check(lib().tl_gemm_tc_pair(x.data_ptr(), x.stride(0), x.shape[0], w2d.data_ptr(), w2d.stride(0), w2d.shape[0],
                                      rows_per_group, ops.ptr(bias), out.data_ptr(), out.stride(0), M, N, K, int(gated),
                                      ops.dtype_code(out.dtype), ops.ptr(tg), ops.ptr(tr0), ops.ptr(trs), ops.ptr(nt),
-                                     max_tiles, plan_rows, self.status.data_ptr(), ops.stream()), "gemm_tc_pair")
+                                     max_tiles, plan_rows, per_sm, self.status.data_ptr(), ops.stream()), "gemm_tc_pair")
 
     def gated(self, x, w_gate_up, out, act: int = 1) -> bool:
         """out = act(x gate^T) * (x up^T) for w_gate_up = [gate rows; up rows], in the persistent kernel with the gated
@@ -256,7 +261,8 @@ class TensorCore:
         swap = avg <= 48
         bn = 16 if avg <= 12 else 32 if avg <= 24 else 64 if swap else 256
         if not swap and PROMPT_PRODUCT == "pair":
-            return swap, bn, lib().tl_tc_pair_token_tile()
+            # few rows an expert: the products are bound by the experts' weights, and run two CTAs an SM on tiles of 128
+            return swap, bn, lib().tl_tc_pair_token_tile(2 if avg <= PAIR_HALF_ROWS else 1)
         return swap, bn, lib().tl_tc_token_tile(int(swap), bn)
 
     def _experts_of_a_tiny_step(self, part, x, ids, wts, plan):

@@ -713,3 +713,23 @@ def test_prompt_products_through_either_kernel(which, monkeypatch):
     assert int(rt.status) == 0 and ops.launches == before + 1
     assert rel(out, x.float() @ w.float().T) < 1e-3
     assert impl.expert_tile(8192, 32)[2] == (256 if which == "pair" else 128)
+
+
+@pytest.mark.parametrize("gated", [0, 1])
+@pytest.mark.parametrize("M,N,K", [(300, 520, 192), (129, 264, 72), (1000, 1792, 256)])
+def test_pair_product_with_two_ctas_an_sm(M, N, K, gated):
+    """The form with half the shared and tensor memory a CTA (the gated product on tiles of 128 token rows), which a
+    routing plan of tiles up to 128 rows selects: the same results as the plain rule, run twice the same bits."""
+    impl, rt = tc()
+    x, w = rnd(M, K, seed=81), rnd((2 if gated else 1) * N, K, seed=82, scale=0.1)
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        impl.gemm_pair(x.to(DEV), w.to(DEV), None, out, gated=gated, n_out=N, per_sm=2)
+        torch.cuda.synchronize()
+        assert int(rt.status) == 0
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    full = x.float() @ w.float().T
+    want = torch.nn.functional.silu(full[:, :N]) * full[:, N:] if gated else full
+    assert rel(outs[0], want) < 1e-2
