@@ -228,6 +228,15 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
   const int split = (ONE_ROW && ROUTE_PER > 0) ? p.split : 1;
   const int rank = split > 1 ? (int)(blockIdx.x % split) : 0;
   const int first_row = (int)(blockIdx.x / split) * p.rows_per_block;
+  if constexpr (ONE_ROW && ROUTE_PER > 0) {
+    // The router's weights that this CTA's warps will read are asked into L2 now (they are cold every step: a step
+    // streams gigabytes through L2), so that their trip to DRAM runs under the row's chain. No registers are held.
+    const int lane_ = threadIdx.x & 31, warp_ = threadIdx.x >> 5, nwarps_ = blockDim.x >> 5;
+    for (int j = warp_; j * split + rank < p.E; j += nwarps_) {
+      const char* w = reinterpret_cast<const char*>(p.router_w + (size_t)(j * split + rank) * hidden);
+      for (int b = lane_ * 128; b < hidden * 4; b += 32 * 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(w + b));
+    }
+  }
   const int n_rows = min(p.rows_per_block, p.out_rows - first_row);
   const int G = blockDim.x / p.rows_per_block;           // threads a row
   const int rr = threadIdx.x / G, t = threadIdx.x - rr * G;
