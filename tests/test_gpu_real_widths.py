@@ -27,8 +27,11 @@ WIDTHS = dict(
 )
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim", [(32, 8, 64), (16, 4, 128)])
-def test_two_layers_at_the_benchmark_widths_against_the_plain_implementation(heads, kv_heads, head_dim):
+@pytest.mark.parametrize("heads,kv_heads,head_dim,product", [(32, 8, 64, "pair"), (16, 4, 128, "pair"), (32, 8, 64, "single")])
+def test_two_layers_at_the_benchmark_widths_against_the_plain_implementation(heads, kv_heads, head_dim, product, monkeypatch):
+    """(`product`: the prompt-sized products on pairs of SMs, the default, or through the one-CTA kernel kept beside it)"""
+    from tandemllm_b200.kernels import tensorcore
+    monkeypatch.setattr(tensorcore, "PROMPT_PRODUCT", product)
     from tandemllm_b200.config import Lfm2MoeConfig
     from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
     from tandemllm_b200.weights.loader import DictWeights
