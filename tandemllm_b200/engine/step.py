@@ -108,6 +108,7 @@ class StepFunction:
         self._device_ints = None
         self._graphs: OrderedDict[tuple, _DecodeGraph] = OrderedDict()      # least recently used first
         self._graph_pool = None
+        self._capture_stream = None
         self.max_graphs = max(1, max_graphs if max_graphs is not None else SETTINGS.get_int("GRAPHS"))
         self.graphs_dropped = 0
         self.trace: dict | None = None      # when a dict: every step runs eagerly and its parts may record into it
@@ -304,12 +305,26 @@ class StepFunction:
             # pool with it; a caller that still holds them from an earlier step has had them read (the stream is idle).
             self._graphs.popitem(last=False)
             self.graphs_dropped += 1
-        if self._graph_pool is None:
+        # one memory pool for all the graphs, as long as one of them lives (a pool whose graphs are all gone may not be
+        # captured into again)
+        if self._graph_pool is None or not any(g.graph is not None for g in self._graphs.values()):
             self._graph_pool = torch.cuda.graph_pool_handle()
         graph = torch.cuda.CUDAGraph()
         before = ops.launches
-        with torch.cuda.graph(graph, pool=self._graph_pool):
-            slot.logits = self.model.forward(slot.step, cache.site_cache)
+        # Captured on a stream of its own between capture_begin and capture_end. (`torch.cuda.graph(...)` would also run
+        # the garbage collector and hand every cached block back to the driver first: hundreds of milliseconds here, and
+        # the steps after it pay for the blocks again. The stream is idle and the shapes were sized by the eager run.)
+        if self._capture_stream is None:
+            self._capture_stream = torch.cuda.Stream(device=self.device)
+        current = torch.cuda.current_stream()
+        self._capture_stream.wait_stream(current)
+        with torch.cuda.stream(self._capture_stream):
+            graph.capture_begin(pool=self._graph_pool)
+            try:
+                slot.logits = self.model.forward(slot.step, cache.site_cache)
+            finally:
+                graph.capture_end()
+        current.wait_stream(self._capture_stream)
         slot.kernels = ops.launches - before        # kernels one replay runs; capturing ran none
         ops.launches = before
         slot.graph = graph
