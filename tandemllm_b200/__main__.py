@@ -32,6 +32,8 @@ def _engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--chunk-size", type=int, default=512, help="longest prompt portion in one step")
     p.add_argument("--graph", default="on", choices=("on", "off"), help="CUDA graphs for decode-only steps")
     p.add_argument("--device", default="cuda:0")
+    p.add_argument("--warm-up", action="store_true",
+                   help="run throwaway requests first: kernel libraries loaded and decode graphs captured before the clock starts")
     p.add_argument("--log", help="append one JSON line a scheduler step here (rows, pages, milliseconds)")
     p.add_argument("--log-routing", action="store_true",
                    help="count the experts every step touches in every routed layer (into the step records and --log)")
@@ -70,6 +72,7 @@ def cmd_generate(a) -> int:
                             max_tokens=a.tokens, ignore_eos=a.ignore_eos, repetition_penalty=a.rep_penalty,
                             presence_penalty=a.presence_penalty, frequency_penalty=a.frequency_penalty,
                             logit_bias=_logit_bias(a.logit_bias))
+    warm = engine.warm_up() if a.warm_up else None
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = engine.generate(prompts, params)
@@ -77,6 +80,8 @@ def cmd_generate(a) -> int:
     dt = time.perf_counter() - t0
     result = {"outputs": outs, "seconds": round(dt, 4), "generated": sum(len(o) for o in outs),
               "tok_s": round(sum(len(o) for o in outs) / dt, 2), "stats": engine.stats()}
+    if warm is not None:
+        result["warm_up"] = warm
     for i, o in enumerate(outs):
         print(f"[{i}] " + " ".join(str(t) for t in o))
     print(json.dumps({k: v for k, v in result.items() if k != "outputs"}), file=sys.stderr)

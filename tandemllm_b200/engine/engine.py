@@ -347,6 +347,45 @@ class Engine:
             self.run_step()
         return [r.output for r in reqs]
 
+    def warm_up(self, batch_sizes: list[int] | None = None, prompt_tokens: int | None = None) -> dict:
+        """Throwaway requests through the step function, so that the first real request finds every kernel library
+        of a prompt step and of a decode step loaded, and the decode graphs of `batch_sizes` (default: 1, 2, 4, ... up
+        to `parallel`) captured for short contexts. Nothing of it stays: pages and slots are given back, no record is
+        written. Only with no request waiting or running."""
+        if self.scheduler.has_unfinished() or self._flight is not None:
+            raise RuntimeError("warm_up() while requests are waiting or running")
+        args, started = self.args, time.perf_counter()
+        if batch_sizes is None:
+            batch_sizes, b = [], 1
+            while b < args.parallel:
+                batch_sizes.append(b)
+                b *= 2
+            batch_sizes.append(args.parallel)
+        bad = [b for b in batch_sizes if not 1 <= b <= args.parallel]
+        if bad:
+            raise ValueError(f"warm_up: batch size {bad[0]} with {args.parallel} requests running at once at most")
+        portion = min(prompt_tokens or args.chunk_size, args.max_batched_tokens, args.max_len - 3)
+        most, before = max(batch_sizes), len(self.step_function._graphs)
+        ids = [("warm-up", i) for i in range(most)]
+        with torch.cuda.device(self.device):
+            try:
+                for rid in ids:
+                    self.admit(rid)
+                # a prompt's portion beside nothing, then a single token of each of the others: every request holds a key
+                self.step([StepEntry(ids[0], [0] * max(1, portion), [max(1, portion) - 1])])
+                if most > 1:
+                    self.step([StepEntry(rid, [0], [0]) for rid in ids[1:]])
+                for b in sorted(set(batch_sizes)):
+                    for _ in range(2):                 # the first is eager and captured behind it, the second a replay
+                        self.step([StepEntry(rid, [0], [0]) for rid in ids[:b]])
+                torch.cuda.synchronize(self.device)
+            finally:
+                for rid in ids:
+                    if self.cache.has(rid):
+                        self.release(rid)
+        return {"seconds": round(time.perf_counter() - started, 3), "batch_sizes": sorted(set(batch_sizes)),
+                "graphs_captured": len(self.step_function._graphs) - before}
+
     def stats(self) -> dict:
         fn = self.step_function
         return {"scheduler": vars(self.scheduler.stats), "cache": self.cache.stats(),

@@ -160,3 +160,37 @@ def test_named_ranges_for_profilers_change_nothing(tmp_path, monkeypatch):
     plain = run()
     monkeypatch.setenv("TANDEMLLM_NVTX", "1")
     assert run() == plain
+
+
+def test_warm_up_leaves_nothing_behind_and_the_first_decode_steps_replay_graphs(tmp_path):
+    """`Engine.warm_up`: the throwaway requests give every page and slot back, the decode graphs of its batch sizes are
+    captured, the tokens generated afterwards are those of an engine that was not warmed, and the first decode steps of
+    the real requests are replays (an engine that was not warmed runs each new shape eagerly once)."""
+    from tandemllm_b200.engine import Engine, EngineArgs
+    from tandemllm_b200.sampling import SamplingParams
+    folder, cfg, W = folder_of("c", tmp_path, torch.bfloat16)
+    args = dict(dtype="bfloat16", max_len=256, parallel=3, chunk_size=16, max_batched_tokens=24)
+    prompts = [T.long_tokens("c", n, seed=5 + n) for n in (23, 9, 14)]
+    params = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+
+    cold = Engine.from_folder(folder, EngineArgs(**args))
+    want = cold.generate(prompts, params)
+    cold_replays = cold.stats()["graph_replays"]
+
+    eng = Engine.from_folder(folder, EngineArgs(**args))
+    def free_now():
+        st = eng.cache.stats()
+        return st["requests"], st["free_slots"], [g["free"] for g in st["groups"]]
+    free_before = free_now()
+    info = eng.warm_up()
+    assert info["batch_sizes"] == [1, 2, 3] and info["graphs_captured"] == 3
+    eng.cache.check()
+    assert free_now() == free_before and not eng.records
+    replays = eng.stats()["graph_replays"]
+    assert eng.generate(prompts, params) == want
+    assert eng.stats()["graph_replays"] - replays > cold_replays
+    with pytest.raises(ValueError, match="batch size 4"):
+        eng.warm_up([4])
+    eng.add_request([1, 2, 3], params)
+    with pytest.raises(RuntimeError, match="waiting or running"):
+        eng.warm_up()
