@@ -461,7 +461,7 @@ def main() -> int:
     ap.add_argument("--graph", default="on", choices=("on", "off"))
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
-                    help="with --only prefill: a prompt of this many tokens in one step (the headline line keeps 2048)")
+                    help="with --only prefill or --profile-table: a prompt of this many tokens in one step (the headline line keeps 2048)")
     ap.add_argument("--only", choices=("prefill",), help="measure only this part and print it (a profiling aid)")
     ap.add_argument("--scenario", choices=("mixed",),
                     help="mixed: 64 requests with prompts of 128 to 32768 tokens (log-uniform) under a cache budget that makes "
@@ -503,7 +503,7 @@ def main() -> int:
     pk = peaks()
     bf16 = a.dtype == "bfloat16"
     max_batch = 64 if not a.skip_points else a.batch
-    only_tokens = a.prefill_tokens if a.only == "prefill" else PREFILL_TOKENS
+    only_tokens = a.prefill_tokens if a.only == "prefill" or a.profile_table else PREFILL_TOKENS
     room = max(a.context, only_tokens) + REPEATS * a.steps + a.warmup + 80
     t0 = time.time()
     engine = Engine.from_config(cfg, seed=0, args=EngineArgs(
@@ -688,15 +688,15 @@ def main() -> int:
                                                  "frac_hbm": round(family_bytes[key] / ms / 1e6 / pk["hbm_gbs"], 4)}
         total = sum(r["ms"] for k, r in decode.items() if not k.startswith("="))
         engine.admit("prefill")
-        prompt = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
-        engine.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])])
+        prompt = torch.randint(0, V, (only_tokens,), generator=g).tolist()
+        engine.step([StepEntry("prefill", prompt, [only_tokens - 1])])
         engine.release("prefill")
         engine.admit("prefill")
         with timer:
-            engine.step([StepEntry("prefill", prompt, [PREFILL_TOKENS - 1])])
+            engine.step([StepEntry("prefill", prompt, [only_tokens - 1])])
             pre = timer.table()
         engine.release("prefill")
-        flops = prefill_flops(cfg, PREFILL_TOKENS)
+        flops = prefill_flops(cfg, only_tokens)
         psums = {"experts": 0.0, "dense": 0.0, "attention": 0.0}
         for fam, row in pre.items():
             key = "experts" if fam.startswith("experts") else "dense" if fam.startswith("dense") else \
@@ -713,7 +713,7 @@ def main() -> int:
                                             "context": a.context, "peaks": pk,
                                             "decode_step": {"eager_ms": round(eager_ms, 4), "sum_of_launches_ms": round(total, 4),
                                                             "families": decode},
-                                            "prefill": {"tokens": PREFILL_TOKENS, "sum_of_launches_ms": round(ptotal, 4),
+                                            "prefill": {"tokens": only_tokens, "sum_of_launches_ms": round(ptotal, 4),
                                                         "families": pre}}}))
         return 0
 
