@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
   // A row that gets a plain tensor added (or nothing) and whose thread holds at most IN_REGS 16-byte pieces of it: all
   // of the thread's loads are sent before the first is used, and the pieces stay in registers until they are normed.
   constexpr int IN_REGS = 4;
-  const bool in_regs = vec && !p.expert_rows && p.parts <= 1 && (hidden >> 2) <= G * IN_REGS;
+  const bool in_regs = vec && !p.expert_rows && (hidden >> 2) <= G * IN_REGS;
   float4 xr[IN_REGS];
   if (in_regs) {
     const int h4 = hidden >> 2;
@@ -284,6 +284,20 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
       const bool ok = live && c < h4;
       xr[i] = ok ? res4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
       dr[i] = ok && d4 ? d4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    // a product left in partial sums: the further parts, added in order, a round of the thread's loads a part
+    for (int s = 1; s < p.parts; ++s) {
+      const float4* ds4 = reinterpret_cast<const float4*>(p.delta + (long long)s * p.part_stride + (size_t)r * hidden);
+      float4 more[IN_REGS];
+#pragma unroll
+      for (int i = 0; i < IN_REGS; ++i) {
+        const int c = t + i * G;
+        more[i] = live && c < h4 ? ds4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int i = 0; i < IN_REGS; ++i) {
+        dr[i].x += more[i].x; dr[i].y += more[i].y; dr[i].z += more[i].z; dr[i].w += more[i].w;
+      }
     }
 #pragma unroll
     for (int i = 0; i < IN_REGS; ++i) {

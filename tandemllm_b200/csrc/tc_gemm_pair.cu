@@ -49,6 +49,9 @@ struct Params {
   int plan_rows;              // the height of the tile map's tiles, at most TOKENS
   int act;                    // the gate's activation (TL_ACT_*), 0 for a plain product
   int skip_kb;                // -1; a test sets the k-block (counted over a cluster's tiles) whose copies both producers leave out
+  int splits;                 // plain, ungrouped: work items a tile, each a run of k-blocks with a 32-bit partial result of its own
+  int kb_per_split;           // k-blocks a run (every run holds at least one)
+  long long part_stride;      // elements from one run's [M, ldc] result to the next one's
   int* status;
 };
 
@@ -220,12 +223,17 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
 
   const int tiles_n = (p.N + 2 * ROWS - 1) / (2 * ROWS);
   const int tiles_m = p.tile_group ? *p.n_tiles : (p.M + S::TOKENS - 1) / S::TOKENS;
-  const int work = tiles_m * tiles_n;
-  const int num_kb = (p.K + TILE_K - 1) / TILE_K;
+  const int work = tiles_m * tiles_n * p.splits;
+  const int all_kb = (p.K + TILE_K - 1) / TILE_K;
   const int cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
 
-  // work item w: token tile w / tiles_n, weight tile w % tiles_n (neighbouring clusters share token rows)
-  auto tile_of = [&](int w, int& tok0, int& tok_rows, long long& w_base, int& n0) {
+  // work item w: token tile w / tiles_n, weight tile w % tiles_n (neighbouring clusters share token rows); with runs of
+  // k-blocks, run w / (tiles_m tiles_n) of that tile
+  auto tile_of = [&](int w, int& tok0, int& tok_rows, long long& w_base, int& n0, int& kb0, int& num_kb) {
+    const int run = w / (tiles_m * tiles_n);
+    w -= run * tiles_m * tiles_n;
+    kb0 = run * p.kb_per_split;
+    num_kb = p.splits > 1 ? min(p.kb_per_split, all_kb - kb0) : all_kb;
     const int tm = w / tiles_n;
     n0 = (w - tm * tiles_n) * 2 * ROWS;
     if (p.tile_group) {
@@ -243,9 +251,9 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
     // ---- producer (each CTA for its own shared memory) ----
     int it = 0, issued = 0;
     for (int w = cluster; w < work && !*aborted; w += clusters) {
-      int tok0, tok_rows, n0;
+      int tok0, tok_rows, n0, kb0, num_kb;
       long long w_base;
-      tile_of(w, tok0, tok_rows, w_base, n0);
+      tile_of(w, tok0, tok_rows, w_base, n0, kb0, num_kb);
       if (tok_rows <= 0) continue;
       const int n_mma = (tok_rows + 15) & ~15;
       const int half = n_mma >> 1;
@@ -263,7 +271,7 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
           uint8_t* st = tiles + s * S::STAGE_BYTES;
           const uint32_t bar = in_cta(&full[s], 0);
           if (first) mbar_expect_tx(&full[s], 2 * cta_bytes);
-          const int kx = kb * TILE_K;
+          const int kx = (kb0 + kb) * TILE_K;
           load_2d(st, &tmW, bar, kx, my_row);
           if (GATED) load_2d(st + S::A_BYTES, &tmW, bar, kx, my_row + p.N);
           load_2d(st + S::W_TILES * S::A_BYTES, tmX, bar, kx, my_tok);
@@ -280,9 +288,9 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
     // ---- MMA issuer (the first CTA for the pair) ----
     int it = 0, n = 0;
     for (int w = cluster; w < work && !*aborted; w += clusters) {
-      int tok0, tok_rows, n0;
+      int tok0, tok_rows, n0, kb0, num_kb;
       long long w_base;
-      tile_of(w, tok0, tok_rows, w_base, n0);
+      tile_of(w, tok0, tok_rows, w_base, n0, kb0, num_kb);
       if (tok_rows <= 0) continue;
       const int n_mma = (tok_rows + 15) & ~15;
       const uint32_t id = idesc(n_mma);
@@ -323,9 +331,9 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
     int n = 0;
     if (p.tile_group && p.plan_rows > S::TOKENS && threadIdx.x == 64) atomicExch(p.status, 5);   // taller tiles than the kernel takes
     for (int w = cluster; w < work && !*aborted; w += clusters) {
-      int tok0, tok_rows, n0;
+      int tok0, tok_rows, n0, kb0, num_kb;
       long long w_base;
-      tile_of(w, tok0, tok_rows, w_base, n0);
+      tile_of(w, tok0, tok_rows, w_base, n0, kb0, num_kb);
       if (tok_rows <= 0) continue;
       const int n_mma = (tok_rows + 15) & ~15;
       const int buf = n % S::ACC_BUFS, round = n / S::ACC_BUFS;
@@ -336,7 +344,7 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * 256;
       const int col = n0 + (int)rank * ROWS + m_row;                 // this thread's output
-      const float b = (!GATED && p.bias && col < p.N) ? p.bias[col] : 0.f;
+      const float b = (!GATED && p.bias && col < p.N && kb0 == 0) ? p.bias[col] : 0.f;
       const int j_tok = lane >> 1, c_half = (lane & 1) * 16;        // after the turn: token c0 + j_tok, 16 outputs
       const int out0 = n0 + (int)rank * ROWS + quad * 32 + c_half;
 #pragma unroll 1
@@ -379,7 +387,7 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
         }
         const int t = c0 + j_tok;
         if (t < tok_rows && out0 < p.N) {
-          TOut* dst = C + (long long)(tok0 + t) * p.ldc + out0;
+          TOut* dst = C + (kb0 / p.kb_per_split) * p.part_stride + (long long)(tok0 + t) * p.ldc + out0;
           if (out0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0) {
             if constexpr (sizeof(TOut) == 2) {
               uint4 lo, hi;
@@ -491,11 +499,14 @@ extern "C" int tl_tc_pair_resident(int gated, int per_sm) {
 // X [M, K] (row stride ldx, x_rows rows in the tensor), W [groups * rows_per_group, K] (row stride ldw). Plain: groups = 1,
 // tile_group = nullptr. gated (an activation code TL_ACT_*, or 0): W holds 2 N rows per group (gate then up) and
 // C = act(gate) * up. out_dtype: TL_BF16 or TL_FP32. Grouped: the tile map's tiles hold at most tl_tc_pair_token_tile()
-// rows (plan_rows: the height the map was built with). per_sm: 1 or 2 CTAs an SM (see Smem).
+// rows (plan_rows: the height the map was built with). per_sm: 1 or 2 CTAs an SM (see Smem). splits > 1 (plain, ungrouped,
+// 32-bit output): the reduction is cut into `splits` runs of k-blocks, each a work item of its own, and C receives the
+// runs' partial results one behind the other, [splits, M, ldc], for the caller to add in order (a product with fewer
+// tiles than the GPU has pairs of SMs: a pair streams a tile's operands at the rate of its two SMs whatever else is idle).
 extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
                                long long rows_per_group, const float* bias, void* C, long long ldc, int M, int N, int K,
                                int gated, int out_dtype, const int* tile_group, const int* tile_row0, const int* tile_rows,
-                               const int* n_tiles, int max_tiles, int plan_rows, int per_sm, int* status,
+                               const int* n_tiles, int max_tiles, int plan_rows, int per_sm, int splits, int* status,
                                cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   TL_REQUIRE(M > 0 && N > 0 && K > 0, "pair product: M %d N %d K %d", M, N, K);
@@ -508,6 +519,12 @@ extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, c
   TL_REQUIRE(!tile_group || (tile_row0 && tile_rows && n_tiles && max_tiles > 0 && plan_rows > 0),
              "pair product: incomplete tile map (tiles of %d rows)", plan_rows);
   TL_REQUIRE(per_sm == 1 || per_sm == 2, "pair product: %d CTAs an SM; 1 or 2", per_sm);
+  const int all_kb = ceil_div(K, pair::TILE_K);
+  TL_REQUIRE(splits >= 1 && splits <= all_kb, "pair product: %d runs of k-blocks; the reduction has %d k-blocks", splits, all_kb);
+  const int kb_per_split = ceil_div(all_kb, splits);
+  TL_REQUIRE(splits == 1 || (!gated && !tile_group && out_dtype == TL_FP32 && (long long)(splits - 1) * kb_per_split < all_kb),
+             "pair product: runs of k-blocks need the plain, ungrouped product with 32-bit output, and none may be empty (%d runs)",
+             splits);
   const int tokens = (gated && per_sm == 2) ? 128 : 256;
   TL_REQUIRE(!tile_group || plan_rows <= tokens, "pair product: a tile map with tiles of %d rows; at most %d", plan_rows, tokens);
   CUtensorMap tmW, tmX[3];
@@ -522,7 +539,8 @@ extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, c
   p.plan_rows = plan_rows;
   p.act = gated; p.status = status;
   p.skip_kb = pair::skip_kb_for_test();
-  const long long work = (long long)ceil_div(N, 2 * pair::ROWS) * (tile_group ? max_tiles : ceil_div(M, tokens));
+  p.splits = splits; p.kb_per_split = kb_per_split; p.part_stride = splits > 1 ? (long long)M * ldc : 0;
+  const long long work = (long long)ceil_div(N, 2 * pair::ROWS) * (tile_group ? max_tiles : ceil_div(M, tokens)) * splits;
 #define TL_PAIR(G_, P_) \
   (out_dtype == TL_BF16 ? pair::launch<G_, P_, bf16>(tmW, tmX, p, work, stream) : pair::launch<G_, P_, float>(tmW, tmX, p, work, stream))
   if (per_sm == 2) return gated ? TL_PAIR(true, 2) : TL_PAIR(false, 2);

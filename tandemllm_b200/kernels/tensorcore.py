@@ -64,7 +64,7 @@ def lib():
         l.tl_gemm_tc.restype = c_int
         l.tl_gemm_tc_pair.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p,
                                       c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                      c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+                                      c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         l.tl_gemm_tc_pair.restype = c_int
         l.tl_tc_pair_token_tile.argtypes = [c_int]
         l.tl_tc_pair_token_tile.restype = c_int
@@ -136,6 +136,7 @@ class TensorCore:
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self._workspace = None
         self._pair_order = None
+        self._pairs = None
         self._outgrown = []
 
     def workspace(self, floats: int) -> torch.Tensor:
@@ -160,6 +161,18 @@ class TensorCore:
             bn = _pow2_at_least(M) if swap else 256        # 256 without swap: the persistent kernel
         if (PROMPT_PRODUCT == "pair" and not swap and bn == 256 and splits == 1 and row_index is None
                 and (plan is None or plan.tile_m <= lib().tl_tc_pair_token_tile(1))):
+            if defer and plan is None and not swiglu and out.dtype == torch.float32:
+                # A portion of a few hundred rows has fewer tiles than the GPU has pairs of SMs, and a pair streams its
+                # tile at the rate of two SMs whatever else is idle: the reduction is cut into runs, each a work item
+                # with partial sums of its own, which the norm kernel behind adds.
+                tiles, kb = -(-N // 256) * -(-M // 256), -(-K // 64)
+                runs = min(self.pairs() // tiles, kb // 4, 8)
+                if runs > 1:
+                    runs = -(-kb // -(-kb // runs))            # no run is empty
+                    partial = self.workspace(runs * M * N)
+                    self.gemm_pair(x, w2d, bias, partial[:runs * M * N].view(runs * M, N), n_out=n_out, rows=rows,
+                                   splits=runs)
+                    return ops.PartialSums(partial, runs, M, N, None)
             self.gemm_pair(x, w2d, bias, out, rows_per_group=rows_per_group, plan=plan, gated=int(swiglu), n_out=n_out,
                            rows=rows)
             return None
@@ -191,12 +204,19 @@ class TensorCore:
             return None
         return ops.PartialSums(partial, splits, M, N, None if out.dtype == torch.float32 else out.dtype)
 
+    def pairs(self) -> int:
+        """Pairs of CTAs of the plain pair product that the GPU holds at a time, one CTA an SM."""
+        if self._pairs is None:
+            self._pairs = max(1, int(lib().tl_tc_pair_resident(0, 1)))
+        return self._pairs
+
     def gemm_pair(self, x, w2d, bias, out, *, rows_per_group=0, plan=None, gated: int = 0, n_out=None,
-                  rows: int | None = None, per_sm: int | None = None) -> None:
+                  rows: int | None = None, per_sm: int | None = None, splits: int = 1) -> None:
         """The product on pairs of SMs (csrc/tc_gemm_pair.cu): 256 outputs by up to 256 token rows a pair, the N side
         of its MMAs as many rows as a tile holds. `plan`: tiles of any height up to 256 rows. `per_sm` 2: two CTAs an
         SM, each with half the shared and tensor memory (gated: tiles of up to 128 rows), the form for products bound
-        by their weights; default: 2 for a plan with tiles of up to 128 rows, else 1."""
+        by their weights; default: 2 for a plan with tiles of up to 128 rows, else 1. `splits` > 1: `out` is
+        [splits, M, N] 32-bit and receives the partial results of as many runs of k-blocks (plain product only)."""
         M, K = (rows if rows is not None else x.shape[0]), x.shape[1]
         N = n_out if n_out is not None else w2d.shape[0]
         tg = tr0 = trs = nt = None
@@ -209,7 +229,8 @@ class TensorCore:
         _check(lib().tl_gemm_tc_pair(x.data_ptr(), x.stride(0), x.shape[0], w2d.data_ptr(), w2d.stride(0), w2d.shape[0],
                                      rows_per_group, ops.ptr(bias), out.data_ptr(), out.stride(0), M, N, K, int(gated),
                                      ops.dtype_code(out.dtype), ops.ptr(tg), ops.ptr(tr0), ops.ptr(trs), ops.ptr(nt),
-                                     max_tiles, plan_rows, per_sm, self.status.data_ptr(), ops.stream()), "gemm_tc_pair")
+                                     max_tiles, plan_rows, per_sm, splits, self.status.data_ptr(), ops.stream()),
+               "gemm_tc_pair")
 
     def gated(self, x, w_gate_up, out, act: int = 1) -> bool:
         """out = act(x gate^T) * (x up^T) for w_gate_up = [gate rows; up rows], in the persistent kernel with the gated

@@ -592,6 +592,62 @@ def test_pair_product_at_every_kind_of_tail(M, N, K):
         assert rel(outs[0], want + (0 if bias is None else bias)) < (1e-2 if out_dtype == torch.bfloat16 else 1e-4), (M, N, K)
 
 
+@pytest.mark.parametrize("M,N,K,runs", [(300, 520, 1000, 4), (512, 2048, 2048, 4), (130, 264, 136, 3), (1000, 136, 520, 2)])
+def test_pair_product_in_runs_of_k_blocks_leaves_partial_sums_that_add_up(M, N, K, runs):
+    """The reduction cut into runs, each a work item with a partial result of its own ([runs, M, N], 32-bit; the bias in
+    the first): the parts add up to the product, a last run shorter than the others and a k that ends a block early
+    included; the same bits twice; a run count that would leave a run empty is refused. Through `linear` with `defer`, a
+    portion of a few hundred rows comes back as such partial sums and its norm adds them."""
+    impl, rt = tc()
+    x, w = rnd(M, K, seed=71), rnd(N, K, seed=72, scale=0.1)
+    b = torch.randn(N, generator=torch.Generator().manual_seed(73))
+    want = x.float() @ w.float().T + b
+    outs = []
+    for _ in range(2):
+        out = torch.full((runs, M, N), float("nan"), dtype=torch.float32, device=DEV)
+        impl.gemm_pair(x.to(DEV), w.to(DEV), b.to(DEV), out.view(runs * M, N), rows=M, splits=runs)
+        torch.cuda.synchronize()
+        assert int(rt.status) == 0
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    total = torch.zeros(M, N, device=DEV)
+    for part in outs[0]:
+        total += part
+    assert rel(total, want) < 1e-4, (M, N, K, runs)
+    kb = -(-K // 64)
+    if kb >= 3:
+        empty = kb - 1 if -(-kb // (kb - 1)) * (kb - 2) >= kb else None       # ceil(kb / runs) * (runs - 1) >= kb: a run is empty
+        if empty:
+            with pytest.raises(RuntimeError, match="none may be empty"):
+                impl.gemm_pair(x.to(DEV), w.to(DEV), None, torch.empty(empty * M, N, device=DEV), rows=M, splits=empty)
+    with pytest.raises(RuntimeError, match="runs of k-blocks need"):
+        impl.gemm_pair(x.to(DEV), w.to(DEV), None, torch.empty(runs * M, N, dtype=torch.bfloat16, device=DEV), rows=M, splits=runs)
+
+
+def test_a_deferred_prompt_product_with_few_tiles_comes_back_in_parts_and_the_norm_adds_them():
+    from tandemllm_b200.kernels import ops
+    impl, rt = tc()
+    M, N, K = 512, 2048, 2048
+    x, w = rnd(M, K, seed=74).to(DEV), rnd(N, K, seed=75, scale=0.05).to(DEV)
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    got = impl.linear(x, w, None, out, defer=True)
+    assert isinstance(got, ops.PartialSums) and got.parts > 1
+    whole = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    impl.gemm_pair(x, w, None, whole)
+    torch.cuda.synchronize()
+    assert int(rt.status) == 0
+    assert rel(got.materialize(), whole.cpu()) < 1e-5
+    # the norm kernel adds the parts itself: the same residual and normed rows as from the materialised sum
+    res_a = rnd(M, N, seed=76).float().to(DEV)
+    res_b = res_a.clone()
+    weight = torch.ones(N, device=DEV)
+    na = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    nb = torch.empty_like(na)
+    ops.add_rmsnorm(res_a, got, weight, 1e-5, na)
+    ops.add_rmsnorm(res_b, got.materialize(), weight, 1e-5, nb)
+    assert rel(res_a, res_b.cpu()) < 1e-6 and rel(na, nb.float().cpu()) < 1e-2
+
+
 def test_pair_product_into_a_wider_output_with_strided_token_rows():
     impl, rt = tc()
     M, N, K = 130, 264, 136
