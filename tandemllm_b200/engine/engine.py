@@ -371,10 +371,11 @@ class Engine:
             try:
                 for rid in ids:
                     self.admit(rid)
-                # a prompt's portion beside nothing, then a single token of each of the others: every request holds a key
+                # a prompt's portion beside nothing, then two tokens of each of the others (a step of portions, which is
+                # not captured): every request holds keys
                 self.step([StepEntry(ids[0], [0] * max(1, portion), [max(1, portion) - 1])])
                 if most > 1:
-                    self.step([StepEntry(rid, [0], [0]) for rid in ids[1:]])
+                    self.step([StepEntry(rid, [0, 0], [1]) for rid in ids[1:]])
                 for b in sorted(set(batch_sizes)):
                     for _ in range(2):                 # the first is eager and captured behind it, the second a replay
                         self.step([StepEntry(rid, [0], [0]) for rid in ids[:b]])
