@@ -548,8 +548,12 @@ p.expert_parts = expert_parts < 1 ? 1 : expert_parts; p.expert_part_stride = exp
   // A decode step's router: one block a row would pull all of the router's weights through one SM (256 KB for 32
   // experts of 2048: a third of the kernel's time). A cluster of CTAs a row shares them out; every CTA of the cluster
   // puts the row together for itself, which a step of many rows no longer pays (measured: 2.415 -> 2.374 ms a step at
-  // batch 8, 773 -> 797 tok/s at batch 1, but 13.2 k -> 12.5 k tok/s at batch 64).
-  p.split = (rows_per_block == 1 && out_rows <= ROUTER_SPLIT_ROWS && router_w && E >= 16 && (hidden & 3) == 0) ? ROUTER_SPLIT : 1;
+  // batch 8, 773 -> 797 tok/s at batch 1, but 13.2 k -> 12.5 k tok/s at batch 64). Above 16 rows the cluster shrinks so
+  // that all CTAs still run at once, one an SM (37 rows x 4, 74 rows x 2: 8119 -> 8246 tok/s at batch 32, 13.2 k -> 13.5 k
+  // at batch 64).
+  p.split = 1;
+  if (rows_per_block == 1 && router_w && E >= 16 && (hidden & 3) == 0)
+    p.split = out_rows <= ROUTER_SPLIT_ROWS ? ROUTER_SPLIT : (out_rows <= 37 ? 4 : (out_rows <= 74 ? 2 : 1));
   const dim3 grid(ceil_div(out_rows, rows_per_block) * p.split);
   const int per = !router_w ? 0 : (E <= 32 ? 1 : (E <= 128 ? 4 : MAX_EXPERTS / 32));
 #define TL_NORM1(T_, PER_, ONE_)                                                                                          \
