@@ -143,6 +143,10 @@ def test_the_router_inside_the_norm_routes_a_row_the_same_alone_and_among_many(d
     tiny = [run(lo, lo + n) for lo, n in ((0, 11), (11, 1), (12, 16), (28, 5))]
     for j in range(3):
         assert torch.equal(torch.cat([t[j] for t in tiny]), alone[j][:33]), ("a few rows", j)
+    # 17 to 37 rows: clusters of four; up to 74 (the runs of 50 above): of two; more, one row a block still: one CTA a row
+    mid = [run(0, 30), run(30, 130)]
+    for j in range(3):
+        assert torch.equal(torch.cat([t[j] for t in mid]), alone[j][:130]), ("clusters of four, one CTA a row", j)
     n32 = P.rms_norm(res0, w, 1e-5)
     cfg = dict(num_experts_per_tok=k, use_expert_bias=True, norm_topk_prob=True, routed_scaling_factor=1.0)
     want_ids, want_w = P.route(n32, {"gate.weight": gate, "expert_bias": bias}, "", cfg)
