@@ -33,6 +33,7 @@ namespace tl {
 
 constexpr int TC_KT = 128;        // keys per tile
 constexpr int TC_M = 128;         // M rows per tile
+constexpr float TC_SLACK = 8.f;   // in units of log 2: how far a row's maximum may rise above its reference before O is rescaled
 constexpr int TC_THREADS = 192;
 
 // K-major operand tile with 128-byte rows and 128-byte swizzle (Q, K and P): 8-row groups 1024 bytes apart.
@@ -397,7 +398,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2) attention_tc_kernel(
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx = mx == -INFINITY ? mx : mx * scale2;
-      const float m_new = fmaxf(m_run, mx);
+      float m_new = fmaxf(m_run, mx);
+      // A maximum that rose by little keeps the old reference: p then reaches 2^TC_SLACK at most, which bfloat16 and the
+      // 32-bit sums hold as well as values below 1, and neither O nor the sum needs rescaling for this tile.
+      if (m_run != -INFINITY && m_new - m_run <= TC_SLACK) m_new = m_run;
       // a row that has seen no key yet keeps 0 as its reference, so that exp2(-inf - reference) is 0, not NaN
       const float ref = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = tc_exp2(m_run - ref);             // 0 where the row had no key before
