@@ -28,8 +28,8 @@ def _engine_options(p: argparse.ArgumentParser) -> None:
     p.add_argument("--parallel", type=int, default=8, help="requests running at once")
     p.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     p.add_argument("--kv-blocks", type=int, help="cache pages (default: enough for --parallel requests of --max-len)")
-    p.add_argument("--max-batched-tokens", type=int, default=2048, help="token budget of one step")
-    p.add_argument("--chunk-size", type=int, default=512, help="longest prompt portion in one step")
+    p.add_argument("--max-batched-tokens", type=int, default=4096, help="token budget of one step")
+    p.add_argument("--chunk-size", type=int, default=2048, help="longest prompt portion in one step")
     p.add_argument("--graph", default="on", choices=("on", "off"), help="CUDA graphs for decode-only steps")
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--warm-up", action="store_true",
