@@ -123,8 +123,15 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_mma_kernel(
 // it multiplies by the expert's gate rows and up rows of those outputs and stores silu(gate) * up. Token rows are
 // fetched through `row_index` (position i of the plan stands for row row_index[i] / row_div of x) or, without it, lie
 // in the plan's order. Tiles past *n_tiles exit at once. Without a plan (`pair_group`: the group of each of n_pairs <= 256
-// pairs, tile_* null) tile p is pair p, out row p, x row p / row_div: the CTAs find each group's pairs themselves. A few experts' weights are all such a step reads: many small
+// pairs, tile_* null) out row p is pair p, x row p / row_div, and the CTAs find each group's pairs themselves: up to 32 pairs,
+// tile j is the j-th group to appear; more, tile p is pair p and the CTA of a group's first pair takes the group. A few experts' weights are all such a step reads: many small
 // CTAs that start at once stream them faster than the few 128-row CTAs of the tcgen05 product.
+// the position of the n-th (from 0) set bit of m, which has more than n bits set
+__device__ __forceinline__ int nth_set_bit(uint32_t m, int n) {
+  for (int i = 0; i < n; ++i) m &= m - 1;
+  return __ffs(m) - 1;
+}
+
 template <bool SWIGLU, typename TOut>
 __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
     const bf16* __restrict__ x, long long ldx, const int* __restrict__ row_index, int row_div, const bf16* __restrict__ w,
@@ -142,8 +149,23 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
   const int tile = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  int rows, group;
-  if (pair_group) {
+  int rows, group, pos_known = -1;
+  if (pair_group && n_pairs <= 32) {
+    // No plan, and the pairs fit a warp: tile j is the j-th group in the order in which the groups first appear among
+    // the pairs, so the CTAs that have work are the first of the grid and start together, and those behind them leave.
+    // Every warp works this out for itself from the same 32 ids: no shared memory, no barrier in front of the loads.
+    const int mine = lane < n_pairs ? pair_group[lane] : -1;
+    const bool ok = mine >= 0 && mine < n_groups;
+    const uint32_t same = __match_any_sync(0xffffffffu, ok ? mine : -1);      // (pairs without a group match each other only)
+    const uint32_t firsts = __ballot_sync(0xffffffffu, ok && lane == __ffs(same) - 1);
+    if (tile >= __popc(firsts)) return;
+    const int leader = nth_set_bit(firsts, tile);
+    group = __shfl_sync(0xffffffffu, mine, leader);
+    const uint32_t members = __shfl_sync(0xffffffffu, same, leader);
+    rows = __popc(members);
+    pos_known = nth_set_bit(members, g < rows ? g : 0);
+    if (threadIdx.x < 8) s_pair[threadIdx.x] = nth_set_bit(members, (int)threadIdx.x < rows ? (int)threadIdx.x : 0);
+  } else if (pair_group) {
     // No plan: tile p stands for pair p. The CTA of the first pair of a group takes all of the group's pairs (they are
     // at most as many as the step has rows), the CTAs of the group's later pairs have nothing to do.
     group = pair_group[tile];
@@ -190,7 +212,7 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
     w_hi[j] = w + (first + (v_hi ? g + 8 : 0)) * ldw + t * 8;
   }
   const bool x_ok = g < rows;
-  const int pos = s_pair[x_ok ? g : 0];
+  const int pos = pos_known >= 0 ? pos_known : s_pair[x_ok ? g : 0];
   const bf16* x_row = x + (long long)(row_index ? row_index[pos] / row_div : pos / row_div) * ldx + t * 8;
   float acc[W_TILES][4];
 #pragma unroll

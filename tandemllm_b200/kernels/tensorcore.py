@@ -42,7 +42,7 @@ SKINNY_BYTES = 64 << 20         # ... against at most this many bytes of weights
 SKINNY_ROWS = 16                # rows of a step up to which the experts go to its grouped form, over plan tiles of 8 (an
                                 # expert with more pairs has two tiles, and the second reads its weights from L2); measured
                                 # against the tcgen05 form: 8 % faster a step at 16 rows, even at 24, 4 % slower at 32
-SKINNY_PAIRS = 16               # routed pairs of such a step up to which its products run without a routing plan
+SKINNY_PAIRS = 24               # routed pairs of such a step up to which its products run without a routing plan
 PROMPT_ATTENTION = "tcgen05"    # prompt portions of head size 64: the tcgen05 kernel (csrc/attention_tc.cu), or "mma" for the
                                 # mma.sync kernel that also takes them (kept for head size 128 and for comparison)
 # prompt-sized products on pairs of SMs (csrc/tc_gemm_pair.cu), or "single": the one-CTA persistent kernel of
@@ -300,8 +300,10 @@ class TensorCore:
             # No plan: the products' CTAs find each expert's pairs in the ids themselves, rows stay in pair order (a CTA
             # takes all of an expert's pairs, at most 8 rows: a row chooses an expert once, so up to 8 rows of a step). A
             # pair whose expert an earlier pair has costs CTAs that start, look and leave in between the working ones.
-            # Measured a step of 22 expert layers, top-4 of 32 experts: 97 us gained with 4 pairs, 82 with 8, 33 with 16;
-            # 26 lost with 24, 74 with 32 (and 45 lost with 32 pairs over 64 experts).
+            # Measured a step of 22 expert layers, top-4 of 32 experts, against the plan: 97 us gained with 4 pairs, 82 with
+            # 8, 33 with 16; 26 lost with 24, 74 with 32 while a CTA a pair looked for its group's earlier pairs. Now that
+            # the CTAs with work are the grid's first (up to 32 pairs, see the kernel): 832 -> 881 tok/s at batch 1, even
+            # at 16 pairs, 2854 -> 2869 tok/s at 24 pairs, 3434 -> 3388 at 32.
             where = (None, None, None, None, 0, ids.data_ptr(), P, E)
             gate_up_rows, pos, div = None, self.pair_order(), k
         else:
