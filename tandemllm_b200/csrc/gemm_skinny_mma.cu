@@ -190,11 +190,13 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
     rows = total;
     __syncthreads();
   } else {
+    // (every thread reads the tile's three words itself: no barrier stands between them and the loads that follow)
     if (tile >= *n_tiles) return;
     rows = tile_rows[tile];
     group = tile_group[tile];
-    if (threadIdx.x < 8) s_pair[threadIdx.x] = tile_row0[tile] + threadIdx.x;
-    __syncthreads();
+    const int row0 = tile_row0[tile];
+    pos_known = row0 + (g < rows ? g : 0);
+    if (threadIdx.x < 8) s_pair[threadIdx.x] = row0 + threadIdx.x;
   }
   if (rows > 8) {                                      // taller tiles than this kernel takes
     if (threadIdx.x == 0) atomicExch(status, 5);
