@@ -271,11 +271,18 @@ __global__ void __launch_bounds__(128) attention_span_kernel(
   }
 }
 
-// grid (rows, Hq): joins the spans of a row in ascending order
+// grid (rows, Hq), JOIN_Q x DT threads: joins the spans of a row. A decode step at a long context has dozens of spans a
+// row and this kernel is a link in the step's chain, so it is laid out for few trips to memory: every warp finds the
+// largest of the spans' maxima with a span a lane (one trip for up to 32 spans), thread (q, d) adds the spans s with
+// s % JOIN_Q == q for dimension d in ascending order, eight loads in flight, and the JOIN_Q partial sums are added in
+// the order of q. The order depends on the row's position and window alone, never on what else the step holds.
+constexpr int JOIN_Q = 4;
 template <typename T>
 __global__ void attention_join_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       const int* __restrict__ positions, int window, T* __restrict__ out, int Hq, int D,
                                       int n_spans, int span_keys) {
+  __shared__ float s_o[JOIN_Q][MAX_D];
+  __shared__ float s_sum[JOIN_Q];
   chain_next();
   chain_wait();
   const int r = blockIdx.x, h = blockIdx.y;
@@ -284,39 +291,50 @@ __global__ void attention_join_kernel(const float* __restrict__ part_o, const fl
   const int s0 = lo / span_keys, s1 = min(pos / span_keys, n_spans - 1);      // never past the scratch's last span
   if (s0 >= s1) return;                                 // one span: written directly by the span kernel
   const long long base = ((long long)r * Hq + h) * n_spans;
-  // Spans are taken eight at a time, with all of a group's loads issued before the first is used: taken one by one,
-  // every span would cost a trip to memory of its own.
-  constexpr int GROUP = 8;
   const float2* ml2 = reinterpret_cast<const float2*>(part_ml);      // (max, sum) pairs
+  const int lane = threadIdx.x & 31;
+  const int DT = blockDim.x / JOIN_Q, q = threadIdx.x / DT, dd = threadIdx.x - q * DT;
   float m = -INFINITY;
-  for (int g0 = s0; g0 <= s1; g0 += GROUP) {
-    float v[GROUP];
+  for (int s = s0 + lane; s <= s1; s += 32) m = fmaxf(m, ml2[base + s].x);
 #pragma unroll
-    for (int i = 0; i < GROUP; ++i) v[i] = g0 + i <= s1 ? ml2[base + g0 + i].x : -INFINITY;
-#pragma unroll
-    for (int i = 0; i < GROUP; ++i) m = fmaxf(m, v[i]);
-  }
-  float denom = 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  constexpr int GROUP = 8;
+  const int first = s0 + ((q - s0 % JOIN_Q) + JOIN_Q) % JOIN_Q;      // the first span >= s0 with s % JOIN_Q == q
+  for (int d0 = 0; d0 < D; d0 += DT) {
+    const int d = d0 + dd;
     float o = 0.f, sum = 0.f;
-    for (int g0 = s0; g0 <= s1; g0 += GROUP) {
-      float2 w[GROUP];
-      float x[GROUP];
+    if (d < D) {
+      for (int g0 = first; g0 <= s1; g0 += GROUP * JOIN_Q) {
+        float2 w[GROUP];
+        float x[GROUP];
 #pragma unroll
-      for (int i = 0; i < GROUP; ++i) {
-        const bool in = g0 + i <= s1;
-        w[i] = in ? ml2[base + g0 + i] : make_float2(-INFINITY, 0.f);
-        x[i] = in ? part_o[(base + g0 + i) * D + d] : 0.f;
-      }
+        for (int i = 0; i < GROUP; ++i) {
+          const int sp = g0 + i * JOIN_Q;
+          const bool in = sp <= s1;
+          w[i] = in ? ml2[base + sp] : make_float2(-INFINITY, 0.f);
+          x[i] = in ? part_o[(base + sp) * D + d] : 0.f;
+        }
 #pragma unroll
-      for (int i = 0; i < GROUP; ++i) {
-        const float f = w[i].x == -INFINITY ? 0.f : expf(w[i].x - m);       // spans in ascending order
-        sum += f * w[i].y;
-        o += f * x[i];
+        for (int i = 0; i < GROUP; ++i) {
+          const float f = w[i].x == -INFINITY ? 0.f : expf(w[i].x - m);
+          sum += f * w[i].y;
+          o += f * x[i];
+        }
       }
+      s_o[q][d] = o;
     }
-    denom = sum;
-    out[((long long)r * Hq + h) * D + d] = from_f32<T>(denom > 0.f ? o / denom : 0.f);
+    if (dd == 0 && d0 == 0) s_sum[q] = sum;
+    __syncthreads();
+    if (q == 0 && d < D) {
+      float denom = 0.f, total = 0.f;
+#pragma unroll
+      for (int i = 0; i < JOIN_Q; ++i) {
+        denom += s_sum[i];
+        total += s_o[i][d];
+      }
+      out[((long long)r * Hq + h) * D + d] = from_f32<T>(denom > 0.f ? total / denom : 0.f);
+    }
+    __syncthreads();
   }
 }
 
@@ -346,7 +364,7 @@ static int launch_spans(const void* q, const void* k_cache, const void* v_cache,
   if (e != cudaSuccess) return (int)e;
   if (n_spans > 1) {
     dim3 join(rows, Hq);
-    attention_join_kernel<T><<<join, D <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, positions, window, (T*)out, Hq, D,
+    attention_join_kernel<T><<<join, JOIN_Q * (D <= 64 ? 64 : 128), 0, stream>>>(part_o, part_ml, positions, window, (T*)out, Hq, D,
                                                                     n_spans, SPAN);
     e = cudaGetLastError();
   }
@@ -398,10 +416,10 @@ extern "C" int tl_attention_join(const float* scratch, const int* positions, int
   dim3 join(rows, Hq);
   cudaError_t e;
   if (dtype == TL_FP32)
-    e = launch_chained(attention_join_kernel<float>, join, dim3(D <= 64 ? 64 : 128), 0, stream, part_o, part_ml, positions,
+    e = launch_chained(attention_join_kernel<float>, join, dim3(JOIN_Q * (D <= 64 ? 64 : 128)), 0, stream, part_o, part_ml, positions,
                        window, (float*)out, Hq, D, n_spans, span_keys);
   else
-    e = launch_chained(attention_join_kernel<bf16>, join, dim3(D <= 64 ? 64 : 128), 0, stream, part_o, part_ml, positions,
+    e = launch_chained(attention_join_kernel<bf16>, join, dim3(JOIN_Q * (D <= 64 ? 64 : 128)), 0, stream, part_o, part_ml, positions,
                        window, (bf16*)out, Hq, D, n_spans, span_keys);
   return (int)e;
 }
