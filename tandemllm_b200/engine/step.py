@@ -91,7 +91,7 @@ class _DecodeGraph:
 
     def __init__(self, dev: torch.Tensor, step: StepContext):
         self.dev, self.step = dev, step
-        self.graph: torch.cuda.CUDAGraph | None = None
+        self.graph: ops.DeviceGraph | None = None
         self.kernels = 0
         self.logits: torch.Tensor | None = None
 
@@ -305,13 +305,13 @@ class StepFunction:
             # pool with it; a caller that still holds them from an earlier step has had them read (the stream is idle).
             self._graphs.popitem(last=False)
             self.graphs_dropped += 1
-        # one memory pool for all the graphs, as long as one of them lives (a pool whose graphs are all gone may not be
-        # captured into again)
-        if self._graph_pool is None or not any(g.graph is not None for g in self._graphs.values()):
-            self._graph_pool = torch.cuda.graph_pool_handle()
-        graph = torch.cuda.CUDAGraph()
+        # One memory pool for all the graphs of this step function: what a graph's kernels write between them lives there,
+        # and a dropped graph's memory is used again by the next capture.
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.MemPool()
+        graph = ops.DeviceGraph()
         before = ops.launches
-        # Captured on a stream of its own between capture_begin and capture_end. (`torch.cuda.graph(...)` would also run
+        # Captured on a stream of its own, on the runtime API (`ops.DeviceGraph`; `torch.cuda.graph(...)` would also run
         # the garbage collector and hand every cached block back to the driver first: hundreds of milliseconds here, and
         # the steps after it pay for the blocks again. The stream is idle and the shapes were sized by the eager run.)
         if self._capture_stream is None:

@@ -35,7 +35,7 @@ NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 LIBRARIES: dict[str, list[str]] = {
     # every kernel of the 32-bit path, and the plain bfloat16 variants of the same kernels
     "core": ["rows.cu", "gemm_simt.cu", "conv.cu", "attention_simt.cu", "attention_split.cu", "moe_route.cu",
-             "sampling.cu"],
+             "sampling.cu", "graphs.cu"],
     # the tcgen05 / TMA kernels of the bfloat16 path; a 32-bit run never builds or loads them
     "tensorcore": ["tc_gemm.cu", "tc_gemm_pair.cu", "attention_mma.cu", "attention_tc.cu", "gemm_skinny_mma.cu"],
 }

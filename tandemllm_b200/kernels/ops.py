@@ -84,6 +84,10 @@ _SIGNATURES = {
                     c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
+    "tl_graph_capture_begin": [c_void_p],
+    "tl_graph_capture_end": [c_void_p, c_void_p, c_void_p],
+    "tl_graph_launch": [c_void_p, c_void_p],
+    "tl_graph_destroy": [c_void_p],
     "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_void_p, c_void_p],
     "tl_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
@@ -443,6 +447,50 @@ def moe_combine(y, plan: MoePlan, ids, wts, out) -> torch.Tensor:
     check(core().tl_moe_combine(ptr(y), ptr(plan.pos_of_pair), ptr(ids), ptr(wts), ptr(out), rows, hidden, ids.shape[1],
                                 stream()), "moe_combine")
     return out
+
+
+# ------------------------------------------------------------------------------------------ CUDA graphs
+class DeviceGraph:
+    """A captured CUDA graph on the runtime API (csrc/graphs.cu says why not `torch.cuda.CUDAGraph`). Between
+    `capture_begin` and `capture_end` the current stream captures and this thread's allocations come from `pool` (a
+    `torch.cuda.MemPool` that the caller keeps as long as any graph captured into it may be replayed): what a captured
+    kernel writes stays where it is until the tensor that holds it is dropped, and the memory of tensors dropped since is
+    used again by later captures into the same pool, whose graphs therefore must not be replayed side by side."""
+
+    def __init__(self):
+        self._exec = ctypes.c_void_p(None)
+        self._pool_context = None
+        self._stream = None
+        self.nodes = 0
+
+    def capture_begin(self, pool) -> None:
+        self._stream = stream()
+        self._pool_context = torch.cuda.use_mem_pool(pool)
+        self._pool_context.__enter__()
+        try:
+            check(core().tl_graph_capture_begin(self._stream), "graph capture", kernels=0)
+        except BaseException:
+            self._pool_context.__exit__(None, None, None)
+            self._pool_context = None
+            raise
+
+    def capture_end(self) -> None:
+        nodes = ctypes.c_int(0)
+        try:
+            code = core().tl_graph_capture_end(self._stream, ctypes.byref(self._exec), ctypes.byref(nodes))
+        finally:
+            self._pool_context.__exit__(None, None, None)
+            self._pool_context = None
+        check(code, "graph capture", kernels=0)
+        self.nodes = nodes.value
+
+    def replay(self) -> None:
+        check(core().tl_graph_launch(self._exec, stream()), "graph launch", kernels=0)
+
+    def __del__(self):
+        ex, self._exec = self._exec, ctypes.c_void_p(None)
+        if ex and _core is not None:
+            _core.tl_graph_destroy(ex)
 
 
 # ------------------------------------------------------------------------------------------ sampling
