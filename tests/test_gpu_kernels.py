@@ -186,6 +186,59 @@ def test_plan_forms_agree_and_copy_rows(P_rows, E, k):
         assert torch.equal(xs.cpu(), x.cpu()[order // k])
 
 
+def test_a_device_graph_replays_what_was_captured_from_a_pool_of_its_own():
+    """`ops.DeviceGraph` (runtime-API capture with torch's allocator pointed at a memory pool): tensors made during the
+    capture keep their memory, a replay runs the captured kernels on whatever the inputs hold by then, a second graph
+    captured into the same pool reuses the memory of tensors dropped since, and a failed capture leaves the stream usable."""
+    o = ops()
+    pool = torch.cuda.MemPool()
+    side = torch.cuda.Stream()
+    res = rnd(4, 256, seed=31).to(DEV)
+    w = (1 + rnd(256, seed=32, scale=0.1)).to(DEV)
+    delta = rnd(4, 256, seed=33).to(DEV)
+    torch.cuda.synchronize()
+
+    def capture(body):
+        g = o.DeviceGraph()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g.capture_begin(pool)
+            try:
+                out = body()
+            finally:
+                g.capture_end()
+        torch.cuda.current_stream().wait_stream(side)
+        return g, out
+
+    def body():
+        work = res.clone()                              # allocated from the pool, written by a captured kernel
+        normed = torch.empty(4, 256, dtype=torch.float32, device=DEV)
+        o.add_rmsnorm(work, delta, w, 1e-5, normed)
+        return normed
+
+    reserved = torch.cuda.memory_reserved()
+    g1, out1 = capture(body)
+    assert g1.nodes >= 2
+    for turn in range(2):
+        delta.fill_(float(turn))
+        g1.replay()
+        torch.cuda.synchronize()
+        want = P.rms_norm(res.cpu() + turn, w.cpu(), 1e-5)
+        close(out1.cpu(), want, torch.float32, f"replay {turn}")
+    grown = torch.cuda.memory_reserved()
+    del g1, out1
+    g2, out2 = capture(body)
+    assert torch.cuda.memory_reserved() == grown >= reserved, "the dropped graph's memory is used again"
+    g2.replay()
+    torch.cuda.synchronize()
+    close(out2.cpu(), P.rms_norm(res.cpu() + 1, w.cpu(), 1e-5), torch.float32, "second graph")
+    with pytest.raises(ZeroDivisionError):
+        capture(lambda: 1 // 0)
+    assert not torch.cuda.is_current_stream_capturing()
+    g2.replay()
+    torch.cuda.synchronize()
+
+
 def test_embed_records_a_bad_token_instead_of_faulting():
     o = ops()
     table = rnd(10, 32).to(DEV)
