@@ -208,6 +208,81 @@ __global__ void __launch_bounds__(128) moe_plan_small_kernel(const int* __restri
   }
 }
 
+// The same plan for at most WARP_PLAN_PAIRS pairs (a decode step of a few rows) by one warp, a pair or two a lane: no
+// shared memory and no barrier, because this kernel is a link in the chain of a step whose kernels each take a few
+// microseconds. A lane finds its pairs' places by looking at every lane's experts; then the experts are taken 32 at a
+// time, an expert a lane, counted the same way and summed up over the lanes for the offsets and the tiles.
+constexpr int WARP_PLAN_PAIRS = 64;
+__global__ void __launch_bounds__(32) moe_plan_warp_kernel(const int* __restrict__ ids, int P, int E, int tile_m,
+                                                           int* __restrict__ counts, int* __restrict__ offsets,
+                                                           int* __restrict__ sorted_pairs, int* __restrict__ pos_of_pair,
+                                                           int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                                                           int* __restrict__ tile_rows, int* __restrict__ n_tiles) {
+  chain_next();
+  chain_wait();
+  const int lane = threadIdx.x;
+  constexpr int PER = WARP_PLAN_PAIRS / 32;             // pair lane + 32 q is this lane's q-th
+  int e[PER], at[PER];
+#pragma unroll
+  for (int q = 0; q < PER; ++q) {
+    e[q] = lane + 32 * q < P ? ids[lane + 32 * q] : 0x7fffffff;
+    at[q] = 0;
+  }
+#pragma unroll
+  for (int qj = 0; qj < PER; ++qj) {
+    const int n = min(32, P - 32 * qj);
+    for (int j = 0; j < n; ++j) {
+      const int ej = __shfl_sync(0xffffffffu, e[qj], j), pj = j + 32 * qj;
+#pragma unroll
+      for (int q = 0; q < PER; ++q) at[q] += (ej < e[q]) || (ej == e[q] && pj < lane + 32 * q);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < PER; ++q)
+    if (lane + 32 * q < P) {
+      sorted_pairs[at[q]] = lane + 32 * q;
+      pos_of_pair[lane + 32 * q] = at[q];
+    }
+  int off_before = 0, tiles_before = 0;                 // over the experts of the groups of 32 already done
+  for (int e0 = 0; e0 < E; e0 += 32) {
+    const int ex = e0 + lane;
+    int cnt = 0;
+#pragma unroll
+    for (int qj = 0; qj < PER; ++qj) {
+      const int n = min(32, P - 32 * qj);
+      for (int j = 0; j < n; ++j) cnt += __shfl_sync(0xffffffffu, e[qj], j) == ex;
+    }
+    const int tl = (cnt + tile_m - 1) / tile_m;
+    int off = cnt, tiles = tl;                          // inclusive sums over the lanes
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int a = __shfl_up_sync(0xffffffffu, off, o), b = __shfl_up_sync(0xffffffffu, tiles, o);
+      if (lane >= o) {
+        off += a;
+        tiles += b;
+      }
+    }
+    const int off_all = __shfl_sync(0xffffffffu, off, 31), tiles_all = __shfl_sync(0xffffffffu, tiles, 31);
+    off += off_before - cnt;                            // exclusive, over all experts before this one
+    tiles += tiles_before - tl;
+    if (ex < E) {
+      counts[ex] = cnt;
+      offsets[ex] = off;
+      for (int t = 0; t < tl; ++t) {
+        tile_group[tiles + t] = ex;
+        tile_row0[tiles + t] = off + t * tile_m;
+        tile_rows[tiles + t] = min(tile_m, cnt - t * tile_m);
+      }
+    }
+    off_before += off_all;
+    tiles_before += tiles_all;
+  }
+  if (lane == 0) {
+    offsets[E] = off_before;
+    *n_tiles = tiles_before;
+  }
+}
+
 // one block per row: out[r, :] = sum over the row's slots in ascending expert id of wts * y[pos_of_pair]  (32-bit)
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair,
                                                           const int* __restrict__ ids, const float* __restrict__ wts,
@@ -278,6 +353,13 @@ extern "C" int tl_moe_plan(const int* ids, int pairs, int E, int tile_m, int top
   TL_REQUIRE(!x || (width % 8 == 0 && ldx % 8 == 0 && x_sorted), "moe plan: row copy of width %d, stride %lld", width, ldx);
   if (launched) *launched = 0;
   if (pairs == 0) return 0;
+  if (pairs <= WARP_PLAN_PAIRS && !x && E <= MAX_EXPERTS) {
+    cudaError_t e = launch_chained(moe_plan_warp_kernel, dim3(1), dim3(32), 0, stream, ids, pairs, E, tile_m, counts, offsets,
+                                   sorted_pairs, pos_of_pair, tile_group, tile_row0, tile_rows, n_tiles);
+    if (e != cudaSuccess) return (int)e;
+    if (launched) *launched = 1;
+    return 0;
+  }
   if (pairs <= SMALL_PLAN_PAIRS && E <= MAX_EXPERTS) {
     cudaError_t e = launch_chained(moe_plan_small_kernel, dim3(pairs), dim3(128), 0, stream, ids, pairs, E, tile_m, top_k,
                                    counts, offsets, sorted_pairs, pos_of_pair, tile_group, tile_row0, tile_rows, n_tiles,

@@ -239,6 +239,33 @@ def test_a_device_graph_replays_what_was_captured_from_a_pool_of_its_own():
     torch.cuda.synchronize()
 
 
+@pytest.mark.parametrize("R,E,k,tile", [(8, 32, 4, 8), (5, 64, 4, 8), (1, 32, 4, 8), (3, 200, 5, 8), (8, 12, 4, 2), (2, 1000, 16, 8),
+                                        (16, 7, 2, 3), (1, 1, 1, 8), (16, 32, 4, 8), (11, 64, 4, 8), (9, 300, 7, 8), (33, 5, 1, 4)])
+def test_the_one_warp_plan_of_a_small_step_equals_the_others(R, E, k, tile):
+    """Up to 64 pairs and no rows to copy: one warp builds the plan, a pair or two a lane, the experts 32 at a time. Field by
+    field what the one-kernel form writes for the same ids, and a stable sort by expert."""
+    o = ops()
+    g = torch.Generator().manual_seed(14)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(R)]).int().to(DEV)
+    P = R * k
+    assert P <= 64
+    warp = o.MoePlan(P, E, tile, DEV)
+    for t in (warp.counts, warp.offsets, warp.sorted_pairs, warp.pos_of_pair, warp.tile_group, warp.tile_row0, warp.tile_rows, warp.n_tiles):
+        t.fill_(-3)
+    warp.build(ids)
+    x = rnd(R, 64, seed=15).to(torch.bfloat16).to(DEV)
+    other = o.MoePlan(P, E, tile, DEV).build(ids, x, torch.zeros(P, 64, dtype=torch.bfloat16, device=DEV))
+    assert other.copied and not warp.copied
+    flat = ids.cpu().reshape(-1).long()
+    assert torch.equal(warp.sorted_pairs[:P].cpu().long(), torch.sort(flat, stable=True).indices)
+    nt = int(other.n_tiles)
+    assert int(warp.n_tiles) == nt == sum(-(-int(c) // tile) for c in torch.bincount(flat, minlength=E))
+    assert torch.equal(warp.counts, other.counts) and torch.equal(warp.offsets, other.offsets)
+    assert torch.equal(warp.sorted_pairs[:P], other.sorted_pairs[:P]) and torch.equal(warp.pos_of_pair[:P], other.pos_of_pair[:P])
+    for a, b in ((warp.tile_group, other.tile_group), (warp.tile_row0, other.tile_row0), (warp.tile_rows, other.tile_rows)):
+        assert torch.equal(a[:nt], b[:nt])
+
+
 def test_embed_records_a_bad_token_instead_of_faulting():
     o = ops()
     table = rnd(10, 32).to(DEV)
