@@ -71,7 +71,8 @@ def cmd_generate(a) -> int:
     params = SamplingParams(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, min_p=a.min_p, seed=a.seed,
                             max_tokens=a.tokens, ignore_eos=a.ignore_eos, repetition_penalty=a.rep_penalty,
                             presence_penalty=a.presence_penalty, frequency_penalty=a.frequency_penalty,
-                            logit_bias=_logit_bias(a.logit_bias))
+                            logit_bias=_logit_bias(a.logit_bias), no_repeat_ngram_size=a.no_repeat_ngram_size,
+                            max_pattern_size=a.max_pattern_size, min_pattern_size=a.min_pattern_size, min_count=a.min_count)
     warm = engine.warm_up() if a.warm_up else None
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -160,6 +161,12 @@ def main(argv=None) -> int:
     g.add_argument("--frequency-penalty", type=float, default=0.0,
                    help="subtracted from the logit of a seen token, times the number of times it was seen")
     g.add_argument("--logit-bias", action="append", metavar="TOKEN:VALUE", help="added to this token's logit (repeatable)")
+    g.add_argument("--no-repeat-ngram-size", type=int, default=0,
+                   help="n >= 2: a token that would repeat an n-gram of the text so far loses 4 from its logit")
+    g.add_argument("--max-pattern-size", type=int, default=0,
+                   help="with --min-count: end a request whose last tokens are one block of up to this many tokens, repeated")
+    g.add_argument("--min-pattern-size", type=int, default=1)
+    g.add_argument("--min-count", type=int, default=0, help="repetitions of the block that end the request (>= 2)")
     g.add_argument("--seed", type=int, help="sampling seed (default: from the operating system)")
     g.add_argument("--ignore-eos", action="store_true")
     g.add_argument("--json", help="write prompts, outputs and timing here")

@@ -25,7 +25,7 @@ from ..cache.manager import CacheManager
 from ..config.registry import read_model_config, resolve_model_folder, spec_of
 from ..parts.base import Runtime
 from ..parts.model import DecoderModel
-from ..sampling.sampler import Sampler, SampleRow, SamplingParams
+from ..sampling.sampler import NoRepeatIndex, Sampler, SampleRow, SamplingParams
 from ..settings import SETTINGS
 from ..weights.loader import DictWeights, FolderWeights
 from ..weights.random_init import random_weights
@@ -275,6 +275,8 @@ class Engine:
         sch = self.scheduler
         if sch.waiting or not sch.running or len(sch.running) > sch.budget:
             return False
+        if any(r.params.no_repeat_ngram_size for r in sch.running):
+            return False            # the rule's next verdict needs this step's token on the host
         if any(r.pending != 1 or r.request_id not in cur.index for r in sch.running):
             return False
         return not sch._pages_short([(r, 1) for r in sch.running])
@@ -284,10 +286,18 @@ class Engine:
         row of counts (its slot in the cache) and how to read its history; (id, arrival, preemptions) tells the sampler
         when that row holds another request's counts, or this one's from before it lost its place."""
         position = len(r.prompt) + len(r.output)
+        blocked = None
+        if r.params.no_repeat_ngram_size:
+            # the rule's memory lives with the request and follows its text (a request that was preempted kept its text)
+            if r.no_repeat is None:
+                r.no_repeat = NoRepeatIndex(r.params.no_repeat_ngram_size)
+            if r.no_repeat.seen < position:
+                r.no_repeat.add(r.span(r.no_repeat.seen, position - r.no_repeat.seen))
+            blocked = r.no_repeat.blocked()
         if not r.params.penalizes:
-            return SampleRow(r.params, position)
+            return SampleRow(r.params, position, blocked=blocked)
         return SampleRow(r.params, position, self.cache.slot_of(r.request_id), (r.request_id, r.order, r.preemptions),
-                         lambda: r.span(0, position))
+                         lambda: r.span(0, position), blocked)
 
     def _launch(self, batch, before: "_Flight | None") -> "_Flight":
         """Run `batch` and its sampling without waiting for them. `before`: the step whose tokens this one's rows

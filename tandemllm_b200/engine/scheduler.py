@@ -30,7 +30,7 @@ from collections import deque
 from dataclasses import dataclass, field
 
 from ..cache.manager import CacheManager
-from ..sampling.sampler import SamplingParams
+from ..sampling.sampler import SamplingParams, repeating_pattern
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
 PENDING = -1        # in a request's output: a token that a launched step is still computing
@@ -48,6 +48,8 @@ class Request:
     preemptions: int = 0
     order: int = 0
     last_slot: int | None = None    # where in `output` the request's last token sits, once that is known
+    no_repeat: object = None        # the no-repeat-n-gram rule's memory (`sampling.NoRepeatIndex`), made at the first draw
+    stop_pattern: tuple | None = None   # the block whose repetition ended the request (`SamplingParams.max_pattern_size`)
 
     @property
     def tokens(self) -> list[int]:
@@ -254,8 +256,13 @@ class Scheduler:
                 continue        # the request ended with an earlier token (or was aborted): this row ran for nothing
             r.output[s.slot] = tok
             stops = r.params.stop_token_ids if r.params.stop_token_ids is not None else self.stop_token_ids
-            if not r.params.ignore_eos and tok in stops:
-                r.finish_reason = "stop"
+            pattern = None
+            if r.params.stops_on_patterns and not s.finishes:
+                tail = r.params.max_pattern_size * r.params.min_count          # no pattern reaches further back
+                pattern = repeating_pattern(r.output[max(0, s.slot + 1 - tail):s.slot + 1], r.params.min_pattern_size,
+                                            r.params.max_pattern_size, r.params.min_count)
+            if (not r.params.ignore_eos and tok in stops) or pattern is not None:
+                r.finish_reason, r.stop_pattern = "stop", pattern
                 del r.output[s.slot + 1:]
                 r.last_slot = s.slot
                 if r.state != FINISHED:

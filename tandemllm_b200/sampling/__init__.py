@@ -1,5 +1,6 @@
-"""Greedy and temperature / min_p / top-k / top-p sampling, with repetition, presence and frequency penalties and added logits."""
+"""Greedy and temperature / min_p / top-k / top-p sampling, with repetition, presence and frequency penalties, added logits,
+the no-repeat-n-gram rule and the stop on a repeating pattern."""
 
-from .sampler import Sampler, SampleRow, SamplingParams
+from .sampler import NoRepeatIndex, Sampler, SampleRow, SamplingParams, repeating_pattern
 
-__all__ = ["Sampler", "SampleRow", "SamplingParams"]
+__all__ = ["NoRepeatIndex", "Sampler", "SampleRow", "SamplingParams", "repeating_pattern"]

@@ -40,6 +40,10 @@ class SamplingParams:
     presence_penalty: float = 0.0       # seen tokens lose this once
     frequency_penalty: float = 0.0      # seen tokens lose this times their count
     logit_bias: dict[int, float] | None = None      # {token id: added logit}
+    no_repeat_ngram_size: int = 0       # n >= 2: a token that would repeat an n-gram of the text so far loses NO_REPEAT_PENALTY
+    max_pattern_size: int = 0           # > 0 with min_count >= 2: the request ends when its last tokens are one block of
+    min_pattern_size: int = 1           # min_pattern_size..max_pattern_size tokens repeated min_count times
+    min_count: int = 0
 
     def __post_init__(self) -> None:
         if self.temperature < 0.0 or self.temperature != self.temperature:
@@ -58,6 +62,10 @@ class SamplingParams:
             raise ValueError(f"presence_penalty must be in [-2, 2], got {self.presence_penalty}")
         if not -2.0 <= self.frequency_penalty <= 2.0:
             raise ValueError(f"frequency_penalty must be in [-2, 2], got {self.frequency_penalty}")
+        if self.no_repeat_ngram_size and self.no_repeat_ngram_size < 2:
+            raise ValueError(f"no_repeat_ngram_size must be 0 or >= 2, got {self.no_repeat_ngram_size}")
+        if self.max_pattern_size < 0 or self.min_pattern_size < 1 or self.min_count < 0:
+            raise ValueError(f"pattern stop: sizes {self.min_pattern_size}..{self.max_pattern_size}, count {self.min_count}")
         if self.logit_bias:
             bias = {}
             for k, v in self.logit_bias.items():         # keys may be strings of digits, as they are in JSON
@@ -85,13 +93,67 @@ class SamplingParams:
 
     @property
     def changes_logits(self) -> bool:
-        return self.penalizes or self.logit_bias is not None
+        return self.penalizes or self.logit_bias is not None or self.no_repeat_ngram_size > 0
+
+    @property
+    def stops_on_patterns(self) -> bool:
+        return self.max_pattern_size > 0 and self.min_count >= 2
 
     def resolved_seed(self) -> int:
         """The request's seed as a 63-bit integer; an unseeded request draws one now."""
         if self.seed is None:
             self.seed = int.from_bytes(os.urandom(8), "little") >> 1
         return int(self.seed) & ((1 << 63) - 1)
+
+
+NO_REPEAT_PENALTY = 4.0      # what a token that would repeat an n-gram loses (the reference's `mask_penalty`: finite, so
+                             # that a token the model is sure of can still win and the rule never forces an early end)
+NO_REPEAT_WINDOW = 2048      # the text the rule looks back over: when it grows past this, the older half is forgotten
+
+
+class NoRepeatIndex:
+    """The no-repeat-n-gram rule's memory for one request, on the host: the request's text (prompt and generated
+    tokens) over a window, and for every run of n - 1 tokens in it the tokens that followed the run
+    (engine/penalty.py:169-254 of the reference: `history`, `followers`, `_add`, `_index_history`, `_mask`)."""
+
+    def __init__(self, n: int):
+        self.n = int(n)
+        self.history: list[int] = []
+        self.followers: dict[tuple, set[int]] = {}
+        self.seen = 0                # tokens of the request's text taken in so far
+
+    def add(self, ids: list[int]) -> None:
+        n, h = self.n, self.history
+        old = len(h)
+        h.extend(int(t) for t in ids)
+        self.seen += len(ids)
+        if len(h) > NO_REPEAT_WINDOW:
+            del h[:len(h) - NO_REPEAT_WINDOW // 2]
+            self.followers.clear()
+            old = 0
+        for i in range(max(n - 1, old), len(h)):
+            self.followers.setdefault(tuple(h[i - (n - 1):i]), set()).add(h[i])
+
+    def blocked(self) -> set[int]:
+        """The tokens that followed the text's last n - 1 tokens somewhere before."""
+        tail = tuple(self.history[-(self.n - 1):])
+        return self.followers.get(tail, set())
+
+
+def repeating_pattern(tokens: list[int], min_size: int, max_size: int, count: int) -> tuple[int, ...] | None:
+    """The block of min_size..max_size tokens that the end of `tokens` repeats `count` times, the shortest such, or None
+    (the reference's `PatternStop.observe`, engine/penalty.py:133-156: a generation that writes one short pattern over and
+    over is ended, not steered)."""
+    n = len(tokens)
+    for size in range(max(1, min_size), max_size + 1):
+        span = size * count
+        if n < span:
+            continue
+        base = n - span
+        block = tokens[base:base + size]
+        if all(tokens[base + k * size:base + (k + 1) * size] == block for k in range(1, count)):
+            return tuple(block)
+    return None
 
 
 @dataclass
@@ -106,6 +168,7 @@ class SampleRow:
     slot: int = -1
     owner: object = None
     history: Callable[[], list[int]] | None = None
+    blocked: set[int] | None = None      # tokens that take the no-repeat penalty in this draw (`NoRepeatIndex.blocked`)
 
 
 class Sampler:
@@ -157,11 +220,15 @@ class Sampler:
 
     def _bias(self, rows: list[SampleRow], vocab: int):
         """(begin, token, value) on the device for the rows' added logits; None when no row has any."""
-        if not any(r.params.logit_bias for r in rows):
+        if not any(r.params.logit_bias or r.blocked for r in rows):
             return None
         begin, token, value = [0], [], []
         for r in rows:
-            for t, v in sorted((r.params.logit_bias or {}).items()):
+            added = dict(r.params.logit_bias or {})
+            if r.blocked and len(r.blocked) < vocab:        # (a rule that would take the whole vocabulary down is skipped)
+                for t in r.blocked:
+                    added[t] = added.get(t, 0.0) - NO_REPEAT_PENALTY
+            for t, v in sorted(added.items()):
                 if t >= vocab:
                     raise ValueError(f"logit_bias names token {t}; the vocabulary has {vocab}")
                 token.append(t)
@@ -185,7 +252,7 @@ class Sampler:
             return out
         rows = [r if isinstance(r, SampleRow) else SampleRow(*r) for r in rows]
         greedy = all(r.params.greedy for r in rows)
-        changed = any(r.params.changes_logits for r in rows)
+        changed = any(r.params.penalizes or r.params.logit_bias or r.blocked for r in rows)
         if greedy and not changed:
             return ops.argmax(logits, out)
         counted = [r for r in rows if r.params.penalizes]

@@ -297,3 +297,30 @@ def penalize(logits: torch.Tensor, history: list[int], repetition: float = 1.0, 
     if frequency != 0.0:
         out = out - frequency * counts.float() * seen
     return out
+
+
+def no_repeat_blocked(calls: list[list[int]], n: int, window: int = 2048) -> set[int]:
+    """The tokens the no-repeat-n-gram rule penalises for the next draw, after the text was taken in by the `calls` one
+    after the other (the prompt, then every committed token): the text is kept over a window (when it grows past
+    `window` tokens at the end of a call, all but the last window // 2 are forgotten; engine/penalty.py:222-244), and a
+    token is blocked when it followed the text's last n - 1 tokens somewhere in what is kept (penalty.py:246-276).
+    Brute force over the kept text, no index."""
+    kept: list[int] = []
+    for ids in calls:
+        kept.extend(ids)
+        if len(kept) > window:
+            del kept[:len(kept) - window // 2]
+    L = n - 1
+    if len(kept) < L:
+        return set()
+    tail = kept[-L:]
+    return {kept[j + L] for j in range(len(kept) - L) if kept[j:j + L] == tail}
+
+
+def pattern_ends(tokens: list[int], min_size: int, max_size: int, count: int) -> bool:
+    """Whether the generated tokens end in one block of min_size..max_size tokens written `count` times over
+    (engine/penalty.py:133-156)."""
+    for size in range(min_size, max_size + 1):
+        if len(tokens) >= size * count and tokens[-size * count:] == tokens[-size:] * count:
+            return True
+    return False

@@ -233,6 +233,33 @@ def test_two_steps_in_the_air_drop_the_row_behind_a_stop_id():
     assert all(g.pool.free == g.pool.num_pages for g in sched.cache.groups)
 
 
+def test_a_repeating_pattern_ends_a_request_also_with_a_step_in_the_air():
+    """`max_pattern_size` / `min_pattern_size` / `min_count`: the request ends with the token that completes the last of
+    `min_count` copies of a block, with reason "stop" and the block on record; shorter runs and other requests go on; a
+    row launched ahead of the news ran for nothing."""
+    sched, fake = make()
+    a = Request("a", [1], SamplingParams(max_tokens=50, ignore_eos=True, max_pattern_size=2, min_pattern_size=2, min_count=3))
+    b = Request("b", [2], SamplingParams(max_tokens=9, ignore_eos=True))
+    sched.add(a), sched.add(b)
+    text = [50, 7, 8, 7, 8, 9, 7, 8, 7, 8, 7, 8, 60, 61]          # 7 8 7 8 (twice) goes on; 7 8 7 8 7 8 ends it
+    fake.run = lambda batch, f=fake.run: [text[len(s.request.output)] if s.request is a else t
+                                          for s, t in zip(batch, f(batch)) if s.samples]
+    drive(sched, fake)
+    assert a.finish_reason == "stop" and a.stop_pattern == (7, 8) and a.output == text[:12]
+    assert b.finish_reason == "length" and len(b.output) == 9 and b.stop_pattern is None
+    # two steps in the air
+    sched, fake = make()
+    c = Request("c", [1], SamplingParams(max_tokens=50, ignore_eos=True, max_pattern_size=1, min_count=2))
+    sched.add(c)
+    first = sched.schedule(); fake.run(first); sched.advance(first)
+    ahead = sched.schedule(); fake.run(ahead); sched.advance(ahead)
+    assert sched.resolve(first, [44]) == []
+    third = sched.schedule(); fake.run(third); sched.advance(third)
+    assert sched.resolve(ahead, [44]) == [c] and c.output == [44, 44] and c.stop_pattern == (44,)
+    assert sched.resolve(third, [45]) == [] and c.output == [44, 44] and not sched.cache.has("c")
+    sched.cache.check()
+
+
 def test_refused_at_the_door():
     sched, _ = make(pages=4, max_len=100)
     with pytest.raises(ValueError, match="empty"):

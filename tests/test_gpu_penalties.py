@@ -197,3 +197,71 @@ def test_generation_with_penalties_under_preemption_matches_the_plain_implementa
                                                       block_size=16))
         for i in (0, 1, 4):
             assert roomy.generate([prompts[i]], [_params(i, new_tokens, prompts[i])])[0] == outs[i], i
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_with_the_no_repeat_rule_and_the_pattern_stop_matches_the_plain_implementation(tmp_path, dtype):
+    """`no_repeat_ngram_size` alone, beside a bias on one of the blocked tokens, beside the count penalties and under
+    temperature; and a request that is ended by a repeating pattern. Every token is held to the plain implementation run on
+    the text so far, with the rule's blocked set found by brute force; requests without the rule decode beside them (and a
+    step is launched ahead only when no running request has the rule)."""
+    from tandemllm_b200.engine import Engine, EngineArgs
+    from tandemllm_b200.sampling import SamplingParams
+    from tandemllm_b200.sampling.sampler import NO_REPEAT_PENALTY
+    cfg = T.TINY_C
+    W = random_model_weights(cfg, T.SEEDS["c"], T.STD["c"], bf16_exact=True)
+    folder = write_folder(str(tmp_path / "c"), cfg, W, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    g = torch.Generator().manual_seed(31)
+    new_tokens = 40
+    prompts = []
+    for n in (30, 90, 14, 55, 70, 21):              # prompts over a few tokens each: n-grams repeat inside the prompt already
+        few = torch.randint(0, cfg["vocab_size"], (4,), generator=g)
+        prompts.append(few[torch.randint(0, 4, (n,), generator=g)].tolist())
+    common = dict(max_tokens=new_tokens, ignore_eos=True)
+    params = [SamplingParams(no_repeat_ngram_size=2, **common),
+              SamplingParams(no_repeat_ngram_size=3, logit_bias={prompts[1][0]: 1.0, prompts[1][1]: -0.5}, **common),
+              SamplingParams(**common),
+              SamplingParams(no_repeat_ngram_size=2, repetition_penalty=1.3, presence_penalty=0.2, **common),
+              SamplingParams(no_repeat_ngram_size=4, temperature=0.7, top_k=30, seed=77, **common),
+              SamplingParams(max_pattern_size=3, min_pattern_size=1, min_count=3, **common)]
+    eng = Engine.from_folder(folder, EngineArgs(dtype=dtype, max_len=160, parallel=4, block_size=16, max_batched_tokens=64,
+                                                chunk_size=32))
+    reqs = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+    while eng.scheduler.has_unfinished():
+        eng.run_step()
+    outs = [r.output for r in reqs]
+    assert all(len(o) == new_tokens for o in outs[:5])
+    exact = total = blocked_moves = 0
+    for i, (prompt, out, sp) in enumerate(zip(prompts, outs, params)):
+        seq, calls = list(prompt), [list(prompt)]
+        for k, tok in enumerate(out):
+            raw = P.forward(cfg, W, seq)[-1]
+            bias = dict(sp.logit_bias or {})
+            if sp.no_repeat_ngram_size:
+                for t in P.no_repeat_blocked(calls, sp.no_repeat_ngram_size):
+                    bias[t] = bias.get(t, 0.0) - NO_REPEAT_PENALTY
+            ref = P.penalize(raw, seq, sp.repetition_penalty, sp.presence_penalty, sp.frequency_penalty, bias)
+            if sp.temperature == 0.0:
+                best = int(ref.argmax())
+                blocked_moves += bool(sp.no_repeat_ngram_size) and best != int(raw.argmax())
+                if tok != best:
+                    assert float(ref[best] - ref[tok]) <= 2 * TOL[dtype] * float(raw.abs().max()), (i, k, tok, best)
+            else:
+                best = P.sample(ref, sp.temperature, sp.top_k, sp.top_p, sp.min_p, seed=sp.seed, position=len(seq))
+            exact += tok == best
+            total += 1
+            seq.append(tok)
+            calls.append([tok])
+            if sp.stops_on_patterns:
+                ended = P.pattern_ends(out[:k + 1], sp.min_pattern_size, sp.max_pattern_size, sp.min_count)
+                assert ended == (k == len(out) - 1 and reqs[i].finish_reason == "stop"), (i, k)
+    assert blocked_moves > 10, "the rule changed the choice often enough for the comparison to mean something"
+    if dtype == "float32":
+        assert exact == total, (exact, total)
+    else:
+        assert exact >= int(0.9 * total), (exact, total)
+    last = reqs[5]
+    assert last.finish_reason in ("stop", "length") and (last.stop_pattern is not None) == (last.finish_reason == "stop")
+    # greedy decoding of a tiny random model falls into a loop: the pattern stop must have seen it
+    assert last.finish_reason == "stop" and len(last.output) < new_tokens
+    assert 1 <= len(last.stop_pattern) <= 3 and last.output[-3 * len(last.stop_pattern):] == list(last.stop_pattern) * 3

@@ -88,3 +88,49 @@ def test_penalties_on_a_hand_made_row():
     out = P.penalize(logits, history, repetition=2.0, bias={1: 3.0, 2: -4.0})
     assert out.tolist() == [1.0, 0.5, -3.0, -1.0, 0.5, 1.5]
     assert torch.equal(P.penalize(logits, history), logits)
+
+
+def test_the_no_repeat_index_equals_the_brute_force_rule_across_the_window():
+    """`NoRepeatIndex` (the product's memory of the rule) against `plain_lfm2.no_repeat_blocked` (no index, the kept text
+    searched each time), over prompts shorter and longer than the window, so that the forgetting of the older half is
+    crossed once by the prompt and again token by token."""
+    import random
+
+    from tandemllm_b200.sampling import NoRepeatIndex
+    rnd = random.Random(3)
+    for n in (2, 3, 5):
+        for prompt_len, vocab, steps in ((0, 3, 40), (7, 4, 60), (1500, 6, 700), (2100, 5, 30), (5000, 50, 1200)):
+            prompt = [rnd.randrange(vocab) for _ in range(prompt_len)]
+            index, calls = NoRepeatIndex(n), [prompt]
+            index.add(prompt)
+            for step in range(steps):
+                assert index.blocked() == P.no_repeat_blocked(calls, n), (n, prompt_len, step)
+                t = rnd.randrange(vocab)
+                index.add([t])
+                calls.append([t])
+            assert index.seen == prompt_len + steps
+
+
+def test_the_pattern_stop_equals_the_plain_rule_and_the_parameters_are_checked():
+    import random
+
+    from tandemllm_b200.sampling import SamplingParams, repeating_pattern
+    rnd = random.Random(4)
+    hits = 0
+    for _ in range(3000):
+        toks = [rnd.randrange(3) for _ in range(rnd.randrange(0, 30))]
+        lo = rnd.randrange(1, 4)
+        hi, count = rnd.randrange(lo, 6), rnd.randrange(2, 5)
+        got = repeating_pattern(toks, lo, hi, count)
+        assert (got is not None) == P.pattern_ends(toks, lo, hi, count)
+        if got is not None:
+            hits += 1
+            assert lo <= len(got) <= hi and toks[-len(got) * count:] == list(got) * count
+    assert hits > 100
+    assert repeating_pattern([5, 5, 5, 5], 1, 2, 4) == (5,) and repeating_pattern([1, 2, 1, 2], 1, 2, 2) == (1, 2)
+    assert not SamplingParams().stops_on_patterns and not SamplingParams(max_pattern_size=4, min_count=1).stops_on_patterns
+    assert SamplingParams(max_pattern_size=4, min_count=2).stops_on_patterns
+    assert SamplingParams(no_repeat_ngram_size=3).changes_logits and not SamplingParams(no_repeat_ngram_size=3).penalizes
+    for bad in (dict(no_repeat_ngram_size=1), dict(no_repeat_ngram_size=-2), dict(min_pattern_size=0), dict(max_pattern_size=-1)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
