@@ -68,7 +68,7 @@ def cmd_generate(a) -> int:
     else:
         g = torch.Generator().manual_seed(a.prompt_seed)
         prompts = [torch.randint(0, vocab, (a.prompt_len,), generator=g).tolist() for _ in range(a.prompts)]
-    params = SamplingParams(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, min_p=a.min_p, seed=a.seed,
+    params = engine.sampling_params(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, min_p=a.min_p, seed=a.seed,
                             max_tokens=a.tokens, ignore_eos=a.ignore_eos, repetition_penalty=a.rep_penalty,
                             presence_penalty=a.presence_penalty, frequency_penalty=a.frequency_penalty,
                             logit_bias=_logit_bias(a.logit_bias), no_repeat_ngram_size=a.no_repeat_ngram_size,
@@ -151,9 +151,9 @@ def main(argv=None) -> int:
     g.add_argument("--prompt-seed", type=int, default=0)
     g.add_argument("--tokens", type=int, default=128, help="new tokens per request at most")
     g.add_argument("--temperature", type=float, default=0.0)
-    g.add_argument("--top-p", type=float, default=1.0)
-    g.add_argument("--top-k", type=int, default=0)
-    g.add_argument("--min-p", type=float, default=0.0)
+    g.add_argument("--top-p", type=float, help="default with a temperature: the model card's (generation_config.json), else 1")
+    g.add_argument("--top-k", type=int, help="default with a temperature: the model card's, else 0 (off)")
+    g.add_argument("--min-p", type=float, help="default 0")
     g.add_argument("--rep-penalty", type=float, default=1.0,
                    help="repetition penalty: a logit of a token seen in the prompt or the output is divided by this if "
                         "positive, multiplied if negative (1.0: off)")

@@ -25,6 +25,7 @@ from ..cache.manager import CacheManager
 from ..config.registry import read_model_config, resolve_model_folder, spec_of
 from ..parts.base import Runtime
 from ..parts.model import DecoderModel
+from ..sampling.defaults import card_sampling, resolve as resolve_filters
 from ..sampling.sampler import NoRepeatIndex, Sampler, SampleRow, SamplingParams
 from ..settings import SETTINGS
 from ..weights.loader import DictWeights, FolderWeights
@@ -95,6 +96,7 @@ class Engine:
                                    chunk_size=args.chunk_size, max_model_len=args.max_len,
                                    stop_token_ids=model.spec.stop_token_ids)
         self._next_id = 0
+        self.card_sampling: dict | None = None      # what the model folder's generation_config.json recommends (top_p, top_k)
         # ---- records: one dict a scheduler step (the reference keeps `route_trace` and `host_ms` per step,
         # engine/models/lfm2_moe/engine.py:125, :236-240, :457) ----
         self.records: deque[dict] = deque(maxlen=4096)
@@ -114,7 +116,9 @@ class Engine:
         folder = resolve_model_folder(folder)
         arch, config = read_model_config(folder)
         spec = spec_of(config)
-        return cls._build(arch, spec, FolderWeights(folder, spec.name_prefixes), args)
+        engine = cls._build(arch, spec, FolderWeights(folder, spec.name_prefixes), args)
+        engine.card_sampling = card_sampling(folder)
+        return engine
 
     @classmethod
     def from_config(cls, config, seed: int, args: EngineArgs | None = None, std: float = 0.02, bias_std: float = 0.1,
@@ -156,6 +160,15 @@ class Engine:
             return self.step_function.run(entries)
 
     # ---- generation ----
+    def sampling_params(self, flags: dict | None = None, **fields) -> SamplingParams:
+        """`SamplingParams(**fields)` with the filters a sampled request runs with when it names none: its own top_p /
+        top_k / min_p if it gives any (the rest from `flags`), else `flags`, else the model card's, else none
+        (`sampling.defaults`). A greedy request is left as it is."""
+        if float(fields.get("temperature") or 0.0) > 0.0:
+            chosen = resolve_filters(fields, flags, self.card_sampling)
+            fields = dict(fields, top_p=chosen["top_p"], top_k=chosen["top_k"], min_p=chosen["min_p"])
+        return SamplingParams(**{k: v for k, v in fields.items() if v is not None})
+
     def add_request(self, prompt: list[int], params: SamplingParams | None = None, request_id=None) -> Request:
         params = params or SamplingParams()
         if request_id is None:

@@ -194,3 +194,32 @@ def test_warm_up_leaves_nothing_behind_and_the_first_decode_steps_replay_graphs(
     eng.add_request([1, 2, 3], params)
     with pytest.raises(RuntimeError, match="waiting or running"):
         eng.warm_up()
+
+
+def test_a_sampled_request_without_filters_takes_the_model_cards(tmp_path):
+    """`Engine.sampling_params`: generation_config.json's top_k / top_p stand in where a request with a temperature names
+    no filter; a filter of the request's own, flags, and greedy requests go before or past them."""
+    import json
+
+    from tandemllm_b200.engine import Engine, EngineArgs
+    folder, cfg, W = folder_of("a", tmp_path, torch.float32)
+    with open(os.path.join(folder, "generation_config.json"), "w") as f:
+        json.dump({"eos_token_id": 3, "top_k": 5, "top_p": 0.9}, f)
+    eng = Engine.from_folder(folder, EngineArgs(dtype="float32", max_len=64, parallel=2))
+    assert eng.card_sampling == {"top_k": 5, "top_p": 0.9}
+    sp = eng.sampling_params(temperature=0.8, seed=4, max_tokens=6)
+    assert (sp.top_k, sp.top_p, sp.min_p, sp.max_tokens) == (5, 0.9, 0.0, 6)
+    sp_own = eng.sampling_params(temperature=0.8, top_k=3, top_p=None)
+    assert (sp_own.top_k, sp_own.top_p) == (3, 1.0)
+    sp_flags = eng.sampling_params({"top_p": 0.5}, temperature=0.8)
+    assert (sp_flags.top_k, sp_flags.top_p) == (0, 0.5)
+    greedy = eng.sampling_params(temperature=0.0, top_k=None, max_tokens=4)
+    assert (greedy.top_k, greedy.top_p) == (0, 1.0)
+    prompt = T.long_tokens("a", 9, seed=2)
+    out = eng.generate([prompt], sp)[0]
+    # every drawn token is among the card's five most likely at its position
+    seq = list(prompt)
+    for tok in out:
+        logits = P.forward(cfg, W, seq)[-1]
+        assert tok in torch.topk(logits, 5).indices.tolist()
+        seq.append(tok)

@@ -134,3 +134,26 @@ def test_the_pattern_stop_equals_the_plain_rule_and_the_parameters_are_checked()
     for bad in (dict(no_repeat_ngram_size=1), dict(no_repeat_ngram_size=-2), dict(min_pattern_size=0), dict(max_pattern_size=-1)):
         with pytest.raises(ValueError):
             SamplingParams(**bad)
+
+
+def test_the_filters_of_a_sampled_request_come_from_the_request_the_flags_the_card_or_nowhere(tmp_path):
+    """`sampling.defaults.resolve` (the reference's server/sampling_defaults.py:41-66): the first of request, flags and
+    card that names a filter decides all three; what the request leaves out comes from the flags, never from the card."""
+    import json
+
+    from tandemllm_b200.sampling import card_sampling, resolve_filters
+    card = {"top_p": 0.95, "top_k": 20}
+    assert resolve_filters({}, None, None) == {"top_p": 1.0, "top_k": 0, "min_p": 0.0, "source": "none"}
+    assert resolve_filters({"temperature": 0.7}, None, card) == {"top_p": 0.95, "top_k": 20, "min_p": 0.0, "source": "card"}
+    assert resolve_filters({"top_k": None}, {"top_p": 0.8}, card) == {"top_p": 0.8, "top_k": 0, "min_p": 0.0, "source": "flags"}
+    assert resolve_filters({"min_p": 0.1}, {"top_p": 0.8, "top_k": None}, card) == \
+        {"top_p": 0.8, "top_k": 0, "min_p": 0.1, "source": "request"}
+    assert resolve_filters({"top_k": "40"}, None, card) == {"top_p": 1.0, "top_k": 40, "min_p": 0.0, "source": "request"}
+    assert resolve_filters(None, None, {"top_k": None, "top_p": 0.9})["top_k"] == 0
+    with pytest.raises(ValueError):
+        resolve_filters({"top_p": "much"})
+    assert card_sampling(str(tmp_path)) is None
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 7, "top_k": 50, "temperature": 0.1}))
+    assert card_sampling(str(tmp_path)) == {"top_k": 50}
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 7}))
+    assert card_sampling(str(tmp_path)) is None
