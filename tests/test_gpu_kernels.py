@@ -232,6 +232,27 @@ def test_a_device_graph_replays_what_was_captured_from_a_pool_of_its_own():
     g2.replay()
     torch.cuda.synchronize()
     close(out2.cpu(), P.rms_norm(res.cpu() + 1, w.cpu(), 1e-5), torch.float32, "second graph")
+    # another thread's CUDA work in the middle of a capture (an allocation, a copy and its wait) neither fails nor breaks
+    # the capture: captures run in thread-local mode, and the pool is the capturing thread's alone
+    import threading
+    seen = {}
+
+    def elsewhere():
+        other = torch.arange(1 << 16, device=DEV, dtype=torch.float32)
+        seen["sum"] = float(other.sum().item())
+
+    def body_with_company():
+        out = body()
+        t = threading.Thread(target=elsewhere)
+        t.start()
+        t.join()
+        return out
+
+    g3, out3 = capture(body_with_company)
+    assert seen["sum"] == float(sum(range(1 << 16)))
+    g3.replay()
+    torch.cuda.synchronize()
+    close(out3.cpu(), P.rms_norm(res.cpu() + 1, w.cpu(), 1e-5), torch.float32, "a capture with company")
     with pytest.raises(ZeroDivisionError):
         capture(lambda: 1 // 0)
     assert not torch.cuda.is_current_stream_capturing()
