@@ -105,6 +105,46 @@ def cmd_random_weights(a) -> int:
     return 0
 
 
+def cmd_audit(a) -> int:
+    """A model folder's audit record from its headers alone (no tensor is read, no GPU is needed; the reference's
+    tools/lfm_check.py:331-347 `audit`): the architecture and its sizes, the stored tensors against what the parts
+    would read (`refused`: the loader's one error, or null), the bytes on disk by stored type, and the bytes of weights
+    one decode step reads at the batch sizes asked for."""
+    import os
+
+    from .config.registry import read_model_config, resolve_model_folder, spec_of
+    from .parts.model import DecoderModel
+    from .weights.loader import FolderWeights
+    from .weights.safetensors_io import CheckpointError
+    folder = resolve_model_folder(a.model)
+    arch, config = read_model_config(folder)
+    spec = spec_of(config)
+    build = arch.build_model if arch is not None and arch.build_model else DecoderModel
+    model = build(spec)
+    weights = FolderWeights(folder, spec.name_prefixes)
+    expected = model.weight_specs(weights.present())
+    ignored = set(spec.ignored_names)
+    try:
+        weights.check(expected, ignore=(lambda n: n in ignored) if ignored else None)
+        refused = None
+    except CheckpointError as e:
+        refused = str(e)
+    by_type: dict[str, dict] = {}
+    for st in weights.stored.values():
+        row = by_type.setdefault(st.dtype, {"tensors": 0, "bytes": 0})
+        row["tensors"] += 1
+        row["bytes"] += st.nbytes
+    files = sorted(f for f in os.listdir(folder) if f.endswith(".safetensors"))
+    out = {"folder": folder, "architecture": arch.name if arch is not None else None, "layers": len(spec.layers),
+           "run_order": len(spec.schedule), "hidden_size": spec.hidden_size, "vocab_size": spec.vocab_size,
+           "tensors_expected": len(expected), "tensors_stored": len(weights.stored), "refused": refused,
+           "stored": by_type, "files": len(files),
+           "safetensors_gb": round(sum(os.path.getsize(os.path.join(folder, f)) for f in files) / 1e9, 3),
+           "decode_bytes": {str(b): model.decode_bytes(b) for b in a.batch}}
+    print(json.dumps(out, indent=1))
+    return 0 if refused is None else 1
+
+
 def cmd_replay(a) -> int:
     import os
     import runpy
@@ -180,6 +220,10 @@ def main(argv=None) -> int:
     r.add_argument("--norm-std", type=float, default=0.0)
     r.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
     r.set_defaults(fn=cmd_random_weights)
+    u = sub.add_parser("audit", help="a model folder checked from its headers alone (CPU): names, shapes, bytes")
+    u.add_argument("--model", required=True)
+    u.add_argument("--batch", type=int, nargs="*", default=[1, 8, 64], help="decode batch sizes to account bytes for")
+    u.set_defaults(fn=cmd_audit)
     p = sub.add_parser("replay", help="the trace replay program; options as for bin/trace_run")
     p.add_argument("rest", nargs=argparse.REMAINDER)
     p.set_defaults(fn=cmd_replay)

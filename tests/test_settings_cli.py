@@ -163,3 +163,30 @@ def test_the_command_line_reads_penalties_and_added_logits():
                          cwd=ROOT).stdout
     for name in ("--rep-penalty", "--presence-penalty", "--frequency-penalty", "--logit-bias"):
         assert name in out
+
+
+def test_the_audit_command_checks_a_folder_from_its_headers_alone(tmp_path):
+    """`python -m tandemllm_b200 audit --model DIR` (no GPU): the stored tensors against what the parts would read, bytes
+    by stored type, bytes of a decode step; a folder that lacks a tensor and has a stray one is refused by name, exit 1."""
+    import json
+
+    from tests.helpers import random_model_weights, write_folder
+    W = random_model_weights(T.TINY_B, 1, 0.02, bf16_exact=True)
+    good = write_folder(str(tmp_path / "good"), T.TINY_B, W, torch.bfloat16)
+    r = run_cli("audit", "--model", good, "--batch", "1", "8")
+    assert r.returncode == 0, r.stderr
+    rec = json.loads(r.stdout)
+    assert rec["architecture"] == "lfm2_moe" and rec["refused"] is None and rec["layers"] == T.TINY_B["num_hidden_layers"]
+    assert rec["tensors_expected"] == rec["tensors_stored"] == len(W) and rec["files"] == 1
+    assert sum(v["tensors"] for v in rec["stored"].values()) == len(W)
+    assert rec["decode_bytes"]["8"]["experts"] > rec["decode_bytes"]["1"]["experts"] > 0
+    assert rec["decode_bytes"]["1"]["dense"] == rec["decode_bytes"]["8"]["dense"]
+    lacking = dict(W)
+    gone = next(n for n in lacking if n.endswith("operator_norm.weight"))
+    del lacking[gone]
+    lacking["stray.weight"] = torch.zeros(3)
+    bad = write_folder(str(tmp_path / "bad"), T.TINY_B, lacking, torch.bfloat16)
+    r = run_cli("audit", "--model", bad)
+    assert r.returncode == 1
+    refused = json.loads(r.stdout)["refused"]
+    assert gone in refused and "stray.weight" in refused and "missing (1)" in refused and "unexpected (1)" in refused
