@@ -145,6 +145,60 @@ def cmd_audit(a) -> int:
     return 0 if refused is None else 1
 
 
+def compare_logits(a_dir: str, b_dir: str, vocab: int) -> dict:
+    """Two replays of one trace (`bin/trace_run --out`), row by row: `b_dir` is the reference (say, the 32-bit run), `a_dir`
+    the run held against it. The record of the reference's teacher-forced comparison (tools/lfm_check.py:100-127):
+    positions, how often the largest logit agrees, disagreements split into near ties (the reference's own margin below
+    8 * 2^-7 of its row's largest logit, what bfloat16 cannot tell apart) and others, and the largest and mean difference
+    relative to a row's largest logit."""
+    import os
+
+    import numpy as np
+    steps = sorted((f for f in os.listdir(b_dir) if f.endswith(".f32")), key=lambda f: int(f[:-4]))
+    agree = total = near = other = 0
+    max_rel, means, bad, missing = 0.0, [], [], []
+    for f in steps:
+        if not os.path.isfile(os.path.join(a_dir, f)):
+            missing.append(f)
+            continue
+        ref = np.fromfile(os.path.join(b_dir, f), dtype="<f4").reshape(-1, vocab).astype(np.float64)
+        got = np.fromfile(os.path.join(a_dir, f), dtype="<f4").reshape(-1, vocab).astype(np.float64)
+        if got.shape != ref.shape:
+            raise SystemExit(f"step {f[:-4]}: {got.shape[0]} rows against {ref.shape[0]}")
+        scale = np.abs(ref).max(-1)
+        d = np.abs(got - ref)
+        max_rel = max(max_rel, float((d.max(-1) / scale).max()))
+        means.append(float((d.mean(-1) / scale).mean()))
+        ga, ra = got.argmax(-1), ref.argmax(-1)
+        for i in range(ref.shape[0]):
+            total += 1
+            if ga[i] == ra[i]:
+                agree += 1
+                continue
+            margin = float(ref[i, ra[i]] - ref[i, ga[i]])
+            tie = margin < 8 * 2 ** -7 * float(scale[i])
+            near += tie
+            other += not tie
+            if len(bad) < 12:
+                bad.append({"step": int(f[:-4]), "row": i, "margin": round(margin, 4), "near_tie": bool(tie)})
+    return {"steps": len(steps) - len(missing), "missing_steps": [int(f[:-4]) for f in missing], "positions": total,
+            "argmax_agree": agree, "agree_pct": round(100 * agree / max(total, 1), 2), "near_tie": near, "other": other,
+            "max_rel_diff": round(max_rel, 6), "mean_rel_diff": round(sum(means) / max(len(means), 1), 7),
+            "disagreements": bad}
+
+
+def cmd_compare(a) -> int:
+    vocab = a.vocab
+    if vocab is None:
+        if not a.model:
+            raise SystemExit("give --vocab N, or --model DIR to read it from")
+        from .config.registry import read_model_config, spec_of
+        vocab = spec_of(read_model_config(a.model)[1]).vocab_size
+    rec = compare_logits(a.run, a.reference, vocab)
+    print(json.dumps(rec, indent=1))
+    return 0 if rec["other"] == 0 and not rec["missing_steps"] else 1
+
+
 def cmd_replay(a) -> int:
     import os
     import runpy
@@ -224,6 +278,12 @@ def main(argv=None) -> int:
     u.add_argument("--model", required=True)
     u.add_argument("--batch", type=int, nargs="*", default=[1, 8, 64], help="decode batch sizes to account bytes for")
     u.set_defaults(fn=cmd_audit)
+    c = sub.add_parser("compare", help="two replays of one trace, row by row (say bfloat16 against float32)")
+    c.add_argument("--run", required=True, help="the --out folder of the replay that is checked")
+    c.add_argument("--reference", required=True, help="the --out folder of the replay it is held against")
+    c.add_argument("--model", help="the model folder (for the vocabulary size)")
+    c.add_argument("--vocab", type=int)
+    c.set_defaults(fn=cmd_compare)
     p = sub.add_parser("replay", help="the trace replay program; options as for bin/trace_run")
     p.add_argument("rest", nargs=argparse.REMAINDER)
     p.set_defaults(fn=cmd_replay)

@@ -223,3 +223,28 @@ def test_a_sampled_request_without_filters_takes_the_model_cards(tmp_path):
         logits = P.forward(cfg, W, seq)[-1]
         assert tok in torch.topk(logits, 5).indices.tolist()
         seq.append(tok)
+
+
+def test_a_bfloat16_replay_held_against_the_32_bit_one_by_the_compare_command(tmp_path):
+    """`bin/trace_run` twice over one trace (float32, bfloat16), then `python -m tandemllm_b200 compare`: every wanted row is
+    there, the two precisions differ by bfloat16's rounding, and where their largest logits differ the record says whether
+    the 32-bit row could tell the two tokens apart."""
+    from tests import traces
+    folder, cfg, W = folder_of("c", tmp_path, torch.bfloat16)
+    reqs = {f"q{i}": T.long_tokens("c", n, seed=40 + i) for i, n in enumerate((50, 23, 37))}
+    trace = traces.mixed(reqs, live=2, seed=3)
+    lines = "\n".join(json.dumps(s) for s in trace) + "\n"
+    held = traces.tokens_held(trace, 64)
+    wanted = sum(len(e["want"]) for s in trace for e in s["entries"])
+    for dtype in ("float32", "bfloat16"):
+        r = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out",
+                            str(tmp_path / dtype), "--max-tokens", str(held)], input=lines, capture_output=True, text=True,
+                           timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+    r = subprocess.run([sys.executable, "-m", "tandemllm_b200", "compare", "--run", str(tmp_path / "bfloat16"), "--reference",
+                        str(tmp_path / "float32"), "--model", folder], cwd=ROOT, capture_output=True, text=True, timeout=120)
+    rec = json.loads(r.stdout)
+    assert rec["positions"] == wanted > 20 and not rec["missing_steps"]
+    assert 0 < rec["max_rel_diff"] < 3e-2 and rec["agree_pct"] > 80
+    assert rec["argmax_agree"] + rec["near_tie"] + rec["other"] == wanted
+    assert r.returncode == (0 if rec["other"] == 0 else 1)

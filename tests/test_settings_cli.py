@@ -190,3 +190,38 @@ def test_the_audit_command_checks_a_folder_from_its_headers_alone(tmp_path):
     assert r.returncode == 1
     refused = json.loads(r.stdout)["refused"]
     assert gone in refused and "stray.weight" in refused and "missing (1)" in refused and "unexpected (1)" in refused
+
+
+def test_the_compare_command_holds_one_replay_against_another(tmp_path):
+    """`python -m tandemllm_b200 compare --run A --reference B --vocab V`: the record of a teacher-forced comparison (rows,
+    agreement of the largest logit, near ties and other disagreements, relative differences); exit 1 on a disagreement that
+    is no near tie or on a step that is missing."""
+    import json
+
+    import numpy as np
+    V = 50
+    rng = np.random.default_rng(0)
+    ref = {0: rng.normal(size=(3, V)).astype("<f4"), 2: rng.normal(size=(1, V)).astype("<f4"), 5: rng.normal(size=(2, V)).astype("<f4")}
+    a, b = tmp_path / "a", tmp_path / "b"
+    a.mkdir(); b.mkdir()
+    order = np.argsort(ref[5][0])
+    ref[5][0, order[-2]] = ref[5][0, order[-1]] - 1e-3           # the reference itself can hardly tell these two apart
+    for step, rows in ref.items():
+        rows.tofile(b / f"{step}.f32")
+        (rows + rng.normal(scale=1e-3, size=rows.shape).astype("<f4")).tofile(a / f"{step}.f32")
+    r = run_cli("compare", "--run", str(a), "--reference", str(b), "--vocab", str(V))
+    rec = json.loads(r.stdout)
+    assert r.returncode == 0 and rec["positions"] == 6 and rec["argmax_agree"] == 6 and rec["steps"] == 3
+    assert 0 < rec["max_rel_diff"] < 5e-3 and rec["mean_rel_diff"] < rec["max_rel_diff"]
+    # a near tie (the runner-up lifted just above the best) and a plain disagreement
+    rows = ref[5].copy()
+    rows[0, order[-2]] = rows[0, order[-1]] + 1e-4
+    rows[1, int(np.argmin(rows[1]))] = 100.0
+    rows.tofile(a / "5.f32")
+    (a / "2.f32").unlink()
+    r = run_cli("compare", "--run", str(a), "--reference", str(b), "--vocab", str(V))
+    rec = json.loads(r.stdout)
+    assert r.returncode == 1 and rec["missing_steps"] == [2] and rec["positions"] == 5
+    assert rec["near_tie"] == 1 and rec["other"] == 1 and rec["argmax_agree"] == 3
+    assert [d["near_tie"] for d in rec["disagreements"]] == [True, False]
+    assert run_cli("compare", "--run", str(a), "--reference", str(b)).returncode != 0       # neither --vocab nor --model
