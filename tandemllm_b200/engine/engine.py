@@ -185,6 +185,16 @@ class Engine:
         self.scheduler.add(req)
         return req
 
+    def abort(self, request: Request) -> None:
+        """Take a request out wherever it is (waiting, between two portions of its prompt, decoding, with a step in the
+        air): its pages and its slot go back at once. A row that a launched step still computes for it counts for nothing,
+        and what that step still writes lands in pages whose next owner overwrites them before reading them (its own
+        steps come later on the stream)."""
+        if request.state != "finished":
+            self.scheduler.abort(request)
+            while request.output and request.output[-1] < 0:        # places kept for tokens of steps still in the air
+                request.output.pop()
+
     # ---- records ----
     def set_routing_record(self, on: bool) -> None:
         """Count (or stop counting) the pairs every step routes to each expert of each routed feed-forward; a step's

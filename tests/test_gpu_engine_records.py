@@ -248,3 +248,38 @@ def test_a_bfloat16_replay_held_against_the_32_bit_one_by_the_compare_command(tm
     assert 0 < rec["max_rel_diff"] < 3e-2 and rec["agree_pct"] > 80
     assert rec["argmax_agree"] + rec["near_tie"] + rec["other"] == wanted
     assert r.returncode == (0 if rec["other"] == 0 else 1)
+
+
+def test_aborting_requests_between_portions_and_with_a_step_in_the_air_leaves_the_others_alone(tmp_path):
+    """`Engine.abort`: one request is taken out between two portions of its prompt, one while it decodes and a step launched
+    ahead still computes a row for it, one while it waits. Pages and slots are back at once, the aborted texts hold no
+    place-holders, and the requests that stay generate what they generate alone."""
+    from tandemllm_b200.engine import Engine, EngineArgs
+    from tandemllm_b200.sampling import SamplingParams
+    folder, cfg, W = folder_of("c", tmp_path, torch.float32)
+    args = dict(dtype="float32", max_len=200, parallel=3, chunk_size=16, max_batched_tokens=40)
+    prompts = [T.long_tokens("c", n, seed=60 + i) for i, n in enumerate((70, 12, 25, 9, 30))]
+    params = lambda: SamplingParams(temperature=0.0, max_tokens=14, ignore_eos=True)
+    eng = Engine.from_folder(folder, EngineArgs(**args))
+    reqs = [eng.add_request(p, params()) for p in prompts]
+    eng.run_step(); eng.run_step()
+    assert 0 < reqs[0].num_computed < len(prompts[0]) and reqs[4].state == "waiting"
+    eng.abort(reqs[0])                                  # between two portions of its prompt
+    eng.abort(reqs[4])                                  # still waiting
+    eng.cache.check()
+    while not (reqs[1].output and eng._flight is not None):     # decoding, with the next step already launched
+        eng.run_step()
+    assert reqs[1].state == "running"
+    eng.abort(reqs[1])
+    eng.abort(reqs[1])                                  # once more: nothing happens
+    while eng.scheduler.has_unfinished():
+        eng.run_step()
+    eng.cache.check()
+    st = eng.cache.stats()
+    assert st["requests"] == 0 and st["free_slots"] == 3 and all(g["free"] == g["pages"] for g in st["groups"])
+    assert [r.finish_reason for r in reqs] == ["aborted", "aborted", "length", "length", "aborted"]
+    assert all(t >= 0 for r in reqs for t in r.output) and reqs[4].output == [] and len(reqs[1].output) < 14
+    alone = Engine.from_folder(folder, EngineArgs(**dict(args, parallel=1)))
+    for i in (2, 3):
+        assert alone.generate([prompts[i]], params())[0] == reqs[i].output, i
+    assert alone.generate([prompts[1]], params())[0][:len(reqs[1].output)] == reqs[1].output
