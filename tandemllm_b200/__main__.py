@@ -2,6 +2,8 @@
 
   generate        token ids in, token ids out, through the scheduler and the step function
   random-weights  write a model folder (config.json, model.safetensors) from a config.json and a seed
+  audit           a model folder checked from its headers alone, on the CPU: names, shapes, bytes
+  compare         two replays of one trace held against each other, row by row
   replay          the trace replay program (the same as bin/trace_run)
   bench           the measurement program (the same as bench.py at the repository's root)
 
